@@ -1,0 +1,336 @@
+#!/usr/bin/env python
+"""Benchmark of the fused-MoE hot path: grouped_topk -> align -> expert GEMMs -> combine.
+
+Workload at N=1: the DeepSeek-V3-shape FP8 block-quant layer (E=256, top-8 of 8
+groups/4 kept, H=7168, I=2048) at M=8192 tokens, synthetic seeded inputs.
+One step = one pass of the whole path over one batch.
+
+    python bench.py [--gpus N] [--steps K] [--warmup W] [--impl reference] [--tokens M]
+
+Prints ONE JSON line (rank 0).  `value` is tokens/s with inputs resident in HBM;
+`e2e` is the same metric through the public API with pinned HOST buffers (H2D of
+activations and router logits, D2H of the layer output inside the timed region);
+`roofline` describes the dominant kernel (GEMM1), timed with CUDA events inside
+the timed steps; `cpu_baseline` is the CPU oracle on a bounded sample.
+"""
+
+from __future__ import annotations
+
+import argparse
+import json
+import os
+import subprocess
+import sys
+import time
+
+import torch
+
+ROOT = os.path.dirname(os.path.abspath(__file__))
+if ROOT not in sys.path:
+    sys.path.insert(0, ROOT)
+
+DSV3 = dict(E=256, topk=8, n_group=8, topk_group=4, H=7168, I=2048, rsf=2.5)
+L2_BYTES = 126 * 1024 * 1024
+
+
+def load_peaks():
+    path = os.path.join(ROOT, "MEASURED_PEAKS.json")
+    if os.path.exists(path):
+        with open(path) as fh:
+            p = json.load(fh)
+        return dict(hbm_gbs=float(p["hbm_gbs"]), bf16_tflops=float(p["bf16_tflops"]),
+                    bf16_tflops_sustained=float(p.get("bf16_tflops_sustained", p["bf16_tflops"])),
+                    source="measured")
+    return dict(hbm_gbs=6650.0, bf16_tflops=1590.0, bf16_tflops_sustained=1400.0, source="fallback")
+
+
+class ClockSampler:
+    """nvidia-smi clock/throttle sampling during the timed region."""
+
+    Q = ("index,clocks.sm,clocks.max.sm,power.draw,clocks_event_reasons.active,"
+         "clocks_event_reasons.hw_slowdown,clocks_event_reasons.hw_thermal_slowdown,"
+         "clocks_event_reasons.sw_thermal_slowdown,clocks_event_reasons.sw_power_cap")
+
+    def __init__(self, gpu_index: int):
+        self.gpu = gpu_index
+        self.proc = None
+
+    def start(self):
+        try:
+            self.proc = subprocess.Popen(
+                ["nvidia-smi", f"--query-gpu={self.Q}", "--format=csv,noheader,nounits", "-lms", "100",
+                 "-i", str(self.gpu)], stdout=subprocess.PIPE, stderr=subprocess.DEVNULL, text=True)
+        except OSError:
+            self.proc = None
+
+    def stop(self):
+        if self.proc is None:
+            return {"sm_mhz": None, "sm_max_mhz": None, "reasons": ["nvidia-smi unavailable"]}
+        time.sleep(0.15)
+        self.proc.terminate()
+        try:
+            out, _ = self.proc.communicate(timeout=5)
+        except subprocess.TimeoutExpired:
+            self.proc.kill()
+            out, _ = self.proc.communicate()
+        sm, mx, reasons = [], [], set()
+        names = ["hw_slowdown", "hw_thermal_slowdown", "sw_thermal_slowdown", "sw_power_cap"]
+        for line in out.strip().splitlines():
+            f = [x.strip() for x in line.split(",")]
+            if len(f) < 9:
+                continue
+            try:
+                sm.append(float(f[1]))
+                mx.append(float(f[2]))
+            except ValueError:
+                continue
+            for nm, v in zip(names, f[5:9]):
+                if v.lower().startswith("active"):
+                    reasons.add(nm)
+        sm.sort()
+        return {"sm_mhz": sm[len(sm) // 2] if sm else None, "sm_max_mhz": max(mx) if mx else None,
+                "samples": len(sm), "reasons": sorted(reasons)}
+
+
+def dist_env():
+    rank = int(os.environ.get("RANK", "0"))
+    world = int(os.environ.get("WORLD_SIZE", "1"))
+    local = int(os.environ.get("LOCAL_RANK", "0"))
+    return rank, world, local
+
+
+def cpu_oracle_run(M_sample, seed_shift=0, E_used=None, threads=None):
+    """Times the CPU oracle (torch-native restatement of the reference's golden
+    path) on `M_sample` tokens of the DSV3 FP8 workload.  Returns tokens/s."""
+    from oracle import moe_oracle as O
+
+    threads = threads or os.cpu_count() or 1
+    torch.set_num_threads(threads)
+    c = DSV3
+    E = c["E"]
+    g = torch.Generator().manual_seed(1234 + seed_shift)
+    x = torch.randn(M_sample, c["H"], generator=g).to(torch.bfloat16)
+    logits = torch.randn(M_sample, E, generator=g)
+    bias = torch.randn(E, generator=g) * 0.1
+    tw, ti = O.grouped_topk_oracle(logits, c["n_group"], c["topk_group"], c["topk"], True, c["rsf"], bias, 1)
+    used = torch.unique(ti).tolist()
+    # Only the experts the sample touches are materialised, as a compact table
+    # (ids remapped); four distinct N(0,0.02) block-quantised experts are
+    # generated and repeated, which changes neither the arithmetic nor the time.
+    n_used = len(used)
+    remap = torch.full((E,), -1, dtype=torch.int64)
+    remap[torch.tensor(used)] = torch.arange(n_used)
+    b1, bs1 = O.quantize_weight_fp8_block(torch.randn(4, 2 * c["I"], c["H"], generator=g) * 0.02)
+    b2, bs2 = O.quantize_weight_fp8_block(torch.randn(4, c["H"], c["I"], generator=g) * 0.02)
+    sel = torch.arange(n_used) % 4
+    w1, s1, w2, s2 = b1[sel], bs1[sel], b2[sel], bs2[sel]
+
+    def step():
+        tw_, ti_ = O.grouped_topk_oracle(logits, c["n_group"], c["topk_group"], c["topk"], True, c["rsf"], bias, 1)
+        O.moe_align_block_size_oracle(ti_, 128, E)
+        return O.fused_moe_fp8_block_oracle(x, w1, w2, s1, s2, tw_, remap[ti_.long()].to(torch.int32))
+
+    return step, threads, len(used)
+
+
+def run_reference(args):
+    """--impl reference: the reference's torch-native path (CPU oracle port) on host cores."""
+    rank, world, _ = dist_env()
+    if rank != 0:
+        return
+    M_s = args.ref_tokens
+    step, threads, n_used = cpu_oracle_run(M_s)
+    for _ in range(max(1, min(args.warmup, 1))):
+        step()
+    t0 = time.perf_counter()
+    for _ in range(args.steps):
+        step()
+    dt = (time.perf_counter() - t0) / args.steps
+    val = M_s / dt
+    line = {
+        "impl": "reference", "metric": "fused_moe_layer_tokens_per_s", "value": val, "unit": "tokens/s",
+        "n_gpus": args.gpus, "steps": args.steps, "warmup": min(args.warmup, 1), "ms_per_step": dt * 1e3,
+        "higher_is_better": True, "scaling": "weak", "vs_baseline": None, "dtype": "fp8_e4m3", "data": "synthetic",
+        "config": {"workload": "deepseek_v3_fp8_block_moe_layer", "tokens": M_s, **DSV3},
+        "cpu_baseline": {"value": val, "unit": "tokens/s", "cores": threads, "kind": "port",
+                         "sample": f"{M_s} tokens per step of the DSV3 FP8 layer ({n_used} distinct experts), "
+                                   "CPU oracle restating the reference's torch goldens"},
+        "e2e": {"value": val, "unit": "tokens/s", "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0},
+        "tflops": 6.0 * M_s * DSV3["topk"] * DSV3["H"] * DSV3["I"] / dt / 1e12,
+    }
+    print(json.dumps(line), flush=True)
+
+
+def main():
+    ap = argparse.ArgumentParser()
+    ap.add_argument("--gpus", type=int, default=1)
+    ap.add_argument("--steps", type=int, default=20)
+    ap.add_argument("--warmup", type=int, default=5)
+    ap.add_argument("--impl", default="b200", choices=["b200", "reference"])
+    ap.add_argument("--tokens", type=int, default=8192, help="tokens per GPU per step")
+    ap.add_argument("--ref-tokens", type=int, default=4, help="tokens per step of the CPU reference arm")
+    ap.add_argument("--cpu-baseline-tokens", type=int, default=16)
+    ap.add_argument("--no-cpu-baseline", action="store_true")
+    args = ap.parse_args()
+    args.warmup = max(args.warmup, 3) if args.impl == "b200" else args.warmup
+    if args.impl == "reference":
+        run_reference(args)
+        return
+
+    import flaggems_vllm_b200 as fg
+    from flaggems_vllm_b200 import fused_moe
+    from flaggems_vllm_b200 import testing as T
+
+    rank, world, local = dist_env()
+    if world > 1:
+        from flaggems_vllm_b200 import ep  # expert-parallel wrapper
+        import torch.distributed as dist
+
+        torch.cuda.set_device(local)
+        dist.init_process_group("nccl", device_id=torch.device("cuda", local))
+    else:
+        ep = None
+        dist = None
+        torch.cuda.set_device(0)
+    dev = torch.device("cuda", torch.cuda.current_device())
+    c = DSV3
+    M, E, H, I, k = args.tokens, c["E"], c["H"], c["I"], c["topk"]
+    E_local = E // world
+    peaks = load_peaks()
+
+    # ---- resident inputs
+    w1, s1 = T.make_fp8_block_weights(E_local, 2 * I, H, dev, seed=100 + rank)
+    w2, s2 = T.make_fp8_block_weights(E_local, H, I, dev, seed=200 + rank)
+    x = T.make_activations(M, H, dev, seed=300 + rank)
+    logits, bias = T.make_router_inputs(M, E, dev, seed=400 + rank)
+    if world > 1:
+        dist.broadcast(bias, 0)
+    flush = torch.empty(2 * L2_BYTES, dtype=torch.uint8, device=dev)
+    layer = ep.ExpertParallelMoE(w1, w2, s1, s2, E, dist.group.WORLD) if world > 1 else None
+
+    def device_step():
+        tw, ti = fg.grouped_topk(logits, c["n_group"], c["topk_group"], k, True, c["rsf"], bias, 1)
+        if layer is not None:
+            return layer.forward(x, tw, ti)
+        return fg.fused_experts_impl(x, w1, w2, tw, ti, use_fp8_w8a8=True, w1_scale=s1, w2_scale=s2,
+                                     block_shape=[128, 128])
+
+    def barrier():
+        if dist is not None:
+            dist.barrier()
+        torch.cuda.synchronize()
+
+    stage_ms = {}
+    stage_events = []
+
+    def hook(name):
+        ev = torch.cuda.Event(enable_timing=True)
+        ev.record(torch.cuda.current_stream())
+        stage_events.append((name, ev))
+
+    def timed(fn, steps, record_stages=False):
+        evs = [(torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)) for _ in range(steps)]
+        barrier()
+        for i in range(steps):
+            flush.zero_()  # L2 flush between iterations (inputs of small M would otherwise stay in L2)
+            if record_stages:
+                fused_moe.STAGE_HOOK = hook
+                hook("begin")
+            evs[i][0].record()
+            fn()
+            evs[i][1].record()
+            fused_moe.STAGE_HOOK = None
+        barrier()
+        total = sum(a.elapsed_time(b) for a, b in evs)
+        t = torch.tensor([total], dtype=torch.float64, device=dev)
+        if dist is not None:
+            dist.all_reduce(t, op=dist.ReduceOp.MAX)
+        return float(t.item()) / steps
+
+    for _ in range(args.warmup):
+        device_step()
+    sampler = ClockSampler(local)
+    sampler.start()
+    ms = timed(device_step, args.steps, record_stages=(world == 1))
+    clocks = sampler.stop()
+    if world == 1:
+        prev = None
+        for name, ev in stage_events:
+            if name != "begin" and prev is not None:
+                stage_ms.setdefault(name, []).append(prev.elapsed_time(ev))
+            prev = ev
+    status = fg.read_status(dev)
+
+    # ---- end to end with host buffers through the public API
+    hx = torch.empty((M, H), dtype=torch.bfloat16).pin_memory()
+    hl = torch.empty((M, E), dtype=torch.float32).pin_memory()
+    hx.copy_(x.cpu())
+    hl.copy_(logits.cpu())
+    hout = torch.empty((M, H), dtype=torch.bfloat16).pin_memory()
+    dx, dl = torch.empty_like(x), torch.empty_like(logits)
+
+    def e2e_step():
+        dx.copy_(hx, non_blocking=True)
+        dl.copy_(hl, non_blocking=True)
+        tw, ti = fg.grouped_topk(dl, c["n_group"], c["topk_group"], k, True, c["rsf"], bias, 1)
+        if layer is not None:
+            out = layer.forward(dx, tw, ti)
+        else:
+            out = fg.fused_experts_impl(dx, w1, w2, tw, ti, use_fp8_w8a8=True, w1_scale=s1, w2_scale=s2,
+                                        block_shape=[128, 128])
+        hout.copy_(out, non_blocking=True)
+
+    for _ in range(3):
+        e2e_step()
+    e2e_ms = timed(e2e_step, max(3, args.steps // 2))
+
+    total_tokens = M * world
+    flops = 6.0 * total_tokens * k * H * I
+    value = total_tokens / (ms * 1e-3)
+    line = {
+        "metric": "fused_moe_layer_tokens_per_s", "value": value, "unit": "tokens/s", "n_gpus": world,
+        "steps": args.steps, "warmup": args.warmup, "ms_per_step": ms, "higher_is_better": True,
+        "scaling": "weak", "vs_baseline": None, "dtype": "fp8_e4m3", "data": "synthetic",
+        "config": {"workload": "deepseek_v3_fp8_block_moe_layer", "tokens_per_gpu": M, "global_tokens": total_tokens,
+                   **c, "experts_per_gpu": E_local, "parallelism": f"ep{world}" if world > 1 else "single",
+                   "l2": "flushed between iterations (252 MB memset); weights 11.3 GB >> L2"},
+        "tflops": flops / (ms * 1e-3) / 1e12,
+        "e2e": {"value": total_tokens / (e2e_ms * 1e-3), "unit": "tokens/s", "ms_per_step": e2e_ms,
+                "h2d_bytes_per_step": hx.numel() * 2 + hl.numel() * 4, "d2h_bytes_per_step": hout.numel() * 2},
+        "gpu_launches": 6 * args.steps if world == 1 else None,
+        "clocks": clocks, "kernel_status": status,
+    }
+    if world == 1:
+        med = {n: sorted(v)[len(v) // 2] for n, v in stage_ms.items()}
+        line["stage_ms"] = med
+        # dominant kernel: GEMM1 (2*M*k*2I*H flop per launch); FP8 peak is not in
+        # MEASURED_PEAKS.json, so 2x the measured bf16 burst figure is used
+        g1 = sum(stage_ms["gemm1"]) / len(stage_ms["gemm1"])
+        f1 = 2.0 * M * k * (2 * I) * H
+        peak = 2.0 * peaks["bf16_tflops"]
+        line["roofline"] = {"kernel": "tc_gemm_kernel<fp8,gemm1>", "bound": "tensor", "achieved": f1 / (g1 * 1e-3) / 1e12,
+                            "peak": peak, "unit": "TFLOP/s", "frac": f1 / (g1 * 1e-3) / 1e12 / peak,
+                            "traffic": None, "peak_source": f"2 x bf16_tflops of {peaks['source']} peaks",
+                            "ms_per_launch": g1}
+        wbytes = E * 3 * H * I + (E * (2 * I // 128) * (H // 128) + E * (H // 128) * (I // 128)) * 4
+        B = wbytes + M * H * 2 * 2 + M * E * 4 + k * 8 * M
+        line["layer_hbm"] = {"algorithmic_bytes": B, "achieved_gbs": B / (ms * 1e-3) / 1e9,
+                             "peak_gbs": peaks["hbm_gbs"], "frac": B / (ms * 1e-3) / 1e9 / peaks["hbm_gbs"]}
+    if rank == 0 and world == 1 and not args.no_cpu_baseline:
+        Ms = args.cpu_baseline_tokens
+        step, threads, n_used = cpu_oracle_run(Ms)
+        step()
+        t0 = time.perf_counter()
+        step()
+        dt = time.perf_counter() - t0
+        line["cpu_baseline"] = {"value": Ms / dt, "unit": "tokens/s", "cores": threads, "kind": "port",
+                                "sample": f"{Ms} tokens of the same layer ({n_used} distinct experts), one timed pass "
+                                          "after one warm-up, CPU oracle (torch-native restatement of the reference goldens)"}
+    if rank == 0:
+        print(json.dumps(line), flush=True)
+    if dist is not None:
+        dist.destroy_process_group()
+
+
+if __name__ == "__main__":
+    main()

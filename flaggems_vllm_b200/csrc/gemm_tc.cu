@@ -1,0 +1,553 @@
+// Expert grouped GEMMs on the 5th-generation tensor cores (tcgen05 / TMEM),
+// fed by TMA.  One persistent CTA per SM walks a static list of
+// (align block, column tile) pairs.
+//
+// Tile: 128 expert-sorted rows x 256 accumulator columns, K consumed 128 bytes
+// per pipeline stage (128 e4m3 or 64 half elements = one 128-byte swizzle row).
+//   A stage : 128 rows x 128 B  (one TMA box)
+//   B stage : 256 rows x 128 B  (four TMA boxes of 64 weight rows each)
+// GEMM1 picks the four boxes as {gate lo, up lo, gate hi, up hi} of a 128-wide
+// output tile, so one accumulator holds gate and up of the same output column
+// in the same thread and SiLU(gate)*up plus the 1x128 re-quantisation are done
+// in registers.  GEMM2 uses four consecutive 64-row boxes (256 output columns).
+//
+// Warp roles (384 threads):
+//   warp 0      TMA producer (one lane)
+//   warp 1      MMA issuer (one lane): tcgen05.mma, tcgen05.commit
+//   warp 2      TMEM allocation (512 columns = two 256-column accumulators)
+//   warps 4-11  accumulator consumers, two groups of four warps; group h owns
+//               accumulator columns [128h, 128h+128), warp w lanes 32*(w%4)...
+// FP8 block-scaled mode: the tensor core cannot apply fp32 128x128 / 1x128
+// scales, so every 128-wide K block is multiplied into a fresh TMEM
+// accumulator (the two accumulators alternate) and the consumer warps fold it
+// into fp32 registers with acc += part * (a_scale[row] * w_scale[block]), the
+// arithmetic of the reference kernel (src/flaggems_vllm/ops/fused_moe.py:1708-1722),
+// while the tensor core works on the next block.
+// Half mode: the whole K loop accumulates in TMEM; the two accumulators let
+// the epilogue of one tile overlap the main loop of the next.
+//
+// Every barrier wait is bounded (wall-clock limit); on expiry the kernel sets
+// MOE_ST_WAIT_TIMEOUT, leaves its loops, frees TMEM and returns.
+#include <cuda.h>
+
+#include <type_traits>
+
+#include "moe_common.cuh"
+
+namespace moe {
+namespace tc {
+
+constexpr int BM = 128;
+constexpr int BN = 256;
+constexpr int STAGES = 4;
+constexpr int A_STAGE_BYTES = BM * 128;
+constexpr int B_STAGE_BYTES = BN * 128;
+constexpr int B_BOX_ROWS = 64;
+constexpr int THREADS = 384;
+constexpr int EPI_THREADS = 256;
+constexpr unsigned long long WAIT_LIMIT_NS = 2000000000ull;  // 2 s
+
+struct SmemAux {
+  uint64_t full[STAGES];
+  uint64_t empty[STAGES];
+  uint64_t tmem_full[2];
+  uint64_t tmem_empty[2];
+  uint64_t xch_bar;
+  uint32_t tmem_base;
+  uint32_t pad;
+  float xch[2][2][BM];  // [tile parity][consumer group][row] amax exchange
+};
+constexpr size_t SMEM_BYTES = (size_t)STAGES * (A_STAGE_BYTES + B_STAGE_BYTES) + sizeof(SmemAux) + 1024;
+
+struct Params {
+  const float* a_scales_t;  // [K/128, rows_cap]          (FP8)
+  const float* w_scale;     // [E, rows_w/128, K/128]     (FP8)
+  const int32_t* expert_ids;
+  const int32_t* sorted_ids;
+  const int32_t* num_post_pad;
+  const float* route_weight;
+  void* out;
+  float* out_scales_t;      // [I/128, rows_cap]          (FP8 GEMM1)
+  int32_t* status;
+  int64_t numel;
+  int64_t rows_cap;
+  int mul_weight;
+  int E;
+  int K;        // contraction length in elements
+  int Nout;     // output columns (I for GEMM1, H for GEMM2)
+  int rows_w;   // weight rows per expert (2I or H)
+  int n_tiles;  // column tiles per align block
+};
+
+// ------------------------------------------------------------------ PTX wrappers
+__device__ __forceinline__ uint32_t smem_u32(const void* p) {
+  return (uint32_t)__cvta_generic_to_shared(p);
+}
+__device__ __forceinline__ void mbar_init(uint64_t* bar, uint32_t count) {
+  asm volatile("mbarrier.init.shared::cta.b64 [%0], %1;" ::"r"(smem_u32(bar)), "r"(count));
+}
+__device__ __forceinline__ void mbar_expect_tx(uint64_t* bar, uint32_t bytes) {
+  asm volatile("mbarrier.arrive.expect_tx.shared::cta.b64 _, [%0], %1;" ::"r"(smem_u32(bar)), "r"(bytes)
+               : "memory");
+}
+__device__ __forceinline__ void mbar_arrive(uint64_t* bar) {
+  asm volatile("mbarrier.arrive.shared::cta.b64 _, [%0];" ::"r"(smem_u32(bar)) : "memory");
+}
+__device__ __forceinline__ bool mbar_try(uint64_t* bar, uint32_t parity) {
+  uint32_t ok;
+  asm volatile(
+      "{\n\t.reg .pred p;\n\t"
+      "mbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2;\n\t"
+      "selp.u32 %0, 1, 0, p;\n\t}"
+      : "=r"(ok)
+      : "r"(smem_u32(bar)), "r"(parity)
+      : "memory");
+  return ok != 0;
+}
+__device__ __forceinline__ unsigned long long now_ns() {
+  unsigned long long t;
+  asm volatile("mov.u64 %0, %globaltimer;" : "=l"(t));
+  return t;
+}
+// Bounded wait: false when the limit ran out (status word is set).
+__device__ __forceinline__ bool mbar_wait(uint64_t* bar, uint32_t parity, int32_t* status) {
+  if (mbar_try(bar, parity)) return true;
+  const unsigned long long t0 = now_ns();
+  uint32_t spins = 0;
+  while (!mbar_try(bar, parity)) {
+    if ((++spins & 0x3FF) == 0 && now_ns() - t0 > WAIT_LIMIT_NS) {
+      set_status(status, MOE_ST_WAIT_TIMEOUT);
+      return false;
+    }
+  }
+  return true;
+}
+__device__ __forceinline__ void tma_load_2d(const CUtensorMap* map, uint64_t* bar, void* dst, int c0, int c1) {
+  asm volatile(
+      "cp.async.bulk.tensor.2d.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1, {%3, %4}], [%2];"
+      ::"r"(smem_u32(dst)), "l"(map), "r"(smem_u32(bar)), "r"(c0), "r"(c1)
+      : "memory");
+}
+__device__ __forceinline__ void tc_fence_before() { asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory"); }
+__device__ __forceinline__ void tc_fence_after() { asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory"); }
+__device__ __forceinline__ void tc_commit(uint64_t* bar) {
+  asm volatile("tcgen05.commit.cta_group::1.mbarrier::arrive::one.shared::cluster.b64 [%0];" ::"r"(smem_u32(bar))
+               : "memory");
+}
+template <bool FP8>
+__device__ __forceinline__ void tc_mma(uint32_t tmem_d, uint64_t adesc, uint64_t bdesc, uint32_t idesc, uint32_t acc) {
+  if constexpr (FP8) {
+    asm volatile(
+        "{\n\t.reg .pred p;\n\tsetp.ne.b32 p, %4, 0;\n\t"
+        "tcgen05.mma.cta_group::1.kind::f8f6f4 [%0], %1, %2, %3, p;\n\t}"
+        ::"r"(tmem_d), "l"(adesc), "l"(bdesc), "r"(idesc), "r"(acc)
+        : "memory");
+  } else {
+    asm volatile(
+        "{\n\t.reg .pred p;\n\tsetp.ne.b32 p, %4, 0;\n\t"
+        "tcgen05.mma.cta_group::1.kind::f16 [%0], %1, %2, %3, p;\n\t}"
+        ::"r"(tmem_d), "l"(adesc), "l"(bdesc), "r"(idesc), "r"(acc)
+        : "memory");
+  }
+}
+__device__ __forceinline__ void tmem_ld32(uint32_t taddr, uint32_t* r) {
+  asm volatile(
+      "tcgen05.ld.sync.aligned.32x32b.x32.b32 "
+      "{%0, %1, %2, %3, %4, %5, %6, %7, %8, %9, %10, %11, %12, %13, %14, %15, "
+      "%16, %17, %18, %19, %20, %21, %22, %23, %24, %25, %26, %27, %28, %29, %30, %31}, [%32];"
+      : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3]), "=r"(r[4]), "=r"(r[5]), "=r"(r[6]), "=r"(r[7]),
+        "=r"(r[8]), "=r"(r[9]), "=r"(r[10]), "=r"(r[11]), "=r"(r[12]), "=r"(r[13]), "=r"(r[14]), "=r"(r[15]),
+        "=r"(r[16]), "=r"(r[17]), "=r"(r[18]), "=r"(r[19]), "=r"(r[20]), "=r"(r[21]), "=r"(r[22]), "=r"(r[23]),
+        "=r"(r[24]), "=r"(r[25]), "=r"(r[26]), "=r"(r[27]), "=r"(r[28]), "=r"(r[29]), "=r"(r[30]), "=r"(r[31])
+      : "r"(taddr));
+}
+__device__ __forceinline__ void tmem_ld_wait() { asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory"); }
+
+// K-major operand tile with 128-byte swizzle: rows are 128 B apart, groups of
+// 8 rows 1024 B apart (stride byte offset), descriptor version 1 (sm_100).
+__device__ __forceinline__ uint64_t make_smem_desc(uint32_t saddr) {
+  uint64_t d = 0;
+  d |= (uint64_t)((saddr & 0x3FFFFu) >> 4);
+  d |= (uint64_t)1 << 16;            // leading byte offset (unused for swizzled K-major)
+  d |= (uint64_t)(1024 >> 4) << 32;  // stride byte offset
+  d |= (uint64_t)1 << 46;            // descriptor version
+  d |= (uint64_t)2 << 61;            // SWIZZLE_128B
+  return d;
+}
+
+// Instruction descriptor: fp32 accumulator (bits 4-5 = 1), A/B element format
+// (bits 7-9 / 10-12: e4m3 = 0 for kind::f8f6f4; f16 = 0, bf16 = 1 for
+// kind::f16), both operands K-major, N >> 3 at bit 17, M >> 4 at bit 24.
+template <bool FP8, typename AT>
+struct IDesc {
+  static constexpr uint32_t fmt = (!FP8 && std::is_same<AT, __nv_bfloat16>::value) ? 1u : 0u;
+  static constexpr uint32_t value =
+      (1u << 4) | (fmt << 7) | (fmt << 10) | ((uint32_t)(BN >> 3) << 17) | ((uint32_t)(BM >> 4) << 24);
+};
+
+// weight row (inside the expert) of the first row of B box `c` of column tile `nt`
+template <bool GEMM1>
+__device__ __forceinline__ int box_row(int nt, int c, int Nout) {
+  if constexpr (GEMM1) return nt * 128 + (c >> 1) * 64 + (c & 1) * Nout;  // gate/up interleaved
+  else return nt * BN + c * 64;
+}
+
+template <typename AT>
+__device__ __forceinline__ uint32_t pack2(float a, float b);
+template <>
+__device__ __forceinline__ uint32_t pack2<__nv_bfloat16>(float a, float b) {
+  __nv_bfloat162 v = __floats2bfloat162_rn(a, b);
+  return *reinterpret_cast<uint32_t*>(&v);
+}
+template <>
+__device__ __forceinline__ uint32_t pack2<__half>(float a, float b) {
+  __half2 v = __floats2half2_rn(a, b);
+  return *reinterpret_cast<uint32_t*>(&v);
+}
+template <typename AT>
+__device__ __forceinline__ float round_act(float v) {
+  return ToF32<AT>::get(from_f32<AT>(v));
+}
+
+template <bool FP8, typename AT, bool GEMM1>
+__global__ void __launch_bounds__(THREADS, 1)
+tc_gemm_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant__ CUtensorMap map_b, const Params P) {
+  extern __shared__ uint8_t smem_raw[];
+  uint8_t* smem = reinterpret_cast<uint8_t*>(((uintptr_t)smem_raw + 1023) & ~(uintptr_t)1023);
+  uint8_t* sA = smem;
+  uint8_t* sB = smem + (size_t)STAGES * A_STAGE_BYTES;
+  SmemAux* aux = reinterpret_cast<SmemAux*>(smem + (size_t)STAGES * (A_STAGE_BYTES + B_STAGE_BYTES));
+
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  constexpr int KBE = FP8 ? 128 : 64;  // elements of K per stage
+  const int KB = (P.K + KBE - 1) / KBE;
+  const int npp = min((int64_t)P.num_post_pad[0], P.rows_cap);
+  const int total_tiles = ((npp + BM - 1) / BM) * P.n_tiles;
+
+  if (threadIdx.x == 0) {
+    for (int s = 0; s < STAGES; ++s) {
+      mbar_init(&aux->full[s], 1);
+      mbar_init(&aux->empty[s], 1);
+    }
+    for (int a = 0; a < 2; ++a) {
+      mbar_init(&aux->tmem_full[a], 1);
+      mbar_init(&aux->tmem_empty[a], EPI_THREADS / 32);
+    }
+    mbar_init(&aux->xch_bar, EPI_THREADS);
+    asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
+  }
+  if (warp == 2) {
+    asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(smem_u32(&aux->tmem_base)),
+                 "r"(512));
+    asm volatile("tcgen05.relinquish_alloc_permit.cta_group::1.sync.aligned;" ::);
+  }
+  tc_fence_before();
+  __syncthreads();
+  tc_fence_after();
+  const uint32_t tmem_base = aux->tmem_base;
+
+  if (warp < 4) {
+    asm volatile("setmaxnreg.dec.sync.aligned.u32 40;");
+    if (warp == 0 && lane == 0) {
+      // ------------------------------------------------------------ TMA producer
+      asm volatile("prefetch.tensormap [%0];" ::"l"(&map_a) : "memory");
+      asm volatile("prefetch.tensormap [%0];" ::"l"(&map_b) : "memory");
+      uint32_t it = 0;
+      bool alive = true;
+      for (int tile = blockIdx.x; tile < total_tiles && alive; tile += gridDim.x) {
+        const int mb = tile / P.n_tiles, nt = tile % P.n_tiles;
+        const int e = P.expert_ids[mb];
+        if (e < 0 || e >= P.E) continue;
+        const int row0 = mb * BM;
+        const int wrow0 = e * P.rows_w;
+        for (int kb = 0; kb < KB; ++kb, ++it) {
+          const int s = it % STAGES;
+          const uint32_t ph = (it / STAGES) & 1;
+          if (!mbar_wait(&aux->empty[s], ph ^ 1, P.status)) { alive = false; break; }
+          mbar_expect_tx(&aux->full[s], A_STAGE_BYTES + B_STAGE_BYTES);
+          tma_load_2d(&map_a, &aux->full[s], sA + (size_t)s * A_STAGE_BYTES, kb * KBE, row0);
+#pragma unroll
+          for (int c = 0; c < 4; ++c)
+            tma_load_2d(&map_b, &aux->full[s], sB + (size_t)s * B_STAGE_BYTES + c * (B_BOX_ROWS * 128), kb * KBE,
+                        wrow0 + box_row<GEMM1>(nt, c, P.Nout));
+        }
+      }
+    } else if (warp == 1 && lane == 0) {
+      // ------------------------------------------------------------ MMA issuer
+      constexpr uint32_t idesc = IDesc<FP8, AT>::value;
+      uint32_t it = 0, acc_it = 0;
+      bool alive = true;
+      for (int tile = blockIdx.x; tile < total_tiles && alive; tile += gridDim.x) {
+        const int mb = tile / P.n_tiles;
+        const int e = P.expert_ids[mb];
+        if (e < 0 || e >= P.E) continue;
+        for (int kb = 0; kb < KB; ++kb, ++it) {
+          const uint32_t a = acc_it & 1;
+          if (FP8 || kb == 0) {
+            if (!mbar_wait(&aux->tmem_empty[a], ((acc_it >> 1) & 1) ^ 1, P.status)) { alive = false; break; }
+            tc_fence_after();
+          }
+          const int s = it % STAGES;
+          if (!mbar_wait(&aux->full[s], (it / STAGES) & 1, P.status)) { alive = false; break; }
+          tc_fence_after();
+          const uint64_t adesc = make_smem_desc(smem_u32(sA + (size_t)s * A_STAGE_BYTES));
+          const uint64_t bdesc = make_smem_desc(smem_u32(sB + (size_t)s * B_STAGE_BYTES));
+          const uint32_t d = tmem_base + a * BN;
+#pragma unroll
+          for (int k4 = 0; k4 < 4; ++k4) {
+            // 32 bytes of K per instruction: start address advances by 32 B >> 4
+            const uint32_t accum = FP8 ? (k4 > 0) : (kb > 0 || k4 > 0);
+            tc_mma<FP8>(d, adesc + (uint64_t)(k4 * 2), bdesc + (uint64_t)(k4 * 2), idesc, accum);
+          }
+          tc_commit(&aux->empty[s]);
+          if (FP8 || kb == KB - 1) {
+            tc_commit(&aux->tmem_full[a]);
+            ++acc_it;
+          }
+        }
+      }
+    }
+  } else {
+    // -------------------------------------------------------------- consumers
+    asm volatile("setmaxnreg.inc.sync.aligned.u32 232;");
+    const int h = (warp - 4) >> 2;                  // column half owned by this group
+    const int row = ((warp & 3) << 5) + lane;       // accumulator lane = tile row
+    const uint32_t t_lane = tmem_base + ((uint32_t)((warp & 3) << 5) << 16) + (uint32_t)(h * 128);
+    uint32_t acc_it = 0, tile_it = 0;
+    bool alive = true;
+    for (int tile = blockIdx.x; tile < total_tiles && alive; tile += gridDim.x) {
+      const int mb = tile / P.n_tiles, nt = tile % P.n_tiles;
+      const int e = P.expert_ids[mb];
+      if (e < 0 || e >= P.E) continue;
+      const int64_t p = (int64_t)mb * BM + row;
+      float acc[128];
+      if constexpr (FP8) {
+#pragma unroll
+        for (int i = 0; i < 128; ++i) acc[i] = 0.0f;
+        const int sblk_per_e = (P.rows_w + 127) / 128;
+        // weight-scale rows of the two 64-column halves this thread owns
+        int sb_lo, sb_hi;
+        if constexpr (GEMM1) {
+          sb_lo = nt;                      // gate rows nt*128 ...
+          sb_hi = (P.Nout >> 7) + nt;      // up rows I + nt*128 ...
+        } else {
+          sb_lo = min(2 * nt + h, sblk_per_e - 1);
+          sb_hi = sb_lo;
+        }
+        const float* ws_lo = P.w_scale + ((int64_t)e * sblk_per_e + sb_lo) * KB;
+        const float* ws_hi = P.w_scale + ((int64_t)e * sblk_per_e + sb_hi) * KB;
+        const float* as = P.a_scales_t + p;
+        float sa_n = as[0], wl_n = ws_lo[0], wh_n = ws_hi[0];
+        for (int kb = 0; kb < KB; ++kb, ++acc_it) {
+          const float s_lo = sa_n * wl_n, s_hi = sa_n * wh_n;
+          if (kb + 1 < KB) {
+            sa_n = as[(int64_t)(kb + 1) * P.rows_cap];
+            wl_n = ws_lo[kb + 1];
+            wh_n = ws_hi[kb + 1];
+          }
+          const uint32_t a = acc_it & 1;
+          if (!mbar_wait(&aux->tmem_full[a], (acc_it >> 1) & 1, P.status)) { alive = false; break; }
+          tc_fence_after();
+#pragma unroll
+          for (int c = 0; c < 4; ++c) {
+            uint32_t r[32];
+            tmem_ld32(t_lane + a * BN + c * 32, r);
+            tmem_ld_wait();
+            const float sc = c < 2 ? s_lo : s_hi;
+#pragma unroll
+            for (int i = 0; i < 32; ++i) acc[c * 32 + i] = fmaf(__uint_as_float(r[i]), sc, acc[c * 32 + i]);
+          }
+          tc_fence_before();
+          __syncwarp();
+          if (lane == 0) mbar_arrive(&aux->tmem_empty[a]);
+        }
+        if (!alive) break;
+      } else {
+        const uint32_t a = acc_it & 1;
+        if (!mbar_wait(&aux->tmem_full[a], (acc_it >> 1) & 1, P.status)) { alive = false; break; }
+        tc_fence_after();
+#pragma unroll
+        for (int c = 0; c < 4; ++c) {
+          uint32_t r[32];
+          tmem_ld32(t_lane + a * BN + c * 32, r);
+          tmem_ld_wait();
+#pragma unroll
+          for (int i = 0; i < 32; ++i) acc[c * 32 + i] = __uint_as_float(r[i]);
+        }
+        tc_fence_before();
+        __syncwarp();
+        if (lane == 0) mbar_arrive(&aux->tmem_empty[a]);
+        ++acc_it;
+      }
+
+      // ---------------------------------------------------------- tile epilogue
+      int64_t sid = P.numel;
+      if (p < P.rows_cap) sid = (int64_t)P.sorted_ids[p];
+      const bool row_ok = sid >= 0 && sid < P.numel;
+      float rw = 1.0f;
+      if (P.mul_weight && row_ok) rw = P.route_weight[sid];
+      if constexpr (GEMM1) {
+        // acc[0..63] gate, acc[64..127] up of output columns nt*128 + 64h + j
+        float amax = 0.0f;
+#pragma unroll
+        for (int j = 0; j < 64; ++j) {
+          acc[j] = round_act<AT>(silu_mul(acc[j] * rw, acc[64 + j] * rw));
+          amax = fmaxf(amax, fabsf(acc[j]));
+        }
+        const int64_t col0 = (int64_t)nt * 128 + 64 * h;
+        if constexpr (FP8) {
+          float* x = &aux->xch[tile_it & 1][0][0];
+          x[h * BM + row] = amax;
+          mbar_arrive(&aux->xch_bar);
+          if (!mbar_wait(&aux->xch_bar, tile_it & 1, P.status)) { alive = false; break; }
+          amax = fmaxf(amax, x[(1 - h) * BM + row]);
+          const float s = fmaxf(amax, kQuantEps) * (1.0f / kFp8Max);
+          if (row_ok) {
+            uint4* o = reinterpret_cast<uint4*>(reinterpret_cast<uint8_t*>(P.out) + p * P.Nout + col0);
+#pragma unroll
+            for (int v = 0; v < 4; ++v) {
+              uint32_t w[4];
+#pragma unroll
+              for (int q = 0; q < 4; ++q) {
+                uint32_t pk = 0;
+#pragma unroll
+                for (int b = 0; b < 4; ++b) {
+                  const float qv = fminf(fmaxf(acc[v * 16 + q * 4 + b] / s, -kFp8Max), kFp8Max);
+                  pk |= (uint32_t)f32_to_fp8e4m3(qv) << (8 * b);
+                }
+                w[q] = pk;
+              }
+              o[v] = make_uint4(w[0], w[1], w[2], w[3]);
+            }
+            if (h == 0) P.out_scales_t[(int64_t)nt * P.rows_cap + p] = s;
+          }
+        } else if (row_ok) {
+          uint4* o = reinterpret_cast<uint4*>(reinterpret_cast<AT*>(P.out) + p * P.Nout + col0);
+#pragma unroll
+          for (int v = 0; v < 8; ++v)
+            o[v] = make_uint4(pack2<AT>(acc[v * 8 + 0], acc[v * 8 + 1]), pack2<AT>(acc[v * 8 + 2], acc[v * 8 + 3]),
+                              pack2<AT>(acc[v * 8 + 4], acc[v * 8 + 5]), pack2<AT>(acc[v * 8 + 6], acc[v * 8 + 7]));
+        }
+      } else if (row_ok) {
+        const int col0 = nt * BN + 128 * h;
+        uint4* o = reinterpret_cast<uint4*>(reinterpret_cast<AT*>(P.out) + sid * P.Nout + col0);
+#pragma unroll
+        for (int v = 0; v < 16; ++v) {
+          if (col0 + v * 8 < P.Nout)
+            o[v] = make_uint4(pack2<AT>(acc[v * 8 + 0] * rw, acc[v * 8 + 1] * rw),
+                              pack2<AT>(acc[v * 8 + 2] * rw, acc[v * 8 + 3] * rw),
+                              pack2<AT>(acc[v * 8 + 4] * rw, acc[v * 8 + 5] * rw),
+                              pack2<AT>(acc[v * 8 + 6] * rw, acc[v * 8 + 7] * rw));
+        }
+      }
+      ++tile_it;
+    }
+  }
+
+  // -------------------------------------------------------------------- teardown
+  tc_fence_before();
+  __syncthreads();
+  if (warp == 2) {
+    tc_fence_after();
+    asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" ::"r"(tmem_base), "r"(512));
+  }
+}
+
+// ------------------------------------------------------------------ host side
+typedef CUresult (*EncodeTiledFn)(CUtensorMap*, CUtensorMapDataType, cuuint32_t, void*, const cuuint64_t*,
+                                  const cuuint64_t*, const cuuint32_t*, const cuuint32_t*, CUtensorMapInterleave,
+                                  CUtensorMapSwizzle, CUtensorMapL2promotion, CUtensorMapFloatOOBfill);
+
+static EncodeTiledFn get_encode() {
+  static EncodeTiledFn fn = nullptr;
+  static bool tried = false;
+  if (!tried) {
+    tried = true;
+    void* p = nullptr;
+    cudaDriverEntryPointQueryResult q;
+    if (cudaGetDriverEntryPoint("cuTensorMapEncodeTiled", &p, cudaEnableDefault, &q) == cudaSuccess &&
+        q == cudaDriverEntryPointSuccess)
+      fn = (EncodeTiledFn)p;
+  }
+  return fn;
+}
+
+// 2-D row-major [rows, cols] tensor, box = 128 bytes of a row x box_rows rows, 128B swizzle.
+static int make_map(CUtensorMap* m, const void* base, CUtensorMapDataType dt, int elem_bytes, uint64_t rows,
+                    uint64_t cols, uint32_t box_rows, bool weights) {
+  EncodeTiledFn enc = get_encode();
+  if (!enc) return fail(MOE_E_DRIVER, "cuTensorMapEncodeTiled is not available from the driver");
+  if (((uintptr_t)base & 15) != 0) return fail(MOE_E_BADARG, "tensor-core GEMM: operand not 16-byte aligned");
+  if ((cols * elem_bytes) % 16 != 0) return fail(MOE_E_SHAPE, "tensor-core GEMM: row pitch must be a multiple of 16 bytes");
+  cuuint64_t gdim[2] = {cols, rows};
+  cuuint64_t gstr[1] = {cols * (uint64_t)elem_bytes};
+  cuuint32_t box[2] = {(cuuint32_t)(128 / elem_bytes), box_rows};
+  cuuint32_t estr[2] = {1, 1};
+  CUresult r = enc(m, dt, 2, const_cast<void*>(base), gdim, gstr, box, estr, CU_TENSOR_MAP_INTERLEAVE_NONE,
+                   CU_TENSOR_MAP_SWIZZLE_128B,
+                   weights ? CU_TENSOR_MAP_L2_PROMOTION_L2_256B : CU_TENSOR_MAP_L2_PROMOTION_L2_128B,
+                   CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+  if (r != CUDA_SUCCESS) return fail(MOE_E_DRIVER, "cuTensorMapEncodeTiled failed with CUresult %d", (int)r);
+  return 0;
+}
+
+template <bool FP8, typename AT, bool GEMM1>
+static int launch(const CUtensorMap& ma, const CUtensorMap& mb, const Params& P, int grid, cudaStream_t st) {
+  auto kern = tc_gemm_kernel<FP8, AT, GEMM1>;
+  cudaError_t ce = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)SMEM_BYTES);
+  if (ce != cudaSuccess) return fail((int)ce, "tensor-core GEMM: shared memory attribute: %s", cudaGetErrorString(ce));
+  kern<<<grid, THREADS, SMEM_BYTES, st>>>(ma, mb, P);
+  return check_launch(GEMM1 ? "gemm1 (tcgen05)" : "gemm2 (tcgen05)");
+}
+
+}  // namespace tc
+
+int tc_gemm(bool gemm1, int mode, int act_dtype, const void* a, const float* a_scales_t, const void* w,
+            const float* w_scale, const int32_t* expert_ids, const int32_t* sorted_ids, const int32_t* npp,
+            const float* route_weight, int mul_weight, int64_t numel, int64_t rows_cap, int block_m, int E, int K,
+            int Nout, void* out, float* out_scales_t, int32_t* status, cudaStream_t st) {
+  using namespace tc;
+  const bool fp8 = mode == MOE_MODE_FP8_BLOCK;
+  if (mode != MOE_MODE_FP8_BLOCK && mode != MOE_MODE_HALF)
+    return fail(MOE_E_SHAPE, "tensor-core GEMM: mode %d is served by the generic kernel", mode);
+  if (act_dtype != MOE_BF16 && act_dtype != MOE_F16)
+    return fail(MOE_E_DTYPE, "tensor-core GEMM: activations must be f16 or bf16");
+  if (block_m != BM) return fail(MOE_E_SHAPE, "tensor-core GEMM: align block must be 128");
+  if (rows_cap % BM != 0 || rows_cap <= 0) return fail(MOE_E_SHAPE, "tensor-core GEMM: row capacity must be a positive multiple of 128");
+  const int kbe = fp8 ? 128 : 64;
+  if (K % kbe != 0) return fail(MOE_E_SHAPE, "tensor-core GEMM: K must be a multiple of %d", kbe);
+  if (gemm1 && Nout % 128 != 0) return fail(MOE_E_SHAPE, "tensor-core GEMM1: intermediate size must be a multiple of 128");
+  if (!gemm1 && Nout % 64 != 0) return fail(MOE_E_SHAPE, "tensor-core GEMM2: hidden size must be a multiple of 64");
+  if (fp8 && !gemm1 && Nout % 128 != 0) return fail(MOE_E_SHAPE, "tensor-core GEMM2 (fp8): hidden size must be a multiple of 128");
+  const int rows_w = gemm1 ? 2 * Nout : Nout;
+  if ((int64_t)E * rows_w >= (1ll << 31) || rows_cap >= (1ll << 31)) return fail(MOE_E_TOOBIG, "tensor-core GEMM: extent exceeds int32 coordinates");
+
+  const int eb = fp8 ? 1 : 2;
+  const CUtensorMapDataType dt = fp8 ? CU_TENSOR_MAP_DATA_TYPE_UINT8
+                                     : (act_dtype == MOE_BF16 ? CU_TENSOR_MAP_DATA_TYPE_BFLOAT16 : CU_TENSOR_MAP_DATA_TYPE_FLOAT16);
+  CUtensorMap ma, mb;
+  int rc = make_map(&ma, a, dt, eb, (uint64_t)rows_cap, (uint64_t)K, BM, false);
+  if (rc) return rc;
+  rc = make_map(&mb, w, dt, eb, (uint64_t)E * rows_w, (uint64_t)K, B_BOX_ROWS, true);
+  if (rc) return rc;
+
+  Params P;
+  P.a_scales_t = a_scales_t; P.w_scale = w_scale; P.expert_ids = expert_ids; P.sorted_ids = sorted_ids;
+  P.num_post_pad = npp; P.route_weight = route_weight; P.out = out; P.out_scales_t = out_scales_t;
+  P.status = status; P.numel = numel; P.rows_cap = rows_cap; P.mul_weight = mul_weight; P.E = E; P.K = K;
+  P.Nout = Nout; P.rows_w = rows_w;
+  P.n_tiles = gemm1 ? Nout / 128 : (Nout + BN - 1) / BN;
+
+  int dev = 0, sms = 148;
+  cudaGetDevice(&dev);
+  cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, dev);
+  const int64_t cap_tiles = (rows_cap / BM) * (int64_t)P.n_tiles;
+  const int grid = (int)(cap_tiles < sms ? cap_tiles : sms);
+
+#define MOE_TC_LAUNCH(F, T) (gemm1 ? launch<F, T, true>(ma, mb, P, grid, st) : launch<F, T, false>(ma, mb, P, grid, st))
+  if (fp8) return act_dtype == MOE_BF16 ? MOE_TC_LAUNCH(true, __nv_bfloat16) : MOE_TC_LAUNCH(true, __half);
+  return act_dtype == MOE_BF16 ? MOE_TC_LAUNCH(false, __nv_bfloat16) : MOE_TC_LAUNCH(false, __half);
+#undef MOE_TC_LAUNCH
+}
+
+}  // namespace moe

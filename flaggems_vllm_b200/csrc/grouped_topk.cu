@@ -1,0 +1,233 @@
+// Group-limited top-k routing: one warp per token, shuffle reductions only,
+// no scratch memory.
+//
+// Per token (fp32 throughout, as the reference's fast kernels compute it,
+// src/flaggems_vllm/ops/grouped_topk.py:333-794):
+//   u = sigmoid(score) or score;  r = u + bias
+//   group score = sum of the two largest r in the group
+//   keep the topk_group best groups, then pick the topk largest r among them
+//   weight = u[id] (/ (sum + 1e-20) when renormalising) * scaling factor
+// Every "largest" uses one ordering: higher value first, equal values -> lower
+// index first.  It is implemented, like the reference's packed keys
+// (:310-317), as an unsigned 64-bit key (order-preserving image of the fp32
+// bits) << 32 | (0xFFFFFFFF - index), reduced with max.
+//
+// Expert e lives in lane e % 32, register e / 32, so loads are coalesced.
+// The sigmoid is evaluated in double and rounded once to fp32, which makes
+// the result the correctly rounded fp32 sigmoid and therefore reproducible
+// bit for bit by a CPU check that does the same.
+#include "moe_common.cuh"
+
+namespace moe {
+namespace {
+
+__device__ __forceinline__ uint32_t ordered_bits(float v) {
+  uint32_t b = __float_as_uint(v);
+  return (b & 0x80000000u) ? ~b : (b | 0x80000000u);
+}
+__device__ __forceinline__ uint64_t make_key(float v, uint32_t idx) {
+  return ((uint64_t)ordered_bits(v) << 32) | (uint64_t)(0xFFFFFFFFu - idx);
+}
+__device__ __forceinline__ uint64_t warp_max_u64(uint64_t k) {
+#pragma unroll
+  for (int off = 16; off > 0; off >>= 1) {
+    uint64_t o = __shfl_xor_sync(0xFFFFFFFFu, k, off);
+    k = o > k ? o : k;
+  }
+  return k;
+}
+
+template <typename ST, typename BT, int VPT>
+__global__ void __launch_bounds__(128) grouped_topk_kernel(
+    const ST* __restrict__ scores, int64_t stride0, int64_t stride1, const BT* __restrict__ bias,
+    const uint8_t* __restrict__ is_padding, int64_t M, int E, int n_group, int topk_group, int topk,
+    int renormalize, float scaling, int scoring_func, float* __restrict__ out_w,
+    int32_t* __restrict__ out_ids) {
+  const int lane = threadIdx.x & 31;
+  const int64_t token = (int64_t)blockIdx.x * (blockDim.x >> 5) + (threadIdx.x >> 5);
+  if (token >= M) return;
+  float* w_row = out_w + token * topk;
+  int32_t* id_row = out_ids + token * topk;
+  if (is_padding != nullptr && is_padding[token]) {
+    if (lane < topk) {
+      w_row[lane] = 0.0f;
+      id_row[lane] = -1;
+    }
+    return;
+  }
+  const int per_group = E / n_group;
+  const float NEG_INF = __int_as_float(0xff800000);
+
+  float u[VPT];      // unbiased score
+  uint64_t key[VPT]; // ranking key of u + bias (0 = absent / consumed)
+  const ST* row = scores + token * stride0;
+#pragma unroll
+  for (int j = 0; j < VPT; ++j) {
+    const int e = j * 32 + lane;
+    if (e < E) {
+      float s = ToF32<ST>::get(row[(int64_t)e * stride1]);
+      if (scoring_func == 1) s = (float)(1.0 / (1.0 + exp(-(double)s)));
+      u[j] = s;
+      key[j] = make_key(s + ToF32<BT>::get(bias[e]), (uint32_t)e);
+    } else {
+      u[j] = 0.0f;
+      key[j] = 0;
+    }
+  }
+
+  if (n_group > 1) {
+    // group score -> lane g holds the score of group g
+    float my_group_score = NEG_INF;
+    for (int g = 0; g < n_group; ++g) {
+      float m1 = NEG_INF, m2 = NEG_INF;
+#pragma unroll
+      for (int j = 0; j < VPT; ++j) {
+        const int e = j * 32 + lane;
+        if (e < E && e / per_group == g) {
+          // recover r from the key's high word
+          uint32_t ob = (uint32_t)(key[j] >> 32);
+          uint32_t b = (ob & 0x80000000u) ? (ob ^ 0x80000000u) : ~ob;
+          float r = __uint_as_float(b);
+          if (r > m1) { m2 = m1; m1 = r; } else if (r > m2) { m2 = r; }
+        }
+      }
+#pragma unroll
+      for (int off = 16; off > 0; off >>= 1) {
+        float o1 = __shfl_xor_sync(0xFFFFFFFFu, m1, off);
+        float o2 = __shfl_xor_sync(0xFFFFFFFFu, m2, off);
+        float hi = fmaxf(m1, o1), lo = fminf(m1, o1);
+        m2 = fmaxf(lo, fmaxf(m2, o2));
+        m1 = hi;
+      }
+      float gs = per_group >= 2 ? m1 + m2 : m1;
+      if (lane == g) my_group_score = gs;
+    }
+    // choose topk_group groups
+    uint32_t keep_mask = 0;
+    uint64_t gkey = lane < n_group ? make_key(my_group_score, (uint32_t)lane) : 0;
+    for (int t = 0; t < topk_group; ++t) {
+      uint64_t best = warp_max_u64(gkey);
+      uint32_t g = 0xFFFFFFFFu - (uint32_t)(best & 0xFFFFFFFFu);
+      keep_mask |= 1u << (g & 31);
+      if (gkey == best) gkey = 0;
+    }
+    // experts of dropped groups rank as -inf (still ordered by index)
+#pragma unroll
+    for (int j = 0; j < VPT; ++j) {
+      const int e = j * 32 + lane;
+      if (e < E && !((keep_mask >> (e / per_group)) & 1u)) key[j] = make_key(NEG_INF, (uint32_t)e);
+    }
+  }
+
+  // top-k extraction
+  float my_w = 0.0f;
+  int32_t my_id = 0;
+  uint64_t local = 0;
+  int local_j = 0;
+#pragma unroll
+  for (int j = 0; j < VPT; ++j)
+    if (key[j] > local) { local = key[j]; local_j = j; }
+  for (int t = 0; t < topk; ++t) {
+    uint64_t best = warp_max_u64(local);
+    uint32_t id = 0xFFFFFFFFu - (uint32_t)(best & 0xFFFFFFFFu);
+    float wsel = 0.0f;
+    if (local == best && best != 0) {
+      // this lane owns the winner: fetch its unbiased value, consume it
+#pragma unroll
+      for (int j = 0; j < VPT; ++j)
+        if (j == local_j) { wsel = u[j]; key[j] = 0; }
+      local = 0;
+#pragma unroll
+      for (int j = 0; j < VPT; ++j)
+        if (key[j] > local) { local = key[j]; local_j = j; }
+    }
+    wsel = __shfl_sync(0xFFFFFFFFu, wsel, id & 31);
+    if (lane == t) { my_w = wsel; my_id = (int32_t)id; }
+  }
+  float sum = lane < topk ? my_w : 0.0f;
+#pragma unroll
+  for (int off = 16; off > 0; off >>= 1) sum += __shfl_xor_sync(0xFFFFFFFFu, sum, off);
+  if (lane < topk) {
+    float w = renormalize ? my_w / (sum + 1e-20f) : my_w;
+    w_row[lane] = w * scaling;
+    id_row[lane] = my_id;
+  }
+}
+
+template <typename ST, typename BT>
+int launch_vpt(const ST* scores, int64_t s0, int64_t s1, const BT* bias, const uint8_t* pad,
+               int64_t M, int E, int n_group, int topk_group, int topk, int renorm, float scaling,
+               int scoring, float* w, int32_t* ids, cudaStream_t st) {
+  const int warps = 4;
+  dim3 grid((unsigned)((M + warps - 1) / warps)), block(warps * 32);
+#define MOE_TOPK_LAUNCH(V)                                                                     \
+  grouped_topk_kernel<ST, BT, V><<<grid, block, 0, st>>>(scores, s0, s1, bias, pad, M, E,      \
+                                                         n_group, topk_group, topk, renorm,   \
+                                                         scaling, scoring, w, ids)
+  if (E <= 32) MOE_TOPK_LAUNCH(1);
+  else if (E <= 64) MOE_TOPK_LAUNCH(2);
+  else if (E <= 128) MOE_TOPK_LAUNCH(4);
+  else if (E <= 256) MOE_TOPK_LAUNCH(8);
+  else if (E <= 512) MOE_TOPK_LAUNCH(16);
+  else MOE_TOPK_LAUNCH(32);
+#undef MOE_TOPK_LAUNCH
+  return check_launch("grouped_topk");
+}
+
+template <typename ST>
+int launch_bias(const ST* scores, int64_t s0, int64_t s1, const void* bias, int bias_dtype,
+                const uint8_t* pad, int64_t M, int E, int n_group, int topk_group, int topk,
+                int renorm, float scaling, int scoring, float* w, int32_t* ids, cudaStream_t st) {
+  switch (bias_dtype) {
+    case MOE_F32:
+      return launch_vpt(scores, s0, s1, (const float*)bias, pad, M, E, n_group, topk_group, topk,
+                        renorm, scaling, scoring, w, ids, st);
+    case MOE_F16:
+      return launch_vpt(scores, s0, s1, (const __half*)bias, pad, M, E, n_group, topk_group, topk,
+                        renorm, scaling, scoring, w, ids, st);
+    case MOE_BF16:
+      return launch_vpt(scores, s0, s1, (const __nv_bfloat16*)bias, pad, M, E, n_group,
+                        topk_group, topk, renorm, scaling, scoring, w, ids, st);
+    default:
+      return fail(MOE_E_DTYPE, "grouped_topk: unsupported bias dtype %d", bias_dtype);
+  }
+}
+
+}  // namespace
+}  // namespace moe
+
+extern "C" int moe_grouped_topk(const void* scores, int scores_dtype, int64_t stride0,
+                                int64_t stride1, const void* bias, int bias_dtype,
+                                const uint8_t* is_padding, int64_t M, int E, int n_group,
+                                int topk_group, int topk, int renormalize,
+                                float routed_scaling_factor, int scoring_func, float* topk_weights,
+                                int32_t* topk_ids, void* stream) {
+  using namespace moe;
+  if (M < 0 || E <= 0 || n_group <= 0 || topk <= 0 || topk_group <= 0)
+    return fail(MOE_E_BADARG, "grouped_topk: non-positive extent");
+  if (E > 1024) return fail(MOE_E_TOOBIG, "grouped_topk: at most 1024 experts (got %d)", E);
+  if (n_group > 32 || topk > 32 || topk_group > n_group || E % n_group != 0 || topk > E)
+    return fail(MOE_E_SHAPE, "grouped_topk: bad group/top-k configuration");
+  if (scoring_func != 0 && scoring_func != 1)
+    return fail(MOE_E_BADARG, "grouped_topk: scoring_func must be 0 or 1");
+  if (M == 0) return 0;
+  if (!scores || !bias || !topk_weights || !topk_ids)
+    return fail(MOE_E_BADARG, "grouped_topk: null pointer");
+  cudaStream_t st = (cudaStream_t)stream;
+  switch (scores_dtype) {
+    case MOE_F32:
+      return launch_bias((const float*)scores, stride0, stride1, bias, bias_dtype, is_padding, M, E,
+                         n_group, topk_group, topk, renormalize, routed_scaling_factor,
+                         scoring_func, topk_weights, topk_ids, st);
+    case MOE_F16:
+      return launch_bias((const __half*)scores, stride0, stride1, bias, bias_dtype, is_padding, M,
+                         E, n_group, topk_group, topk, renormalize, routed_scaling_factor,
+                         scoring_func, topk_weights, topk_ids, st);
+    case MOE_BF16:
+      return launch_bias((const __nv_bfloat16*)scores, stride0, stride1, bias, bias_dtype,
+                         is_padding, M, E, n_group, topk_group, topk, renormalize,
+                         routed_scaling_factor, scoring_func, topk_weights, topk_ids, st);
+    default:
+      return fail(MOE_E_DTYPE, "grouped_topk: unsupported scores dtype %d", scores_dtype);
+  }
+}

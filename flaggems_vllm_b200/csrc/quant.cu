@@ -1,0 +1,237 @@
+// Row kernels around the grouped GEMMs:
+//   * gather_rows: copies (or e4m3-quantises) activation rows into
+//     expert-sorted order so the GEMM kernels read plain 2-D tiles.
+//   * per_token_group_quant_fp8: the stand-alone 1x128 quantiser.
+//   * moe_sum: fixed-order fp32 reduction over the top-k axis.
+// Quantisation follows the reference kernel exactly
+// (src/flaggems_vllm/ops/per_token_group_quant_fp8.py:150-156):
+//   s = max(amax, 1e-10) * (1/448);  q = clamp(x / s, -448, 448) -> e4m3 (RN).
+#include "moe_common.cuh"
+
+namespace moe {
+namespace {
+
+constexpr int kRowThreads = 256;
+
+// One warp quantises one 128-wide group: 4 consecutive elements per lane.
+template <typename T>
+__device__ __forceinline__ void quant_group_128(const T* __restrict__ src, uint8_t* __restrict__ dst,
+                                                float* __restrict__ scale_out, int lane) {
+  float v[4];
+  if constexpr (sizeof(T) == 2) {
+    uint2 raw = *reinterpret_cast<const uint2*>(src + lane * 4);
+    const T* p = reinterpret_cast<const T*>(&raw);
+#pragma unroll
+    for (int i = 0; i < 4; ++i) v[i] = ToF32<T>::get(p[i]);
+  } else {
+    float4 raw = *reinterpret_cast<const float4*>(src + lane * 4);
+    v[0] = raw.x; v[1] = raw.y; v[2] = raw.z; v[3] = raw.w;
+  }
+  float amax = fmaxf(fmaxf(fabsf(v[0]), fabsf(v[1])), fmaxf(fabsf(v[2]), fabsf(v[3])));
+#pragma unroll
+  for (int off = 16; off > 0; off >>= 1) amax = fmaxf(amax, __shfl_xor_sync(0xFFFFFFFFu, amax, off));
+  const float s = fmaxf(amax, kQuantEps) * (1.0f / kFp8Max);
+  uint32_t packed = 0;
+#pragma unroll
+  for (int i = 0; i < 4; ++i) {
+    float q = fminf(fmaxf(v[i] / s, -kFp8Max), kFp8Max);
+    packed |= (uint32_t)f32_to_fp8e4m3(q) << (8 * i);
+  }
+  *reinterpret_cast<uint32_t*>(dst + lane * 4) = packed;
+  if (lane == 0) *scale_out = s;
+}
+
+// grid-stride over output rows; one CTA per row at a time.
+template <typename T, bool QUANT>
+__global__ void __launch_bounds__(kRowThreads) gather_rows_kernel(
+    const T* __restrict__ x, int64_t M, int64_t cols, int topk, const int32_t* __restrict__ sorted_ids,
+    const int32_t* __restrict__ num_post_pad, int64_t out_rows, void* __restrict__ out,
+    float* __restrict__ scales_t) {
+  const int64_t numel = M * topk;
+  int64_t rows = out_rows;
+  if (num_post_pad != nullptr) rows = min((int64_t)num_post_pad[0], out_rows);
+  const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5, n_warps = kRowThreads / 32;
+  for (int64_t p = blockIdx.x; p < rows; p += gridDim.x) {
+    const int64_t sid = sorted_ids != nullptr ? (int64_t)sorted_ids[p] : p;
+    if (sid < 0 || sid >= numel) continue;  // padding slot: row content is never used
+    const T* src = x + (sid / topk) * cols;
+    if constexpr (QUANT) {
+      uint8_t* dst = reinterpret_cast<uint8_t*>(out) + p * cols;
+      const int groups = (int)(cols / 128);
+      for (int g = warp; g < groups; g += n_warps)
+        quant_group_128<T>(src + g * 128, dst + g * 128, scales_t + (int64_t)g * out_rows + p, lane);
+    } else {
+      T* dst = reinterpret_cast<T*>(out) + p * cols;
+      const int64_t n16 = cols * sizeof(T) / 16;
+      const uint4* s4 = reinterpret_cast<const uint4*>(src);
+      uint4* d4 = reinterpret_cast<uint4*>(dst);
+      for (int64_t i = threadIdx.x; i < n16; i += kRowThreads) d4[i] = s4[i];
+    }
+  }
+}
+
+template <typename T>
+__global__ void __launch_bounds__(kRowThreads) quant_rows_kernel(
+    const T* __restrict__ x, int64_t rows, int64_t cols, uint8_t* __restrict__ q,
+    float* __restrict__ scales, int transposed, int64_t scale_ld) {
+  const int lane = threadIdx.x & 31;
+  const int64_t groups_per_row = cols / 128;
+  const int64_t total = rows * groups_per_row;
+  const int64_t warp0 = (int64_t)blockIdx.x * (kRowThreads / 32) + (threadIdx.x >> 5);
+  const int64_t stride = (int64_t)gridDim.x * (kRowThreads / 32);
+  for (int64_t w = warp0; w < total; w += stride) {
+    const int64_t r = w / groups_per_row, g = w % groups_per_row;
+    float* so = transposed ? scales + g * scale_ld + r : scales + r * groups_per_row + g;
+    quant_group_128<T>(x + r * cols + g * 128, q + r * cols + g * 128, so, lane);
+  }
+}
+
+// out[m, h] = sum_j in[m, j, h]; 8 elements (16 B) of 2-byte types per thread.
+template <typename T, typename IdT>
+__global__ void __launch_bounds__(256) moe_sum_kernel(
+    const T* __restrict__ in, T* __restrict__ out, int64_t M, int topk, int64_t H,
+    const IdT* __restrict__ ids, int num_experts, const int32_t* __restrict__ expert_map, bool aligned) {
+  constexpr int V = 16 / sizeof(T);
+  const int64_t vec_per_row = (H + V - 1) / V;
+  const int64_t total = M * vec_per_row;
+  for (int64_t idx = (int64_t)blockIdx.x * blockDim.x + threadIdx.x; idx < total;
+       idx += (int64_t)gridDim.x * blockDim.x) {
+    const int64_t m = idx / vec_per_row, h0 = (idx % vec_per_row) * V;
+    float acc[V];
+#pragma unroll
+    for (int i = 0; i < V; ++i) acc[i] = 0.0f;
+    const bool full = aligned && (h0 + V <= H) && (H % V == 0);
+    for (int j = 0; j < topk; ++j) {
+      if (ids != nullptr) {
+        long long e = (long long)ids[m * topk + j];
+        if (e < 0 || e >= num_experts) continue;
+        if (expert_map != nullptr && expert_map[e] < 0) continue;
+      }
+      const T* src = in + (m * topk + j) * H + h0;
+      if (full) {
+        uint4 raw = *reinterpret_cast<const uint4*>(src);
+        const T* p = reinterpret_cast<const T*>(&raw);
+#pragma unroll
+        for (int i = 0; i < V; ++i) acc[i] += ToF32<T>::get(p[i]);
+      } else {
+        for (int i = 0; i < V && h0 + i < H; ++i) acc[i] += ToF32<T>::get(src[i]);
+      }
+    }
+    T* dst = out + m * H + h0;
+    if (full) {
+      uint4 raw;
+      T* p = reinterpret_cast<T*>(&raw);
+#pragma unroll
+      for (int i = 0; i < V; ++i) p[i] = from_f32<T>(acc[i]);
+      *reinterpret_cast<uint4*>(dst) = raw;
+    } else {
+      for (int i = 0; i < V && h0 + i < H; ++i) dst[i] = from_f32<T>(acc[i]);
+    }
+  }
+}
+
+int grid_for(int64_t work_items, int per_sm) {
+  int dev = 0, sms = 148;
+  cudaGetDevice(&dev);
+  cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, dev);
+  int64_t cap = (int64_t)sms * per_sm;
+  return (int)(work_items < 1 ? 1 : (work_items < cap ? work_items : cap));
+}
+
+template <typename T>
+int launch_gather(const void* x, int64_t M, int64_t cols, int topk, const int32_t* sorted_ids,
+                  const int32_t* npp, int64_t out_rows, int mode, void* out, float* scales_t,
+                  cudaStream_t st) {
+  const int grid = grid_for(out_rows, 8);
+  if (mode == MOE_MODE_FP8_BLOCK)
+    gather_rows_kernel<T, true><<<grid, kRowThreads, 0, st>>>((const T*)x, M, cols, topk, sorted_ids,
+                                                              npp, out_rows, out, scales_t);
+  else
+    gather_rows_kernel<T, false><<<grid, kRowThreads, 0, st>>>((const T*)x, M, cols, topk, sorted_ids,
+                                                               npp, out_rows, out, scales_t);
+  return check_launch("gather_rows");
+}
+
+template <typename T>
+int launch_sum(const void* in, void* out, int64_t M, int topk, int64_t H, const void* ids,
+               int ids_int64, int E, const int32_t* emap, cudaStream_t st) {
+  constexpr int V = 16 / sizeof(T);
+  const int64_t total = M * ((H + V - 1) / V);
+  const int grid = grid_for((total + 255) / 256, 8);
+  const bool aligned = (((uintptr_t)in | (uintptr_t)out) & 15) == 0;
+  if (ids_int64)
+    moe_sum_kernel<T, int64_t><<<grid, 256, 0, st>>>((const T*)in, (T*)out, M, topk, H,
+                                                     (const int64_t*)ids, E, emap, aligned);
+  else
+    moe_sum_kernel<T, int32_t><<<grid, 256, 0, st>>>((const T*)in, (T*)out, M, topk, H,
+                                                     (const int32_t*)ids, E, emap, aligned);
+  return check_launch("moe_sum");
+}
+
+}  // namespace
+}  // namespace moe
+
+extern "C" int moe_gather_rows(const void* x, int x_dtype, int64_t M, int64_t cols, int topk,
+                               const int32_t* sorted_ids, const int32_t* num_post_pad,
+                               int64_t out_rows, int mode, void* out, float* scales_t,
+                               void* stream) {
+  using namespace moe;
+  if (M < 0 || cols <= 0 || topk <= 0 || out_rows < 0) return fail(MOE_E_BADARG, "gather_rows: bad extent");
+  if (out_rows == 0 || M == 0) return 0;
+  if (!x || !out || !sorted_ids) return fail(MOE_E_BADARG, "gather_rows: null pointer");
+  if (mode == MOE_MODE_FP8_BLOCK) {
+    if (cols % 128 != 0) return fail(MOE_E_SHAPE, "gather_rows: fp8 mode needs cols %% 128 == 0");
+    if (!scales_t) return fail(MOE_E_BADARG, "gather_rows: fp8 mode needs a scale buffer");
+  }
+  if ((cols * (x_dtype == MOE_F32 ? 4 : 2)) % 16 != 0)
+    return fail(MOE_E_SHAPE, "gather_rows: row bytes must be a multiple of 16");
+  cudaStream_t st = (cudaStream_t)stream;
+  switch (x_dtype) {
+    case MOE_F32: return launch_gather<float>(x, M, cols, topk, sorted_ids, num_post_pad, out_rows, mode, out, scales_t, st);
+    case MOE_F16: return launch_gather<__half>(x, M, cols, topk, sorted_ids, num_post_pad, out_rows, mode, out, scales_t, st);
+    case MOE_BF16: return launch_gather<__nv_bfloat16>(x, M, cols, topk, sorted_ids, num_post_pad, out_rows, mode, out, scales_t, st);
+    default: return fail(MOE_E_DTYPE, "gather_rows: unsupported dtype %d", x_dtype);
+  }
+}
+
+extern "C" int moe_per_token_group_quant_fp8(const void* x, int x_dtype, int64_t rows, int64_t cols,
+                                             int group, void* q, float* scales,
+                                             int scales_transposed, int64_t scale_ld, void* stream) {
+  using namespace moe;
+  if (rows < 0 || cols <= 0) return fail(MOE_E_BADARG, "quant_fp8: bad extent");
+  if (group != 128) return fail(MOE_E_SHAPE, "quant_fp8: group size must be 128 (got %d)", group);
+  if (cols % 128 != 0) return fail(MOE_E_SHAPE, "quant_fp8: cols must be a multiple of 128");
+  if (rows == 0) return 0;
+  if (!x || !q || !scales) return fail(MOE_E_BADARG, "quant_fp8: null pointer");
+  cudaStream_t st = (cudaStream_t)stream;
+  const int grid = grid_for((rows * (cols / 128) + 7) / 8, 8);
+  switch (x_dtype) {
+    case MOE_F32:
+      quant_rows_kernel<float><<<grid, kRowThreads, 0, st>>>((const float*)x, rows, cols, (uint8_t*)q, scales, scales_transposed, scale_ld);
+      break;
+    case MOE_F16:
+      quant_rows_kernel<__half><<<grid, kRowThreads, 0, st>>>((const __half*)x, rows, cols, (uint8_t*)q, scales, scales_transposed, scale_ld);
+      break;
+    case MOE_BF16:
+      quant_rows_kernel<__nv_bfloat16><<<grid, kRowThreads, 0, st>>>((const __nv_bfloat16*)x, rows, cols, (uint8_t*)q, scales, scales_transposed, scale_ld);
+      break;
+    default: return fail(MOE_E_DTYPE, "quant_fp8: unsupported dtype %d", x_dtype);
+  }
+  return check_launch("per_token_group_quant_fp8");
+}
+
+extern "C" int moe_sum(const void* in, void* out, int dtype, int64_t M, int topk, int64_t H,
+                       const void* topk_ids, int ids_int64, int num_experts,
+                       const int32_t* expert_map, void* stream) {
+  using namespace moe;
+  if (M < 0 || topk <= 0 || H <= 0) return fail(MOE_E_BADARG, "moe_sum: bad extent");
+  if (M == 0) return 0;
+  if (!in || !out) return fail(MOE_E_BADARG, "moe_sum: null pointer");
+  cudaStream_t st = (cudaStream_t)stream;
+  switch (dtype) {
+    case MOE_F32: return launch_sum<float>(in, out, M, topk, H, topk_ids, ids_int64, num_experts, expert_map, st);
+    case MOE_F16: return launch_sum<__half>(in, out, M, topk, H, topk_ids, ids_int64, num_experts, expert_map, st);
+    case MOE_BF16: return launch_sum<__nv_bfloat16>(in, out, M, topk, H, topk_ids, ids_int64, num_experts, expert_map, st);
+    default: return fail(MOE_E_DTYPE, "moe_sum: unsupported dtype %d", dtype);
+  }
+}

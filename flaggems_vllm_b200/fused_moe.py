@@ -1,0 +1,330 @@
+"""fused_experts_impl: the MoE layer on expert-sorted rows.
+
+Pipeline per chunk of at most 32768 tokens (the reference's chunk size,
+src/flaggems_vllm/ops/fused_moe.py:2399-2400):
+
+    moe_align_block_size          stable sort of routes by expert, 1 launch
+    gather_rows                   activation rows -> sorted order (+ e4m3 1x128 quant)
+    gemm1                         SiLU(x Wg^T) * (x Wu^T)   (+ 1x128 re-quant, FP8)
+    gemm2                         (act W2^T) * route weight -> y[route, H]
+    moe_sum                       fixed-order fp32 sum over the top-k routes
+
+The signature, accepted arguments and error types are those of the reference
+function (src/flaggems_vllm/ops/fused_moe.py:2314-2390).  Modes served:
+f16/bf16/f32 weights, FP8 e4m3 with 128x128 block scales, INT8/INT4-in-INT8
+weight-only with per-channel scales.  Every other mode raises
+NotImplementedError: there is no fallback path.
+"""
+
+from __future__ import annotations
+
+import logging
+import os
+from typing import Optional
+
+import torch
+
+from . import _lib
+from .align import ceil_div, round_up
+
+logger = logging.getLogger(__name__)
+
+CHUNK_SIZE = 32 * 1024
+TC_BLOCK_M = 128
+GENERIC_BLOCK_M = 16
+
+_SUPPORTED_ACTIVATIONS = ("silu", "swigluoai_uninterleave")
+_ALL_ACTIVATIONS = ("silu", "gelu", "relu2", "swigluoai", "swigluoai_uninterleave", "swiglustep",
+                    "silu_no_mul", "gelu_no_mul", "relu2_no_mul")
+
+
+# bench.py sets this to a callable(name) to time the stages of a step
+STAGE_HOOK = None
+
+
+def _no_mark(_name):
+    return None
+
+
+def _force_generic() -> bool:
+    return os.environ.get("FLAGGEMS_B200_GENERIC_GEMM", "0").lower() in ("1", "true", "yes", "on")
+
+
+def _tc_eligible(mode: int, act_dtype: torch.dtype, H: int, I: int) -> bool:
+    if act_dtype not in (torch.bfloat16, torch.float16):
+        return False
+    if mode == _lib.MODE_FP8_BLOCK:
+        return H % 128 == 0 and I % 128 == 0
+    if mode == _lib.MODE_HALF:
+        return H % 64 == 0 and I % 128 == 0
+    return False
+
+
+def _check_activation(activation, gemm1_alpha, gemm1_beta, gemm1_clamp_limit):
+    if activation not in _ALL_ACTIVATIONS:
+        raise ValueError(f"Unknown MoE activation: {activation!r}. Valid activations: {list(_ALL_ACTIVATIONS)}")
+    if activation == "swigluoai_uninterleave":
+        raise NotImplementedError("activation 'swigluoai_uninterleave' is not implemented by the B200 kernels")
+    if activation == "silu":
+        if any(v is not None for v in (gemm1_alpha, gemm1_beta, gemm1_clamp_limit)):
+            raise ValueError("gemm1_alpha/beta/clamp_limit require swigluoai_uninterleave")
+        return
+    raise ValueError(
+        f"Only 'silu' and 'swigluoai_uninterleave' activations are supported, got {activation!r}")
+
+
+def run_chunk(x, w1, w2, topk_weights, topk_ids, out, *, mode, w1_scale, w2_scale, global_num_experts,
+              expert_map, apply_router_weight_on_input, use_tensor_cores=None, keep=None, mark=None):
+    """One chunk of the layer.  ``keep`` (a dict) receives the intermediates for
+    tests; ``mark(name)`` is called after each stage has been enqueued (bench.py
+    records CUDA events there)."""
+    if mark is None:
+        mark = STAGE_HOOK or _no_mark
+    L = _lib.lib()
+    dev = x.device
+    st = _lib.stream_of(x)
+    status = _lib.status_word(dev)
+    M, H = x.shape
+    k = topk_ids.shape[1]
+    E_local, N2, _ = w1.shape
+    I = N2 // 2
+    numel = M * k
+    act_dt = x.dtype
+    act_code = _lib.dtype_code(act_dt)
+    if use_tensor_cores is None:
+        use_tensor_cores = _tc_eligible(mode, act_dt, H, I) and not _force_generic()
+    block_m = TC_BLOCK_M if use_tensor_cores else GENERIC_BLOCK_M
+
+    # every expert that owns at least one route pads by < block_m
+    rows_cap = round_up(numel + min(numel, global_num_experts) * (block_m - 1), block_m)
+    sorted_ids = torch.empty(rows_cap, dtype=torch.int32, device=dev)
+    expert_ids = torch.empty(rows_cap // block_m, dtype=torch.int32, device=dev)
+    npp = torch.empty(1, dtype=torch.int32, device=dev)
+    ids = topk_ids if topk_ids.is_contiguous() else topk_ids.contiguous()
+    _lib.check(L.moe_align_block_size(ids.data_ptr(), int(ids.dtype == torch.int64), numel, global_num_experts,
+                                      block_m, sorted_ids.data_ptr(), rows_cap, expert_ids.data_ptr(),
+                                      expert_ids.numel(), npp.data_ptr(), status.data_ptr(), st))
+    mark("align")
+    if expert_map is not None:
+        # same post-hoc lookup as the reference (moe_align_block_size.py:924-925);
+        # unused blocks (-1) lie beyond num_tokens_post_padded and are never visited
+        expert_ids = expert_map[expert_ids.long()].to(torch.int32)
+
+    fp8 = mode == _lib.MODE_FP8_BLOCK
+    if fp8:
+        a_sorted = torch.empty((rows_cap, H), dtype=torch.float8_e4m3fn, device=dev)
+        a_scales = torch.empty((H // 128, rows_cap), dtype=torch.float32, device=dev)
+        act = torch.empty((rows_cap, I), dtype=torch.float8_e4m3fn, device=dev)
+        act_scales = torch.empty((I // 128, rows_cap), dtype=torch.float32, device=dev)
+    else:
+        a_sorted = torch.empty((rows_cap, H), dtype=act_dt, device=dev)
+        a_scales = None
+        act = torch.empty((rows_cap, I), dtype=act_dt, device=dev)
+        act_scales = None
+    _lib.check(L.moe_gather_rows(x.data_ptr(), act_code, M, H, k, sorted_ids.data_ptr(), npp.data_ptr(), rows_cap,
+                                 mode if fp8 else _lib.MODE_HALF, a_sorted.data_ptr(), _lib.ptr(a_scales), st))
+
+    mark("gather")
+    rw = topk_weights if topk_weights.dtype == torch.float32 else topk_weights.float()
+    rw = rw if rw.is_contiguous() else rw.contiguous()
+    tc = int(bool(use_tensor_cores))
+    _lib.check(L.moe_gemm1(mode, act_code, a_sorted.data_ptr(), _lib.ptr(a_scales), w1.data_ptr(),
+                           _lib.ptr(w1_scale), expert_ids.data_ptr(), sorted_ids.data_ptr(), npp.data_ptr(),
+                           rw.data_ptr(), int(apply_router_weight_on_input), numel, rows_cap, block_m, E_local, H,
+                           I, act.data_ptr(), _lib.ptr(act_scales), tc, status.data_ptr(), st))
+    mark("gemm1")
+    y = torch.empty((numel, H), dtype=act_dt, device=dev)
+    _lib.check(L.moe_gemm2(mode, act_code, act.data_ptr(), _lib.ptr(act_scales), w2.data_ptr(), _lib.ptr(w2_scale),
+                           expert_ids.data_ptr(), sorted_ids.data_ptr(), npp.data_ptr(), rw.data_ptr(),
+                           int(not apply_router_weight_on_input), numel, rows_cap, block_m, E_local, H, I,
+                           y.data_ptr(), tc, status.data_ptr(), st))
+    mark("gemm2")
+    emap = None
+    if expert_map is not None:
+        emap = expert_map if expert_map.dtype == torch.int32 else expert_map.to(torch.int32)
+        emap = emap.contiguous()
+    _lib.check(L.moe_sum(y.data_ptr(), out.data_ptr(), act_code, M, k, H, ids.data_ptr(),
+                         int(ids.dtype == torch.int64), global_num_experts, _lib.ptr(emap), st))
+    mark("sum")
+    if keep is not None:
+        keep.update(sorted_ids=sorted_ids, expert_ids=expert_ids, num_post_pad=npp, a_sorted=a_sorted,
+                    a_scales_t=a_scales, act=act, act_scales_t=act_scales, y=y, block_m=block_m,
+                    rows_cap=rows_cap, used_tensor_cores=bool(use_tensor_cores))
+
+
+def fused_experts_impl(
+    hidden_states: torch.Tensor,
+    w1: torch.Tensor,
+    w2: torch.Tensor,
+    topk_weights: torch.Tensor,
+    topk_ids: torch.Tensor,
+    inplace: bool = False,
+    activation: str = "silu",
+    apply_router_weight_on_input: bool = False,
+    use_fp8_w8a8: bool = False,
+    use_int8_w8a8: bool = False,
+    use_int8_w8a16: bool = False,
+    use_int4_w4a16: bool = False,
+    ocp_mx_scheme: str | None = None,
+    per_channel_quant: bool = False,
+    global_num_experts: int = -1,
+    expert_map: torch.Tensor | None = None,
+    w1_scale: Optional[torch.Tensor] = None,
+    w2_scale: Optional[torch.Tensor] = None,
+    w1_zp: torch.Tensor | None = None,
+    w2_zp: torch.Tensor | None = None,
+    a1_scale: Optional[torch.Tensor] = None,
+    a2_scale: Optional[torch.Tensor] = None,
+    block_shape: Optional[list[int]] = None,
+    w1_bias: Optional[torch.Tensor] = None,
+    w2_bias: Optional[torch.Tensor] = None,
+    *,
+    gemm1_alpha: float | None = None,
+    gemm1_beta: float | None = None,
+    gemm1_clamp_limit: float | None = None,
+) -> torch.Tensor:
+    logger.debug("GEMS FUSED MOE")
+    _check_activation(activation, gemm1_alpha, gemm1_beta, gemm1_clamp_limit)
+
+    if ocp_mx_scheme is not None:
+        if not (ocp_mx_scheme.startswith("w_mxfp4") or ocp_mx_scheme.startswith("w_mxfp6")):
+            raise NotImplementedError(f"Unsupported ocp_mx_scheme={ocp_mx_scheme}")
+        raise NotImplementedError("OCP MX weight formats are not implemented by the B200 kernels")
+    assert hidden_states.size(1) == w1.size(2), f"Hidden size mismatch {hidden_states.size(1)} != {w1.size(2)}"
+    assert topk_weights.size() == topk_ids.size(), "topk shape mismatch"
+    assert hidden_states.is_contiguous(), "Hidden_states must be contiguous"
+    assert w1.stride(-1) == 1, "Stride of last dimension must be 1"
+    assert w2.stride(-1) == 1, "Stride of last dimension must be 1"
+    assert hidden_states.dtype in [torch.float32, torch.float16, torch.bfloat16]
+
+    if use_int8_w8a8:
+        raise NotImplementedError("INT8 W8A8 is not implemented by the B200 kernels")
+    if w1_zp is not None or w2_zp is not None:
+        raise NotImplementedError("zero points are not implemented by the B200 kernels")
+    if w1_bias is not None or w2_bias is not None:
+        raise NotImplementedError("expert biases are not implemented by the B200 kernels")
+    if a1_scale is not None or a2_scale is not None:
+        raise NotImplementedError("static activation scales are not implemented by the B200 kernels")
+
+    num_tokens = hidden_states.size(0)
+    E, N, _ = w1.size()
+    K = w2.size(1)
+    assert N % 2 == 0 and w2.size(2) == N // 2 and w2.size(0) == E and K == hidden_states.size(1), \
+        "w1/w2 shapes do not describe a gated MoE layer"
+    if global_num_experts == -1:
+        global_num_experts = E
+
+    if use_fp8_w8a8:
+        if block_shape is None or list(block_shape) != [128, 128]:
+            raise NotImplementedError("FP8 W8A8 is implemented for block_shape=[128, 128] only")
+        if per_channel_quant:
+            raise NotImplementedError("per-token FP8 activation scales are not implemented")
+        assert w1.dtype == torch.float8_e4m3fn and w2.dtype == torch.float8_e4m3fn, "FP8 weights expected"
+        assert w1_scale is not None and w2_scale is not None, "FP8 block scales expected"
+        assert hidden_states.dtype != torch.float32, "FP8 path needs f16/bf16 activations"
+        assert K % 128 == 0 and (N // 2) % 128 == 0, "FP8 block quantisation needs sizes divisible by 128"
+        assert tuple(w1_scale.shape) == (E, ceil_div(N, 128), K // 128), "w1_scale shape"
+        assert tuple(w2_scale.shape) == (E, K // 128, (N // 2) // 128), "w2_scale shape"
+        mode = _lib.MODE_FP8_BLOCK
+    elif use_int8_w8a16 or use_int4_w4a16:
+        if block_shape is not None and len(block_shape) == 2 and block_shape[1] > 0:
+            raise NotImplementedError("group-quantised weight-only formats are not implemented")
+        assert w1.dtype == torch.int8 and w2.dtype == torch.int8, "INT8 weight containers expected"
+        assert w1_scale is not None and w2_scale is not None, "per-channel weight scales expected"
+        assert w1_scale.numel() == E * N and w2_scale.numel() == E * K, "per-channel scale shape"
+        mode = _lib.MODE_W8A16
+    else:
+        assert w1.dtype == hidden_states.dtype and w2.dtype == hidden_states.dtype, \
+            "weights must have the activation dtype"
+        mode = _lib.MODE_HALF
+
+    _lib.require_cuda(hidden_states, "fused_experts_impl")
+    w1c = w1 if w1.is_contiguous() else w1.contiguous()
+    w2c = w2 if w2.is_contiguous() else w2.contiguous()
+    s1 = s2 = None
+    if mode != _lib.MODE_HALF:
+        s1 = w1_scale.to(torch.float32).contiguous()
+        s2 = w2_scale.to(torch.float32).contiguous()
+
+    out_hidden_states = hidden_states if inplace else torch.empty_like(hidden_states)
+    for chunk in range((num_tokens // CHUNK_SIZE) + 1):
+        begin, end = chunk * CHUNK_SIZE, min((chunk + 1) * CHUNK_SIZE, num_tokens)
+        if end - begin <= 0:
+            break
+        run_chunk(hidden_states[begin:end], w1c, w2c, topk_weights[begin:end], topk_ids[begin:end],
+                  out_hidden_states[begin:end], mode=mode, w1_scale=s1, w2_scale=s2,
+                  global_num_experts=global_num_experts, expert_map=expert_map,
+                  apply_router_weight_on_input=apply_router_weight_on_input)
+    return out_hidden_states
+
+
+def inplace_fused_experts(
+    hidden_states: torch.Tensor,
+    w1: torch.Tensor,
+    w2: torch.Tensor,
+    topk_weights: torch.Tensor,
+    topk_ids: torch.Tensor,
+    activation: str = "silu",
+    apply_router_weight_on_input: bool = False,
+    use_fp8_w8a8: bool = False,
+    use_int8_w8a8: bool = False,
+    use_int8_w8a16: bool = False,
+    use_int4_w4a16: bool = False,
+    per_channel_quant: bool = False,
+    global_num_experts: int = -1,
+    w1_scale: Optional[torch.Tensor] = None,
+    w2_scale: Optional[torch.Tensor] = None,
+    a1_scale: Optional[torch.Tensor] = None,
+    a2_scale: Optional[torch.Tensor] = None,
+    block_shape: Optional[list[int]] = None,
+    w1_bias: Optional[torch.Tensor] = None,
+    w2_bias: Optional[torch.Tensor] = None,
+    *,
+    gemm1_alpha: float | None = None,
+    gemm1_beta: float | None = None,
+    gemm1_clamp_limit: float | None = None,
+) -> None:
+    """Writes the layer output into ``hidden_states``; returns None."""
+    fused_experts_impl(
+        hidden_states, w1, w2, topk_weights, topk_ids, inplace=True, activation=activation,
+        apply_router_weight_on_input=apply_router_weight_on_input, use_fp8_w8a8=use_fp8_w8a8,
+        use_int8_w8a8=use_int8_w8a8, use_int8_w8a16=use_int8_w8a16, use_int4_w4a16=use_int4_w4a16,
+        per_channel_quant=per_channel_quant, global_num_experts=global_num_experts, w1_scale=w1_scale,
+        w2_scale=w2_scale, a1_scale=a1_scale, a2_scale=a2_scale, block_shape=block_shape, w1_bias=w1_bias,
+        w2_bias=w2_bias, gemm1_alpha=gemm1_alpha, gemm1_beta=gemm1_beta, gemm1_clamp_limit=gemm1_clamp_limit)
+
+
+def outplace_fused_experts(
+    hidden_states: torch.Tensor,
+    w1: torch.Tensor,
+    w2: torch.Tensor,
+    topk_weights: torch.Tensor,
+    topk_ids: torch.Tensor,
+    activation: str = "silu",
+    apply_router_weight_on_input: bool = False,
+    use_fp8_w8a8: bool = False,
+    use_int8_w8a8: bool = False,
+    use_int8_w8a16: bool = False,
+    use_int4_w4a16: bool = False,
+    per_channel_quant: bool = False,
+    global_num_experts: int = -1,
+    w1_scale: Optional[torch.Tensor] = None,
+    w2_scale: Optional[torch.Tensor] = None,
+    a1_scale: Optional[torch.Tensor] = None,
+    a2_scale: Optional[torch.Tensor] = None,
+    block_shape: Optional[list[int]] = None,
+    w1_bias: Optional[torch.Tensor] = None,
+    w2_bias: Optional[torch.Tensor] = None,
+    *,
+    gemm1_alpha: float | None = None,
+    gemm1_beta: float | None = None,
+    gemm1_clamp_limit: float | None = None,
+) -> torch.Tensor:
+    """Allocates and returns the layer output; ``hidden_states`` is left untouched."""
+    return fused_experts_impl(
+        hidden_states, w1, w2, topk_weights, topk_ids, inplace=False, activation=activation,
+        apply_router_weight_on_input=apply_router_weight_on_input, use_fp8_w8a8=use_fp8_w8a8,
+        use_int8_w8a8=use_int8_w8a8, use_int8_w8a16=use_int8_w8a16, use_int4_w4a16=use_int4_w4a16,
+        per_channel_quant=per_channel_quant, global_num_experts=global_num_experts, w1_scale=w1_scale,
+        w2_scale=w2_scale, a1_scale=a1_scale, a2_scale=a2_scale, block_shape=block_shape, w1_bias=w1_bias,
+        w2_bias=w2_bias, gemm1_alpha=gemm1_alpha, gemm1_beta=gemm1_beta, gemm1_clamp_limit=gemm1_clamp_limit)

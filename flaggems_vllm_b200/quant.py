@@ -1,0 +1,82 @@
+"""per_token_group_quant_fp8 and moe_sum: thin host wrappers.
+
+Signatures follow src/flaggems_vllm/ops/per_token_group_quant_fp8.py:226-233
+and src/flaggems_vllm/ops/moe_sum.py:250-253."""
+
+from __future__ import annotations
+
+import logging
+from typing import Optional, Tuple
+
+import torch
+
+from . import _lib
+
+logger = logging.getLogger(__name__)
+
+SUPPORTED_FP8_DTYPE = torch.float8_e4m3fn
+
+
+def per_token_group_quant_fp8(
+    x: torch.Tensor,
+    group_size: int,
+    eps: float = 1e-10,
+    dtype: Optional[torch.dtype] = None,
+    column_major_scales: bool = False,
+    scale_ue8m0: bool = False,
+) -> Tuple[torch.Tensor, torch.Tensor]:
+    """1 x group_size e4m3 quantisation of the last dimension.
+
+    Returns (x_q, x_s) with x_s of shape x.shape[:-1] + (cols / group_size,),
+    column-major in memory when ``column_major_scales``."""
+    logger.debug("GEMS PER TOKEN GROUP QUANT FP8")
+    fp8_dtype = SUPPORTED_FP8_DTYPE if dtype is None else dtype
+    assert x.shape[-1] % group_size == 0, (
+        f"the last dimension of `x` {x.shape[-1]} must be divisible by `group_size` {group_size}"
+    )
+    assert x.stride(-1) == 1, "`x` groups must be contiguous"
+    _lib.require_cuda(x, "per_token_group_quant_fp8")
+    if fp8_dtype != torch.float8_e4m3fn:
+        raise NotImplementedError("only float8_e4m3fn output is implemented")
+    if scale_ue8m0:
+        raise NotImplementedError("UE8M0 scales are not implemented")
+    if group_size != 128:
+        raise NotImplementedError("only group_size=128 is implemented")
+    if abs(eps - 1e-10) > 1e-16:
+        raise NotImplementedError("only eps=1e-10 is implemented")
+    xc = x if x.is_contiguous() else x.contiguous()
+    cols = xc.shape[-1]
+    rows = xc.numel() // cols if cols else 0
+    x_q = torch.empty(xc.shape, device=x.device, dtype=fp8_dtype)
+    groups = cols // group_size
+    if column_major_scales:
+        x_s = torch.empty((groups,) + tuple(xc.shape[:-1]), device=x.device, dtype=torch.float32)
+        if xc.ndim != 2:
+            raise NotImplementedError("column-major scales need a 2-D input")
+    else:
+        x_s = torch.empty(tuple(xc.shape[:-1]) + (groups,), device=x.device, dtype=torch.float32)
+    rc = _lib.lib().moe_per_token_group_quant_fp8(
+        xc.data_ptr(), _lib.dtype_code(xc.dtype), rows, cols, group_size, x_q.data_ptr(), x_s.data_ptr(),
+        int(column_major_scales), rows, _lib.stream_of(x))
+    _lib.check(rc)
+    if column_major_scales:
+        x_s = x_s.permute(-1, -2)
+    return x_q, x_s
+
+
+def moe_sum(input: torch.Tensor, output: torch.Tensor):
+    """output[m, :] = sum over the top-k axis of input[m, :, :] (fp32 accumulate)."""
+    logger.debug("GEMS MOE SUM")
+    if input.ndim != 3 or output.ndim != 2:
+        raise ValueError("moe_sum expects input [M, topk, H] and output [M, H]")
+    M, topk, H = input.shape
+    if output.shape != (M, H) or output.dtype != input.dtype or output.device != input.device:
+        raise ValueError("moe_sum: output must be [M, H] with the dtype and device of input")
+    _lib.require_cuda(input, "moe_sum")
+    src = input if input.is_contiguous() else input.contiguous()
+    dst = output if output.is_contiguous() else torch.empty_like(output, memory_format=torch.contiguous_format)
+    rc = _lib.lib().moe_sum(src.data_ptr(), dst.data_ptr(), _lib.dtype_code(src.dtype), M, topk, H, None, 0, 0,
+                            None, _lib.stream_of(input))
+    _lib.check(rc)
+    if dst is not output:
+        output.copy_(dst)

@@ -1,0 +1,156 @@
+/*
+ * moe_sm100.h — C ABI of libmoe_sm100.so: the B200 (sm_100a) kernels of the
+ * fused Mixture-of-Experts path (group-limited top-k routing, block alignment
+ * of routed tokens, the two expert grouped GEMMs and the top-k combine).
+ *
+ * Conventions
+ *   - Every pointer is a DEVICE pointer unless the parameter says "host".
+ *   - `stream` is a cudaStream_t passed as void*; all work is enqueued on it and
+ *     nothing synchronises with the host, so every call can be captured in a
+ *     CUDA graph (tensor maps are built on the host before the launch).
+ *   - Return value: 0 on success, a negative MOE_E_* code for a rejected
+ *     argument, a positive cudaError_t value when a launch failed.
+ *     moe_last_error() gives the text of the last failure of the calling thread.
+ *   - `status` is an optional device int32 word.  Kernels never trap: on bad
+ *     data (an expert id outside the table, a wait that ran out) they OR a
+ *     MOE_ST_* bit into it and carry on or return; the host reads it when it
+ *     chooses to.
+ *   - dtype codes: MOE_F32 0, MOE_F16 1, MOE_BF16 2, MOE_FP8E4M3 3, MOE_INT8 4.
+ *
+ * Each entry point names the reference interface it stands in for, as
+ * path:line inside the FlagGems-vllm source tree.
+ */
+#ifndef MOE_SM100_H_
+#define MOE_SM100_H_
+
+#include <stdint.h>
+
+#ifdef __cplusplus
+extern "C" {
+#endif
+
+enum { MOE_F32 = 0, MOE_F16 = 1, MOE_BF16 = 2, MOE_FP8E4M3 = 3, MOE_INT8 = 4 };
+
+enum {
+  MOE_E_BADARG = -1,     /* null pointer, negative extent, unsupported size */
+  MOE_E_DTYPE = -2,      /* dtype code not handled by this entry point */
+  MOE_E_SHAPE = -3,      /* shape not supported by the requested kernel */
+  MOE_E_DRIVER = -4,     /* CUDA driver entry point unavailable */
+  MOE_E_TOOBIG = -5      /* exceeds a fixed capacity (see the entry point) */
+};
+
+enum {
+  MOE_ST_BAD_EXPERT_ID = 1,  /* an expert id outside [0, num_experts) was skipped */
+  MOE_ST_WAIT_TIMEOUT = 2,   /* a bounded barrier wait ran out; results invalid */
+  MOE_ST_BAD_ROW = 4         /* a sorted row index outside its buffer was skipped */
+};
+
+/* GEMM modes (moe_gemm*_ entry points) */
+enum { MOE_MODE_HALF = 0, MOE_MODE_FP8_BLOCK = 1, MOE_MODE_W8A16 = 2 };
+
+int moe_abi_version(void);
+const char* moe_last_error(void);
+
+/*
+ * Group-limited top-k routing, one warp per token.
+ * Stands in for grouped_topk (src/flaggems_vllm/ops/grouped_topk.py:1674-1976)
+ * and its kernels (:333-794, :887-1081).  scores[M,E] with element strides
+ * (stride0, stride1); bias[E] contiguous; is_padding[M] bytes or NULL.
+ * Outputs topk_weights[M,topk] fp32 and topk_ids[M,topk] int32, row-major.
+ * Limits: E <= 1024, n_group <= 32, topk <= 32.
+ */
+int moe_grouped_topk(const void* scores, int scores_dtype, int64_t stride0, int64_t stride1,
+                     const void* bias, int bias_dtype, const uint8_t* is_padding,
+                     int64_t M, int E, int n_group, int topk_group, int topk,
+                     int renormalize, float routed_scaling_factor, int scoring_func,
+                     float* topk_weights, int32_t* topk_ids, void* stream);
+
+/*
+ * Stable counting sort of the flat expert-id array with per-expert padding to
+ * block_size.  Stands in for moe_align_block_size_triton
+ * (src/flaggems_vllm/ops/moe_align_block_size.py:607-718; stages :414-527).
+ * topk_ids: numel ids, int32 (ids_int64 = 0) or int64 (1).
+ * sorted_ids[sorted_cap] is fully written (pad value = numel),
+ * expert_ids[expert_cap] is fully written (unused = -1), num_post_pad[1].
+ * Order inside an expert is ascending flat index (deterministic).
+ * Limits: num_experts <= 4096, numel < 2^31.
+ */
+int moe_align_block_size(const void* topk_ids, int ids_int64, int64_t numel, int num_experts,
+                         int block_size, int32_t* sorted_ids, int64_t sorted_cap,
+                         int32_t* expert_ids, int64_t expert_cap, int32_t* num_post_pad,
+                         int32_t* status, void* stream);
+
+/*
+ * 1 x group e4m3 quantisation of rows: scale = max(amax,1e-10) * (1/448),
+ * q = clamp(x / scale).  Stands in for per_token_group_quant_fp8
+ * (src/flaggems_vllm/ops/per_token_group_quant_fp8.py:226-335, kernel :115-162).
+ * x[rows, cols] contiguous (F32/F16/BF16); q[rows, cols]; scales row-major
+ * [rows, cols/group] (scales_transposed = 0) or [cols/group, scale_ld]
+ * (scales_transposed = 1).  group must be 128.
+ */
+int moe_per_token_group_quant_fp8(const void* x, int x_dtype, int64_t rows, int64_t cols, int group,
+                                  void* q, float* scales, int scales_transposed, int64_t scale_ld,
+                                  void* stream);
+
+/*
+ * Gather activation rows into expert-sorted order, optionally quantising to
+ * e4m3 on the way (MOE_MODE_FP8_BLOCK).  Row p of the output is the row
+ * sorted_ids[p] / topk of x, for p < *num_post_pad and sorted_ids[p] < numel.
+ * Fuses moe_kernel_quantize_input (src/flaggems_vllm/ops/fused_moe.py:2533-2540)
+ * with the row gather the reference GEMM does on load (:1559).
+ * out[out_rows, cols] (same dtype as x, or e4m3); scales_t[cols/128, out_rows].
+ */
+int moe_gather_rows(const void* x, int x_dtype, int64_t M, int64_t cols, int topk,
+                    const int32_t* sorted_ids, const int32_t* num_post_pad, int64_t out_rows,
+                    int mode, void* out, float* scales_t, void* stream);
+
+/*
+ * Expert grouped GEMM 1: act = SiLU(A Wg^T) * (A Wu^T) on expert-sorted rows.
+ * Stands in for fused_moe_kernel with FUSE_SILU
+ * (src/flaggems_vllm/ops/fused_moe.py:1634-1795, launch :2078-2220).
+ *   a_sorted [rows_cap, H]   activations in sorted order (act dtype or e4m3)
+ *   a_scales_t [H/128, rows_cap] (FP8 mode)
+ *   w1 [E, 2I, H] contiguous (act dtype, e4m3 or int8), gate rows first
+ *   w1_scale: FP8 [E, 2I/128, H/128]; W8A16 [E, 2I]; else NULL
+ *   expert_ids [rows_cap / block_m], num_post_pad[1] from the align step
+ *   route_weight/sorted_ids: when mul_weight != 0 gate and up are multiplied by
+ *     route_weight[sorted_ids[p]] before the activation
+ *   out [rows_cap, I]: act dtype, or e4m3 with out_scales_t [I/128, rows_cap]
+ *     when mode is FP8 (the activation is rounded to act dtype, then quantised)
+ * use_tensor_cores: 1 = tcgen05 kernel (block_m must be 128, H and I multiples
+ *   of 128 for FP8 / 64 for half), 0 = generic kernel (block_m % 16 == 0).
+ */
+int moe_gemm1(int mode, int act_dtype, const void* a_sorted, const float* a_scales_t,
+              const void* w1, const float* w1_scale, const int32_t* expert_ids,
+              const int32_t* sorted_ids, const int32_t* num_post_pad, const float* route_weight,
+              int mul_weight, int64_t numel, int64_t rows_cap, int block_m, int E, int H, int I,
+              void* out, float* out_scales_t, int use_tensor_cores, int32_t* status, void* stream);
+
+/*
+ * Expert grouped GEMM 2: y[sorted_ids[p], :] = (act[p] W2[e]^T) * route_weight.
+ * Stands in for fused_moe_kernel as called for the down projection
+ * (src/flaggems_vllm/ops/fused_moe.py:1797-1985, call :2703-2728).
+ *   act_sorted [rows_cap, I] (act dtype or e4m3 with act_scales_t [I/128, rows_cap])
+ *   w2 [E, H, I] contiguous; w2_scale: FP8 [E, H/128, I/128]; W8A16 [E, H]
+ *   y [numel, H] in act dtype, row = flat route index (token * topk + slot)
+ */
+int moe_gemm2(int mode, int act_dtype, const void* act_sorted, const float* act_scales_t,
+              const void* w2, const float* w2_scale, const int32_t* expert_ids,
+              const int32_t* sorted_ids, const int32_t* num_post_pad, const float* route_weight,
+              int mul_weight, int64_t numel, int64_t rows_cap, int block_m, int E, int H, int I,
+              void* y, int use_tensor_cores, int32_t* status, void* stream);
+
+/*
+ * out[m, :] = sum_j in[m, j, :] in fp32, fixed order j = 0..topk-1, stored in
+ * the io dtype.  Stands in for moe_sum (src/flaggems_vllm/ops/moe_sum.py:250-310).
+ * When topk_ids is given, slot j is skipped if its id is outside
+ * [0, num_experts) or expert_map[id] < 0 (expert-parallel ranks).
+ */
+int moe_sum(const void* in, void* out, int dtype, int64_t M, int topk, int64_t H,
+            const void* topk_ids, int ids_int64, int num_experts, const int32_t* expert_map,
+            void* stream);
+
+#ifdef __cplusplus
+}
+#endif
+#endif /* MOE_SM100_H_ */

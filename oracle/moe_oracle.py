@@ -46,6 +46,15 @@ FP8_MAX = 448.0
 # ----------------------------------------------------------------------------
 # Routing
 # ----------------------------------------------------------------------------
+def _sigmoid_f32(x: torch.Tensor) -> torch.Tensor:
+    """fp32 sigmoid defined as the double-precision value rounded once to
+    fp32 (i.e. correctly rounded).  torch's fp32 sigmoid and the reference
+    kernel's ``1/(1+exp2(-x*log2e))`` (src/flaggems_vllm/ops/grouped_topk.py:304-307)
+    are both within an ulp or two of this value; fixing the definition makes
+    the ranking reproducible bit for bit on any device."""
+    return torch.sigmoid(x.double()).float()
+
+
 def grouped_topk_oracle(
     scores: torch.Tensor,
     n_group: int,
@@ -74,7 +83,7 @@ def grouped_topk_oracle(
     rows, experts = s.shape
     per_group = experts // n_group
     u = s.float()
-    unbiased = torch.sigmoid(u) if scoring_func == 1 else u
+    unbiased = _sigmoid_f32(u) if scoring_func == 1 else u
     ranked = unbiased + b
     if per_group >= 2:
         group_score = ranked.view(rows, n_group, per_group).topk(2, dim=-1)[0].sum(-1)
@@ -113,7 +122,7 @@ def routing_margin_ulps(
     b = bias.detach().to("cpu").flatten().float()
     rows, experts = s.shape
     per_group = experts // n_group
-    unbiased = torch.sigmoid(s) if scoring_func == 1 else s
+    unbiased = _sigmoid_f32(s) if scoring_func == 1 else s
     ranked = unbiased + b
     if per_group >= 2:
         top2 = ranked.view(rows, n_group, per_group).topk(2, dim=-1)[0]

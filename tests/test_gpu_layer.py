@@ -1,0 +1,336 @@
+"""GPU parity of fused_experts_impl against the CPU oracle.
+
+Tolerance (stated by the task's parity definition): relative L2 <= 1e-2 and
+cosine >= 0.9999 against the oracle's fp32-accumulate result on the same
+seeded inputs; the reference's own assert_close tolerances are checked too."""
+
+import os
+
+import pytest
+import torch
+
+import flaggems_vllm_b200 as fg
+from conftest import golden_files, load_golden
+from flaggems_vllm_b200 import _lib, fused_moe
+from flaggems_vllm_b200 import testing as T
+from oracle import moe_oracle as O
+
+pytestmark = pytest.mark.gpu
+DEV = "cuda"
+REL_L2, COS = 1e-2, 0.9999
+DT = {"torch.float32": torch.float32, "torch.bfloat16": torch.bfloat16, "torch.float16": torch.float16}
+
+
+def _assert_parity(out, ref, what=""):
+    rl2, cs = O.rel_l2(out.float(), ref), O.cosine(out.float(), ref)
+    assert fg.read_status() == 0, f"{what}: kernel status word set"
+    assert rl2 <= REL_L2 and cs >= COS, f"{what}: rel_l2={rl2:.3e} cos={cs:.6f}"
+    return rl2, cs
+
+
+def _route(M, E, k, dtype, seed=0):
+    logits, _ = T.make_router_inputs(M, E, DEV, seed=seed)
+    w, ids = fg.grouped_topk(torch.softmax(logits, -1), 1, 1, k, True, 1.0, torch.zeros(E, device=DEV), 0)
+    return w.to(dtype), ids
+
+
+def _both_kernels(run):
+    """Runs ``run()`` with the generic kernels and with the tensor-core kernels."""
+    outs = {}
+    which = os.environ.get("MOE_TEST_KERNELS", "both")  # generic | tensor | both
+    for name, val in (("generic", "1"), ("tensor", "0")):
+        if which not in ("both", name):
+            continue
+        os.environ["FLAGGEMS_B200_GENERIC_GEMM"] = val
+        try:
+            outs[name] = run()
+        finally:
+            os.environ.pop("FLAGGEMS_B200_GENERIC_GEMM", None)
+    return outs
+
+
+# ---------------------------------------------------------------- golden vectors
+@pytest.mark.parametrize("name", golden_files("layer_half_"))
+def test_golden_half(name):
+    g = load_golden(name)
+    dt = DT[g["dtype"]]
+    x, w1, w2 = (g[n].to(dt).to(DEV) for n in ("x", "w1", "w2"))
+    tw, ti = g["topk_weights"].to(dt).to(DEV), g["topk_ids"].to(DEV)
+    for name_, out in _both_kernels(lambda: fg.ops_experts_impl(x, w1, w2, tw, ti)).items():
+        _assert_parity(out, O.fused_moe_half_oracle(x, w1, w2, tw, ti), name_)
+        ref = g["out"]
+        torch.testing.assert_close(out.float().cpu(), ref, rtol=1e-1, atol=max(1e-2, ref.abs().max().item() * 1e-5))
+
+
+@pytest.mark.parametrize("name", golden_files("layer_fp8_"))
+def test_golden_fp8(name):
+    g = load_golden(name)
+    x, w1, w2, s1, s2 = (g[n].to(DEV) for n in ("x", "w1", "w2", "w1_scale", "w2_scale"))
+    tw, ti = g["topk_weights"].to(x.dtype).to(DEV), g["topk_ids"].to(DEV)
+    run = lambda: fg.ops_experts_impl(x, w1, w2, tw, ti, use_fp8_w8a8=True, w1_scale=s1, w2_scale=s2,
+                                      block_shape=[128, 128])
+    for name_, out in _both_kernels(run).items():
+        _assert_parity(out, O.fused_moe_fp8_block_oracle(x, w1, w2, s1, s2, tw, ti), name_)
+        ref = g["out"]
+        torch.testing.assert_close(out.float().cpu(), ref, rtol=2e-1, atol=max(5e-2, ref.abs().max().item() * 5e-2))
+
+
+@pytest.mark.parametrize("name", golden_files("layer_w8a16_"))
+def test_golden_w8a16(name):
+    g = load_golden(name)
+    x, w1, w2, s1, s2 = (g[n].to(DEV) for n in ("x", "w1", "w2", "w1_scale", "w2_scale"))
+    tw, ti = g["topk_weights"].to(x.dtype).to(DEV), g["topk_ids"].to(DEV)
+    out = fg.ops_experts_impl(x, w1, w2, tw, ti, use_int8_w8a16=True, per_channel_quant=True, w1_scale=s1,
+                              w2_scale=s2)
+    _assert_parity(out, O.fused_moe_w8a16_oracle(x, w1, w2, s1, s2, tw, ti))
+    ref = g["out"]
+    torch.testing.assert_close(out.float().cpu(), ref, rtol=2e-1, atol=max(5e-2, ref.abs().max().item() * 2e-2))
+
+
+# ---------------------------------------------------------------- reference test shapes
+HALF_SHAPES = [(1, 8, 128, 256, 2), (4, 8, 128, 256, 2), (8, 4, 64, 128, 2), (16, 8, 256, 512, 2),
+               (32, 8, 128, 256, 4), (64, 8, 256, 512, 2), (128, 16, 128, 256, 4), (4, 16, 512, 1024, 2),
+               (10, 256, 2048, 128, 8), (256, 256, 2048, 128, 8)]
+
+
+@pytest.mark.parametrize("cfg", HALF_SHAPES)
+@pytest.mark.parametrize("dtype", [torch.bfloat16, torch.float16])
+def test_half_shapes(cfg, dtype):
+    M, E, H, I, k = cfg
+    x = T.make_activations(M, H, DEV, dtype=dtype)
+    w1 = T.make_half_weights(E, 2 * I, H, DEV, seed=1, dtype=dtype, std=H**-0.5)
+    w2 = T.make_half_weights(E, H, I, DEV, seed=2, dtype=dtype, std=I**-0.5)
+    tw, ti = _route(M, E, k, dtype)
+    ref = O.fused_moe_half_oracle(x, w1, w2, tw, ti)
+    for name, out in _both_kernels(lambda: fg.fused_experts_impl(x, w1, w2, tw, ti)).items():
+        _assert_parity(out, ref, name)
+
+
+QUANT_SHAPES = [(1, 8, 128, 256, 2), (4, 8, 128, 256, 2), (16, 8, 256, 512, 2), (32, 8, 128, 256, 4),
+                (64, 8, 256, 512, 2), (128, 16, 128, 256, 4), (300, 16, 512, 384, 4)]
+
+
+@pytest.mark.parametrize("cfg", QUANT_SHAPES)
+@pytest.mark.parametrize("dtype", [torch.bfloat16, torch.float16])
+def test_fp8_block_shapes(cfg, dtype):
+    M, E, H, I, k = cfg
+    x = T.make_activations(M, H, DEV, dtype=dtype)
+    w1, s1 = T.make_fp8_block_weights(E, 2 * I, H, DEV, seed=1, std=H**-0.5)
+    w2, s2 = T.make_fp8_block_weights(E, H, I, DEV, seed=2, std=I**-0.5)
+    tw, ti = _route(M, E, k, dtype)
+    ref = O.fused_moe_fp8_block_oracle(x, w1, w2, s1, s2, tw, ti)
+    run = lambda: fg.fused_experts_impl(x, w1, w2, tw, ti, use_fp8_w8a8=True, w1_scale=s1, w2_scale=s2,
+                                        block_shape=[128, 128])
+    for name, out in _both_kernels(run).items():
+        _assert_parity(out, ref, name)
+
+
+@pytest.mark.parametrize("cfg", QUANT_SHAPES[:6] + [(64, 128, 2048, 768, 8)])
+def test_w8a16_shapes(cfg):
+    M, E, H, I, k = cfg
+    x = T.make_activations(M, H, DEV)
+    w1, s1 = T.make_int8_channel_weights(E, 2 * I, H, DEV, seed=1, std=H**-0.5)
+    w2, s2 = T.make_int8_channel_weights(E, H, I, DEV, seed=2, std=I**-0.5)
+    tw, ti = _route(M, E, k, torch.bfloat16)
+    out = fg.fused_experts_impl(x, w1, w2, tw, ti, use_int8_w8a16=True, per_channel_quant=True, w1_scale=s1,
+                                w2_scale=s2)
+    _assert_parity(out, O.fused_moe_w8a16_oracle(x, w1, w2, s1, s2, tw, ti))
+
+
+# ---------------------------------------------------------------- benchmark configurations
+def test_config1_small_bf16_layer():
+    M, E, H, I, k = 64, 8, 1024, 2048, 2
+    x = T.make_activations(M, H, DEV)
+    w1 = T.make_half_weights(E, 2 * I, H, DEV, seed=1)
+    w2 = T.make_half_weights(E, H, I, DEV, seed=2)
+    tw, ti = _route(M, E, k, torch.bfloat16)
+    s, e, n = fg.moe_align_block_size(ti, 16, E)
+    os_, oe, on = O.moe_align_block_size_oracle(ti, 16, E)
+    assert torch.equal(s.cpu(), torch.from_numpy(os_)) and torch.equal(e.cpu(), torch.from_numpy(oe))
+    out = fg.fused_experts_impl(x, w1, w2, tw, ti)
+    _assert_parity(out, O.fused_moe_half_oracle(x, w1, w2, tw, ti))
+
+
+def test_config3_deepseek_shape_reduced_expert_count():
+    # full H and I, 32 experts so the CPU oracle finishes in seconds
+    M, E, H, I, k = 256, 32, 7168, 2048, 8
+    x = T.make_activations(M, H, DEV)
+    w1, s1 = T.make_fp8_block_weights(E, 2 * I, H, DEV, seed=1)
+    w2, s2 = T.make_fp8_block_weights(E, H, I, DEV, seed=2)
+    logits, bias = T.make_router_inputs(M, E, DEV)
+    tw, ti = fg.grouped_topk(logits, 8, 4, k, True, 2.5, bias, 1)
+    out = fg.fused_experts_impl(x, w1, w2, tw, ti, use_fp8_w8a8=True, w1_scale=s1, w2_scale=s2,
+                                block_shape=[128, 128])
+    _assert_parity(out, O.fused_moe_fp8_block_oracle(x, w1, w2, s1, s2, tw, ti))
+
+
+def _sampled_oracle_fp8(x, w1, s1, w2, s2, tw, ti, rows):
+    """Oracle on a sample of tokens: only the experts those tokens use are copied to the host."""
+    xs, tws, tis = x[rows].cpu(), tw[rows].cpu(), ti[rows].cpu()
+    used = torch.unique(tis).tolist()
+    remap = {e: i for i, e in enumerate(used)}
+    idx = torch.tensor(used, device=x.device)
+    lw1, ls1, lw2, ls2 = w1[idx].cpu(), s1[idx].cpu(), w2[idx].cpu(), s2[idx].cpu()
+    lti = torch.tensor([[remap[int(e)] for e in r] for r in tis], dtype=torch.int32)
+    return O.fused_moe_fp8_block_oracle(xs, lw1, lw2, ls1, ls2, tws, lti)
+
+
+@pytest.mark.parametrize("M", [1, 32, 1024, 8192])
+def test_config3_full_size_sampled_parity_and_properties(M):
+    E, H, I, k = 256, 7168, 2048, 8
+    x = T.make_activations(M, H, DEV)
+    w1, s1 = T.make_fp8_block_weights(E, 2 * I, H, DEV, seed=1)
+    w2, s2 = T.make_fp8_block_weights(E, H, I, DEV, seed=2)
+    logits, bias = T.make_router_inputs(M, E, DEV)
+    tw, ti = fg.grouped_topk(logits, 8, 4, k, True, 2.5, bias, 1)
+    kw = dict(use_fp8_w8a8=True, w1_scale=s1, w2_scale=s2, block_shape=[128, 128])
+    out = fg.fused_experts_impl(x, w1, w2, tw, ti, **kw)
+    rows = torch.randperm(M, generator=torch.Generator().manual_seed(0))[: min(M, 8)].to(DEV)
+    _assert_parity(out[rows], _sampled_oracle_fp8(x, w1, s1, w2, s2, tw, ti, rows), f"M={M}")
+    # run-to-run determinism (bitwise)
+    assert torch.equal(out, fg.fused_experts_impl(x, w1, w2, tw, ti, **kw))
+    # token permutation commutes with the layer (bitwise: rows are independent)
+    perm = torch.randperm(M, device=DEV)
+    assert torch.equal(fg.fused_experts_impl(x[perm].contiguous(), w1, w2, tw[perm].contiguous(),
+                                             ti[perm].contiguous(), **kw), out[perm])
+    # linear in the route weights
+    out2 = fg.fused_experts_impl(x, w1, w2, tw * 2.0, ti, **kw)
+    assert O.rel_l2(out2.float(), out.float() * 2.0) < 5e-3
+
+
+def test_config2_mixtral_shape_sampled():
+    M, E, H, I, k = 1024, 8, 4096, 14336, 2
+    x = T.make_activations(M, H, DEV)
+    w1 = T.make_half_weights(E, 2 * I, H, DEV, seed=1, chunk=1)
+    w2 = T.make_half_weights(E, H, I, DEV, seed=2, chunk=1)
+    tw, ti = _route(M, E, k, torch.bfloat16)
+    out = fg.fused_experts_impl(x, w1, w2, tw, ti)
+    rows = torch.arange(0, M, 64, device=DEV)
+    ref = O.fused_moe_half_oracle(x[rows], w1, w2, tw[rows], ti[rows])
+    _assert_parity(out[rows], ref)
+
+
+def test_config4_qwen3_shape():
+    M, E, H, I, k = 64, 128, 2048, 768, 8
+    x = T.make_activations(M, H, DEV)
+    w1, s1 = T.make_int8_channel_weights(E, 2 * I, H, DEV, seed=1)
+    w2, s2 = T.make_int8_channel_weights(E, H, I, DEV, seed=2)
+    tw, ti = _route(M, E, k, torch.bfloat16)
+    out = fg.fused_experts_impl(x, w1, w2, tw, ti, use_int8_w8a16=True, per_channel_quant=True, w1_scale=s1,
+                                w2_scale=s2)
+    _assert_parity(out, O.fused_moe_w8a16_oracle(x, w1, w2, s1, s2, tw, ti))
+
+
+# ---------------------------------------------------------------- API behaviour
+def _small_half(dtype=torch.bfloat16, M=16, E=8, H=256, I=512, k=2):
+    x = T.make_activations(M, H, DEV, dtype=dtype)
+    w1 = T.make_half_weights(E, 2 * I, H, DEV, seed=1, dtype=dtype, std=H**-0.5)
+    w2 = T.make_half_weights(E, H, I, DEV, seed=2, dtype=dtype, std=I**-0.5)
+    tw, ti = _route(M, E, k, dtype)
+    return x, w1, w2, tw, ti
+
+
+@pytest.mark.parametrize("dtype", [torch.bfloat16, torch.float16])
+def test_inplace_outplace_bitwise(dtype):
+    x, w1, w2, tw, ti = _small_half(dtype)
+    ref = fg.fused_experts_impl(x.clone(), w1, w2, tw, ti, inplace=False)
+    buf = x.clone()
+    res = fg.fused_experts_impl(buf, w1, w2, tw, ti, inplace=True)
+    assert res.data_ptr() == buf.data_ptr()
+    assert torch.equal(res, ref)
+    buf2 = x.clone()
+    assert fg.inplace_fused_experts(buf2, w1, w2, tw, ti) is None
+    assert torch.equal(buf2, ref)
+    keep = x.clone()
+    out = fg.outplace_fused_experts(x, w1, w2, tw, ti)
+    assert torch.equal(x, keep) and torch.equal(out, ref) and out.data_ptr() != x.data_ptr()
+
+
+def test_router_weight_on_input():
+    x, w1, w2, tw, ti = _small_half()
+    out = fg.fused_experts_impl(x, w1, w2, tw, ti, apply_router_weight_on_input=True)
+    ref = O.fused_moe_half_oracle(x, w1, w2, tw, ti, apply_router_weight_on_input=True)
+    _assert_parity(out, ref)
+
+
+def test_int64_ids_and_fp32_activations():
+    x, w1, w2, tw, ti = _small_half()
+    a = fg.fused_experts_impl(x, w1, w2, tw, ti)
+    b = fg.fused_experts_impl(x, w1, w2, tw, ti.long())
+    assert torch.equal(a, b)
+    xf, w1f, w2f = x.float(), w1.float(), w2.float()
+    c = fg.fused_experts_impl(xf, w1f, w2f, tw.float(), ti)
+    _assert_parity(c, O.fused_moe_half_oracle(xf, w1f, w2f, tw.float(), ti))
+
+
+def test_expert_parallel_halves_sum_to_the_full_layer():
+    M, E, H, I, k = 64, 16, 256, 256, 4
+    x = T.make_activations(M, H, DEV)
+    w1, s1 = T.make_fp8_block_weights(E, 2 * I, H, DEV, seed=1, std=H**-0.5)
+    w2, s2 = T.make_fp8_block_weights(E, H, I, DEV, seed=2, std=I**-0.5)
+    tw, ti = _route(M, E, k, torch.bfloat16)
+    kw = dict(use_fp8_w8a8=True, block_shape=[128, 128])
+    full = fg.fused_experts_impl(x, w1, w2, tw, ti, w1_scale=s1, w2_scale=s2, **kw)
+    total = torch.zeros_like(full, dtype=torch.float32)
+    for r in range(2):
+        lo, hi = r * 8, (r + 1) * 8
+        emap = torch.full((E,), -1, dtype=torch.int32, device=DEV)
+        emap[lo:hi] = torch.arange(8, dtype=torch.int32, device=DEV)
+        part = fg.fused_experts_impl(x, w1[lo:hi].contiguous(), w2[lo:hi].contiguous(), tw, ti,
+                                     global_num_experts=E, expert_map=emap, w1_scale=s1[lo:hi].contiguous(),
+                                     w2_scale=s2[lo:hi].contiguous(), **kw)
+        total += part.float()
+    assert O.rel_l2(total, full.float()) < 5e-3
+    assert fg.read_status() == 0
+
+
+def test_more_tokens_than_one_chunk():
+    M, E, H, I, k = 32768 + 100, 8, 128, 128, 2
+    x = T.make_activations(M, H, DEV)
+    w1 = T.make_half_weights(E, 2 * I, H, DEV, seed=1, std=H**-0.5)
+    w2 = T.make_half_weights(E, H, I, DEV, seed=2, std=I**-0.5)
+    tw, ti = _route(M, E, k, torch.bfloat16)
+    out = fg.fused_experts_impl(x, w1, w2, tw, ti)
+    rows = torch.cat([torch.arange(0, 64), torch.arange(32768 - 8, 32768 + 100)]).to(DEV)
+    _assert_parity(out[rows], O.fused_moe_half_oracle(x[rows], w1, w2, tw[rows], ti[rows]))
+
+
+def test_intermediates_follow_the_documented_layout():
+    M, E, H, I, k = 40, 8, 256, 256, 2
+    x = T.make_activations(M, H, DEV)
+    w1, s1 = T.make_fp8_block_weights(E, 2 * I, H, DEV, seed=1, std=H**-0.5)
+    w2, s2 = T.make_fp8_block_weights(E, H, I, DEV, seed=2, std=I**-0.5)
+    tw, ti = _route(M, E, k, torch.bfloat16)
+    keep = {}
+    out = torch.empty_like(x)
+    fused_moe.run_chunk(x, w1, w2, tw, ti, out, mode=_lib.MODE_FP8_BLOCK, w1_scale=s1, w2_scale=s2,
+                        global_num_experts=E, expert_map=None, apply_router_weight_on_input=False, keep=keep)
+    torch.cuda.synchronize()
+    assert keep["used_tensor_cores"] and keep["block_m"] == 128
+    n = int(keep["num_post_pad"].item())
+    sid = keep["sorted_ids"][:n].cpu()
+    valid = sid < M * k
+    xq, xs = O.per_token_group_quant_fp8_oracle(x, 128)
+    tok = (sid[valid] // k).long()
+    got_q = keep["a_sorted"][:n].cpu()[valid].view(torch.uint8)
+    assert torch.equal(got_q, xq[tok].view(torch.uint8))
+    got_s = keep["a_scales_t"][:, :n].cpu().t()[valid]
+    assert torch.equal(got_s, xs[tok])
+
+
+def test_quant_and_sum_wrappers():
+    x = torch.randn(33, 512, device=DEV, dtype=torch.bfloat16) * 3
+    x[0, :128] = 0
+    q, s = fg.per_token_group_quant_fp8(x, 128)
+    oq, os_ = O.per_token_group_quant_fp8_oracle(x, 128)
+    assert torch.equal(q.cpu().view(torch.uint8), oq.view(torch.uint8)) and torch.equal(s.cpu(), os_)
+    q2, s2 = fg.per_token_group_quant_fp8(x, 128, column_major_scales=True)
+    assert s2.shape == s.shape and s2.stride(0) == 1 and torch.equal(s2.contiguous(), s) and torch.equal(
+        q2.view(torch.uint8), q.view(torch.uint8))
+    for dt in (torch.float32, torch.float16, torch.bfloat16):
+        for (m, k, h) in [(1, 2, 128), (33, 6, 511), (222, 2, 1024)]:
+            inp = torch.randn(m, k, h, device=DEV, dtype=dt)
+            o = torch.empty(m, h, device=DEV, dtype=dt)
+            fg.moe_sum(inp, o)
+            torch.testing.assert_close(o.float().cpu(), O.moe_sum_oracle(inp).to(dt).float(),
+                                       rtol=1.6e-2 if dt != torch.float32 else 1.3e-6, atol=1e-4 * k)

@@ -1,0 +1,137 @@
+"""GPU parity of grouped_topk against the CPU oracle and the reference-made
+golden vectors: ids bit-exact (ties toward the lower expert id), weights within
+2e-6 (the tolerance of the reference's own eager-oracle tests,
+tests/test_grouped_topk.py:737)."""
+
+import pytest
+import torch
+
+import flaggems_vllm_b200 as fg
+from conftest import golden_files, load_golden
+from flaggems_vllm_b200 import testing as T
+from oracle import moe_oracle as O
+
+pytestmark = pytest.mark.gpu
+DEV = "cuda"
+DT = {"torch.float32": torch.float32, "torch.bfloat16": torch.bfloat16, "torch.float16": torch.float16}
+
+
+def _check(scores, G, keep, k, ren, scale, bias, sf, pad=None):
+    w, ids = fg.grouped_topk(scores, G, keep, k, ren, scale, bias, sf, pad)
+    ow, oi = O.grouped_topk_oracle(scores, G, keep, k, ren, scale, bias, sf, pad)
+    assert w.dtype == torch.float32 and ids.dtype == torch.int32
+    assert w.shape == ids.shape == (scores.shape[0], k)
+    assert torch.equal(ids.cpu(), oi)
+    torch.testing.assert_close(w.cpu(), ow, rtol=2e-6, atol=2e-6)
+    return w, ids
+
+
+@pytest.mark.parametrize("name", golden_files("routing_"))
+def test_golden_vectors(name):
+    g = load_golden(name)
+    E, G, keep, k, ren, sf = [int(v) for v in g["params"]]
+    scores = g["scores"].to(DT[g["score_dtype"]]).to(DEV)
+    w, ids = fg.grouped_topk(scores, G, keep, k, bool(ren), float(g["scale"][0]), g["bias"].to(DEV), sf)
+    assert torch.equal(ids.cpu(), g["ids"])
+    torch.testing.assert_close(w.cpu(), g["weights"], rtol=2e-6, atol=2e-6)
+
+
+@pytest.mark.parametrize("M", [1, 32, 128, 1024, 8192])
+@pytest.mark.parametrize("dtype", [torch.float32, torch.bfloat16])
+def test_deepseek_v3_routing(M, dtype):
+    logits, bias = T.make_router_inputs(M, 256, DEV, seed=M)
+    _check(logits.to(dtype), 8, 4, 8, True, 2.5, bias, 1)
+
+
+@pytest.mark.parametrize("E,k,M", [(8, 2, 64), (8, 2, 4096), (128, 8, 512), (128, 8, 4096)])
+def test_softmax_routing_single_group(E, k, M):
+    logits, _ = T.make_router_inputs(M, E, DEV, seed=E + M)
+    scores = torch.softmax(logits, dim=-1)
+    _check(scores, 1, 1, k, True, 1.0, torch.zeros(E, device=DEV), 0)
+
+
+@pytest.mark.parametrize("E,G,keep,k", [(16, 4, 2, 2), (64, 4, 2, 6), (384, 3, 2, 4), (512, 1, 1, 16),
+                                        (1024, 32, 4, 32), (24, 2, 1, 3)])
+@pytest.mark.parametrize("sf", [0, 1])
+def test_other_shapes(E, G, keep, k, sf):
+    logits, bias = T.make_router_inputs(37, E, DEV, seed=E)
+    for ren in (True, False):
+        _check(logits, G, keep, k, ren, 1.5, bias, sf)
+        _check(logits.half(), G, keep, k, ren, 1.5, bias.half(), sf)
+
+
+@pytest.mark.parametrize("groups,keep", [(1, 1), (8, 4)])
+@pytest.mark.parametrize("dtype", [torch.float32, torch.float16, torch.bfloat16])
+@pytest.mark.parametrize("separate", [False, True])
+def test_known_answer_ties_and_tiny_bias(groups, keep, dtype, separate):
+    scores = torch.ones((3, 256), device=DEV, dtype=dtype)
+    bias = torch.arange(256, device=DEV, dtype=torch.float32) * (2**-20 if separate else 0.0)
+    w, ids = fg.grouped_topk(scores, groups, keep, 8, True, 2.5, bias, 0)
+    exp = torch.arange(255, 247, -1) if separate else torch.arange(8)
+    assert torch.equal(ids.cpu(), exp.expand(3, -1).int())
+    torch.testing.assert_close(w, torch.full_like(w, 2.5 / 8))
+
+
+@pytest.mark.parametrize("experts,topk", [(8, 3), (17, 5), (63, 7), (129, 8)])
+@pytest.mark.parametrize("dtype", [torch.float32, torch.float16, torch.bfloat16])
+def test_known_answer_strided_ties(experts, topk, dtype):
+    backing = torch.ones((5, experts + 11), device=DEV, dtype=dtype)
+    scores = backing[:, :experts]
+    w, ids = fg.grouped_topk(scores, 1, 1, topk, True, 1.0, torch.zeros(experts, device=DEV), 0)
+    assert torch.equal(ids.cpu(), torch.arange(topk, dtype=torch.int32).expand(5, -1))
+    torch.testing.assert_close(w, torch.full_like(w, 1.0 / topk))
+
+
+@pytest.mark.parametrize("groups,keep", [(1, 1), (8, 4)])
+def test_known_answer_inf_and_signed_zero(groups, keep):
+    scores = torch.ones((2, 256), device=DEV)
+    scores[:, [1, 253]] = float("inf")
+    bias = torch.zeros(256, device=DEV)
+    w, ids = fg.grouped_topk(scores, groups, keep, 8, False, 1.0, bias, 0)
+    assert torch.equal(ids.cpu(), torch.tensor([1, 253, 0, 2, 3, 4, 5, 6]).int().expand(2, -1))
+    assert torch.isposinf(w[:, :2]).all()
+    torch.testing.assert_close(w[:, 2:], torch.ones_like(w[:, 2:]))
+    scores.zero_()
+    scores[:, ::2] = -0.0
+    w, ids = fg.grouped_topk(scores, groups, keep, 8, False, 1.0, bias, 0)
+    assert torch.equal(ids.cpu(), torch.arange(8).int().expand(2, -1))
+    assert torch.equal(torch.signbit(w), torch.signbit(scores[:, :8]))
+
+
+@pytest.mark.parametrize("mode", ["mixed", "all", "none"])
+def test_padding_rows(mode):
+    rows, E = 9, 256
+    score = torch.linspace(-2.0, 2.0, E, device=DEV)
+    scores = torch.stack([score.roll(i * 17) for i in range(rows)])
+    bias = torch.linspace(-0.30, 0.30, E, device=DEV)
+    if mode == "mixed":
+        mask = torch.arange(rows, device=DEV) % 3 == 1
+    else:
+        mask = torch.full((rows,), mode == "all", device=DEV, dtype=torch.bool)
+    w, ids = _check(scores, 8, 4, 8, True, 3.998, bias, 1, mask)
+    assert torch.all(w[mask] == 0) and torch.all(ids[mask] == -1)
+
+
+def test_empty_and_2d_bias():
+    w, ids = fg.grouped_topk(torch.zeros((0, 256), device=DEV), 8, 4, 8, True, 2.5, torch.zeros(256, device=DEV), 1)
+    assert w.shape == (0, 8) and ids.shape == (0, 8)
+    logits, bias = T.make_router_inputs(5, 64, DEV)
+    _check(logits, 4, 2, 4, True, 1.0, bias.view(1, 64), 1)
+
+
+def test_cuda_graph_replay_with_new_scores():
+    logits, bias = T.make_router_inputs(64, 256, DEV, seed=5)
+    static = logits.clone()
+    fg.grouped_topk(static, 8, 4, 8, True, 2.5, bias, 1)  # warm-up outside capture
+    torch.cuda.synchronize()
+    graph = torch.cuda.CUDAGraph()
+    with torch.cuda.graph(graph):
+        w, ids = fg.grouped_topk(static, 8, 4, 8, True, 2.5, bias, 1)
+    for seed in (6, 7):
+        fresh, _ = T.make_router_inputs(64, 256, DEV, seed=seed)
+        static.copy_(fresh)
+        graph.replay()
+        torch.cuda.synchronize()
+        ow, oi = O.grouped_topk_oracle(fresh, 8, 4, 8, True, 2.5, bias, 1)
+        assert torch.equal(ids.cpu(), oi)
+        torch.testing.assert_close(w.cpu(), ow, rtol=2e-6, atol=2e-6)

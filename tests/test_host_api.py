@@ -1,0 +1,137 @@
+"""CPU-only checks: the C-ABI library loads and exports every declared symbol,
+the Python entry points keep the reference's signatures, argument validation
+raises the reference's error types before any device work."""
+
+import ctypes
+import inspect
+import os
+import re
+
+import pytest
+import torch
+
+import flaggems_vllm
+import flaggems_vllm_b200 as fg
+from flaggems_vllm_b200 import _lib, build
+
+ROOT = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
+
+
+def test_library_builds_and_exports_every_declared_symbol():
+    path = build.build()
+    handle = ctypes.CDLL(path)
+    header = open(os.path.join(ROOT, "include", "moe_sm100.h")).read()
+    declared = set(re.findall(r"^(?:int|const char\*)\s+(moe_[a-z0-9_]+)\s*\(", header, flags=re.M))
+    assert declared, "no declarations found in the header"
+    for name in declared:
+        assert hasattr(handle, name), f"{name} declared in the header but not exported"
+    assert declared == set(_lib.SYMBOLS), "ctypes table and header disagree"
+    assert handle.moe_abi_version() >= 1
+
+
+def _sig(fn):
+    return [(n, p.kind, p.default) for n, p in inspect.signature(fn).parameters.items()]
+
+
+def test_signatures_match_reference():
+    # names, order, kinds and defaults of src/flaggems_vllm/ops/grouped_topk.py:1674-1684
+    assert _sig(fg.grouped_topk) == [
+        ("scores", inspect.Parameter.POSITIONAL_OR_KEYWORD, inspect._empty),
+        ("n_group", inspect.Parameter.POSITIONAL_OR_KEYWORD, inspect._empty),
+        ("topk_group", inspect.Parameter.POSITIONAL_OR_KEYWORD, inspect._empty),
+        ("topk", inspect.Parameter.POSITIONAL_OR_KEYWORD, inspect._empty),
+        ("renormalize", inspect.Parameter.POSITIONAL_OR_KEYWORD, inspect._empty),
+        ("routed_scaling_factor", inspect.Parameter.POSITIONAL_OR_KEYWORD, inspect._empty),
+        ("bias", inspect.Parameter.POSITIONAL_OR_KEYWORD, inspect._empty),
+        ("scoring_func", inspect.Parameter.POSITIONAL_OR_KEYWORD, 0),
+        ("is_padding", inspect.Parameter.POSITIONAL_OR_KEYWORD, None),
+    ]
+    # src/flaggems_vllm/ops/moe_align_block_size.py:896-902
+    assert [(n, d) for n, _, d in _sig(fg.moe_align_block_size)] == [
+        ("topk_ids", inspect._empty), ("block_size", inspect._empty), ("num_experts", inspect._empty),
+        ("expert_map", None), ("pad_sorted_ids", False)]
+    # src/flaggems_vllm/ops/fused_moe.py:2314-2344
+    names = [n for n, _, _ in _sig(fg.fused_experts_impl)]
+    assert names == [
+        "hidden_states", "w1", "w2", "topk_weights", "topk_ids", "inplace", "activation",
+        "apply_router_weight_on_input", "use_fp8_w8a8", "use_int8_w8a8", "use_int8_w8a16", "use_int4_w4a16",
+        "ocp_mx_scheme", "per_channel_quant", "global_num_experts", "expert_map", "w1_scale", "w2_scale",
+        "w1_zp", "w2_zp", "a1_scale", "a2_scale", "block_shape", "w1_bias", "w2_bias", "gemm1_alpha",
+        "gemm1_beta", "gemm1_clamp_limit"]
+    kinds = [k for _, k, _ in _sig(fg.fused_experts_impl)]
+    assert kinds[:25] == [inspect.Parameter.POSITIONAL_OR_KEYWORD] * 25
+    assert kinds[25:] == [inspect.Parameter.KEYWORD_ONLY] * 3
+    assert inspect.signature(fg.fused_experts_impl).parameters["global_num_experts"].default == -1
+    assert fg.ops_experts_impl is fg.fused_experts_impl
+    assert flaggems_vllm.grouped_topk is fg.grouped_topk
+    assert flaggems_vllm.ops_experts_impl is fg.fused_experts_impl
+    assert "inplace" not in inspect.signature(fg.inplace_fused_experts).parameters
+
+
+def test_grouped_topk_validation_errors():
+    s = torch.zeros(4, 16)
+    b = torch.zeros(16)
+    with pytest.raises(ValueError, match="2D"):
+        fg.grouped_topk(torch.zeros(16), 1, 1, 2, True, 1.0, b)
+    with pytest.raises(ValueError, match="divisible"):
+        fg.grouped_topk(s, 3, 1, 2, True, 1.0, b)
+    with pytest.raises(ValueError, match="n_group"):
+        fg.grouped_topk(torch.zeros(4, 64), 64, 1, 2, True, 1.0, torch.zeros(64))
+    with pytest.raises(ValueError, match="topk"):
+        fg.grouped_topk(torch.zeros(4, 64), 1, 1, 33, True, 1.0, torch.zeros(64))
+    with pytest.raises(ValueError, match="scoring_func"):
+        fg.grouped_topk(s, 1, 1, 2, True, 1.0, b, 2)
+    with pytest.raises(ValueError, match="bias length"):
+        fg.grouped_topk(s, 1, 1, 2, True, 1.0, torch.zeros(8))
+    with pytest.raises(ValueError, match="Unsupported dtype"):
+        fg.grouped_topk(s.double(), 1, 1, 2, True, 1.0, b)
+    with pytest.raises(RuntimeError, match="no CPU path"):
+        fg.grouped_topk(s, 1, 1, 2, True, 1.0, b)  # valid arguments, CPU tensors
+
+
+def test_fused_experts_validation_errors():
+    x = torch.zeros(4, 64, dtype=torch.bfloat16)
+    w1 = torch.zeros(2, 256, 64, dtype=torch.bfloat16)
+    w2 = torch.zeros(2, 64, 128, dtype=torch.bfloat16)
+    tw = torch.zeros(4, 2)
+    ti = torch.zeros(4, 2, dtype=torch.int32)
+    with pytest.raises(ValueError, match="Unknown MoE activation"):
+        fg.fused_experts_impl(x, w1, w2, tw, ti, activation="tanh")
+    with pytest.raises(ValueError, match="Only 'silu'"):
+        fg.fused_experts_impl(x, w1, w2, tw, ti, activation="gelu")
+    with pytest.raises(ValueError, match="require swigluoai"):
+        fg.fused_experts_impl(x, w1, w2, tw, ti, gemm1_alpha=1.0)
+    with pytest.raises(NotImplementedError):
+        fg.fused_experts_impl(x, w1, w2, tw, ti, ocp_mx_scheme="w_bogus")
+    with pytest.raises(AssertionError, match="Hidden size mismatch"):
+        fg.fused_experts_impl(torch.zeros(4, 32, dtype=torch.bfloat16), w1, w2, tw, ti)
+    with pytest.raises(AssertionError, match="topk shape"):
+        fg.fused_experts_impl(x, w1, w2, torch.zeros(4, 3), ti)
+    with pytest.raises(AssertionError, match="contiguous"):
+        fg.fused_experts_impl(torch.zeros(64, 4, dtype=torch.bfloat16).t(), w1, w2, tw, ti)
+    with pytest.raises(NotImplementedError, match="W8A8"):
+        fg.fused_experts_impl(x, w1, w2, tw, ti, use_int8_w8a8=True)
+    with pytest.raises(NotImplementedError, match="block_shape"):
+        fg.fused_experts_impl(x, w1, w2, tw, ti, use_fp8_w8a8=True)
+    with pytest.raises(RuntimeError, match="no CPU path"):
+        fg.fused_experts_impl(x, w1, w2, tw, ti)
+
+
+def test_align_rejects_cpu_tensors_and_bad_dtypes():
+    with pytest.raises(RuntimeError, match="no CPU path"):
+        fg.moe_align_block_size(torch.zeros(4, 2, dtype=torch.int32), 16, 8)
+
+
+def test_missing_library_fails_loudly(monkeypatch, tmp_path):
+    monkeypatch.setattr(_lib, "_lib", None)
+    monkeypatch.setattr(_lib, "LIB_PATH", str(tmp_path / "nope.so"))
+    with pytest.raises(RuntimeError, match="no CPU or Triton fallback"):
+        _lib.lib()
+
+
+def test_product_package_never_imports_the_oracle():
+    pkg = os.path.join(ROOT, "flaggems_vllm_b200")
+    for fn in os.listdir(pkg):
+        if fn.endswith(".py"):
+            src = open(os.path.join(pkg, fn)).read()
+            assert "oracle" not in src, f"{fn} mentions the oracle"
