@@ -171,6 +171,8 @@ def main():
     ap.add_argument("--ref-tokens", type=int, default=4, help="tokens per step of the CPU reference arm")
     ap.add_argument("--cpu-baseline-tokens", type=int, default=16)
     ap.add_argument("--no-cpu-baseline", action="store_true")
+    ap.add_argument("--experts", type=int, default=DSV3["E"],
+                    help="expert count (smaller values give the small case used for ncu captures)")
     args = ap.parse_args()
     args.warmup = max(args.warmup, 3) if args.impl == "b200" else args.warmup
     if args.impl == "reference":
@@ -193,7 +195,7 @@ def main():
         dist = None
         torch.cuda.set_device(0)
     dev = torch.device("cuda", torch.cuda.current_device())
-    c = DSV3
+    c = dict(DSV3, E=args.experts)
     M, E, H, I, k = args.tokens, c["E"], c["H"], c["I"], c["topk"]
     E_local = E // world
     peaks = load_peaks()
@@ -316,7 +318,7 @@ def main():
         B = wbytes + M * H * 2 * 2 + M * E * 4 + k * 8 * M
         line["layer_hbm"] = {"algorithmic_bytes": B, "achieved_gbs": B / (ms * 1e-3) / 1e9,
                              "peak_gbs": peaks["hbm_gbs"], "frac": B / (ms * 1e-3) / 1e9 / peaks["hbm_gbs"]}
-    if rank == 0 and world == 1 and not args.no_cpu_baseline:
+    if rank == 0 and world == 1 and not args.no_cpu_baseline and E == DSV3["E"]:
         Ms = args.cpu_baseline_tokens
         step, threads, n_used = cpu_oracle_run(Ms)
         step()
