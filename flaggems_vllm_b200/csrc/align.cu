@@ -16,7 +16,18 @@
 //            reference kernels rank by atomic arrival order instead
 //            (src/flaggems_vllm/ops/moe_align_block_size.py:505-527).
 // Ids outside [0, num_experts) are skipped and flagged in the status word.
+//
+// Large inputs (thousands of ids) use the same algorithm spread over a
+// thread-block cluster of 8 CTAs: each CTA owns a contiguous eighth of the ids,
+// the per-CTA expert totals are exchanged through distributed shared memory
+// (plain remote loads, two cluster barriers), every CTA derives the same
+// expert bases and scatters its own ids.  The result is bit-identical to the
+// single-CTA kernel.
+#include <cooperative_groups.h>
+
 #include "moe_common.cuh"
+
+namespace cg = cooperative_groups;
 
 namespace moe {
 namespace {
@@ -149,6 +160,148 @@ __global__ void __launch_bounds__(kAlignThreads) align_kernel(
   }
 }
 
+
+constexpr int kClusterSize = 8;
+
+// Cluster variant.  Shared memory per CTA:
+//   hist[W][E] | cta_tot[E] | blk_start[E + 1] | warp_sums[32] | carry[1]
+template <typename IdT>
+__global__ void __cluster_dims__(kClusterSize, 1, 1) __launch_bounds__(kAlignThreads)
+align_cluster_kernel(const IdT* __restrict__ ids, int numel, int E, int block_size, int W,
+                     int32_t* __restrict__ sorted_ids, int sorted_cap, int32_t* __restrict__ expert_ids,
+                     int expert_cap, int32_t* __restrict__ num_post_pad, int32_t* __restrict__ status) {
+  extern __shared__ int32_t smem[];
+  int32_t* hist = smem;
+  int32_t* cta_tot = hist + (size_t)W * E;
+  int32_t* blk_start = cta_tot + E;
+  int32_t* warp_sums = blk_start + (E + 1);
+  int32_t* carry = warp_sums + 32;
+
+  cg::cluster_group cluster = cg::this_cluster();
+  const int rank = (int)cluster.block_rank();
+  const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5, T = blockDim.x;
+  const int gtid = rank * T + tid, GT = kClusterSize * T;
+
+  for (int i = tid; i < W * E; i += T) hist[i] = 0;
+  for (int i = gtid; i < sorted_cap; i += GT) sorted_ids[i] = numel;
+  for (int i = gtid; i < expert_cap; i += GT) expert_ids[i] = -1;
+  if (tid == 0) carry[0] = 0;
+  __syncthreads();
+
+  // slice of this CTA, then of this warp (multiples of 32)
+  const int per_cta = ((numel + kClusterSize - 1) / kClusterSize + 31) & ~31;
+  const int cbegin = rank * per_cta, cend = min(numel, cbegin + per_cta);
+  const int per_warp = (((per_cta + W - 1) / W) + 31) & ~31;
+  const int begin = cbegin + warp * per_warp;
+  const int end = min(cend, begin + per_warp);
+  bool bad = false;
+  if (warp < W) {
+    int32_t* h = hist + (size_t)warp * E;
+    for (int i = begin + lane; i < end; i += 32) {
+      long long e = (long long)ids[i];
+      if (e >= 0 && e < E) atomicAdd(&h[(int)e], 1);
+      else bad = true;
+    }
+  }
+  if (bad) set_status(status, MOE_ST_BAD_EXPERT_ID);
+  __syncthreads();
+  for (int e = tid; e < E; e += T) {
+    int run = 0;
+    for (int w = 0; w < W; ++w) {
+      int c = hist[(size_t)w * E + e];
+      hist[(size_t)w * E + e] = run;
+      run += c;
+    }
+    cta_tot[e] = run;
+  }
+  cluster.sync();  // every CTA's cta_tot is final and visible cluster-wide
+
+  for (int e0 = 0; e0 < E; e0 += T) {
+    const int e = e0 + tid;
+    int padded = 0, before = 0;
+    if (e < E) {
+      int total = 0;
+#pragma unroll
+      for (int r = 0; r < kClusterSize; ++r) {
+        const int32_t* remote = cluster.map_shared_rank(cta_tot, r);
+        const int c = remote[e];
+        if (r < rank) before += c;
+        total += c;
+      }
+      padded = (total + block_size - 1) / block_size * block_size;
+    }
+    int incl = padded;
+#pragma unroll
+    for (int off = 1; off < 32; off <<= 1) {
+      int o = __shfl_up_sync(0xFFFFFFFFu, incl, off);
+      if (lane >= off) incl += o;
+    }
+    if (lane == 31) warp_sums[warp] = incl;
+    __syncthreads();
+    if (warp == 0) {
+      int v = lane < (T >> 5) ? warp_sums[lane] : 0;
+      int sc = v;
+#pragma unroll
+      for (int off = 1; off < 32; off <<= 1) {
+        int o = __shfl_up_sync(0xFFFFFFFFu, sc, off);
+        if (lane >= off) sc += o;
+      }
+      warp_sums[lane] = sc - v;
+    }
+    __syncthreads();
+    const int base = carry[0] + warp_sums[warp] + incl - padded;
+    if (e < E) {
+      blk_start[e] = base;
+      for (int w = 0; w < W; ++w) hist[(size_t)w * E + e] += base + before;
+    }
+    __syncthreads();
+    if (tid == T - 1) carry[0] = base + padded;
+    __syncthreads();
+  }
+  const int total = carry[0];
+  if (tid == 0) blk_start[E] = total;
+  if (gtid == 0) num_post_pad[0] = total;
+  __syncthreads();
+
+  const int n_blocks = total / block_size;
+  for (int b = gtid; b < n_blocks && b < expert_cap; b += GT) {
+    const int pos = b * block_size;
+    int lo = 0, hi = E;
+    while (hi - lo > 1) {
+      int mid = (lo + hi) >> 1;
+      if (blk_start[mid] <= pos) lo = mid; else hi = mid;
+    }
+    expert_ids[b] = lo;
+  }
+  // sentinel fill of all CTAs must be complete before anyone scatters; the
+  // same barrier keeps every CTA's shared memory alive while peers read it
+  cluster.sync();
+
+  if (warp < W) {
+    int32_t* h = hist + (size_t)warp * E;
+    for (int i0 = begin; i0 < end; i0 += 32) {
+      const int i = i0 + lane;
+      long long e = i < end ? (long long)ids[i] : -1;
+      const bool valid = e >= 0 && e < E;
+      const unsigned vmask = __ballot_sync(0xFFFFFFFFu, valid);
+      if (valid) {
+        const unsigned same = __match_any_sync(vmask, (int)e);
+        const int rk = __popc(same & ((1u << lane) - 1u));
+        const int leader = __ffs(same) - 1;
+        int pos0 = 0;
+        if (lane == leader) {
+          pos0 = h[(int)e];
+          h[(int)e] = pos0 + __popc(same);
+        }
+        pos0 = __shfl_sync(same, pos0, leader);
+        const int pos = pos0 + rk;
+        if (pos < sorted_cap) sorted_ids[pos] = i;
+      }
+      __syncwarp();
+    }
+  }
+}
+
 }  // namespace
 }  // namespace moe
 
@@ -167,12 +320,32 @@ extern "C" int moe_align_block_size(const void* topk_ids, int ids_int64, int64_t
   // worst case padded total must fit the buffers the caller gave
   // (numel + E*(bs-1) is the reference's bound); the kernel clips writes anyway.
   const int E = num_experts;
+  cudaStream_t st = (cudaStream_t)stream;
+  cudaError_t ce;
+  if (numel >= 4096 && E <= 1024) {
+    // cluster of 8 CTAs; hist[W][E] + cta_tot[E] + blk_start[E+1] + 33 words per CTA
+    int W = kAlignThreads / 32;
+    while (W > 1 && ((size_t)W * E + 2 * (size_t)E + 34) * 4 > 96 * 1024) W >>= 1;
+    const size_t smem = ((size_t)W * E + 2 * (size_t)E + 34) * 4;
+    if (ids_int64) {
+      ce = cudaFuncSetAttribute(align_cluster_kernel<int64_t>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
+      if (ce != cudaSuccess) return fail((int)ce, "align: smem attribute: %s", cudaGetErrorString(ce));
+      align_cluster_kernel<int64_t><<<kClusterSize, kAlignThreads, smem, st>>>(
+          (const int64_t*)topk_ids, (int)numel, E, block_size, W, sorted_ids, (int)sorted_cap, expert_ids,
+          (int)expert_cap, num_post_pad, status);
+    } else {
+      ce = cudaFuncSetAttribute(align_cluster_kernel<int32_t>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
+      if (ce != cudaSuccess) return fail((int)ce, "align: smem attribute: %s", cudaGetErrorString(ce));
+      align_cluster_kernel<int32_t><<<kClusterSize, kAlignThreads, smem, st>>>(
+          (const int32_t*)topk_ids, (int)numel, E, block_size, W, sorted_ids, (int)sorted_cap, expert_ids,
+          (int)expert_cap, num_post_pad, status);
+    }
+    return check_launch("align (cluster)");
+  }
   int n_warps = kAlignThreads / 32;
   const size_t budget = 200 * 1024;
   while (n_warps > 1 && ((size_t)n_warps * E + E + 1 + 33) * 4 > budget) n_warps >>= 1;
   const size_t smem = ((size_t)n_warps * E + E + 1 + 33) * 4;
-  cudaStream_t st = (cudaStream_t)stream;
-  cudaError_t ce;
   if (ids_int64) {
     ce = cudaFuncSetAttribute(align_kernel<int64_t>, cudaFuncAttributeMaxDynamicSharedMemorySize,
                               (int)smem);

@@ -5,14 +5,14 @@
 namespace moe {
 int simt_gemm(bool gemm1, int mode, int act_dtype, const void* a, const float* a_scales_t, const void* w,
               const float* w_scale, const int32_t* expert_ids, const int32_t* sorted_ids, const int32_t* npp,
-              const float* route_weight, int mul_weight, int64_t numel, int64_t rows_cap, int block_m, int E, int K,
-              int Nout, void* out, float* out_scales_t, int32_t* status, cudaStream_t st);
+              const float* route_weight, int mul_weight, int64_t numel, int64_t rows_cap, int64_t a_tokens, int topk,
+              int block_m, int E, int K, int Nout, void* out, float* out_scales_t, int32_t* status, cudaStream_t st);
 int tc_gemm(bool gemm1, int mode, int act_dtype, const void* a, const float* a_scales_t, const void* w,
             const float* w_scale, const int32_t* expert_ids, const int32_t* sorted_ids, const int32_t* npp,
-            const float* route_weight, int mul_weight, int64_t numel, int64_t rows_cap, int block_m, int E, int K,
-            int Nout, void* out, float* out_scales_t, int32_t* status, cudaStream_t st);
+            const float* route_weight, int mul_weight, int64_t numel, int64_t rows_cap, int64_t a_tokens, int topk,
+            int block_m, int E, int K, int Nout, void* out, float* out_scales_t, int32_t* status, cudaStream_t st);
 
-static int check_common(const char* who, int mode, const void* a, const float* a_scales_t, const void* w,
+static int check_common(const char* who, int mode, const void* a, const float* a_scales, const void* w,
                         const float* w_scale, const int32_t* expert_ids, const int32_t* sorted_ids,
                         const int32_t* npp, const float* route_weight, int mul_weight, int64_t numel,
                         int64_t rows_cap, int block_m, int E, int H, int I, const void* out) {
@@ -20,26 +20,28 @@ static int check_common(const char* who, int mode, const void* a, const float* a
     return fail(MOE_E_BADARG, "%s: bad extent", who);
   if (!a || !w || !expert_ids || !sorted_ids || !npp || !out) return fail(MOE_E_BADARG, "%s: null pointer", who);
   if (mul_weight && !route_weight) return fail(MOE_E_BADARG, "%s: route weights missing", who);
-  if (mode == MOE_MODE_FP8_BLOCK && (!a_scales_t || !w_scale)) return fail(MOE_E_BADARG, "%s: scales missing", who);
+  if (mode == MOE_MODE_FP8_BLOCK && (!a_scales || !w_scale)) return fail(MOE_E_BADARG, "%s: scales missing", who);
   if (mode == MOE_MODE_W8A16 && !w_scale) return fail(MOE_E_BADARG, "%s: weight scales missing", who);
   return 0;
 }
 }  // namespace moe
 
-extern "C" int moe_gemm1(int mode, int act_dtype, const void* a_sorted, const float* a_scales_t, const void* w1,
-                         const float* w1_scale, const int32_t* expert_ids, const int32_t* sorted_ids,
-                         const int32_t* num_post_pad, const float* route_weight, int mul_weight, int64_t numel,
-                         int64_t rows_cap, int block_m, int E, int H, int I, void* out, float* out_scales_t,
-                         int use_tensor_cores, int32_t* status, void* stream) {
+extern "C" int moe_gemm1(int mode, int act_dtype, const void* a, const float* a_scales_t, int64_t num_tokens,
+                         int topk, const void* w1, const float* w1_scale, const int32_t* expert_ids,
+                         const int32_t* sorted_ids, const int32_t* num_post_pad, const float* route_weight,
+                         int mul_weight, int64_t rows_cap, int block_m, int E, int H, int I, void* out,
+                         float* out_scales_t, int use_tensor_cores, int32_t* status, void* stream) {
   using namespace moe;
-  int rc = check_common("gemm1", mode, a_sorted, a_scales_t, w1, w1_scale, expert_ids, sorted_ids, num_post_pad,
+  if (num_tokens < 0 || topk <= 0) return fail(MOE_E_BADARG, "gemm1: bad token count or topk");
+  const int64_t numel = num_tokens * topk;
+  int rc = check_common("gemm1", mode, a, a_scales_t, w1, w1_scale, expert_ids, sorted_ids, num_post_pad,
                         route_weight, mul_weight, numel, rows_cap, block_m, E, H, I, out);
   if (rc) return rc;
   if (mode == MOE_MODE_FP8_BLOCK && !out_scales_t) return fail(MOE_E_BADARG, "gemm1: output scale buffer missing");
-  if (rows_cap == 0) return 0;
+  if (rows_cap == 0 || numel == 0) return 0;
   auto fn = use_tensor_cores ? tc_gemm : simt_gemm;
-  return fn(true, mode, act_dtype, a_sorted, a_scales_t, w1, w1_scale, expert_ids, sorted_ids, num_post_pad,
-            route_weight, mul_weight, numel, rows_cap, block_m, E, H, I, out, out_scales_t, status,
+  return fn(true, mode, act_dtype, a, a_scales_t, w1, w1_scale, expert_ids, sorted_ids, num_post_pad, route_weight,
+            mul_weight, numel, rows_cap, num_tokens, topk, block_m, E, H, I, out, out_scales_t, status,
             (cudaStream_t)stream);
 }
 
@@ -52,8 +54,9 @@ extern "C" int moe_gemm2(int mode, int act_dtype, const void* act_sorted, const 
   int rc = check_common("gemm2", mode, act_sorted, act_scales_t, w2, w2_scale, expert_ids, sorted_ids, num_post_pad,
                         route_weight, mul_weight, numel, rows_cap, block_m, E, H, I, y);
   if (rc) return rc;
-  if (rows_cap == 0) return 0;
+  if (rows_cap == 0 || numel == 0) return 0;
   auto fn = use_tensor_cores ? tc_gemm : simt_gemm;
   return fn(false, mode, act_dtype, act_sorted, act_scales_t, w2, w2_scale, expert_ids, sorted_ids, num_post_pad,
-            route_weight, mul_weight, numel, rows_cap, block_m, E, I, H, y, nullptr, status, (cudaStream_t)stream);
+            route_weight, mul_weight, numel, rows_cap, 0, 1, block_m, E, I, H, y, nullptr, status,
+            (cudaStream_t)stream);
 }

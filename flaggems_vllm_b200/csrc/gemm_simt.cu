@@ -37,8 +37,8 @@ __global__ void __launch_bounds__(256) simt_gemm_kernel(
     const typename Elem<MODE, AT>::W* __restrict__ w, const float* __restrict__ w_scale,
     const int32_t* __restrict__ expert_ids, const int32_t* __restrict__ sorted_ids,
     const int32_t* __restrict__ num_post_pad, const float* __restrict__ route_weight, int mul_weight,
-    int64_t numel, int64_t rows_cap, int block_m, int E, int K, int Nout, void* __restrict__ out,
-    float* __restrict__ out_scales_t, int32_t* __restrict__ status) {
+    int64_t numel, int64_t rows_cap, int64_t a_tokens, int topk, int block_m, int E, int K, int Nout,
+    void* __restrict__ out, float* __restrict__ out_scales_t, int32_t* __restrict__ status) {
   using WT = typename Elem<MODE, AT>::W;
   using AE = typename Elem<MODE, AT>::A;
   __shared__ float As[TM][BK + 1];
@@ -66,9 +66,20 @@ __global__ void __launch_bounds__(256) simt_gemm_kernel(
       const int idx = tid + i * 256, r = idx / BK, c = idx % BK;
       const int64_t p = row0 + r;
       float v = 0.0f;
-      if (p < rows_cap && k0 + c < K) {
-        v = load_a<MODE, AE>(a + p * K + k0 + c);
-        if constexpr (MODE == MOE_MODE_FP8_BLOCK) v *= a_scales_t[(int64_t)((k0 + c) / 128) * rows_cap + p];
+      // GEMM1 reads token rows (row p <- token sorted_ids[p] / topk), GEMM2 sorted rows
+      int64_t arow = -1, ald = rows_cap;
+      if (p < rows_cap) {
+        if constexpr (GEMM1) {
+          const int64_t s_ = (int64_t)sorted_ids[p];
+          if (s_ >= 0 && s_ < numel) arow = s_ / topk;
+          ald = a_tokens;
+        } else {
+          arow = p;
+        }
+      }
+      if (arow >= 0 && k0 + c < K) {
+        v = load_a<MODE, AE>(a + arow * K + k0 + c);
+        if constexpr (MODE == MOE_MODE_FP8_BLOCK) v *= a_scales_t[(int64_t)((k0 + c) / 128) * ald + arow];
       }
       As[r][c] = v;
     }
@@ -168,13 +179,13 @@ __global__ void __launch_bounds__(256) simt_gemm_kernel(
 template <int MODE, typename AT, bool GEMM1>
 int launch(const void* a, const float* a_scales_t, const void* w, const float* w_scale,
            const int32_t* expert_ids, const int32_t* sorted_ids, const int32_t* npp,
-           const float* route_weight, int mul_weight, int64_t numel, int64_t rows_cap, int block_m,
+           const float* route_weight, int mul_weight, int64_t numel, int64_t rows_cap, int64_t a_tokens, int topk, int block_m,
            int E, int K, int Nout, void* out, float* out_scales_t, int32_t* status, cudaStream_t st) {
   dim3 grid((unsigned)((Nout + TN - 1) / TN), (unsigned)((rows_cap + TM - 1) / TM));
   if (grid.y > 65535) return fail(MOE_E_TOOBIG, "generic GEMM: more than 65535 row tiles");
   simt_gemm_kernel<MODE, AT, GEMM1><<<grid, 256, 0, st>>>(
       (const typename Elem<MODE, AT>::A*)a, a_scales_t, (const typename Elem<MODE, AT>::W*)w, w_scale,
-      expert_ids, sorted_ids, npp, route_weight, mul_weight, numel, rows_cap, block_m, E, K, Nout, out,
+      expert_ids, sorted_ids, npp, route_weight, mul_weight, numel, rows_cap, a_tokens, topk, block_m, E, K, Nout, out,
       out_scales_t, status);
   return check_launch(GEMM1 ? "gemm1 (generic)" : "gemm2 (generic)");
 }
@@ -183,15 +194,15 @@ template <bool GEMM1, typename AT>
 int dispatch_mode(int mode, const void* a, const float* a_scales_t, const void* w,
                   const float* w_scale, const int32_t* expert_ids, const int32_t* sorted_ids,
                   const int32_t* npp, const float* route_weight, int mul_weight, int64_t numel,
-                  int64_t rows_cap, int block_m, int E, int K, int Nout, void* out,
+                  int64_t rows_cap, int64_t a_tokens, int topk, int block_m, int E, int K, int Nout, void* out,
                   float* out_scales_t, int32_t* status, cudaStream_t st) {
   switch (mode) {
     case MOE_MODE_HALF:
-      return launch<MOE_MODE_HALF, AT, GEMM1>(a, a_scales_t, w, w_scale, expert_ids, sorted_ids, npp, route_weight, mul_weight, numel, rows_cap, block_m, E, K, Nout, out, out_scales_t, status, st);
+      return launch<MOE_MODE_HALF, AT, GEMM1>(a, a_scales_t, w, w_scale, expert_ids, sorted_ids, npp, route_weight, mul_weight, numel, rows_cap, a_tokens, topk, block_m, E, K, Nout, out, out_scales_t, status, st);
     case MOE_MODE_FP8_BLOCK:
-      return launch<MOE_MODE_FP8_BLOCK, AT, GEMM1>(a, a_scales_t, w, w_scale, expert_ids, sorted_ids, npp, route_weight, mul_weight, numel, rows_cap, block_m, E, K, Nout, out, out_scales_t, status, st);
+      return launch<MOE_MODE_FP8_BLOCK, AT, GEMM1>(a, a_scales_t, w, w_scale, expert_ids, sorted_ids, npp, route_weight, mul_weight, numel, rows_cap, a_tokens, topk, block_m, E, K, Nout, out, out_scales_t, status, st);
     case MOE_MODE_W8A16:
-      return launch<MOE_MODE_W8A16, AT, GEMM1>(a, a_scales_t, w, w_scale, expert_ids, sorted_ids, npp, route_weight, mul_weight, numel, rows_cap, block_m, E, K, Nout, out, out_scales_t, status, st);
+      return launch<MOE_MODE_W8A16, AT, GEMM1>(a, a_scales_t, w, w_scale, expert_ids, sorted_ids, npp, route_weight, mul_weight, numel, rows_cap, a_tokens, topk, block_m, E, K, Nout, out, out_scales_t, status, st);
     default:
       return fail(MOE_E_BADARG, "unknown GEMM mode %d", mode);
   }
@@ -203,14 +214,14 @@ int dispatch_mode(int mode, const void* a, const float* a_scales_t, const void* 
 int simt_gemm(bool gemm1, int mode, int act_dtype, const void* a, const float* a_scales_t,
               const void* w, const float* w_scale, const int32_t* expert_ids,
               const int32_t* sorted_ids, const int32_t* npp, const float* route_weight,
-              int mul_weight, int64_t numel, int64_t rows_cap, int block_m, int E, int K, int Nout,
+              int mul_weight, int64_t numel, int64_t rows_cap, int64_t a_tokens, int topk, int block_m, int E, int K, int Nout,
               void* out, float* out_scales_t, int32_t* status, cudaStream_t st) {
   if (block_m % TM != 0) return fail(MOE_E_SHAPE, "generic GEMM: align block must be a multiple of 16");
   if (mode == MOE_MODE_FP8_BLOCK && (K % 128 != 0 || (gemm1 && Nout % 128 != 0)))
     return fail(MOE_E_SHAPE, "generic GEMM: FP8 block mode needs sizes that are multiples of 128");
 #define MOE_SIMT_DISPATCH(G1, T)                                                                    \
   dispatch_mode<G1, T>(mode, a, a_scales_t, w, w_scale, expert_ids, sorted_ids, npp, route_weight, \
-                       mul_weight, numel, rows_cap, block_m, E, K, Nout, out, out_scales_t, status, st)
+                       mul_weight, numel, rows_cap, a_tokens, topk, block_m, E, K, Nout, out, out_scales_t, status, st)
   if (act_dtype == MOE_BF16) return gemm1 ? MOE_SIMT_DISPATCH(true, __nv_bfloat16) : MOE_SIMT_DISPATCH(false, __nv_bfloat16);
   if (act_dtype == MOE_F16) return gemm1 ? MOE_SIMT_DISPATCH(true, __half) : MOE_SIMT_DISPATCH(false, __half);
   if (act_dtype == MOE_F32) {

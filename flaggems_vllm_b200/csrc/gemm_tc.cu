@@ -4,7 +4,11 @@
 //
 // Tile: 128 expert-sorted rows x 256 accumulator columns, K consumed 128 bytes
 // per pipeline stage (128 e4m3 or 64 half elements = one 128-byte swizzle row).
-//   A stage : 128 rows x 128 B  (one TMA box)
+//   A stage : 128 rows x 128 B.  GEMM2 reads its (already expert-sorted) input
+//             with one TMA box.  GEMM1 gathers token rows: row p of the tile is
+//             token sorted_ids[p] / topk, copied by 64 producer threads with
+//             16-byte cp.async into the same 128-byte-swizzled layout TMA
+//             would produce, so no sorted copy of the activations ever exists.
 //   B stage : 256 rows x 128 B  (four TMA boxes of 64 weight rows each)
 // GEMM1 picks the four boxes as {gate lo, up lo, gate hi, up hi} of a 128-wide
 // output tile, so one accumulator holds gate and up of the same output column
@@ -15,6 +19,7 @@
 //   warp 0      TMA producer (one lane)
 //   warp 1      MMA issuer (one lane): tcgen05.mma, tcgen05.commit
 //   warp 2      TMEM allocation (512 columns = two 256-column accumulators)
+//   warps 2-3   GEMM1 only: cp.async gather of the A rows (2 rows per thread)
 //   warps 4-11  accumulator consumers, two groups of four warps; group h owns
 //               accumulator columns [128h, 128h+128), warp w lanes 32*(w%4)...
 // FP8 block-scaled mode: the tensor core cannot apply fp32 128x128 / 1x128
@@ -22,7 +27,9 @@
 // accumulator (the two accumulators alternate) and the consumer warps fold it
 // into fp32 registers with acc += part * (a_scale[row] * w_scale[block]), the
 // arithmetic of the reference kernel (src/flaggems_vllm/ops/fused_moe.py:1708-1722),
-// while the tensor core works on the next block.
+// while the tensor core works on the next block.  The fold keeps two
+// tcgen05.ld in flight, uses packed fma.rn.f32x2, and hands the accumulator
+// back to the tensor core before its last FMAs.
 // Half mode: the whole K loop accumulates in TMEM; the two accumulators let
 // the epilogue of one tile overlap the main loop of the next.
 //
@@ -30,6 +37,7 @@
 // MOE_ST_WAIT_TIMEOUT, leaves its loops, frees TMEM and returns.
 #include <cuda.h>
 
+#include <cstring>
 #include <type_traits>
 
 #include "moe_common.cuh"
@@ -45,6 +53,7 @@ constexpr int B_STAGE_BYTES = BN * 128;
 constexpr int B_BOX_ROWS = 64;
 constexpr int THREADS = 384;
 constexpr int EPI_THREADS = 256;
+constexpr int GATHER_THREADS = 64;  // warps 2-3 (GEMM1)
 constexpr unsigned long long WAIT_LIMIT_NS = 2000000000ull;  // 2 s
 
 struct SmemAux {
@@ -60,7 +69,8 @@ struct SmemAux {
 constexpr size_t SMEM_BYTES = (size_t)STAGES * (A_STAGE_BYTES + B_STAGE_BYTES) + sizeof(SmemAux) + 1024;
 
 struct Params {
-  const float* a_scales_t;  // [K/128, rows_cap]          (FP8)
+  const uint8_t* a_rows;    // GEMM1: activations [tokens, K] in token order (gathered by cp.async)
+  const float* a_scales_t;  // [K/128, a_scale_ld]        (FP8)
   const float* w_scale;     // [E, rows_w/128, K/128]     (FP8)
   const int32_t* expert_ids;
   const int32_t* sorted_ids;
@@ -71,6 +81,8 @@ struct Params {
   int32_t* status;
   int64_t numel;
   int64_t rows_cap;
+  int64_t a_scale_ld;       // tokens (GEMM1) or rows_cap (GEMM2)
+  int topk;
   int mul_weight;
   int E;
   int K;        // contraction length in elements
@@ -162,6 +174,41 @@ __device__ __forceinline__ void tmem_ld32(uint32_t taddr, uint32_t* r) {
       : "r"(taddr));
 }
 __device__ __forceinline__ void tmem_ld_wait() { asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory"); }
+// Wait for outstanding tcgen05.ld and tie the loaded registers to the wait, so
+// no use of them can be scheduled ahead of it.
+__device__ __forceinline__ void tmem_ld_wait_dep(uint32_t* r) {
+  asm volatile("tcgen05.wait::ld.sync.aligned;"
+               : "+r"(r[0]), "+r"(r[1]), "+r"(r[2]), "+r"(r[3]), "+r"(r[4]), "+r"(r[5]), "+r"(r[6]), "+r"(r[7]),
+                 "+r"(r[8]), "+r"(r[9]), "+r"(r[10]), "+r"(r[11]), "+r"(r[12]), "+r"(r[13]), "+r"(r[14]), "+r"(r[15]),
+                 "+r"(r[16]), "+r"(r[17]), "+r"(r[18]), "+r"(r[19]), "+r"(r[20]), "+r"(r[21]), "+r"(r[22]), "+r"(r[23]),
+                 "+r"(r[24]), "+r"(r[25]), "+r"(r[26]), "+r"(r[27]), "+r"(r[28]), "+r"(r[29]), "+r"(r[30]), "+r"(r[31])
+               :
+               : "memory");
+}
+__device__ __forceinline__ void cp_async16(uint32_t dst_smem, const void* src) {
+  asm volatile("cp.async.cg.shared.global [%0], [%1], 16;" ::"r"(dst_smem), "l"(src) : "memory");
+}
+// The barrier receives one arrival when all earlier cp.async of this thread have landed.
+__device__ __forceinline__ void cp_async_arrive_noinc(uint64_t* bar) {
+  asm volatile("cp.async.mbarrier.arrive.noinc.shared::cta.b64 [%0];" ::"r"(smem_u32(bar)) : "memory");
+}
+__device__ __forceinline__ uint64_t pack_f32x2(float lo, float hi) {
+  uint64_t v;
+  asm("mov.b64 %0, {%1, %2};" : "=l"(v) : "f"(lo), "f"(hi));
+  return v;
+}
+// acc(2 x fp32) += part(2 x fp32 bit patterns) * scale(2 x fp32)
+__device__ __forceinline__ void fma_f32x2(uint64_t& acc, uint32_t lo, uint32_t hi, uint64_t s2) {
+  uint64_t r;
+  asm("mov.b64 %0, {%1, %2};" : "=l"(r) : "r"(lo), "r"(hi));
+  asm("fma.rn.f32x2 %0, %1, %2, %0;" : "+l"(acc) : "l"(r), "l"(s2));
+}
+__device__ __forceinline__ void fold16(uint64_t* acc2, const uint32_t* r, uint64_t s2) {
+#pragma unroll
+  for (int i = 0; i < 16; ++i) fma_f32x2(acc2[i], r[2 * i], r[2 * i + 1], s2);
+}
+__device__ __forceinline__ float lo_f32(uint64_t v) { return __uint_as_float((uint32_t)v); }
+__device__ __forceinline__ float hi_f32(uint64_t v) { return __uint_as_float((uint32_t)(v >> 32)); }
 
 // K-major operand tile with 128-byte swizzle: rows are 128 B apart, groups of
 // 8 rows 1024 B apart (stride byte offset), descriptor version 1 (sm_100).
@@ -226,7 +273,7 @@ tc_gemm_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant_
 
   if (threadIdx.x == 0) {
     for (int s = 0; s < STAGES; ++s) {
-      mbar_init(&aux->full[s], 1);
+      mbar_init(&aux->full[s], GEMM1 ? 1 + GATHER_THREADS : 1);
       mbar_init(&aux->empty[s], 1);
     }
     for (int a = 0; a < 2; ++a) {
@@ -247,10 +294,10 @@ tc_gemm_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant_
   const uint32_t tmem_base = aux->tmem_base;
 
   if (warp < 4) {
-    asm volatile("setmaxnreg.dec.sync.aligned.u32 40;");
+    asm volatile("setmaxnreg.dec.sync.aligned.u32 48;");
     if (warp == 0 && lane == 0) {
       // ------------------------------------------------------------ TMA producer
-      asm volatile("prefetch.tensormap [%0];" ::"l"(&map_a) : "memory");
+      if constexpr (!GEMM1) asm volatile("prefetch.tensormap [%0];" ::"l"(&map_a) : "memory");
       asm volatile("prefetch.tensormap [%0];" ::"l"(&map_b) : "memory");
       uint32_t it = 0;
       bool alive = true;
@@ -258,14 +305,18 @@ tc_gemm_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant_
         const int mb = tile / P.n_tiles, nt = tile % P.n_tiles;
         const int e = P.expert_ids[mb];
         if (e < 0 || e >= P.E) continue;
-        const int row0 = mb * BM;
+        [[maybe_unused]] const int row0 = mb * BM;
         const int wrow0 = e * P.rows_w;
         for (int kb = 0; kb < KB; ++kb, ++it) {
           const int s = it % STAGES;
           const uint32_t ph = (it / STAGES) & 1;
           if (!mbar_wait(&aux->empty[s], ph ^ 1, P.status)) { alive = false; break; }
-          mbar_expect_tx(&aux->full[s], A_STAGE_BYTES + B_STAGE_BYTES);
-          tma_load_2d(&map_a, &aux->full[s], sA + (size_t)s * A_STAGE_BYTES, kb * KBE, row0);
+          if constexpr (GEMM1) {
+            mbar_expect_tx(&aux->full[s], B_STAGE_BYTES);  // A rows arrive by cp.async (warps 2-3)
+          } else {
+            mbar_expect_tx(&aux->full[s], A_STAGE_BYTES + B_STAGE_BYTES);
+            tma_load_2d(&map_a, &aux->full[s], sA + (size_t)s * A_STAGE_BYTES, kb * KBE, row0);
+          }
 #pragma unroll
           for (int c = 0; c < 4; ++c)
             tma_load_2d(&map_b, &aux->full[s], sB + (size_t)s * B_STAGE_BYTES + c * (B_BOX_ROWS * 128), kb * KBE,
@@ -289,6 +340,7 @@ tc_gemm_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant_
           }
           const int s = it % STAGES;
           if (!mbar_wait(&aux->full[s], (it / STAGES) & 1, P.status)) { alive = false; break; }
+          if constexpr (GEMM1) asm volatile("fence.proxy.async.shared::cta;" ::: "memory");  // cp.async writes -> tensor core reads
           tc_fence_after();
           const uint64_t adesc = make_smem_desc(smem_u32(sA + (size_t)s * A_STAGE_BYTES));
           const uint64_t bdesc = make_smem_desc(smem_u32(sB + (size_t)s * B_STAGE_BYTES));
@@ -306,6 +358,46 @@ tc_gemm_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant_
           }
         }
       }
+    } else if (GEMM1 && warp >= 2) {
+      // ------------------------------------------------------------ A-row gather (cp.async)
+      const int g = threadIdx.x - 64;  // 0..63: rows g and g + 64 of every tile
+      const int64_t pitch = (int64_t)P.K * (FP8 ? 1 : 2);
+      uint32_t it = 0;
+      bool alive = true;
+      for (int tile = blockIdx.x; tile < total_tiles && alive; tile += gridDim.x) {
+        const int mb = tile / P.n_tiles;
+        const int e = P.expert_ids[mb];
+        if (e < 0 || e >= P.E) continue;
+        const uint8_t* src[2];
+        uint32_t dst_off[2];
+        bool ok[2];
+#pragma unroll
+        for (int j = 0; j < 2; ++j) {
+          const int r = g + 64 * j;
+          const int64_t p = (int64_t)mb * BM + r;
+          const int64_t sid = p < P.rows_cap ? (int64_t)P.sorted_ids[p] : P.numel;
+          ok[j] = sid >= 0 && sid < P.numel;  // padding slot: the row keeps stale bytes, its results are never stored
+          src[j] = P.a_rows + (ok[j] ? sid / P.topk : 0) * pitch;
+          dst_off[j] = (uint32_t)r * 128u;
+        }
+        for (int kb = 0; kb < KB; ++kb, ++it) {
+          const int s = it % STAGES;
+          if (!mbar_wait(&aux->empty[s], ((it / STAGES) & 1) ^ 1, P.status)) { alive = false; break; }
+          const uint32_t base = smem_u32(sA + (size_t)s * A_STAGE_BYTES);
+#pragma unroll
+          for (int j = 0; j < 2; ++j) {
+            if (ok[j]) {
+              const int r = g + 64 * j;
+              const uint8_t* sp = src[j] + (int64_t)kb * 128;
+#pragma unroll
+              for (int c = 0; c < 8; ++c)  // 128-byte swizzle: 16-byte chunk index XOR (row mod 8)
+                cp_async16(base + dst_off[j] + (uint32_t)((c ^ (r & 7)) << 4), sp + c * 16);
+            }
+          }
+          cp_async_arrive_noinc(&aux->full[s]);
+        }
+      }
+      asm volatile("cp.async.wait_all;" ::: "memory");
     }
   } else {
     // -------------------------------------------------------------- consumers
@@ -320,10 +412,14 @@ tc_gemm_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant_
       const int e = P.expert_ids[mb];
       if (e < 0 || e >= P.E) continue;
       const int64_t p = (int64_t)mb * BM + row;
+      int64_t sid = P.numel;
+      if (p < P.rows_cap) sid = (int64_t)P.sorted_ids[p];
+      const bool row_ok = sid >= 0 && sid < P.numel;
       float acc[128];
       if constexpr (FP8) {
+        uint64_t acc2[64];  // packed pairs: acc2[i] = columns (2i, 2i+1) of this thread's 128
 #pragma unroll
-        for (int i = 0; i < 128; ++i) acc[i] = 0.0f;
+        for (int i = 0; i < 64; ++i) acc2[i] = 0ull;
         const int sblk_per_e = (P.rows_w + 127) / 128;
         // weight-scale rows of the two 64-column halves this thread owns
         int sb_lo, sb_hi;
@@ -336,44 +432,59 @@ tc_gemm_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant_
         }
         const float* ws_lo = P.w_scale + ((int64_t)e * sblk_per_e + sb_lo) * KB;
         const float* ws_hi = P.w_scale + ((int64_t)e * sblk_per_e + sb_hi) * KB;
-        const float* as = P.a_scales_t + p;
+        // activation scales: per token (GEMM1, gathered rows) or per sorted row (GEMM2)
+        const float* as = P.a_scales_t + (GEMM1 ? (row_ok ? sid / P.topk : 0) : p);
         float sa_n = as[0], wl_n = ws_lo[0], wh_n = ws_hi[0];
         for (int kb = 0; kb < KB; ++kb, ++acc_it) {
           const float s_lo = sa_n * wl_n, s_hi = sa_n * wh_n;
+          const uint64_t s_lo2 = pack_f32x2(s_lo, s_lo), s_hi2 = pack_f32x2(s_hi, s_hi);
           if (kb + 1 < KB) {
-            sa_n = as[(int64_t)(kb + 1) * P.rows_cap];
+            sa_n = as[(int64_t)(kb + 1) * P.a_scale_ld];
             wl_n = ws_lo[kb + 1];
             wh_n = ws_hi[kb + 1];
           }
           const uint32_t a = acc_it & 1;
           if (!mbar_wait(&aux->tmem_full[a], (acc_it >> 1) & 1, P.status)) { alive = false; break; }
           tc_fence_after();
-#pragma unroll
-          for (int c = 0; c < 4; ++c) {
-            uint32_t r[32];
-            tmem_ld32(t_lane + a * BN + c * 32, r);
-            tmem_ld_wait();
-            const float sc = c < 2 ? s_lo : s_hi;
-#pragma unroll
-            for (int i = 0; i < 32; ++i) acc[c * 32 + i] = fmaf(__uint_as_float(r[i]), sc, acc[c * 32 + i]);
-          }
+          const uint32_t t0 = t_lane + a * BN;
+          uint32_t ra[32], rb[32];
+          tmem_ld32(t0, ra);
+          tmem_ld32(t0 + 32, rb);
+          tmem_ld_wait_dep(ra);
+          tmem_ld_wait_dep(rb);
+          fold16(acc2, ra, s_lo2);
+          tmem_ld32(t0 + 64, ra);
+          fold16(acc2 + 16, rb, s_lo2);
+          tmem_ld32(t0 + 96, rb);
+          tmem_ld_wait_dep(ra);
+          tmem_ld_wait_dep(rb);
+          // everything is in registers: hand the accumulator back before the last FMAs
           tc_fence_before();
           __syncwarp();
           if (lane == 0) mbar_arrive(&aux->tmem_empty[a]);
+          fold16(acc2 + 32, ra, s_hi2);
+          fold16(acc2 + 48, rb, s_hi2);
         }
         if (!alive) break;
+#pragma unroll
+        for (int i = 0; i < 64; ++i) {
+          acc[2 * i] = lo_f32(acc2[i]);
+          acc[2 * i + 1] = hi_f32(acc2[i]);
+        }
       } else {
         const uint32_t a = acc_it & 1;
         if (!mbar_wait(&aux->tmem_full[a], (acc_it >> 1) & 1, P.status)) { alive = false; break; }
         tc_fence_after();
-#pragma unroll
-        for (int c = 0; c < 4; ++c) {
-          uint32_t r[32];
-          tmem_ld32(t_lane + a * BN + c * 32, r);
-          tmem_ld_wait();
-#pragma unroll
-          for (int i = 0; i < 32; ++i) acc[c * 32 + i] = __uint_as_float(r[i]);
-        }
+        const uint32_t t0 = t_lane + a * BN;
+        uint32_t* r = reinterpret_cast<uint32_t*>(acc);
+        tmem_ld32(t0, r);
+        tmem_ld32(t0 + 32, r + 32);
+        tmem_ld32(t0 + 64, r + 64);
+        tmem_ld32(t0 + 96, r + 96);
+        tmem_ld_wait_dep(r);
+        tmem_ld_wait_dep(r + 32);
+        tmem_ld_wait_dep(r + 64);
+        tmem_ld_wait_dep(r + 96);
         tc_fence_before();
         __syncwarp();
         if (lane == 0) mbar_arrive(&aux->tmem_empty[a]);
@@ -381,9 +492,6 @@ tc_gemm_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant_
       }
 
       // ---------------------------------------------------------- tile epilogue
-      int64_t sid = P.numel;
-      if (p < P.rows_cap) sid = (int64_t)P.sorted_ids[p];
-      const bool row_ok = sid >= 0 && sid < P.numel;
       float rw = 1.0f;
       if (P.mul_weight && row_ok) rw = P.route_weight[sid];
       if constexpr (GEMM1) {
@@ -502,10 +610,12 @@ static int launch(const CUtensorMap& ma, const CUtensorMap& mb, const Params& P,
 
 }  // namespace tc
 
+// gemm1: `a` holds [a_tokens, K] activations in token order (row p of a tile is token
+// sorted_ids[p] / topk); gemm2: `a` holds [rows_cap, K] rows in sorted order.
 int tc_gemm(bool gemm1, int mode, int act_dtype, const void* a, const float* a_scales_t, const void* w,
             const float* w_scale, const int32_t* expert_ids, const int32_t* sorted_ids, const int32_t* npp,
-            const float* route_weight, int mul_weight, int64_t numel, int64_t rows_cap, int block_m, int E, int K,
-            int Nout, void* out, float* out_scales_t, int32_t* status, cudaStream_t st) {
+            const float* route_weight, int mul_weight, int64_t numel, int64_t rows_cap, int64_t a_tokens, int topk,
+            int block_m, int E, int K, int Nout, void* out, float* out_scales_t, int32_t* status, cudaStream_t st) {
   using namespace tc;
   const bool fp8 = mode == MOE_MODE_FP8_BLOCK;
   if (mode != MOE_MODE_FP8_BLOCK && mode != MOE_MODE_HALF)
@@ -526,12 +636,20 @@ int tc_gemm(bool gemm1, int mode, int act_dtype, const void* a, const float* a_s
   const CUtensorMapDataType dt = fp8 ? CU_TENSOR_MAP_DATA_TYPE_UINT8
                                      : (act_dtype == MOE_BF16 ? CU_TENSOR_MAP_DATA_TYPE_BFLOAT16 : CU_TENSOR_MAP_DATA_TYPE_FLOAT16);
   CUtensorMap ma, mb;
-  int rc = make_map(&ma, a, dt, eb, (uint64_t)rows_cap, (uint64_t)K, BM, false);
-  if (rc) return rc;
+  int rc = 0;
+  if (gemm1) {
+    memset(&ma, 0, sizeof(ma));  // A rows are gathered with cp.async, no tensor map
+    if (((uintptr_t)a & 15) != 0) return fail(MOE_E_BADARG, "tensor-core GEMM1: activations not 16-byte aligned");
+    if (topk <= 0 || a_tokens * topk != numel) return fail(MOE_E_BADARG, "tensor-core GEMM1: tokens * topk != numel");
+  } else {
+    rc = make_map(&ma, a, dt, eb, (uint64_t)rows_cap, (uint64_t)K, BM, false);
+    if (rc) return rc;
+  }
   rc = make_map(&mb, w, dt, eb, (uint64_t)E * rows_w, (uint64_t)K, B_BOX_ROWS, true);
   if (rc) return rc;
 
   Params P;
+  P.a_rows = (const uint8_t*)a; P.a_scale_ld = gemm1 ? a_tokens : rows_cap; P.topk = gemm1 ? topk : 1;
   P.a_scales_t = a_scales_t; P.w_scale = w_scale; P.expert_ids = expert_ids; P.sorted_ids = sorted_ids;
   P.num_post_pad = npp; P.route_weight = route_weight; P.out = out; P.out_scales_t = out_scales_t;
   P.status = status; P.numel = numel; P.rows_cap = rows_cap; P.mul_weight = mul_weight; P.E = E; P.K = K;

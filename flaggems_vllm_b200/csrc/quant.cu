@@ -1,7 +1,5 @@
 // Row kernels around the grouped GEMMs:
-//   * gather_rows: copies (or e4m3-quantises) activation rows into
-//     expert-sorted order so the GEMM kernels read plain 2-D tiles.
-//   * per_token_group_quant_fp8: the stand-alone 1x128 quantiser.
+//   * per_token_group_quant_fp8: 1x128 e4m3 quantiser (row-major or transposed scales).
 //   * moe_sum: fixed-order fp32 reduction over the top-k axis.
 // Quantisation follows the reference kernel exactly
 // (src/flaggems_vllm/ops/per_token_group_quant_fp8.py:150-156):
@@ -41,35 +39,6 @@ __device__ __forceinline__ void quant_group_128(const T* __restrict__ src, uint8
   if (lane == 0) *scale_out = s;
 }
 
-// grid-stride over output rows; one CTA per row at a time.
-template <typename T, bool QUANT>
-__global__ void __launch_bounds__(kRowThreads) gather_rows_kernel(
-    const T* __restrict__ x, int64_t M, int64_t cols, int topk, const int32_t* __restrict__ sorted_ids,
-    const int32_t* __restrict__ num_post_pad, int64_t out_rows, void* __restrict__ out,
-    float* __restrict__ scales_t) {
-  const int64_t numel = M * topk;
-  int64_t rows = out_rows;
-  if (num_post_pad != nullptr) rows = min((int64_t)num_post_pad[0], out_rows);
-  const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5, n_warps = kRowThreads / 32;
-  for (int64_t p = blockIdx.x; p < rows; p += gridDim.x) {
-    const int64_t sid = sorted_ids != nullptr ? (int64_t)sorted_ids[p] : p;
-    if (sid < 0 || sid >= numel) continue;  // padding slot: row content is never used
-    const T* src = x + (sid / topk) * cols;
-    if constexpr (QUANT) {
-      uint8_t* dst = reinterpret_cast<uint8_t*>(out) + p * cols;
-      const int groups = (int)(cols / 128);
-      for (int g = warp; g < groups; g += n_warps)
-        quant_group_128<T>(src + g * 128, dst + g * 128, scales_t + (int64_t)g * out_rows + p, lane);
-    } else {
-      T* dst = reinterpret_cast<T*>(out) + p * cols;
-      const int64_t n16 = cols * sizeof(T) / 16;
-      const uint4* s4 = reinterpret_cast<const uint4*>(src);
-      uint4* d4 = reinterpret_cast<uint4*>(dst);
-      for (int64_t i = threadIdx.x; i < n16; i += kRowThreads) d4[i] = s4[i];
-    }
-  }
-}
-
 template <typename T>
 __global__ void __launch_bounds__(kRowThreads) quant_rows_kernel(
     const T* __restrict__ x, int64_t rows, int64_t cols, uint8_t* __restrict__ q,
@@ -101,19 +70,38 @@ __global__ void __launch_bounds__(256) moe_sum_kernel(
 #pragma unroll
     for (int i = 0; i < V; ++i) acc[i] = 0.0f;
     const bool full = aligned && (h0 + V <= H) && (H % V == 0);
-    for (int j = 0; j < topk; ++j) {
-      if (ids != nullptr) {
-        long long e = (long long)ids[m * topk + j];
-        if (e < 0 || e >= num_experts) continue;
-        if (expert_map != nullptr && expert_map[e] < 0) continue;
-      }
-      const T* src = in + (m * topk + j) * H + h0;
-      if (full) {
-        uint4 raw = *reinterpret_cast<const uint4*>(src);
-        const T* p = reinterpret_cast<const T*>(&raw);
+    if (full) {
+      // four 16-byte loads in flight per thread; the adds stay in slot order
+      for (int j0 = 0; j0 < topk; j0 += 4) {
+        uint4 raw[4];
+        bool use[4];
 #pragma unroll
-        for (int i = 0; i < V; ++i) acc[i] += ToF32<T>::get(p[i]);
-      } else {
+        for (int u = 0; u < 4; ++u) {
+          const int j = j0 + u;
+          use[u] = j < topk;
+          if (use[u] && ids != nullptr) {
+            long long e = (long long)ids[m * topk + j];
+            use[u] = e >= 0 && e < num_experts && (expert_map == nullptr || expert_map[e] >= 0);
+          }
+          if (use[u]) raw[u] = *reinterpret_cast<const uint4*>(in + (m * topk + j) * H + h0);
+        }
+#pragma unroll
+        for (int u = 0; u < 4; ++u) {
+          if (use[u]) {
+            const T* p = reinterpret_cast<const T*>(&raw[u]);
+#pragma unroll
+            for (int i = 0; i < V; ++i) acc[i] += ToF32<T>::get(p[i]);
+          }
+        }
+      }
+    } else {
+      for (int j = 0; j < topk; ++j) {
+        if (ids != nullptr) {
+          long long e = (long long)ids[m * topk + j];
+          if (e < 0 || e >= num_experts) continue;
+          if (expert_map != nullptr && expert_map[e] < 0) continue;
+        }
+        const T* src = in + (m * topk + j) * H + h0;
         for (int i = 0; i < V && h0 + i < H; ++i) acc[i] += ToF32<T>::get(src[i]);
       }
     }
@@ -139,20 +127,6 @@ int grid_for(int64_t work_items, int per_sm) {
 }
 
 template <typename T>
-int launch_gather(const void* x, int64_t M, int64_t cols, int topk, const int32_t* sorted_ids,
-                  const int32_t* npp, int64_t out_rows, int mode, void* out, float* scales_t,
-                  cudaStream_t st) {
-  const int grid = grid_for(out_rows, 8);
-  if (mode == MOE_MODE_FP8_BLOCK)
-    gather_rows_kernel<T, true><<<grid, kRowThreads, 0, st>>>((const T*)x, M, cols, topk, sorted_ids,
-                                                              npp, out_rows, out, scales_t);
-  else
-    gather_rows_kernel<T, false><<<grid, kRowThreads, 0, st>>>((const T*)x, M, cols, topk, sorted_ids,
-                                                               npp, out_rows, out, scales_t);
-  return check_launch("gather_rows");
-}
-
-template <typename T>
 int launch_sum(const void* in, void* out, int64_t M, int topk, int64_t H, const void* ids,
                int ids_int64, int E, const int32_t* emap, cudaStream_t st) {
   constexpr int V = 16 / sizeof(T);
@@ -170,29 +144,6 @@ int launch_sum(const void* in, void* out, int64_t M, int topk, int64_t H, const 
 
 }  // namespace
 }  // namespace moe
-
-extern "C" int moe_gather_rows(const void* x, int x_dtype, int64_t M, int64_t cols, int topk,
-                               const int32_t* sorted_ids, const int32_t* num_post_pad,
-                               int64_t out_rows, int mode, void* out, float* scales_t,
-                               void* stream) {
-  using namespace moe;
-  if (M < 0 || cols <= 0 || topk <= 0 || out_rows < 0) return fail(MOE_E_BADARG, "gather_rows: bad extent");
-  if (out_rows == 0 || M == 0) return 0;
-  if (!x || !out || !sorted_ids) return fail(MOE_E_BADARG, "gather_rows: null pointer");
-  if (mode == MOE_MODE_FP8_BLOCK) {
-    if (cols % 128 != 0) return fail(MOE_E_SHAPE, "gather_rows: fp8 mode needs cols %% 128 == 0");
-    if (!scales_t) return fail(MOE_E_BADARG, "gather_rows: fp8 mode needs a scale buffer");
-  }
-  if ((cols * (x_dtype == MOE_F32 ? 4 : 2)) % 16 != 0)
-    return fail(MOE_E_SHAPE, "gather_rows: row bytes must be a multiple of 16");
-  cudaStream_t st = (cudaStream_t)stream;
-  switch (x_dtype) {
-    case MOE_F32: return launch_gather<float>(x, M, cols, topk, sorted_ids, num_post_pad, out_rows, mode, out, scales_t, st);
-    case MOE_F16: return launch_gather<__half>(x, M, cols, topk, sorted_ids, num_post_pad, out_rows, mode, out, scales_t, st);
-    case MOE_BF16: return launch_gather<__nv_bfloat16>(x, M, cols, topk, sorted_ids, num_post_pad, out_rows, mode, out, scales_t, st);
-    default: return fail(MOE_E_DTYPE, "gather_rows: unsupported dtype %d", x_dtype);
-  }
-}
 
 extern "C" int moe_per_token_group_quant_fp8(const void* x, int x_dtype, int64_t rows, int64_t cols,
                                              int group, void* q, float* scales,

@@ -4,8 +4,8 @@ Pipeline per chunk of at most 32768 tokens (the reference's chunk size,
 src/flaggems_vllm/ops/fused_moe.py:2399-2400):
 
     moe_align_block_size          stable sort of routes by expert, 1 launch
-    gather_rows                   activation rows -> sorted order (+ e4m3 1x128 quant)
-    gemm1                         SiLU(x Wg^T) * (x Wu^T)   (+ 1x128 re-quant, FP8)
+    per_token_group_quant_fp8     FP8 mode only: activations -> e4m3 + 1x128 scales, once per token
+    gemm1                         gathers token rows; SiLU(x Wg^T) * (x Wu^T)   (+ 1x128 re-quant, FP8)
     gemm2                         (act W2^T) * route weight -> y[route, H]
     moe_sum                       fixed-order fp32 sum over the top-k routes
 
@@ -112,26 +112,26 @@ def run_chunk(x, w1, w2, topk_weights, topk_ids, out, *, mode, w1_scale, w2_scal
 
     fp8 = mode == _lib.MODE_FP8_BLOCK
     if fp8:
-        a_sorted = torch.empty((rows_cap, H), dtype=torch.float8_e4m3fn, device=dev)
-        a_scales = torch.empty((H // 128, rows_cap), dtype=torch.float32, device=dev)
+        # activations are quantised once per token; the GEMM gathers rows by token
+        a_rows = torch.empty((M, H), dtype=torch.float8_e4m3fn, device=dev)
+        a_scales = torch.empty((H // 128, M), dtype=torch.float32, device=dev)
+        _lib.check(L.moe_per_token_group_quant_fp8(x.data_ptr(), act_code, M, H, 128, a_rows.data_ptr(),
+                                                   a_scales.data_ptr(), 1, M, st))
         act = torch.empty((rows_cap, I), dtype=torch.float8_e4m3fn, device=dev)
         act_scales = torch.empty((I // 128, rows_cap), dtype=torch.float32, device=dev)
     else:
-        a_sorted = torch.empty((rows_cap, H), dtype=act_dt, device=dev)
+        a_rows = x
         a_scales = None
         act = torch.empty((rows_cap, I), dtype=act_dt, device=dev)
         act_scales = None
-    _lib.check(L.moe_gather_rows(x.data_ptr(), act_code, M, H, k, sorted_ids.data_ptr(), npp.data_ptr(), rows_cap,
-                                 mode if fp8 else _lib.MODE_HALF, a_sorted.data_ptr(), _lib.ptr(a_scales), st))
-
-    mark("gather")
+    mark("quant")
     rw = topk_weights if topk_weights.dtype == torch.float32 else topk_weights.float()
     rw = rw if rw.is_contiguous() else rw.contiguous()
     tc = int(bool(use_tensor_cores))
-    _lib.check(L.moe_gemm1(mode, act_code, a_sorted.data_ptr(), _lib.ptr(a_scales), w1.data_ptr(),
+    _lib.check(L.moe_gemm1(mode, act_code, a_rows.data_ptr(), _lib.ptr(a_scales), M, k, w1.data_ptr(),
                            _lib.ptr(w1_scale), expert_ids.data_ptr(), sorted_ids.data_ptr(), npp.data_ptr(),
-                           rw.data_ptr(), int(apply_router_weight_on_input), numel, rows_cap, block_m, E_local, H,
-                           I, act.data_ptr(), _lib.ptr(act_scales), tc, status.data_ptr(), st))
+                           rw.data_ptr(), int(apply_router_weight_on_input), rows_cap, block_m, E_local, H, I,
+                           act.data_ptr(), _lib.ptr(act_scales), tc, status.data_ptr(), st))
     mark("gemm1")
     y = torch.empty((numel, H), dtype=act_dt, device=dev)
     _lib.check(L.moe_gemm2(mode, act_code, act.data_ptr(), _lib.ptr(act_scales), w2.data_ptr(), _lib.ptr(w2_scale),
@@ -147,7 +147,7 @@ def run_chunk(x, w1, w2, topk_weights, topk_ids, out, *, mode, w1_scale, w2_scal
                          int(ids.dtype == torch.int64), global_num_experts, _lib.ptr(emap), st))
     mark("sum")
     if keep is not None:
-        keep.update(sorted_ids=sorted_ids, expert_ids=expert_ids, num_post_pad=npp, a_sorted=a_sorted,
+        keep.update(sorted_ids=sorted_ids, expert_ids=expert_ids, num_post_pad=npp, a_rows=a_rows,
                     a_scales_t=a_scales, act=act, act_scales_t=act_scales, y=y, block_m=block_m,
                     rows_cap=rows_cap, used_tensor_cores=bool(use_tensor_cores))
 

@@ -93,38 +93,30 @@ int moe_per_token_group_quant_fp8(const void* x, int x_dtype, int64_t rows, int6
                                   void* stream);
 
 /*
- * Gather activation rows into expert-sorted order, optionally quantising to
- * e4m3 on the way (MOE_MODE_FP8_BLOCK).  Row p of the output is the row
- * sorted_ids[p] / topk of x, for p < *num_post_pad and sorted_ids[p] < numel.
- * Fuses moe_kernel_quantize_input (src/flaggems_vllm/ops/fused_moe.py:2533-2540)
- * with the row gather the reference GEMM does on load (:1559).
- * out[out_rows, cols] (same dtype as x, or e4m3); scales_t[cols/128, out_rows].
- */
-int moe_gather_rows(const void* x, int x_dtype, int64_t M, int64_t cols, int topk,
-                    const int32_t* sorted_ids, const int32_t* num_post_pad, int64_t out_rows,
-                    int mode, void* out, float* scales_t, void* stream);
-
-/*
- * Expert grouped GEMM 1: act = SiLU(A Wg^T) * (A Wu^T) on expert-sorted rows.
- * Stands in for fused_moe_kernel with FUSE_SILU
- * (src/flaggems_vllm/ops/fused_moe.py:1634-1795, launch :2078-2220).
- *   a_sorted [rows_cap, H]   activations in sorted order (act dtype or e4m3)
- *   a_scales_t [H/128, rows_cap] (FP8 mode)
+ * Expert grouped GEMM 1: act[p] = SiLU(x_t Wg^T) * (x_t Wu^T) for every sorted
+ * row p, where t = sorted_ids[p] / topk is the token of that route.  The kernel
+ * gathers the token rows itself; no sorted copy of the activations is needed.
+ * Stands in for fused_moe_kernel with FUSE_SILU, including its row gather
+ * (src/flaggems_vllm/ops/fused_moe.py:1559, 1634-1795, launch :2078-2220).
+ *   a [num_tokens, H]        activations in token order (act dtype, or e4m3 in FP8 mode)
+ *   a_scales_t [H/128, num_tokens]  1x128 activation scales, transposed (FP8 mode)
  *   w1 [E, 2I, H] contiguous (act dtype, e4m3 or int8), gate rows first
  *   w1_scale: FP8 [E, 2I/128, H/128]; W8A16 [E, 2I]; else NULL
- *   expert_ids [rows_cap / block_m], num_post_pad[1] from the align step
- *   route_weight/sorted_ids: when mul_weight != 0 gate and up are multiplied by
- *     route_weight[sorted_ids[p]] before the activation
- *   out [rows_cap, I]: act dtype, or e4m3 with out_scales_t [I/128, rows_cap]
- *     when mode is FP8 (the activation is rounded to act dtype, then quantised)
- * use_tensor_cores: 1 = tcgen05 kernel (block_m must be 128, H and I multiples
- *   of 128 for FP8 / 64 for half), 0 = generic kernel (block_m % 16 == 0).
+ *   expert_ids [rows_cap / block_m], sorted_ids [rows_cap], num_post_pad[1] from the align step
+ *   route_weight [num_tokens * topk]: when mul_weight != 0 gate and up are
+ *     multiplied by route_weight[sorted_ids[p]] before the activation
+ *   out [rows_cap, I] in sorted order: act dtype, or e4m3 with
+ *     out_scales_t [I/128, rows_cap] in FP8 mode (the activation is rounded to
+ *     act dtype, then quantised 1x128, as the reference does between its GEMMs)
+ * use_tensor_cores: 1 = tcgen05 kernel (block_m must be 128, rows_cap % 128 == 0,
+ *   I % 128 == 0, H % 128 == 0 for FP8 / H % 64 == 0 for half), 0 = generic
+ *   kernel (block_m % 16 == 0, any mode).
  */
-int moe_gemm1(int mode, int act_dtype, const void* a_sorted, const float* a_scales_t,
-              const void* w1, const float* w1_scale, const int32_t* expert_ids,
+int moe_gemm1(int mode, int act_dtype, const void* a, const float* a_scales_t, int64_t num_tokens,
+              int topk, const void* w1, const float* w1_scale, const int32_t* expert_ids,
               const int32_t* sorted_ids, const int32_t* num_post_pad, const float* route_weight,
-              int mul_weight, int64_t numel, int64_t rows_cap, int block_m, int E, int H, int I,
-              void* out, float* out_scales_t, int use_tensor_cores, int32_t* status, void* stream);
+              int mul_weight, int64_t rows_cap, int block_m, int E, int H, int I, void* out,
+              float* out_scales_t, int use_tensor_cores, int32_t* status, void* stream);
 
 /*
  * Expert grouped GEMM 2: y[sorted_ids[p], :] = (act[p] W2[e]^T) * route_weight.

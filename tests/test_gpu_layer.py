@@ -307,15 +307,17 @@ def test_intermediates_follow_the_documented_layout():
                         global_num_experts=E, expert_map=None, apply_router_weight_on_input=False, keep=keep)
     torch.cuda.synchronize()
     assert keep["used_tensor_cores"] and keep["block_m"] == 128
+    xq, xs = O.per_token_group_quant_fp8_oracle(x, 128)
+    assert torch.equal(keep["a_rows"].cpu().view(torch.uint8), xq.view(torch.uint8))
+    assert torch.equal(keep["a_scales_t"].cpu().t(), xs)
+    # the intermediate is in sorted order: row p belongs to route sorted_ids[p]
     n = int(keep["num_post_pad"].item())
     sid = keep["sorted_ids"][:n].cpu()
     valid = sid < M * k
-    xq, xs = O.per_token_group_quant_fp8_oracle(x, 128)
-    tok = (sid[valid] // k).long()
-    got_q = keep["a_sorted"][:n].cpu()[valid].view(torch.uint8)
-    assert torch.equal(got_q, xq[tok].view(torch.uint8))
-    got_s = keep["a_scales_t"][:, :n].cpu().t()[valid]
-    assert torch.equal(got_s, xs[tok])
+    os_, oe, on = O.moe_align_block_size_oracle(ti, 128, E, pad_sorted_ids=True)
+    assert n == int(on[0]) and torch.equal(sid, torch.from_numpy(os_[:n]))
+    act = keep["act"][:n].cpu().float() * keep["act_scales_t"][:, :n].cpu().t().repeat_interleave(128, dim=1)
+    assert torch.isfinite(act[valid]).all()
 
 
 def test_quant_and_sum_wrappers():
