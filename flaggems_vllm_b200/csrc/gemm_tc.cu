@@ -54,6 +54,16 @@ constexpr int B_BOX_ROWS = 64;
 constexpr int THREADS = 384;
 constexpr int EPI_THREADS = 256;
 constexpr int GATHER_THREADS = 64;  // warps 2-3 (GEMM1)
+// setmaxnreg only moves registers inside the allocation the CTA got at launch
+// (THREADS x the per-thread count ptxas reports under __launch_bounds__, 168).
+// The consumers' increase must be covered by what the producer group gives
+// up, otherwise setmaxnreg.inc waits forever.
+constexpr int LAUNCH_REGS = 168;
+constexpr int PRODUCER_REGS = 56;
+constexpr int CONSUMER_REGS = 224;
+static_assert((THREADS - EPI_THREADS) * PRODUCER_REGS + EPI_THREADS * CONSUMER_REGS <= THREADS * LAUNCH_REGS,
+              "register redistribution exceeds the CTA's allocation");
+static_assert(THREADS * LAUNCH_REGS <= 65536, "CTA does not fit the register file");
 constexpr unsigned long long WAIT_LIMIT_NS = 2000000000ull;  // 2 s
 
 struct SmemAux {
@@ -294,7 +304,7 @@ tc_gemm_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant_
   const uint32_t tmem_base = aux->tmem_base;
 
   if (warp < 4) {
-    asm volatile("setmaxnreg.dec.sync.aligned.u32 48;");
+    asm volatile("setmaxnreg.dec.sync.aligned.u32 %0;" ::"n"(PRODUCER_REGS));
     if (warp == 0 && lane == 0) {
       // ------------------------------------------------------------ TMA producer
       if constexpr (!GEMM1) asm volatile("prefetch.tensormap [%0];" ::"l"(&map_a) : "memory");
@@ -401,7 +411,7 @@ tc_gemm_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant_
     }
   } else {
     // -------------------------------------------------------------- consumers
-    asm volatile("setmaxnreg.inc.sync.aligned.u32 232;");
+    asm volatile("setmaxnreg.inc.sync.aligned.u32 %0;" ::"n"(CONSUMER_REGS));
     const int h = (warp - 4) >> 2;                  // column half owned by this group
     const int row = ((warp & 3) << 5) + lane;       // accumulator lane = tile row
     const uint32_t t_lane = tmem_base + ((uint32_t)((warp & 3) << 5) << 16) + (uint32_t)(h * 128);
@@ -602,7 +612,14 @@ static int make_map(CUtensorMap* m, const void* base, CUtensorMapDataType dt, in
 template <bool FP8, typename AT, bool GEMM1>
 static int launch(const CUtensorMap& ma, const CUtensorMap& mb, const Params& P, int grid, cudaStream_t st) {
   auto kern = tc_gemm_kernel<FP8, AT, GEMM1>;
-  cudaError_t ce = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)SMEM_BYTES);
+  cudaFuncAttributes fa;
+  cudaError_t ce = cudaFuncGetAttributes(&fa, kern);
+  if (ce != cudaSuccess) return fail((int)ce, "tensor-core GEMM: cudaFuncGetAttributes: %s", cudaGetErrorString(ce));
+  // see LAUNCH_REGS: refuse to launch rather than let setmaxnreg.inc wait for registers that do not exist
+  if ((THREADS - EPI_THREADS) * PRODUCER_REGS + EPI_THREADS * CONSUMER_REGS > THREADS * fa.numRegs)
+    return fail(MOE_E_DRIVER, "tensor-core GEMM: kernel was built with %d registers per thread, %d needed",
+                fa.numRegs, LAUNCH_REGS);
+  ce = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)SMEM_BYTES);
   if (ce != cudaSuccess) return fail((int)ce, "tensor-core GEMM: shared memory attribute: %s", cudaGetErrorString(ce));
   kern<<<grid, THREADS, SMEM_BYTES, st>>>(ma, mb, P);
   return check_launch(GEMM1 ? "gemm1 (tcgen05)" : "gemm2 (tcgen05)");
