@@ -36,7 +36,7 @@ SYMBOLS = {
                           c_void_p, c_int, c_int64, c_int64, c_int, c_int, c_int, c_int, c_void_p, c_int,
                           c_void_p, c_void_p]),
     "moe_sum": (c_int, [c_void_p, c_void_p, c_int, c_int64, c_int, c_int64, c_void_p, c_int, c_int, c_void_p,
-                        c_void_p]),
+                        c_void_p, c_void_p]),
 }
 
 _lib = None

@@ -28,8 +28,10 @@
 // into fp32 registers with acc += part * (a_scale[row] * w_scale[block]), the
 // arithmetic of the reference kernel (src/flaggems_vllm/ops/fused_moe.py:1708-1722),
 // while the tensor core works on the next block.  The fold keeps two
-// tcgen05.ld in flight, uses packed fma.rn.f32x2, and hands the accumulator
-// back to the tensor core before its last FMAs.
+// tcgen05.ld in flight and hands the accumulator
+// back to the tensor core before its last FMAs.  The scales of the K blocks
+// in flight sit in a small shared-memory ring filled by the producer side, so
+// the consumers issue no global loads inside the K loop.
 // Half mode: the whole K loop accumulates in TMEM; the two accumulators let
 // the epilogue of one tile overlap the main loop of the next.
 //
@@ -54,6 +56,8 @@ constexpr int B_BOX_ROWS = 64;
 constexpr int THREADS = 384;
 constexpr int EPI_THREADS = 256;
 constexpr int GATHER_THREADS = 64;  // warps 2-3 (GEMM1)
+constexpr int SCALE_THREADS = 32;   // warp 3 (FP8 GEMM2): scale staging
+constexpr int SCALE_SLOTS = 8;
 // setmaxnreg only moves registers inside the allocation the CTA got at launch
 // (THREADS x the per-thread count ptxas reports under __launch_bounds__, 168).
 // The consumers' increase must be covered by what the producer group gives
@@ -75,6 +79,12 @@ struct SmemAux {
   uint32_t tmem_base;
   uint32_t pad;
   float xch[2][2][BM];  // [tile parity][consumer group][row] amax exchange
+  // FP8: scales of the K blocks in flight, written by the producer-side threads
+  // with cp.async and read by the consumers.  The ring is deeper than
+  // STAGES + the two accumulators, so a slot is never rewritten before the
+  // consumers have read it.
+  float sc_a[SCALE_SLOTS][BM];  // activation scale of each tile row
+  float sc_w[SCALE_SLOTS][4];   // weight scales of the two column halves
 };
 constexpr size_t SMEM_BYTES = (size_t)STAGES * (A_STAGE_BYTES + B_STAGE_BYTES) + sizeof(SmemAux) + 1024;
 
@@ -172,54 +182,39 @@ __device__ __forceinline__ void tc_mma(uint32_t tmem_d, uint64_t adesc, uint64_t
         : "memory");
   }
 }
-__device__ __forceinline__ void tmem_ld32(uint32_t taddr, uint32_t* r) {
+// Two 32-column loads and the wait in ONE asm statement: the 64 results only
+// become visible to the compiler after the wait, so nothing can be scheduled
+// between the loads and the wait, and no extra register copies are needed.
+__device__ __forceinline__ void tmem_ld64_sync(uint32_t taddr, uint32_t* a, uint32_t* b) {
   asm volatile(
       "tcgen05.ld.sync.aligned.32x32b.x32.b32 "
       "{%0, %1, %2, %3, %4, %5, %6, %7, %8, %9, %10, %11, %12, %13, %14, %15, "
-      "%16, %17, %18, %19, %20, %21, %22, %23, %24, %25, %26, %27, %28, %29, %30, %31}, [%32];"
-      : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3]), "=r"(r[4]), "=r"(r[5]), "=r"(r[6]), "=r"(r[7]),
-        "=r"(r[8]), "=r"(r[9]), "=r"(r[10]), "=r"(r[11]), "=r"(r[12]), "=r"(r[13]), "=r"(r[14]), "=r"(r[15]),
-        "=r"(r[16]), "=r"(r[17]), "=r"(r[18]), "=r"(r[19]), "=r"(r[20]), "=r"(r[21]), "=r"(r[22]), "=r"(r[23]),
-        "=r"(r[24]), "=r"(r[25]), "=r"(r[26]), "=r"(r[27]), "=r"(r[28]), "=r"(r[29]), "=r"(r[30]), "=r"(r[31])
-      : "r"(taddr));
-}
-__device__ __forceinline__ void tmem_ld_wait() { asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory"); }
-// Wait for outstanding tcgen05.ld and tie the loaded registers to the wait, so
-// no use of them can be scheduled ahead of it.
-__device__ __forceinline__ void tmem_ld_wait_dep(uint32_t* r) {
-  asm volatile("tcgen05.wait::ld.sync.aligned;"
-               : "+r"(r[0]), "+r"(r[1]), "+r"(r[2]), "+r"(r[3]), "+r"(r[4]), "+r"(r[5]), "+r"(r[6]), "+r"(r[7]),
-                 "+r"(r[8]), "+r"(r[9]), "+r"(r[10]), "+r"(r[11]), "+r"(r[12]), "+r"(r[13]), "+r"(r[14]), "+r"(r[15]),
-                 "+r"(r[16]), "+r"(r[17]), "+r"(r[18]), "+r"(r[19]), "+r"(r[20]), "+r"(r[21]), "+r"(r[22]), "+r"(r[23]),
-                 "+r"(r[24]), "+r"(r[25]), "+r"(r[26]), "+r"(r[27]), "+r"(r[28]), "+r"(r[29]), "+r"(r[30]), "+r"(r[31])
-               :
-               : "memory");
+      "%16, %17, %18, %19, %20, %21, %22, %23, %24, %25, %26, %27, %28, %29, %30, %31}, [%64];\n\t"
+      "tcgen05.ld.sync.aligned.32x32b.x32.b32 "
+      "{%32, %33, %34, %35, %36, %37, %38, %39, %40, %41, %42, %43, %44, %45, %46, %47, "
+      "%48, %49, %50, %51, %52, %53, %54, %55, %56, %57, %58, %59, %60, %61, %62, %63}, [%65];\n\t"
+      "tcgen05.wait::ld.sync.aligned;"
+      : "=r"(a[0]), "=r"(a[1]), "=r"(a[2]), "=r"(a[3]), "=r"(a[4]), "=r"(a[5]), "=r"(a[6]), "=r"(a[7]),
+        "=r"(a[8]), "=r"(a[9]), "=r"(a[10]), "=r"(a[11]), "=r"(a[12]), "=r"(a[13]), "=r"(a[14]), "=r"(a[15]),
+        "=r"(a[16]), "=r"(a[17]), "=r"(a[18]), "=r"(a[19]), "=r"(a[20]), "=r"(a[21]), "=r"(a[22]), "=r"(a[23]),
+        "=r"(a[24]), "=r"(a[25]), "=r"(a[26]), "=r"(a[27]), "=r"(a[28]), "=r"(a[29]), "=r"(a[30]), "=r"(a[31]),
+        "=r"(b[0]), "=r"(b[1]), "=r"(b[2]), "=r"(b[3]), "=r"(b[4]), "=r"(b[5]), "=r"(b[6]), "=r"(b[7]),
+        "=r"(b[8]), "=r"(b[9]), "=r"(b[10]), "=r"(b[11]), "=r"(b[12]), "=r"(b[13]), "=r"(b[14]), "=r"(b[15]),
+        "=r"(b[16]), "=r"(b[17]), "=r"(b[18]), "=r"(b[19]), "=r"(b[20]), "=r"(b[21]), "=r"(b[22]), "=r"(b[23]),
+        "=r"(b[24]), "=r"(b[25]), "=r"(b[26]), "=r"(b[27]), "=r"(b[28]), "=r"(b[29]), "=r"(b[30]), "=r"(b[31])
+      : "r"(taddr), "r"(taddr + 32)
+      : "memory");
 }
 __device__ __forceinline__ void cp_async16(uint32_t dst_smem, const void* src) {
   asm volatile("cp.async.cg.shared.global [%0], [%1], 16;" ::"r"(dst_smem), "l"(src) : "memory");
+}
+__device__ __forceinline__ void cp_async4(uint32_t dst_smem, const void* src) {
+  asm volatile("cp.async.ca.shared.global [%0], [%1], 4;" ::"r"(dst_smem), "l"(src) : "memory");
 }
 // The barrier receives one arrival when all earlier cp.async of this thread have landed.
 __device__ __forceinline__ void cp_async_arrive_noinc(uint64_t* bar) {
   asm volatile("cp.async.mbarrier.arrive.noinc.shared::cta.b64 [%0];" ::"r"(smem_u32(bar)) : "memory");
 }
-__device__ __forceinline__ uint64_t pack_f32x2(float lo, float hi) {
-  uint64_t v;
-  asm("mov.b64 %0, {%1, %2};" : "=l"(v) : "f"(lo), "f"(hi));
-  return v;
-}
-// acc(2 x fp32) += part(2 x fp32 bit patterns) * scale(2 x fp32)
-__device__ __forceinline__ void fma_f32x2(uint64_t& acc, uint32_t lo, uint32_t hi, uint64_t s2) {
-  uint64_t r;
-  asm("mov.b64 %0, {%1, %2};" : "=l"(r) : "r"(lo), "r"(hi));
-  asm("fma.rn.f32x2 %0, %1, %2, %0;" : "+l"(acc) : "l"(r), "l"(s2));
-}
-__device__ __forceinline__ void fold16(uint64_t* acc2, const uint32_t* r, uint64_t s2) {
-#pragma unroll
-  for (int i = 0; i < 16; ++i) fma_f32x2(acc2[i], r[2 * i], r[2 * i + 1], s2);
-}
-__device__ __forceinline__ float lo_f32(uint64_t v) { return __uint_as_float((uint32_t)v); }
-__device__ __forceinline__ float hi_f32(uint64_t v) { return __uint_as_float((uint32_t)(v >> 32)); }
-
 // K-major operand tile with 128-byte swizzle: rows are 128 B apart, groups of
 // 8 rows 1024 B apart (stride byte offset), descriptor version 1 (sm_100).
 __device__ __forceinline__ uint64_t make_smem_desc(uint32_t saddr) {
@@ -261,6 +256,12 @@ __device__ __forceinline__ uint32_t pack2<__half>(float a, float b) {
   __half2 v = __floats2half2_rn(a, b);
   return *reinterpret_cast<uint32_t*>(&v);
 }
+// SiLU(g) * u with the fast exponential and division; like the reference kernel
+// (tl.exp / tl.fdiv, src/flaggems_vllm/ops/fused_moe.py:1795) it is accurate
+// to a couple of ulp, far inside the layer tolerance.
+__device__ __forceinline__ float silu_mul_fast(float g, float u) {
+  return __fdividef(g, 1.0f + __expf(-g)) * u;
+}
 template <typename AT>
 __device__ __forceinline__ float round_act(float v) {
   return ToF32<AT>::get(from_f32<AT>(v));
@@ -283,7 +284,7 @@ tc_gemm_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant_
 
   if (threadIdx.x == 0) {
     for (int s = 0; s < STAGES; ++s) {
-      mbar_init(&aux->full[s], GEMM1 ? 1 + GATHER_THREADS : 1);
+      mbar_init(&aux->full[s], GEMM1 ? 1 + GATHER_THREADS : (FP8 ? 1 + SCALE_THREADS : 1));
       mbar_init(&aux->empty[s], 1);
     }
     for (int a = 0; a < 2; ++a) {
@@ -379,15 +380,25 @@ tc_gemm_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant_
         const int e = P.expert_ids[mb];
         if (e < 0 || e >= P.E) continue;
         const uint8_t* src[2];
+        [[maybe_unused]] const float* as_src[2];
         uint32_t dst_off[2];
         bool ok[2];
+        // weight-scale row of this thread (g = 0: gate rows nt*128.., g = 1: up rows I + nt*128..)
+        [[maybe_unused]] const float* ws_src = nullptr;
+        if constexpr (FP8) {
+          const int nt = tile % P.n_tiles;
+          const int sblk_per_e = (P.rows_w + 127) / 128;
+          ws_src = P.w_scale + ((int64_t)e * sblk_per_e + (g == 1 ? (P.Nout >> 7) + nt : nt)) * KB;
+        }
 #pragma unroll
         for (int j = 0; j < 2; ++j) {
           const int r = g + 64 * j;
           const int64_t p = (int64_t)mb * BM + r;
           const int64_t sid = p < P.rows_cap ? (int64_t)P.sorted_ids[p] : P.numel;
           ok[j] = sid >= 0 && sid < P.numel;  // padding slot: the row keeps stale bytes, its results are never stored
-          src[j] = P.a_rows + (ok[j] ? sid / P.topk : 0) * pitch;
+          const int64_t tok = ok[j] ? sid / P.topk : 0;
+          src[j] = P.a_rows + tok * pitch;
+          if constexpr (FP8) as_src[j] = P.a_scales_t + tok;
           dst_off[j] = (uint32_t)r * 128u;
         }
         for (int kb = 0; kb < KB; ++kb, ++it) {
@@ -404,6 +415,34 @@ tc_gemm_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant_
                 cp_async16(base + dst_off[j] + (uint32_t)((c ^ (r & 7)) << 4), sp + c * 16);
             }
           }
+          if constexpr (FP8) {
+            const int slot = it % SCALE_SLOTS;
+#pragma unroll
+            for (int j = 0; j < 2; ++j)
+              if (ok[j]) cp_async4(smem_u32(&aux->sc_a[slot][g + 64 * j]), as_src[j] + (int64_t)kb * P.a_scale_ld);
+            if (g < 2) cp_async4(smem_u32(&aux->sc_w[slot][g]), ws_src + kb);
+          }
+          cp_async_arrive_noinc(&aux->full[s]);
+        }
+      }
+      asm volatile("cp.async.wait_all;" ::: "memory");
+    } else if (FP8 && !GEMM1 && warp == 3) {
+      // ------------------------------------------------------------ scale staging (FP8 GEMM2)
+      uint32_t it = 0;
+      bool alive = true;
+      const int sblk_per_e = (P.rows_w + 127) / 128;
+      for (int tile = blockIdx.x; tile < total_tiles && alive; tile += gridDim.x) {
+        const int mb = tile / P.n_tiles, nt = tile % P.n_tiles;
+        const int e = P.expert_ids[mb];
+        if (e < 0 || e >= P.E) continue;
+        const float* as_row = P.a_scales_t + (int64_t)mb * BM + 4 * lane;
+        const float* ws_src = P.w_scale + ((int64_t)e * sblk_per_e + min(2 * nt + lane, sblk_per_e - 1)) * KB;
+        for (int kb = 0; kb < KB; ++kb, ++it) {
+          const int s = it % STAGES;
+          if (!mbar_wait(&aux->empty[s], ((it / STAGES) & 1) ^ 1, P.status)) { alive = false; break; }
+          const int slot = it % SCALE_SLOTS;
+          cp_async16(smem_u32(&aux->sc_a[slot][4 * lane]), as_row + (int64_t)kb * P.a_scale_ld);
+          if (lane < 2) cp_async4(smem_u32(&aux->sc_w[slot][lane]), ws_src + kb);
           cp_async_arrive_noinc(&aux->full[s]);
         }
       }
@@ -427,74 +466,52 @@ tc_gemm_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant_
       const bool row_ok = sid >= 0 && sid < P.numel;
       float acc[128];
       if constexpr (FP8) {
-        uint64_t acc2[64];  // packed pairs: acc2[i] = columns (2i, 2i+1) of this thread's 128
 #pragma unroll
-        for (int i = 0; i < 64; ++i) acc2[i] = 0ull;
-        const int sblk_per_e = (P.rows_w + 127) / 128;
-        // weight-scale rows of the two 64-column halves this thread owns
-        int sb_lo, sb_hi;
-        if constexpr (GEMM1) {
-          sb_lo = nt;                      // gate rows nt*128 ...
-          sb_hi = (P.Nout >> 7) + nt;      // up rows I + nt*128 ...
-        } else {
-          sb_lo = min(2 * nt + h, sblk_per_e - 1);
-          sb_hi = sb_lo;
-        }
-        const float* ws_lo = P.w_scale + ((int64_t)e * sblk_per_e + sb_lo) * KB;
-        const float* ws_hi = P.w_scale + ((int64_t)e * sblk_per_e + sb_hi) * KB;
-        // activation scales: per token (GEMM1, gathered rows) or per sorted row (GEMM2)
-        const float* as = P.a_scales_t + (GEMM1 ? (row_ok ? sid / P.topk : 0) : p);
-        float sa_n = as[0], wl_n = ws_lo[0], wh_n = ws_hi[0];
-        for (int kb = 0; kb < KB; ++kb, ++acc_it) {
-          const float s_lo = sa_n * wl_n, s_hi = sa_n * wh_n;
-          const uint64_t s_lo2 = pack_f32x2(s_lo, s_lo), s_hi2 = pack_f32x2(s_hi, s_hi);
-          if (kb + 1 < KB) {
-            sa_n = as[(int64_t)(kb + 1) * P.a_scale_ld];
-            wl_n = ws_lo[kb + 1];
-            wh_n = ws_hi[kb + 1];
-          }
+        for (int i = 0; i < 128; ++i) acc[i] = 0.0f;
+        // one K block: wait for its accumulator, fold it into acc, release it
+        auto fold_block = [&](float s_lo, float s_hi) -> bool {
           const uint32_t a = acc_it & 1;
-          if (!mbar_wait(&aux->tmem_full[a], (acc_it >> 1) & 1, P.status)) { alive = false; break; }
+          if (!mbar_wait(&aux->tmem_full[a], (acc_it >> 1) & 1, P.status)) return false;
           tc_fence_after();
           const uint32_t t0 = t_lane + a * BN;
           uint32_t ra[32], rb[32];
-          tmem_ld32(t0, ra);
-          tmem_ld32(t0 + 32, rb);
-          tmem_ld_wait_dep(ra);
-          tmem_ld_wait_dep(rb);
-          fold16(acc2, ra, s_lo2);
-          tmem_ld32(t0 + 64, ra);
-          fold16(acc2 + 16, rb, s_lo2);
-          tmem_ld32(t0 + 96, rb);
-          tmem_ld_wait_dep(ra);
-          tmem_ld_wait_dep(rb);
-          // everything is in registers: hand the accumulator back before the last FMAs
+          // two loads in flight, one wait; the second pair is issued after the first
+          // pair has been folded, and the accumulator is released before the last FMAs
+          tmem_ld64_sync(t0, ra, rb);
+#pragma unroll
+          for (int i = 0; i < 32; ++i) acc[i] = fmaf(__uint_as_float(ra[i]), s_lo, acc[i]);
+#pragma unroll
+          for (int i = 0; i < 32; ++i) acc[32 + i] = fmaf(__uint_as_float(rb[i]), s_lo, acc[32 + i]);
+          tmem_ld64_sync(t0 + 64, ra, rb);
           tc_fence_before();
           __syncwarp();
           if (lane == 0) mbar_arrive(&aux->tmem_empty[a]);
-          fold16(acc2 + 32, ra, s_hi2);
-          fold16(acc2 + 48, rb, s_hi2);
+#pragma unroll
+          for (int i = 0; i < 32; ++i) acc[64 + i] = fmaf(__uint_as_float(ra[i]), s_hi, acc[64 + i]);
+#pragma unroll
+          for (int i = 0; i < 32; ++i) acc[96 + i] = fmaf(__uint_as_float(rb[i]), s_hi, acc[96 + i]);
+          ++acc_it;
+          return true;
+        };
+        // scales come from the shared-memory ring filled by the producer side:
+        // GEMM1 halves are (gate, up) -> sc_w[0], sc_w[1]; GEMM2 group h owns one weight block
+        for (int kb = 0; kb < KB; ++kb) {
+          const int slot = acc_it % SCALE_SLOTS;
+          if (!mbar_wait(&aux->tmem_full[acc_it & 1], (acc_it >> 1) & 1, P.status)) { alive = false; break; }
+          const float sa = aux->sc_a[slot][row];
+          const float s_lo = sa * aux->sc_w[slot][GEMM1 ? 0 : h];
+          const float s_hi = sa * aux->sc_w[slot][GEMM1 ? 1 : h];
+          if (!fold_block(s_lo, s_hi)) { alive = false; break; }
         }
         if (!alive) break;
-#pragma unroll
-        for (int i = 0; i < 64; ++i) {
-          acc[2 * i] = lo_f32(acc2[i]);
-          acc[2 * i + 1] = hi_f32(acc2[i]);
-        }
       } else {
         const uint32_t a = acc_it & 1;
         if (!mbar_wait(&aux->tmem_full[a], (acc_it >> 1) & 1, P.status)) { alive = false; break; }
         tc_fence_after();
         const uint32_t t0 = t_lane + a * BN;
         uint32_t* r = reinterpret_cast<uint32_t*>(acc);
-        tmem_ld32(t0, r);
-        tmem_ld32(t0 + 32, r + 32);
-        tmem_ld32(t0 + 64, r + 64);
-        tmem_ld32(t0 + 96, r + 96);
-        tmem_ld_wait_dep(r);
-        tmem_ld_wait_dep(r + 32);
-        tmem_ld_wait_dep(r + 64);
-        tmem_ld_wait_dep(r + 96);
+        tmem_ld64_sync(t0, r, r + 32);
+        tmem_ld64_sync(t0 + 64, r + 64, r + 96);
         tc_fence_before();
         __syncwarp();
         if (lane == 0) mbar_arrive(&aux->tmem_empty[a]);
@@ -509,7 +526,7 @@ tc_gemm_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant_
         float amax = 0.0f;
 #pragma unroll
         for (int j = 0; j < 64; ++j) {
-          acc[j] = round_act<AT>(silu_mul(acc[j] * rw, acc[64 + j] * rw));
+          acc[j] = round_act<AT>(silu_mul_fast(acc[j] * rw, acc[64 + j] * rw));
           amax = fmaxf(amax, fabsf(acc[j]));
         }
         const int64_t col0 = (int64_t)nt * 128 + 64 * h;
@@ -520,6 +537,7 @@ tc_gemm_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant_
           if (!mbar_wait(&aux->xch_bar, tile_it & 1, P.status)) { alive = false; break; }
           amax = fmaxf(amax, x[(1 - h) * BM + row]);
           const float s = fmaxf(amax, kQuantEps) * (1.0f / kFp8Max);
+          const float inv_s = 1.0f / s;  // one reciprocal per row instead of 64 divisions
           if (row_ok) {
             uint4* o = reinterpret_cast<uint4*>(reinterpret_cast<uint8_t*>(P.out) + p * P.Nout + col0);
 #pragma unroll
@@ -530,7 +548,7 @@ tc_gemm_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant_
                 uint32_t pk = 0;
 #pragma unroll
                 for (int b = 0; b < 4; ++b) {
-                  const float qv = fminf(fmaxf(acc[v * 16 + q * 4 + b] / s, -kFp8Max), kFp8Max);
+                  const float qv = fminf(fmaxf(acc[v * 16 + q * 4 + b] * inv_s, -kFp8Max), kFp8Max);
                   pk |= (uint32_t)f32_to_fp8e4m3(qv) << (8 * b);
                 }
                 w[q] = pk;

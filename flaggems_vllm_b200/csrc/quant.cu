@@ -59,7 +59,8 @@ __global__ void __launch_bounds__(kRowThreads) quant_rows_kernel(
 template <typename T, typename IdT>
 __global__ void __launch_bounds__(256) moe_sum_kernel(
     const T* __restrict__ in, T* __restrict__ out, int64_t M, int topk, int64_t H,
-    const IdT* __restrict__ ids, int num_experts, const int32_t* __restrict__ expert_map, bool aligned) {
+    const IdT* __restrict__ ids, int num_experts, const int32_t* __restrict__ expert_map,
+    const int32_t* __restrict__ row_index, bool aligned) {
   constexpr int V = 16 / sizeof(T);
   const int64_t vec_per_row = (H + V - 1) / V;
   const int64_t total = M * vec_per_row;
@@ -83,7 +84,10 @@ __global__ void __launch_bounds__(256) moe_sum_kernel(
             long long e = (long long)ids[m * topk + j];
             use[u] = e >= 0 && e < num_experts && (expert_map == nullptr || expert_map[e] >= 0);
           }
-          if (use[u]) raw[u] = *reinterpret_cast<const uint4*>(in + (m * topk + j) * H + h0);
+          if (use[u]) {
+            const int64_t src_row = row_index != nullptr ? (int64_t)row_index[m * topk + j] : m * topk + j;
+            raw[u] = *reinterpret_cast<const uint4*>(in + src_row * H + h0);
+          }
         }
 #pragma unroll
         for (int u = 0; u < 4; ++u) {
@@ -101,7 +105,8 @@ __global__ void __launch_bounds__(256) moe_sum_kernel(
           if (e < 0 || e >= num_experts) continue;
           if (expert_map != nullptr && expert_map[e] < 0) continue;
         }
-        const T* src = in + (m * topk + j) * H + h0;
+        const int64_t src_row = row_index != nullptr ? (int64_t)row_index[m * topk + j] : m * topk + j;
+        const T* src = in + src_row * H + h0;
         for (int i = 0; i < V && h0 + i < H; ++i) acc[i] += ToF32<T>::get(src[i]);
       }
     }
@@ -128,17 +133,17 @@ int grid_for(int64_t work_items, int per_sm) {
 
 template <typename T>
 int launch_sum(const void* in, void* out, int64_t M, int topk, int64_t H, const void* ids,
-               int ids_int64, int E, const int32_t* emap, cudaStream_t st) {
+               int ids_int64, int E, const int32_t* emap, const int32_t* row_index, cudaStream_t st) {
   constexpr int V = 16 / sizeof(T);
   const int64_t total = M * ((H + V - 1) / V);
   const int grid = grid_for((total + 255) / 256, 8);
   const bool aligned = (((uintptr_t)in | (uintptr_t)out) & 15) == 0;
   if (ids_int64)
     moe_sum_kernel<T, int64_t><<<grid, 256, 0, st>>>((const T*)in, (T*)out, M, topk, H,
-                                                     (const int64_t*)ids, E, emap, aligned);
+                                                     (const int64_t*)ids, E, emap, row_index, aligned);
   else
     moe_sum_kernel<T, int32_t><<<grid, 256, 0, st>>>((const T*)in, (T*)out, M, topk, H,
-                                                     (const int32_t*)ids, E, emap, aligned);
+                                                     (const int32_t*)ids, E, emap, row_index, aligned);
   return check_launch("moe_sum");
 }
 
@@ -173,16 +178,16 @@ extern "C" int moe_per_token_group_quant_fp8(const void* x, int x_dtype, int64_t
 
 extern "C" int moe_sum(const void* in, void* out, int dtype, int64_t M, int topk, int64_t H,
                        const void* topk_ids, int ids_int64, int num_experts,
-                       const int32_t* expert_map, void* stream) {
+                       const int32_t* expert_map, const int32_t* row_index, void* stream) {
   using namespace moe;
   if (M < 0 || topk <= 0 || H <= 0) return fail(MOE_E_BADARG, "moe_sum: bad extent");
   if (M == 0) return 0;
   if (!in || !out) return fail(MOE_E_BADARG, "moe_sum: null pointer");
   cudaStream_t st = (cudaStream_t)stream;
   switch (dtype) {
-    case MOE_F32: return launch_sum<float>(in, out, M, topk, H, topk_ids, ids_int64, num_experts, expert_map, st);
-    case MOE_F16: return launch_sum<__half>(in, out, M, topk, H, topk_ids, ids_int64, num_experts, expert_map, st);
-    case MOE_BF16: return launch_sum<__nv_bfloat16>(in, out, M, topk, H, topk_ids, ids_int64, num_experts, expert_map, st);
+    case MOE_F32: return launch_sum<float>(in, out, M, topk, H, topk_ids, ids_int64, num_experts, expert_map, row_index, st);
+    case MOE_F16: return launch_sum<__half>(in, out, M, topk, H, topk_ids, ids_int64, num_experts, expert_map, row_index, st);
+    case MOE_BF16: return launch_sum<__nv_bfloat16>(in, out, M, topk, H, topk_ids, ids_int64, num_experts, expert_map, row_index, st);
     default: return fail(MOE_E_DTYPE, "moe_sum: unsupported dtype %d", dtype);
   }
 }

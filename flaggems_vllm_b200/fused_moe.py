@@ -73,26 +73,39 @@ def _check_activation(activation, gemm1_alpha, gemm1_beta, gemm1_clamp_limit):
         f"Only 'silu' and 'swigluoai_uninterleave' activations are supported, got {activation!r}")
 
 
-def run_chunk(x, w1, w2, topk_weights, topk_ids, out, *, mode, w1_scale, w2_scale, global_num_experts,
-              expert_map, apply_router_weight_on_input, use_tensor_cores=None, keep=None, mark=None):
-    """One chunk of the layer.  ``keep`` (a dict) receives the intermediates for
-    tests; ``mark(name)`` is called after each stage has been enqueued (bench.py
-    records CUDA events there)."""
+def quantize_rows(x, mark=None):
+    """FP8 mode: e4m3 rows [M, H] plus transposed 1x128 scales [H/128, M]."""
+    M, H = x.shape
+    q = torch.empty((M, H), dtype=torch.float8_e4m3fn, device=x.device)
+    s_t = torch.empty((H // 128, M), dtype=torch.float32, device=x.device)
+    _lib.check(_lib.lib().moe_per_token_group_quant_fp8(x.data_ptr(), _lib.dtype_code(x.dtype), M, H, 128,
+                                                        q.data_ptr(), s_t.data_ptr(), 1, M, _lib.stream_of(x)))
+    return q, s_t
+
+
+def route_pipeline(a_rows, a_scales_t, w1, w2, route_weight, topk_ids, *, mode, act_dtype, w1_scale, w2_scale,
+                   global_num_experts, expert_map, apply_router_weight_on_input, use_tensor_cores=None,
+                   keep=None, mark=None):
+    """align -> GEMM1 -> GEMM2 for ``a_rows`` [tokens, H] (activation dtype, or
+    e4m3 with ``a_scales_t`` [H/128, tokens] in FP8 mode) and ``topk_ids``
+    [tokens, k].  Returns y [tokens * k, H] in ``act_dtype``: row = flat route
+    index, already multiplied by the route weight (unless the weight was
+    applied on the input).  Rows of routes whose expert is not local are left
+    unwritten."""
     if mark is None:
         mark = STAGE_HOOK or _no_mark
     L = _lib.lib()
-    dev = x.device
-    st = _lib.stream_of(x)
+    dev = a_rows.device
+    st = _lib.stream_of(a_rows)
     status = _lib.status_word(dev)
-    M, H = x.shape
+    M, H = a_rows.shape
     k = topk_ids.shape[1]
     E_local, N2, _ = w1.shape
     I = N2 // 2
     numel = M * k
-    act_dt = x.dtype
-    act_code = _lib.dtype_code(act_dt)
+    act_code = _lib.dtype_code(act_dtype)
     if use_tensor_cores is None:
-        use_tensor_cores = _tc_eligible(mode, act_dt, H, I) and not _force_generic()
+        use_tensor_cores = _tc_eligible(mode, act_dtype, H, I) and not _force_generic()
     block_m = TC_BLOCK_M if use_tensor_cores else GENERIC_BLOCK_M
 
     # every expert that owns at least one route pads by < block_m
@@ -112,44 +125,66 @@ def run_chunk(x, w1, w2, topk_weights, topk_ids, out, *, mode, w1_scale, w2_scal
 
     fp8 = mode == _lib.MODE_FP8_BLOCK
     if fp8:
-        # activations are quantised once per token; the GEMM gathers rows by token
-        a_rows = torch.empty((M, H), dtype=torch.float8_e4m3fn, device=dev)
-        a_scales = torch.empty((H // 128, M), dtype=torch.float32, device=dev)
-        _lib.check(L.moe_per_token_group_quant_fp8(x.data_ptr(), act_code, M, H, 128, a_rows.data_ptr(),
-                                                   a_scales.data_ptr(), 1, M, st))
         act = torch.empty((rows_cap, I), dtype=torch.float8_e4m3fn, device=dev)
         act_scales = torch.empty((I // 128, rows_cap), dtype=torch.float32, device=dev)
     else:
-        a_rows = x
-        a_scales = None
-        act = torch.empty((rows_cap, I), dtype=act_dt, device=dev)
+        act = torch.empty((rows_cap, I), dtype=act_dtype, device=dev)
         act_scales = None
-    mark("quant")
-    rw = topk_weights if topk_weights.dtype == torch.float32 else topk_weights.float()
+    rw = route_weight if route_weight.dtype == torch.float32 else route_weight.float()
     rw = rw if rw.is_contiguous() else rw.contiguous()
     tc = int(bool(use_tensor_cores))
-    _lib.check(L.moe_gemm1(mode, act_code, a_rows.data_ptr(), _lib.ptr(a_scales), M, k, w1.data_ptr(),
+    _lib.check(L.moe_gemm1(mode, act_code, a_rows.data_ptr(), _lib.ptr(a_scales_t), M, k, w1.data_ptr(),
                            _lib.ptr(w1_scale), expert_ids.data_ptr(), sorted_ids.data_ptr(), npp.data_ptr(),
                            rw.data_ptr(), int(apply_router_weight_on_input), rows_cap, block_m, E_local, H, I,
                            act.data_ptr(), _lib.ptr(act_scales), tc, status.data_ptr(), st))
     mark("gemm1")
-    y = torch.empty((numel, H), dtype=act_dt, device=dev)
+    y = torch.empty((numel, H), dtype=act_dtype, device=dev)
     _lib.check(L.moe_gemm2(mode, act_code, act.data_ptr(), _lib.ptr(act_scales), w2.data_ptr(), _lib.ptr(w2_scale),
                            expert_ids.data_ptr(), sorted_ids.data_ptr(), npp.data_ptr(), rw.data_ptr(),
                            int(not apply_router_weight_on_input), numel, rows_cap, block_m, E_local, H, I,
                            y.data_ptr(), tc, status.data_ptr(), st))
     mark("gemm2")
+    if keep is not None:
+        keep.update(sorted_ids=sorted_ids, expert_ids=expert_ids, num_post_pad=npp, a_rows=a_rows,
+                    a_scales_t=a_scales_t, act=act, act_scales_t=act_scales, y=y, block_m=block_m,
+                    rows_cap=rows_cap, used_tensor_cores=bool(use_tensor_cores))
+    return y
+
+
+def combine_routes(y, out, topk_ids, global_num_experts, expert_map=None, row_index=None):
+    """out[m] = sum over the k routes of token m (fp32, fixed order), skipping
+    routes whose expert id is invalid or not local."""
+    M, k = topk_ids.shape
+    H = out.shape[1]
+    ids = topk_ids if topk_ids.is_contiguous() else topk_ids.contiguous()
     emap = None
     if expert_map is not None:
         emap = expert_map if expert_map.dtype == torch.int32 else expert_map.to(torch.int32)
         emap = emap.contiguous()
-    _lib.check(L.moe_sum(y.data_ptr(), out.data_ptr(), act_code, M, k, H, ids.data_ptr(),
-                         int(ids.dtype == torch.int64), global_num_experts, _lib.ptr(emap), st))
+    _lib.check(_lib.lib().moe_sum(y.data_ptr(), out.data_ptr(), _lib.dtype_code(out.dtype), M, k, H, ids.data_ptr(),
+                                  int(ids.dtype == torch.int64), global_num_experts, _lib.ptr(emap),
+                                  _lib.ptr(row_index), _lib.stream_of(out)))
+
+
+def run_chunk(x, w1, w2, topk_weights, topk_ids, out, *, mode, w1_scale, w2_scale, global_num_experts,
+              expert_map, apply_router_weight_on_input, use_tensor_cores=None, keep=None, mark=None):
+    """One chunk of the layer.  ``keep`` (a dict) receives the intermediates for
+    tests; ``mark(name)`` is called after each stage has been enqueued (bench.py
+    records CUDA events there)."""
+    if mark is None:
+        mark = STAGE_HOOK or _no_mark
+    if mode == _lib.MODE_FP8_BLOCK:
+        # activations are quantised once per token; the GEMM gathers rows by token
+        a_rows, a_scales = quantize_rows(x)
+    else:
+        a_rows, a_scales = x, None
+    mark("quant")
+    y = route_pipeline(a_rows, a_scales, w1, w2, topk_weights, topk_ids, mode=mode, act_dtype=x.dtype,
+                       w1_scale=w1_scale, w2_scale=w2_scale, global_num_experts=global_num_experts,
+                       expert_map=expert_map, apply_router_weight_on_input=apply_router_weight_on_input,
+                       use_tensor_cores=use_tensor_cores, keep=keep, mark=mark)
+    combine_routes(y, out, topk_ids, global_num_experts, expert_map)
     mark("sum")
-    if keep is not None:
-        keep.update(sorted_ids=sorted_ids, expert_ids=expert_ids, num_post_pad=npp, a_rows=a_rows,
-                    a_scales_t=a_scales, act=act, act_scales_t=act_scales, y=y, block_m=block_m,
-                    rows_cap=rows_cap, used_tensor_cores=bool(use_tensor_cores))
 
 
 def fused_experts_impl(

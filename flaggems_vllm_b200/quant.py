@@ -76,7 +76,7 @@ def moe_sum(input: torch.Tensor, output: torch.Tensor):
     src = input if input.is_contiguous() else input.contiguous()
     dst = output if output.is_contiguous() else torch.empty_like(output, memory_format=torch.contiguous_format)
     rc = _lib.lib().moe_sum(src.data_ptr(), dst.data_ptr(), _lib.dtype_code(src.dtype), M, topk, H, None, 0, 0,
-                            None, _lib.stream_of(input))
+                            None, None, _lib.stream_of(input))
     _lib.check(rc)
     if dst is not output:
         output.copy_(dst)

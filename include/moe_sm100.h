@@ -137,10 +137,13 @@ int moe_gemm2(int mode, int act_dtype, const void* act_sorted, const float* act_
  * the io dtype.  Stands in for moe_sum (src/flaggems_vllm/ops/moe_sum.py:250-310).
  * When topk_ids is given, slot j is skipped if its id is outside
  * [0, num_experts) or expert_map[id] < 0 (expert-parallel ranks).
+ * When row_index is given, the row of slot (m, j) is in[row_index[m*topk + j]]
+ * instead of in[m*topk + j] (used after the expert-parallel combine, where the
+ * returned rows are ordered by the rank that computed them).
  */
 int moe_sum(const void* in, void* out, int dtype, int64_t M, int topk, int64_t H,
             const void* topk_ids, int ids_int64, int num_experts, const int32_t* expert_map,
-            void* stream);
+            const int32_t* row_index, void* stream);
 
 #ifdef __cplusplus
 }
