@@ -43,7 +43,10 @@ class ExpertParallelMoE:
     """Holds this rank's expert shard and runs the dispatch/compute/combine step."""
 
     def __init__(self, w1, w2, w1_scale, w2_scale, num_experts_global: int, group=None, *,
-                 mode: int = _lib.MODE_FP8_BLOCK):
+                 mode: int = _lib.MODE_FP8_BLOCK, compute_fn=None, combine_fn=None):
+        """``compute_fn(a_rows, a_scales_t, route_weight, local_ids) -> y`` and
+        ``combine_fn(y_back, out, topk_ids, row_index)`` replace the CUDA steps;
+        the CPU (gloo) tests of the dispatch/combine plumbing inject them."""
         self.group = group if group is not None else dist.group.WORLD
         self.world = dist.get_world_size(self.group)
         self.rank = dist.get_rank(self.group)
@@ -54,6 +57,17 @@ class ExpertParallelMoE:
         self.w1, self.w2, self.s1, self.s2 = w1, w2, w1_scale, w2_scale
         self.mode = mode
         self.last_counts = None
+        self.compute_fn = compute_fn or self._compute_cuda
+        self.combine_fn = combine_fn or self._combine_cuda
+
+    def _compute_cuda(self, a_rows, a_scales_t, route_weight, local_ids, act_dtype):
+        return route_pipeline(a_rows, a_scales_t, self.w1, self.w2, route_weight, local_ids, mode=self.mode,
+                              act_dtype=act_dtype, w1_scale=self.s1, w2_scale=self.s2,
+                              global_num_experts=self.E_local, expert_map=None,
+                              apply_router_weight_on_input=False)
+
+    def _combine_cuda(self, y_back, out, topk_ids, row_index):
+        combine_routes(y_back, out, topk_ids, self.E, None, row_index=row_index)
 
     def _a2a(self, out, inp, out_splits, in_splits):
         dist.all_to_all_single(out, inp, output_split_sizes=out_splits, input_split_sizes=in_splits,
@@ -100,10 +114,7 @@ class ExpertParallelMoE:
         # ---- local experts over the received rows (top-k = 1)
         if n_recv > 0:
             local_ids = meta_recv[:, 0].to(torch.int32).view(n_recv, 1)
-            y = route_pipeline(a_rows, a_scales_t, self.w1, self.w2, meta_recv[:, 1].contiguous(), local_ids,
-                               mode=self.mode, act_dtype=x.dtype, w1_scale=self.s1, w2_scale=self.s2,
-                               global_num_experts=self.E_local, expert_map=None,
-                               apply_router_weight_on_input=False)
+            y = self.compute_fn(a_rows, a_scales_t, meta_recv[:, 1].contiguous(), local_ids, x.dtype)
         else:
             y = torch.empty((0, H), dtype=x.dtype, device=dev)
 
@@ -113,5 +124,5 @@ class ExpertParallelMoE:
         inverse = torch.empty_like(order, dtype=torch.int32)
         inverse[order] = torch.arange(order.numel(), device=dev, dtype=torch.int32)
         out = torch.empty_like(x)
-        combine_routes(y_back, out, topk_ids, self.E, None, row_index=inverse)
+        self.combine_fn(y_back, out, topk_ids, inverse)
         return out
