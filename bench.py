@@ -161,6 +161,121 @@ def run_reference(args):
     print(json.dumps(line), flush=True)
 
 
+def run_sweep(args):
+    """--sweep: every (configuration, M) point of the benchmark plan on one GPU.
+    Prints one JSON line per point: ms (median, L2 flushed), TFLOP/s, algorithmic
+    GB/s, the binding roofline and the achieved fraction of it."""
+    import flaggems_vllm_b200 as fg
+    from flaggems_vllm_b200 import testing as T
+
+    torch.cuda.set_device(0)
+    dev = torch.device("cuda", 0)
+    peaks = load_peaks()
+    flush = torch.empty(2 * L2_BYTES, dtype=torch.uint8, device=dev)
+
+    def timeit(fn, iters):
+        for _ in range(3):
+            fn()
+        ts = []
+        for _ in range(iters):
+            flush.zero_()
+            a, b = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+            a.record()
+            fn()
+            b.record()
+            torch.cuda.synchronize()
+            ts.append(a.elapsed_time(b))
+        ts.sort()
+        return ts[len(ts) // 2]
+
+    def report(name, M, ms, flops, nbytes, peak_tf, extra=None):
+        t_c, t_m = flops / (peak_tf * 1e12), nbytes / (peaks["hbm_gbs"] * 1e9)
+        bound = "tensor" if t_c > t_m else "hbm"
+        line = {"sweep": name, "M": M, "ms": ms, "tokens_per_s": M / (ms * 1e-3), "tflops": flops / (ms * 1e-3) / 1e12,
+                "gbs": nbytes / (ms * 1e-3) / 1e9, "bound": bound, "floor_ms": max(t_c, t_m) * 1e3,
+                "frac_of_roofline": max(t_c, t_m) * 1e3 / ms, "peaks": peaks["source"]}
+        if extra:
+            line.update(extra)
+        print(json.dumps(line), flush=True)
+
+    which = args.sweep.split(",")
+    if "dsv3" in which:
+        c = DSV3
+        E, H, I, k = c["E"], c["H"], c["I"], c["topk"]
+        w1, s1 = T.make_fp8_block_weights(E, 2 * I, H, dev, seed=100)
+        w2, s2 = T.make_fp8_block_weights(E, H, I, dev, seed=200)
+        for M in (1, 32, 128, 1024, 8192):
+            x = T.make_activations(M, H, dev)
+            logits, bias = T.make_router_inputs(M, E, dev)
+
+            def step():
+                tw, ti = fg.grouped_topk(logits, c["n_group"], c["topk_group"], k, True, c["rsf"], bias, 1)
+                return fg.fused_experts_impl(x, w1, w2, tw, ti, use_fp8_w8a8=True, w1_scale=s1, w2_scale=s2,
+                                             block_shape=[128, 128])
+
+            _, ti = fg.grouped_topk(logits, c["n_group"], c["topk_group"], k, True, c["rsf"], bias, 1)
+            e_act = int(torch.unique(ti).numel())
+            nbytes = e_act * (3 * H * I + (2 * I // 128) * (H // 128) * 4 + (H // 128) * (I // 128) * 4) \
+                + M * H * 2 * 2 + M * E * 4 + k * 8 * M
+            report("dsv3_fp8", M, timeit(step, 10), 6.0 * M * k * H * I, nbytes, 2 * peaks["bf16_tflops"],
+                   {"distinct_experts": e_act})
+        del w1, w2, s1, s2
+    if "mixtral" in which:
+        E, H, I, k = 8, 4096, 14336, 2
+        w1 = T.make_half_weights(E, 2 * I, H, dev, seed=1, chunk=1)
+        w2 = T.make_half_weights(E, H, I, dev, seed=2, chunk=1)
+        for M in (1, 16, 64, 256, 1024, 4096, 16384):
+            x = T.make_activations(M, H, dev)
+            logits, _ = T.make_router_inputs(M, E, dev)
+            zero = torch.zeros(E, device=dev)
+
+            def step():
+                tw, ti = fg.grouped_topk(torch.softmax(logits, -1), 1, 1, k, True, 1.0, zero, 0)
+                return fg.fused_experts_impl(x, w1, w2, tw.to(torch.bfloat16), ti)
+
+            _, ti = fg.grouped_topk(torch.softmax(logits, -1), 1, 1, k, True, 1.0, zero, 0)
+            e_act = int(torch.unique(ti).numel())
+            nbytes = e_act * 3 * H * I * 2 + M * H * 2 * 2 + M * E * 4 + k * 8 * M
+            report("mixtral_bf16", M, timeit(step, 6), 6.0 * M * k * H * I, nbytes, peaks["bf16_tflops"],
+                   {"distinct_experts": e_act})
+        del w1, w2
+    if "qwen3" in which:
+        E, H, I, k = 128, 2048, 768, 8
+        w1, s1 = T.make_int8_channel_weights(E, 2 * I, H, dev, seed=1)
+        w2, s2 = T.make_int8_channel_weights(E, H, I, dev, seed=2)
+        for M in (1, 64, 512, 4096):
+            x = T.make_activations(M, H, dev)
+            logits, _ = T.make_router_inputs(M, E, dev)
+            zero = torch.zeros(E, device=dev)
+
+            def step():
+                tw, ti = fg.grouped_topk(torch.softmax(logits, -1), 1, 1, k, True, 1.0, zero, 0)
+                return fg.fused_experts_impl(x, w1, w2, tw.to(torch.bfloat16), ti, use_int8_w8a16=True,
+                                             per_channel_quant=True, w1_scale=s1, w2_scale=s2)
+
+            _, ti = fg.grouped_topk(torch.softmax(logits, -1), 1, 1, k, True, 1.0, zero, 0)
+            e_act = int(torch.unique(ti).numel())
+            nbytes = e_act * (3 * H * I + 3 * I * 4 + H * 4) + M * H * 2 * 2 + M * E * 4 + k * 8 * M
+            report("qwen3_w8a16", M, timeit(step, 6), 6.0 * M * k * H * I, nbytes, peaks["bf16_tflops"],
+                   {"distinct_experts": e_act})
+    if "align" in which:
+        for M in (1, 128, 2048, 8192):
+            for skewed in (False, True):
+                for bs in (64, 128):
+                    ids = T.make_align_ids(M, 8, 256, dev, skewed=skewed)
+                    ms = timeit(lambda: fg.moe_align_block_size(ids, bs, 256), 20)
+                    nbytes = 4 * ids.numel() + 4 * (ids.numel() + 256 * (bs - 1)) + 4 * ((ids.numel() + 256 * (bs - 1)) // bs) + 4
+                    print(json.dumps({"sweep": "align", "M": M, "skewed": skewed, "block_size": bs, "ms": ms,
+                                      "ids_per_s": ids.numel() / (ms * 1e-3), "gbs": nbytes / (ms * 1e-3) / 1e9}),
+                          flush=True)
+    if "routing" in which:
+        for M in (1, 32, 128, 1024, 8192, 16384):
+            logits, bias = T.make_router_inputs(M, 256, dev)
+            ms = timeit(lambda: fg.grouped_topk(logits, 8, 4, 8, True, 2.5, bias, 1), 20)
+            print(json.dumps({"sweep": "grouped_topk_dsv3", "M": M, "ms": ms, "tokens_per_s": M / (ms * 1e-3)}),
+                  flush=True)
+
+
 def main():
     ap = argparse.ArgumentParser()
     ap.add_argument("--gpus", type=int, default=1)
@@ -173,8 +288,12 @@ def main():
     ap.add_argument("--no-cpu-baseline", action="store_true")
     ap.add_argument("--experts", type=int, default=DSV3["E"],
                     help="expert count (smaller values give the small case used for ncu captures)")
+    ap.add_argument("--sweep", default="", help="comma list of dsv3,mixtral,qwen3,align,routing: print one line per point")
     args = ap.parse_args()
     args.warmup = max(args.warmup, 3) if args.impl == "b200" else args.warmup
+    if args.sweep:
+        run_sweep(args)
+        return
     if args.impl == "reference":
         run_reference(args)
         return
@@ -299,7 +418,7 @@ def main():
         "tflops": flops / (ms * 1e-3) / 1e12,
         "e2e": {"value": total_tokens / (e2e_ms * 1e-3), "unit": "tokens/s", "ms_per_step": e2e_ms,
                 "h2d_bytes_per_step": hx.numel() * 2 + hl.numel() * 4, "d2h_bytes_per_step": hout.numel() * 2},
-        "gpu_launches": 6 * args.steps if world == 1 else None,
+        "gpu_launches": 6 * args.steps,
         "clocks": clocks, "kernel_status": status,
     }
     if world == 1:
