@@ -122,7 +122,7 @@ __global__ void __launch_bounds__(256) simt_gemm_kernel(
   const bool row_ok = sid >= 0 && sid < numel;
   float rw = 1.0f;
   if (mul_weight && row_ok) rw = route_weight[sid];
-  if constexpr (MODE == MOE_MODE_W8A16) {
+  if (MODE == MOE_MODE_W8A16 || (MODE == MOE_MODE_HALF && w_scale != nullptr)) {
 #pragma unroll
     for (int i = 0; i < CPT; ++i) {
       const int n = n0 + tx + 16 * i;

@@ -91,7 +91,7 @@ constexpr size_t SMEM_BYTES = (size_t)STAGES * (A_STAGE_BYTES + B_STAGE_BYTES) +
 struct Params {
   const uint8_t* a_rows;    // GEMM1: activations [tokens, K] in token order (gathered by cp.async)
   const float* a_scales_t;  // [K/128, a_scale_ld]        (FP8)
-  const float* w_scale;     // [E, rows_w/128, K/128]     (FP8)
+  const float* w_scale;     // FP8: [E, rows_w/128, K/128]; half mode: optional per-row scale [E, rows_w]
   const int32_t* expert_ids;
   const int32_t* sorted_ids;
   const int32_t* num_post_pad;
@@ -519,6 +519,33 @@ tc_gemm_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant_
       }
 
       // ---------------------------------------------------------- tile epilogue
+      if constexpr (!FP8) {
+        if (P.w_scale != nullptr) {
+          // weight-only int8: weights were widened exactly to the activation dtype, the
+          // per-output-channel scale is applied here in fp32
+          const float* cs = P.w_scale + (int64_t)e * P.rows_w;
+          if constexpr (GEMM1) {
+            const int n0 = nt * 128 + 64 * h;
+#pragma unroll
+            for (int j4 = 0; j4 < 16; ++j4) {
+              const float4 sg = *reinterpret_cast<const float4*>(cs + n0 + 4 * j4);
+              const float4 su = *reinterpret_cast<const float4*>(cs + P.Nout + n0 + 4 * j4);
+              acc[4 * j4 + 0] *= sg.x; acc[4 * j4 + 1] *= sg.y; acc[4 * j4 + 2] *= sg.z; acc[4 * j4 + 3] *= sg.w;
+              acc[64 + 4 * j4 + 0] *= su.x; acc[64 + 4 * j4 + 1] *= su.y;
+              acc[64 + 4 * j4 + 2] *= su.z; acc[64 + 4 * j4 + 3] *= su.w;
+            }
+          } else {
+            const int n0 = nt * BN + 128 * h;
+#pragma unroll
+            for (int j4 = 0; j4 < 32; ++j4) {
+              if (n0 + 4 * j4 < P.Nout) {
+                const float4 sc = *reinterpret_cast<const float4*>(cs + n0 + 4 * j4);
+                acc[4 * j4 + 0] *= sc.x; acc[4 * j4 + 1] *= sc.y; acc[4 * j4 + 2] *= sc.z; acc[4 * j4 + 3] *= sc.w;
+              }
+            }
+          }
+        }
+      }
       float rw = 1.0f;
       if (P.mul_weight && row_ok) rw = P.route_weight[sid];
       if constexpr (GEMM1) {

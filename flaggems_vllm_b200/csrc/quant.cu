@@ -39,6 +39,21 @@ __device__ __forceinline__ void quant_group_128(const T* __restrict__ src, uint8
   if (lane == 0) *scale_out = s;
 }
 
+// int8 -> f16/bf16, exact; 16 elements per thread per step
+template <typename T>
+__global__ void __launch_bounds__(256) widen_int8_kernel(const int8_t* __restrict__ src, T* __restrict__ dst, int64_t n16) {
+  for (int64_t i = (int64_t)blockIdx.x * blockDim.x + threadIdx.x; i < n16; i += (int64_t)gridDim.x * blockDim.x) {
+    const uint4 raw = reinterpret_cast<const uint4*>(src)[i];
+    const int8_t* p = reinterpret_cast<const int8_t*>(&raw);
+    uint4 o[2];
+    T* q = reinterpret_cast<T*>(o);
+#pragma unroll
+    for (int j = 0; j < 16; ++j) q[j] = from_f32<T>((float)p[j]);
+    reinterpret_cast<uint4*>(dst)[2 * i] = o[0];
+    reinterpret_cast<uint4*>(dst)[2 * i + 1] = o[1];
+  }
+}
+
 template <typename T>
 __global__ void __launch_bounds__(kRowThreads) quant_rows_kernel(
     const T* __restrict__ x, int64_t rows, int64_t cols, uint8_t* __restrict__ q,
@@ -174,6 +189,25 @@ extern "C" int moe_per_token_group_quant_fp8(const void* x, int x_dtype, int64_t
     default: return fail(MOE_E_DTYPE, "quant_fp8: unsupported dtype %d", x_dtype);
   }
   return check_launch("per_token_group_quant_fp8");
+}
+
+extern "C" int moe_widen_int8(const void* src, void* dst, int dst_dtype, int64_t n, void* stream) {
+  using namespace moe;
+  if (n < 0) return fail(MOE_E_BADARG, "widen_int8: negative size");
+  if (n == 0) return 0;
+  if (!src || !dst) return fail(MOE_E_BADARG, "widen_int8: null pointer");
+  if (n % 16 != 0 || ((uintptr_t)src & 15) || ((uintptr_t)dst & 15))
+    return fail(MOE_E_SHAPE, "widen_int8: size and pointers must be multiples of 16");
+  cudaStream_t st = (cudaStream_t)stream;
+  const int64_t n16 = n / 16;
+  const int grid = grid_for((n16 + 255) / 256, 16);
+  if (dst_dtype == MOE_BF16)
+    widen_int8_kernel<__nv_bfloat16><<<grid, 256, 0, st>>>((const int8_t*)src, (__nv_bfloat16*)dst, n16);
+  else if (dst_dtype == MOE_F16)
+    widen_int8_kernel<__half><<<grid, 256, 0, st>>>((const int8_t*)src, (__half*)dst, n16);
+  else
+    return fail(MOE_E_DTYPE, "widen_int8: destination must be f16 or bf16");
+  return check_launch("widen_int8");
 }
 
 extern "C" int moe_sum(const void* in, void* out, int dtype, int64_t M, int topk, int64_t H,

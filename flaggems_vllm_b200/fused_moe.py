@@ -73,6 +73,13 @@ def _check_activation(activation, gemm1_alpha, gemm1_beta, gemm1_clamp_limit):
         f"Only 'silu' and 'swigluoai_uninterleave' activations are supported, got {activation!r}")
 
 
+def _widen_int8(w, dtype):
+    out = torch.empty(w.shape, dtype=dtype, device=w.device)
+    _lib.check(_lib.lib().moe_widen_int8(w.data_ptr(), out.data_ptr(), _lib.dtype_code(dtype), w.numel(),
+                                         _lib.stream_of(w)))
+    return out
+
+
 def quantize_rows(x, mark=None):
     """FP8 mode: e4m3 rows [M, H] plus transposed 1x128 scales [H/128, M]."""
     M, H = x.shape
@@ -280,6 +287,13 @@ def fused_experts_impl(
     if mode != _lib.MODE_HALF:
         s1 = w1_scale.to(torch.float32).contiguous()
         s2 = w2_scale.to(torch.float32).contiguous()
+
+    if (mode == _lib.MODE_W8A16 and not _force_generic()
+            and _tc_eligible(_lib.MODE_HALF, hidden_states.dtype, K, N // 2)):
+        # tensor-core route for weight-only int8: widen the weights exactly to the
+        # activation dtype, per-channel scales go to the GEMM epilogues
+        w1c, w2c = _widen_int8(w1c, hidden_states.dtype), _widen_int8(w2c, hidden_states.dtype)
+        mode = _lib.MODE_HALF
 
     out_hidden_states = hidden_states if inplace else torch.empty_like(hidden_states)
     for chunk in range((num_tokens // CHUNK_SIZE) + 1):

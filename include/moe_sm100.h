@@ -93,6 +93,15 @@ int moe_per_token_group_quant_fp8(const void* x, int x_dtype, int64_t rows, int6
                                   void* stream);
 
 /*
+ * Exact widening of int8 weights to f16/bf16 (n elements, n % 16 == 0).  The
+ * weight-only INT8 layer runs the tensor-core GEMMs on the widened copy and
+ * applies the per-channel scale in the GEMM epilogue; the reference instead
+ * multiplies the whole weight tensor by its scales in the activation dtype on
+ * every call (src/flaggems_vllm/ops/fused_moe.py:2493-2500).
+ */
+int moe_widen_int8(const void* src, void* dst, int dst_dtype, int64_t n, void* stream);
+
+/*
  * Expert grouped GEMM 1: act[p] = SiLU(x_t Wg^T) * (x_t Wu^T) for every sorted
  * row p, where t = sorted_ids[p] / topk is the token of that route.  The kernel
  * gathers the token rows itself; no sorted copy of the activations is needed.
@@ -101,7 +110,8 @@ int moe_per_token_group_quant_fp8(const void* x, int x_dtype, int64_t rows, int6
  *   a [num_tokens, H]        activations in token order (act dtype, or e4m3 in FP8 mode)
  *   a_scales_t [H/128, num_tokens]  1x128 activation scales, transposed (FP8 mode)
  *   w1 [E, 2I, H] contiguous (act dtype, e4m3 or int8), gate rows first
- *   w1_scale: FP8 [E, 2I/128, H/128]; W8A16 [E, 2I]; else NULL
+ *   w1_scale: FP8 [E, 2I/128, H/128]; W8A16 [E, 2I]; HALF: NULL, or [E, 2I]
+ *     per-output-channel scales applied in the epilogue (widened int8 weights)
  *   expert_ids [rows_cap / block_m], sorted_ids [rows_cap], num_post_pad[1] from the align step
  *   route_weight [num_tokens * topk]: when mul_weight != 0 gate and up are
  *     multiplied by route_weight[sorted_ids[p]] before the activation
@@ -123,7 +133,8 @@ int moe_gemm1(int mode, int act_dtype, const void* a, const float* a_scales_t, i
  * Stands in for fused_moe_kernel as called for the down projection
  * (src/flaggems_vllm/ops/fused_moe.py:1797-1985, call :2703-2728).
  *   act_sorted [rows_cap, I] (act dtype or e4m3 with act_scales_t [I/128, rows_cap])
- *   w2 [E, H, I] contiguous; w2_scale: FP8 [E, H/128, I/128]; W8A16 [E, H]
+ *   w2 [E, H, I] contiguous; w2_scale: FP8 [E, H/128, I/128]; W8A16 [E, H];
+ *     HALF: NULL or [E, H] per-output-channel scales
  *   y [numel, H] in act dtype, row = flat route index (token * topk + slot)
  */
 int moe_gemm2(int mode, int act_dtype, const void* act_sorted, const float* act_scales_t,

@@ -80,11 +80,12 @@ def test_golden_w8a16(name):
     g = load_golden(name)
     x, w1, w2, s1, s2 = (g[n].to(DEV) for n in ("x", "w1", "w2", "w1_scale", "w2_scale"))
     tw, ti = g["topk_weights"].to(x.dtype).to(DEV), g["topk_ids"].to(DEV)
-    out = fg.ops_experts_impl(x, w1, w2, tw, ti, use_int8_w8a16=True, per_channel_quant=True, w1_scale=s1,
-                              w2_scale=s2)
-    _assert_parity(out, O.fused_moe_w8a16_oracle(x, w1, w2, s1, s2, tw, ti))
-    ref = g["out"]
-    torch.testing.assert_close(out.float().cpu(), ref, rtol=2e-1, atol=max(5e-2, ref.abs().max().item() * 2e-2))
+    run = lambda: fg.ops_experts_impl(x, w1, w2, tw, ti, use_int8_w8a16=True, per_channel_quant=True, w1_scale=s1,
+                                      w2_scale=s2)
+    for name_, out in _both_kernels(run).items():
+        _assert_parity(out, O.fused_moe_w8a16_oracle(x, w1, w2, s1, s2, tw, ti), name_)
+        ref = g["out"]
+        torch.testing.assert_close(out.float().cpu(), ref, rtol=2e-1, atol=max(5e-2, ref.abs().max().item() * 2e-2))
 
 
 # ---------------------------------------------------------------- reference test shapes
@@ -132,9 +133,11 @@ def test_w8a16_shapes(cfg):
     w1, s1 = T.make_int8_channel_weights(E, 2 * I, H, DEV, seed=1, std=H**-0.5)
     w2, s2 = T.make_int8_channel_weights(E, H, I, DEV, seed=2, std=I**-0.5)
     tw, ti = _route(M, E, k, torch.bfloat16)
-    out = fg.fused_experts_impl(x, w1, w2, tw, ti, use_int8_w8a16=True, per_channel_quant=True, w1_scale=s1,
-                                w2_scale=s2)
-    _assert_parity(out, O.fused_moe_w8a16_oracle(x, w1, w2, s1, s2, tw, ti))
+    ref = O.fused_moe_w8a16_oracle(x, w1, w2, s1, s2, tw, ti)
+    run = lambda: fg.fused_experts_impl(x, w1, w2, tw, ti, use_int8_w8a16=True, per_channel_quant=True,
+                                        w1_scale=s1, w2_scale=s2)
+    for name, out in _both_kernels(run).items():
+        _assert_parity(out, ref, name)
 
 
 # ---------------------------------------------------------------- benchmark configurations
