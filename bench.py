@@ -188,6 +188,23 @@ def run_sweep(args):
         ts.sort()
         return ts[len(ts) // 2]
 
+    def graph_ms(fn, iters=20):
+        """Device time of one step replayed from a CUDA graph (no launch gaps, L2 warm)."""
+        fn()
+        torch.cuda.synchronize()
+        g = torch.cuda.CUDAGraph()
+        with torch.cuda.graph(g):
+            fn()
+        g.replay()
+        torch.cuda.synchronize()
+        a, b = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        a.record()
+        for _ in range(iters):
+            g.replay()
+        b.record()
+        torch.cuda.synchronize()
+        return a.elapsed_time(b) / iters
+
     def report(name, M, ms, flops, nbytes, peak_tf, extra=None):
         t_c, t_m = flops / (peak_tf * 1e12), nbytes / (peaks["hbm_gbs"] * 1e9)
         bound = "tensor" if t_c > t_m else "hbm"
@@ -217,8 +234,10 @@ def run_sweep(args):
             e_act = int(torch.unique(ti).numel())
             nbytes = e_act * (3 * H * I + (2 * I // 128) * (H // 128) * 4 + (H // 128) * (I // 128) * 4) \
                 + M * H * 2 * 2 + M * E * 4 + k * 8 * M
-            report("dsv3_fp8", M, timeit(step, 10), 6.0 * M * k * H * I, nbytes, 2 * peaks["bf16_tflops"],
-                   {"distinct_experts": e_act})
+            extra = {"distinct_experts": e_act}
+            if M <= 128:
+                extra["cuda_graph_replay_ms"] = graph_ms(step)
+            report("dsv3_fp8", M, timeit(step, 10), 6.0 * M * k * H * I, nbytes, 2 * peaks["bf16_tflops"], extra)
         del w1, w2, s1, s2
     if "mixtral" in which:
         E, H, I, k = 8, 4096, 14336, 2
