@@ -49,9 +49,15 @@ namespace tc {
 
 constexpr int BM = 128;
 constexpr int BN = 256;
-constexpr int STAGES = 4;
 constexpr int A_STAGE_BYTES = BM * 128;
-constexpr int B_STAGE_BYTES = BN * 128;
+constexpr int B_STAGE_BYTES = BN * 128;       // whole B tile (single-CTA kernel)
+constexpr int B_HALF_BYTES = B_STAGE_BYTES / 2;  // what each CTA of a pair holds
+constexpr int MAX_STAGES = 6;
+// single CTA: 4 stages of A + B; CTA pair (cta_group::2): 6 stages of A + half of B
+template <bool PAIR> struct Cfg {
+  static constexpr int STAGES = PAIR ? 6 : 4;
+  static constexpr int STAGE_BYTES = A_STAGE_BYTES + (PAIR ? B_HALF_BYTES : B_STAGE_BYTES);
+};
 constexpr int B_BOX_ROWS = 64;
 constexpr int THREADS = 384;
 constexpr int EPI_THREADS = 256;
@@ -71,8 +77,9 @@ static_assert(THREADS * LAUNCH_REGS <= 65536, "CTA does not fit the register fil
 constexpr unsigned long long WAIT_LIMIT_NS = 2000000000ull;  // 2 s
 
 struct SmemAux {
-  uint64_t full[STAGES];
-  uint64_t empty[STAGES];
+  uint64_t full[MAX_STAGES];       // this CTA's operands (and scales) of the stage have landed
+  uint64_t empty[MAX_STAGES];      // the tensor core has finished reading the stage
+  uint64_t peer_full[MAX_STAGES];  // pair leader only: the partner CTA's stage has landed
   uint64_t tmem_full[2];
   uint64_t tmem_empty[2];
   uint64_t xch_bar;
@@ -86,7 +93,7 @@ struct SmemAux {
   float sc_a[SCALE_SLOTS][BM];  // activation scale of each tile row
   float sc_w[SCALE_SLOTS][4];   // weight scales of the two column halves
 };
-constexpr size_t SMEM_BYTES = (size_t)STAGES * (A_STAGE_BYTES + B_STAGE_BYTES) + sizeof(SmemAux) + 1024;
+template <bool PAIR> constexpr size_t smem_bytes() { return (size_t)Cfg<PAIR>::STAGES * Cfg<PAIR>::STAGE_BYTES + sizeof(SmemAux) + 1024; }
 
 struct Params {
   const uint8_t* a_rows;    // GEMM1: activations [tokens, K] in token order (gathered by cp.async)
@@ -136,17 +143,48 @@ __device__ __forceinline__ bool mbar_try(uint64_t* bar, uint32_t parity) {
       : "memory");
   return ok != 0;
 }
+__device__ __forceinline__ uint32_t cluster_ctarank() {
+  uint32_t r;
+  asm volatile("mov.u32 %0, %%cluster_ctarank;" : "=r"(r));
+  return r;
+}
+// Arrive on the barrier at the same shared-memory offset in CTA `rank` of the cluster.
+__device__ __forceinline__ void mbar_arrive_remote(uint64_t* bar, uint32_t rank) {
+  asm volatile(
+      "{\n\t.reg .b32 ra;\n\t"
+      "mapa.shared::cluster.u32 ra, %0, %1;\n\t"
+      "mbarrier.arrive.release.cluster.shared::cluster.b64 _, [ra];\n\t}"
+      ::"r"(smem_u32(bar)), "r"(rank)
+      : "memory");
+}
+__device__ __forceinline__ bool mbar_try_cluster(uint64_t* bar, uint32_t parity) {
+  uint32_t ok;
+  asm volatile(
+      "{\n\t.reg .pred p;\n\t"
+      "mbarrier.try_wait.parity.acquire.cluster.shared::cta.b64 p, [%1], %2;\n\t"
+      "selp.u32 %0, 1, 0, p;\n\t}"
+      : "=r"(ok)
+      : "r"(smem_u32(bar)), "r"(parity)
+      : "memory");
+  return ok != 0;
+}
+__device__ __forceinline__ void cluster_sync_all() {
+  asm volatile("barrier.cluster.arrive.release.aligned;\n\tbarrier.cluster.wait.acquire.aligned;" ::: "memory");
+}
 __device__ __forceinline__ unsigned long long now_ns() {
   unsigned long long t;
   asm volatile("mov.u64 %0, %globaltimer;" : "=l"(t));
   return t;
 }
 // Bounded wait: false when the limit ran out (status word is set).
+// CLUSTER: the barrier is also arrived on by the partner CTA (acquire at cluster scope).
+template <bool CLUSTER = false>
 __device__ __forceinline__ bool mbar_wait(uint64_t* bar, uint32_t parity, int32_t* status) {
-  if (mbar_try(bar, parity)) return true;
+  auto probe = [&]() { return CLUSTER ? mbar_try_cluster(bar, parity) : mbar_try(bar, parity); };
+  if (probe()) return true;
   const unsigned long long t0 = now_ns();
   uint32_t spins = 0;
-  while (!mbar_try(bar, parity)) {
+  while (!probe()) {
     if ((++spins & 0x3FF) == 0 && now_ns() - t0 > WAIT_LIMIT_NS) {
       set_status(status, MOE_ST_WAIT_TIMEOUT);
       return false;
@@ -165,6 +203,30 @@ __device__ __forceinline__ void tc_fence_after() { asm volatile("tcgen05.fence::
 __device__ __forceinline__ void tc_commit(uint64_t* bar) {
   asm volatile("tcgen05.commit.cta_group::1.mbarrier::arrive::one.shared::cluster.b64 [%0];" ::"r"(smem_u32(bar))
                : "memory");
+}
+// cta_group::2: completion is signalled on the barrier at this offset in BOTH CTAs of the pair
+__device__ __forceinline__ void tc_commit_pair(uint64_t* bar) {
+  asm volatile(
+      "tcgen05.commit.cta_group::2.mbarrier::arrive::one.shared::cluster.multicast::cluster.b64 [%0], %1;"
+      ::"r"(smem_u32(bar)), "h"((uint16_t)3)
+      : "memory");
+}
+// One instruction for the pair: M = 256 (128 rows from each CTA), N = 256 (128 B rows from each CTA)
+template <bool FP8>
+__device__ __forceinline__ void tc_mma_pair(uint32_t tmem_d, uint64_t adesc, uint64_t bdesc, uint32_t idesc, uint32_t acc) {
+  if constexpr (FP8) {
+    asm volatile(
+        "{\n\t.reg .pred p;\n\tsetp.ne.b32 p, %4, 0;\n\t"
+        "tcgen05.mma.cta_group::2.kind::f8f6f4 [%0], %1, %2, %3, p;\n\t}"
+        ::"r"(tmem_d), "l"(adesc), "l"(bdesc), "r"(idesc), "r"(acc)
+        : "memory");
+  } else {
+    asm volatile(
+        "{\n\t.reg .pred p;\n\tsetp.ne.b32 p, %4, 0;\n\t"
+        "tcgen05.mma.cta_group::2.kind::f16 [%0], %1, %2, %3, p;\n\t}"
+        ::"r"(tmem_d), "l"(adesc), "l"(bdesc), "r"(idesc), "r"(acc)
+        : "memory");
+  }
 }
 template <bool FP8>
 __device__ __forceinline__ void tc_mma(uint32_t tmem_d, uint64_t adesc, uint64_t bdesc, uint32_t idesc, uint32_t acc) {
@@ -230,11 +292,12 @@ __device__ __forceinline__ uint64_t make_smem_desc(uint32_t saddr) {
 // Instruction descriptor: fp32 accumulator (bits 4-5 = 1), A/B element format
 // (bits 7-9 / 10-12: e4m3 = 0 for kind::f8f6f4; f16 = 0, bf16 = 1 for
 // kind::f16), both operands K-major, N >> 3 at bit 17, M >> 4 at bit 24.
-template <bool FP8, typename AT>
+template <bool FP8, typename AT, bool PAIR>
 struct IDesc {
   static constexpr uint32_t fmt = (!FP8 && std::is_same<AT, __nv_bfloat16>::value) ? 1u : 0u;
+  static constexpr uint32_t m = PAIR ? 2 * BM : BM;  // a pair multiplies 256 rows per instruction
   static constexpr uint32_t value =
-      (1u << 4) | (fmt << 7) | (fmt << 10) | ((uint32_t)(BN >> 3) << 17) | ((uint32_t)(BM >> 4) << 24);
+      (1u << 4) | (fmt << 7) | (fmt << 10) | ((uint32_t)(BN >> 3) << 17) | ((uint32_t)(m >> 4) << 24);
 };
 
 // weight row (inside the expert) of the first row of B box `c` of column tile `nt`
@@ -267,40 +330,70 @@ __device__ __forceinline__ float round_act(float v) {
   return ToF32<AT>::get(from_f32<AT>(v));
 }
 
-template <bool FP8, typename AT, bool GEMM1>
+// PAIR = true: two CTAs of a cluster work as one cta_group::2 unit on a 256-row
+// align block.  Each CTA holds its own 128 rows of A and ONE HALF of the B tile;
+// the leader CTA (cluster rank 0) issues a single M=256 instruction per K step
+// that reads both CTAs' shared memory and writes each CTA's own TMEM.  Every
+// weight tile therefore crosses L2 -> shared memory once per 256 rows instead
+// of once per 128.  Nothing is multicast: every TMA load and cp.async lands in
+// the issuing CTA and signals a local barrier; the partner CTA forwards "stage
+// landed" to the leader with a remote mbarrier arrive, and the leader's
+// tcgen05.commit signals the stage-free / accumulator-ready barriers of both
+// CTAs.
+template <bool FP8, typename AT, bool GEMM1, bool PAIR>
 __global__ void __launch_bounds__(THREADS, 1)
 tc_gemm_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant__ CUtensorMap map_b, const Params P) {
+  constexpr int STAGES = Cfg<PAIR>::STAGES;
+  constexpr int B_LOCAL_BYTES = PAIR ? B_HALF_BYTES : B_STAGE_BYTES;
   extern __shared__ uint8_t smem_raw[];
   uint8_t* smem = reinterpret_cast<uint8_t*>(((uintptr_t)smem_raw + 1023) & ~(uintptr_t)1023);
   uint8_t* sA = smem;
   uint8_t* sB = smem + (size_t)STAGES * A_STAGE_BYTES;
-  SmemAux* aux = reinterpret_cast<SmemAux*>(smem + (size_t)STAGES * (A_STAGE_BYTES + B_STAGE_BYTES));
+  SmemAux* aux = reinterpret_cast<SmemAux*>(smem + (size_t)STAGES * Cfg<PAIR>::STAGE_BYTES);
 
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
   constexpr int KBE = FP8 ? 128 : 64;  // elements of K per stage
   const int KB = (P.K + KBE - 1) / KBE;
   const int npp = min((int64_t)P.num_post_pad[0], P.rows_cap);
-  const int total_tiles = ((npp + BM - 1) / BM) * P.n_tiles;
+  // work unit: one CTA and a 128-row align block, or a CTA pair and a 256-row align block
+  constexpr int UNIT = PAIR ? 2 : 1;
+  const int cr = PAIR ? (int)cluster_ctarank() : 0;  // rank inside the pair; 0 leads
+  const int tile0 = blockIdx.x / UNIT, tile_step = gridDim.x / UNIT;
+  const int total_tiles = ((npp + UNIT * BM - 1) / (UNIT * BM)) * P.n_tiles;
+  // tile -> expert_ids index (blk), this CTA's 128-row block (mb), column tile (nt)
+#define MOE_TILE_COORDS(tile)                      \
+  const int blk = (tile) / P.n_tiles;              \
+  [[maybe_unused]] const int nt = (tile) % P.n_tiles; \
+  [[maybe_unused]] const int mb = UNIT * blk + cr; \
+  const int e = P.expert_ids[blk];
 
   if (threadIdx.x == 0) {
     for (int s = 0; s < STAGES; ++s) {
       mbar_init(&aux->full[s], GEMM1 ? 1 + GATHER_THREADS : (FP8 ? 1 + SCALE_THREADS : 1));
       mbar_init(&aux->empty[s], 1);
+      mbar_init(&aux->peer_full[s], 1);
     }
     for (int a = 0; a < 2; ++a) {
       mbar_init(&aux->tmem_full[a], 1);
-      mbar_init(&aux->tmem_empty[a], EPI_THREADS / 32);
+      mbar_init(&aux->tmem_empty[a], UNIT * (EPI_THREADS / 32));  // the leader also collects the partner's warps
     }
     mbar_init(&aux->xch_bar, EPI_THREADS);
     asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
   }
   if (warp == 2) {
-    asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(smem_u32(&aux->tmem_base)),
-                 "r"(512));
-    asm volatile("tcgen05.relinquish_alloc_permit.cta_group::1.sync.aligned;" ::);
+    if constexpr (PAIR) {
+      asm volatile("tcgen05.alloc.cta_group::2.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(smem_u32(&aux->tmem_base)),
+                   "r"(512));
+      asm volatile("tcgen05.relinquish_alloc_permit.cta_group::2.sync.aligned;" ::);
+    } else {
+      asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(smem_u32(&aux->tmem_base)),
+                   "r"(512));
+      asm volatile("tcgen05.relinquish_alloc_permit.cta_group::1.sync.aligned;" ::);
+    }
   }
   tc_fence_before();
-  __syncthreads();
+  if constexpr (PAIR) cluster_sync_all();  // both CTAs' barriers exist before anyone signals across
+  else __syncthreads();
   tc_fence_after();
   const uint32_t tmem_base = aux->tmem_base;
 
@@ -312,9 +405,8 @@ tc_gemm_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant_
       asm volatile("prefetch.tensormap [%0];" ::"l"(&map_b) : "memory");
       uint32_t it = 0;
       bool alive = true;
-      for (int tile = blockIdx.x; tile < total_tiles && alive; tile += gridDim.x) {
-        const int mb = tile / P.n_tiles, nt = tile % P.n_tiles;
-        const int e = P.expert_ids[mb];
+      for (int tile = tile0; tile < total_tiles && alive; tile += tile_step) {
+        MOE_TILE_COORDS(tile)
         if (e < 0 || e >= P.E) continue;
         [[maybe_unused]] const int row0 = mb * BM;
         const int wrow0 = e * P.rows_w;
@@ -323,50 +415,69 @@ tc_gemm_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant_
           const uint32_t ph = (it / STAGES) & 1;
           if (!mbar_wait(&aux->empty[s], ph ^ 1, P.status)) { alive = false; break; }
           if constexpr (GEMM1) {
-            mbar_expect_tx(&aux->full[s], B_STAGE_BYTES);  // A rows arrive by cp.async (warps 2-3)
+            mbar_expect_tx(&aux->full[s], B_LOCAL_BYTES);  // A rows arrive by cp.async (warps 2-3)
           } else {
-            mbar_expect_tx(&aux->full[s], A_STAGE_BYTES + B_STAGE_BYTES);
+            mbar_expect_tx(&aux->full[s], A_STAGE_BYTES + B_LOCAL_BYTES);
             tma_load_2d(&map_a, &aux->full[s], sA + (size_t)s * A_STAGE_BYTES, kb * KBE, row0);
           }
+          // 64-row boxes of the B tile: all four, or (pair) the two of this CTA's column half
+          constexpr int NBOX = PAIR ? 2 : 4;
 #pragma unroll
-          for (int c = 0; c < 4; ++c)
-            tma_load_2d(&map_b, &aux->full[s], sB + (size_t)s * B_STAGE_BYTES + c * (B_BOX_ROWS * 128), kb * KBE,
-                        wrow0 + box_row<GEMM1>(nt, c, P.Nout));
+          for (int c = 0; c < NBOX; ++c)
+            tma_load_2d(&map_b, &aux->full[s], sB + (size_t)s * B_LOCAL_BYTES + c * (B_BOX_ROWS * 128), kb * KBE,
+                        wrow0 + box_row<GEMM1>(nt, NBOX * cr + c, P.Nout));
         }
       }
-    } else if (warp == 1 && lane == 0) {
-      // ------------------------------------------------------------ MMA issuer
-      constexpr uint32_t idesc = IDesc<FP8, AT>::value;
+    } else if (warp == 1 && lane == 0 && cr == 0) {
+      // ------------------------------------------------------------ MMA issuer (pair: leader only)
+      constexpr uint32_t idesc = IDesc<FP8, AT, PAIR>::value;
       uint32_t it = 0, acc_it = 0;
       bool alive = true;
-      for (int tile = blockIdx.x; tile < total_tiles && alive; tile += gridDim.x) {
-        const int mb = tile / P.n_tiles;
-        const int e = P.expert_ids[mb];
+      for (int tile = tile0; tile < total_tiles && alive; tile += tile_step) {
+        MOE_TILE_COORDS(tile)
         if (e < 0 || e >= P.E) continue;
         for (int kb = 0; kb < KB; ++kb, ++it) {
           const uint32_t a = acc_it & 1;
           if (FP8 || kb == 0) {
-            if (!mbar_wait(&aux->tmem_empty[a], ((acc_it >> 1) & 1) ^ 1, P.status)) { alive = false; break; }
+            if (!mbar_wait<PAIR>(&aux->tmem_empty[a], ((acc_it >> 1) & 1) ^ 1, P.status)) { alive = false; break; }
             tc_fence_after();
           }
           const int s = it % STAGES;
           if (!mbar_wait(&aux->full[s], (it / STAGES) & 1, P.status)) { alive = false; break; }
+          if constexpr (PAIR) {
+            if (!mbar_wait<true>(&aux->peer_full[s], (it / STAGES) & 1, P.status)) { alive = false; break; }
+          }
           if constexpr (GEMM1) asm volatile("fence.proxy.async.shared::cta;" ::: "memory");  // cp.async writes -> tensor core reads
           tc_fence_after();
           const uint64_t adesc = make_smem_desc(smem_u32(sA + (size_t)s * A_STAGE_BYTES));
-          const uint64_t bdesc = make_smem_desc(smem_u32(sB + (size_t)s * B_STAGE_BYTES));
+          const uint64_t bdesc = make_smem_desc(smem_u32(sB + (size_t)s * B_LOCAL_BYTES));
           const uint32_t d = tmem_base + a * BN;
 #pragma unroll
           for (int k4 = 0; k4 < 4; ++k4) {
             // 32 bytes of K per instruction: start address advances by 32 B >> 4
             const uint32_t accum = FP8 ? (k4 > 0) : (kb > 0 || k4 > 0);
-            tc_mma<FP8>(d, adesc + (uint64_t)(k4 * 2), bdesc + (uint64_t)(k4 * 2), idesc, accum);
+            if constexpr (PAIR) tc_mma_pair<FP8>(d, adesc + (uint64_t)(k4 * 2), bdesc + (uint64_t)(k4 * 2), idesc, accum);
+            else tc_mma<FP8>(d, adesc + (uint64_t)(k4 * 2), bdesc + (uint64_t)(k4 * 2), idesc, accum);
           }
-          tc_commit(&aux->empty[s]);
+          if constexpr (PAIR) tc_commit_pair(&aux->empty[s]); else tc_commit(&aux->empty[s]);
           if (FP8 || kb == KB - 1) {
-            tc_commit(&aux->tmem_full[a]);
+            if constexpr (PAIR) tc_commit_pair(&aux->tmem_full[a]); else tc_commit(&aux->tmem_full[a]);
             ++acc_it;
           }
+        }
+      }
+    } else if (PAIR && warp == 1 && lane == 0 && cr == 1) {
+      // ------------------------------------------------------------ partner CTA: tell the leader a stage has landed
+      uint32_t it = 0;
+      bool alive = true;
+      for (int tile = tile0; tile < total_tiles && alive; tile += tile_step) {
+        MOE_TILE_COORDS(tile)
+        if (e < 0 || e >= P.E) continue;
+        for (int kb = 0; kb < KB; ++kb, ++it) {
+          const int s = it % STAGES;
+          if (!mbar_wait(&aux->full[s], (it / STAGES) & 1, P.status)) { alive = false; break; }
+          asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
+          mbar_arrive_remote(&aux->peer_full[s], 0);
         }
       }
     } else if (GEMM1 && warp >= 2) {
@@ -375,9 +486,8 @@ tc_gemm_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant_
       const int64_t pitch = (int64_t)P.K * (FP8 ? 1 : 2);
       uint32_t it = 0;
       bool alive = true;
-      for (int tile = blockIdx.x; tile < total_tiles && alive; tile += gridDim.x) {
-        const int mb = tile / P.n_tiles;
-        const int e = P.expert_ids[mb];
+      for (int tile = tile0; tile < total_tiles && alive; tile += tile_step) {
+        MOE_TILE_COORDS(tile)
         if (e < 0 || e >= P.E) continue;
         const uint8_t* src[2];
         [[maybe_unused]] const float* as_src[2];
@@ -386,7 +496,6 @@ tc_gemm_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant_
         // weight-scale row of this thread (g = 0: gate rows nt*128.., g = 1: up rows I + nt*128..)
         [[maybe_unused]] const float* ws_src = nullptr;
         if constexpr (FP8) {
-          const int nt = tile % P.n_tiles;
           const int sblk_per_e = (P.rows_w + 127) / 128;
           ws_src = P.w_scale + ((int64_t)e * sblk_per_e + (g == 1 ? (P.Nout >> 7) + nt : nt)) * KB;
         }
@@ -431,9 +540,8 @@ tc_gemm_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant_
       uint32_t it = 0;
       bool alive = true;
       const int sblk_per_e = (P.rows_w + 127) / 128;
-      for (int tile = blockIdx.x; tile < total_tiles && alive; tile += gridDim.x) {
-        const int mb = tile / P.n_tiles, nt = tile % P.n_tiles;
-        const int e = P.expert_ids[mb];
+      for (int tile = tile0; tile < total_tiles && alive; tile += tile_step) {
+        MOE_TILE_COORDS(tile)
         if (e < 0 || e >= P.E) continue;
         const float* as_row = P.a_scales_t + (int64_t)mb * BM + 4 * lane;
         const float* ws_src = P.w_scale + ((int64_t)e * sblk_per_e + min(2 * nt + lane, sblk_per_e - 1)) * KB;
@@ -456,9 +564,17 @@ tc_gemm_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant_
     const uint32_t t_lane = tmem_base + ((uint32_t)((warp & 3) << 5) << 16) + (uint32_t)(h * 128);
     uint32_t acc_it = 0, tile_it = 0;
     bool alive = true;
-    for (int tile = blockIdx.x; tile < total_tiles && alive; tile += gridDim.x) {
-      const int mb = tile / P.n_tiles, nt = tile % P.n_tiles;
-      const int e = P.expert_ids[mb];
+    // releasing an accumulator: the pair's leader collects the arrivals of both CTAs
+    auto release_acc = [&](uint32_t a) {
+      tc_fence_before();
+      __syncwarp();
+      if (lane == 0) {
+        if (PAIR && cr == 1) mbar_arrive_remote(&aux->tmem_empty[a], 0);
+        else mbar_arrive(&aux->tmem_empty[a]);
+      }
+    };
+    for (int tile = tile0; tile < total_tiles && alive; tile += tile_step) {
+      MOE_TILE_COORDS(tile)
       if (e < 0 || e >= P.E) continue;
       const int64_t p = (int64_t)mb * BM + row;
       int64_t sid = P.numel;
@@ -483,9 +599,7 @@ tc_gemm_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant_
 #pragma unroll
           for (int i = 0; i < 32; ++i) acc[32 + i] = fmaf(__uint_as_float(rb[i]), s_lo, acc[32 + i]);
           tmem_ld64_sync(t0 + 64, ra, rb);
-          tc_fence_before();
-          __syncwarp();
-          if (lane == 0) mbar_arrive(&aux->tmem_empty[a]);
+          release_acc(a);
 #pragma unroll
           for (int i = 0; i < 32; ++i) acc[64 + i] = fmaf(__uint_as_float(ra[i]), s_hi, acc[64 + i]);
 #pragma unroll
@@ -512,9 +626,7 @@ tc_gemm_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant_
         uint32_t* r = reinterpret_cast<uint32_t*>(acc);
         tmem_ld64_sync(t0, r, r + 32);
         tmem_ld64_sync(t0 + 64, r + 64, r + 96);
-        tc_fence_before();
-        __syncwarp();
-        if (lane == 0) mbar_arrive(&aux->tmem_empty[a]);
+        release_acc(a);
         ++acc_it;
       }
 
@@ -609,11 +721,16 @@ tc_gemm_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant_
 
   // -------------------------------------------------------------------- teardown
   tc_fence_before();
-  __syncthreads();
+  if constexpr (PAIR) cluster_sync_all();  // no CTA leaves while its partner may still signal its barriers
+  else __syncthreads();
   if (warp == 2) {
     tc_fence_after();
-    asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" ::"r"(tmem_base), "r"(512));
+    if constexpr (PAIR)
+      asm volatile("tcgen05.dealloc.cta_group::2.sync.aligned.b32 %0, %1;" ::"r"(tmem_base), "r"(512));
+    else
+      asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" ::"r"(tmem_base), "r"(512));
   }
+#undef MOE_TILE_COORDS
 }
 
 // ------------------------------------------------------------------ host side
@@ -654,9 +771,10 @@ static int make_map(CUtensorMap* m, const void* base, CUtensorMapDataType dt, in
   return 0;
 }
 
-template <bool FP8, typename AT, bool GEMM1>
+template <bool FP8, typename AT, bool GEMM1, bool PAIR>
 static int launch(const CUtensorMap& ma, const CUtensorMap& mb, const Params& P, int grid, cudaStream_t st) {
-  auto kern = tc_gemm_kernel<FP8, AT, GEMM1>;
+  auto kern = tc_gemm_kernel<FP8, AT, GEMM1, PAIR>;
+  constexpr size_t smem = smem_bytes<PAIR>();
   cudaFuncAttributes fa;
   cudaError_t ce = cudaFuncGetAttributes(&fa, kern);
   if (ce != cudaSuccess) return fail((int)ce, "tensor-core GEMM: cudaFuncGetAttributes: %s", cudaGetErrorString(ce));
@@ -664,9 +782,22 @@ static int launch(const CUtensorMap& ma, const CUtensorMap& mb, const Params& P,
   if ((THREADS - EPI_THREADS) * PRODUCER_REGS + EPI_THREADS * CONSUMER_REGS > THREADS * fa.numRegs)
     return fail(MOE_E_DRIVER, "tensor-core GEMM: kernel was built with %d registers per thread, %d needed",
                 fa.numRegs, LAUNCH_REGS);
-  ce = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)SMEM_BYTES);
+  ce = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
   if (ce != cudaSuccess) return fail((int)ce, "tensor-core GEMM: shared memory attribute: %s", cudaGetErrorString(ce));
-  kern<<<grid, THREADS, SMEM_BYTES, st>>>(ma, mb, P);
+  cudaLaunchConfig_t cfg = {};
+  cfg.gridDim = dim3((unsigned)grid);
+  cfg.blockDim = dim3(THREADS);
+  cfg.dynamicSmemBytes = smem;
+  cfg.stream = st;
+  cudaLaunchAttribute attr[1];
+  attr[0].id = cudaLaunchAttributeClusterDimension;
+  attr[0].val.clusterDim.x = PAIR ? 2 : 1;
+  attr[0].val.clusterDim.y = 1;
+  attr[0].val.clusterDim.z = 1;
+  cfg.attrs = attr;
+  cfg.numAttrs = 1;
+  ce = cudaLaunchKernelEx(&cfg, kern, ma, mb, P);
+  if (ce != cudaSuccess) return fail((int)ce, "tensor-core GEMM launch: %s", cudaGetErrorString(ce));
   return check_launch(GEMM1 ? "gemm1 (tcgen05)" : "gemm2 (tcgen05)");
 }
 
@@ -677,15 +808,18 @@ static int launch(const CUtensorMap& ma, const CUtensorMap& mb, const Params& P,
 int tc_gemm(bool gemm1, int mode, int act_dtype, const void* a, const float* a_scales_t, const void* w,
             const float* w_scale, const int32_t* expert_ids, const int32_t* sorted_ids, const int32_t* npp,
             const float* route_weight, int mul_weight, int64_t numel, int64_t rows_cap, int64_t a_tokens, int topk,
-            int block_m, int E, int K, int Nout, void* out, float* out_scales_t, int32_t* status, cudaStream_t st) {
+            int block_m, int E, int K, int Nout, void* out, float* out_scales_t, int32_t* status, cudaStream_t st,
+            bool pair) {
   using namespace tc;
   const bool fp8 = mode == MOE_MODE_FP8_BLOCK;
   if (mode != MOE_MODE_FP8_BLOCK && mode != MOE_MODE_HALF)
     return fail(MOE_E_SHAPE, "tensor-core GEMM: mode %d is served by the generic kernel", mode);
   if (act_dtype != MOE_BF16 && act_dtype != MOE_F16)
     return fail(MOE_E_DTYPE, "tensor-core GEMM: activations must be f16 or bf16");
-  if (block_m != BM) return fail(MOE_E_SHAPE, "tensor-core GEMM: align block must be 128");
-  if (rows_cap % BM != 0 || rows_cap <= 0) return fail(MOE_E_SHAPE, "tensor-core GEMM: row capacity must be a positive multiple of 128");
+  const int unit_rows = pair ? 2 * BM : BM;
+  if (block_m != unit_rows) return fail(MOE_E_SHAPE, "tensor-core GEMM: align block must be %d", unit_rows);
+  if (rows_cap % unit_rows != 0 || rows_cap <= 0)
+    return fail(MOE_E_SHAPE, "tensor-core GEMM: row capacity must be a positive multiple of %d", unit_rows);
   const int kbe = fp8 ? 128 : 64;
   if (K % kbe != 0) return fail(MOE_E_SHAPE, "tensor-core GEMM: K must be a multiple of %d", kbe);
   if (gemm1 && Nout % 128 != 0) return fail(MOE_E_SHAPE, "tensor-core GEMM1: intermediate size must be a multiple of 128");
@@ -721,13 +855,16 @@ int tc_gemm(bool gemm1, int mode, int act_dtype, const void* a, const float* a_s
   int dev = 0, sms = 148;
   cudaGetDevice(&dev);
   cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, dev);
-  const int64_t cap_tiles = (rows_cap / BM) * (int64_t)P.n_tiles;
-  const int grid = (int)(cap_tiles < sms ? cap_tiles : sms);
+  const int64_t cap_tiles = (rows_cap / unit_rows) * (int64_t)P.n_tiles;
+  const int units = pair ? sms / 2 : sms;  // work units resident at once: CTAs, or CTA pairs
+  const int grid = (int)(cap_tiles < units ? cap_tiles : units) * (pair ? 2 : 1);
 
-#define MOE_TC_LAUNCH(F, T) (gemm1 ? launch<F, T, true>(ma, mb, P, grid, st) : launch<F, T, false>(ma, mb, P, grid, st))
+#define MOE_TC_LAUNCH2(F, T, G) (pair ? launch<F, T, G, true>(ma, mb, P, grid, st) : launch<F, T, G, false>(ma, mb, P, grid, st))
+#define MOE_TC_LAUNCH(F, T) (gemm1 ? MOE_TC_LAUNCH2(F, T, true) : MOE_TC_LAUNCH2(F, T, false))
   if (fp8) return act_dtype == MOE_BF16 ? MOE_TC_LAUNCH(true, __nv_bfloat16) : MOE_TC_LAUNCH(true, __half);
   return act_dtype == MOE_BF16 ? MOE_TC_LAUNCH(false, __nv_bfloat16) : MOE_TC_LAUNCH(false, __half);
 #undef MOE_TC_LAUNCH
+#undef MOE_TC_LAUNCH2
 }
 
 }  // namespace moe

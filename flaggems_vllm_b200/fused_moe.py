@@ -31,7 +31,10 @@ logger = logging.getLogger(__name__)
 
 CHUNK_SIZE = 32 * 1024
 TC_BLOCK_M = 128
+TC_PAIR_BLOCK_M = 256
 GENERIC_BLOCK_M = 16
+# kernel selector passed to moe_gemm1 / moe_gemm2
+KERNEL_GENERIC, KERNEL_TC, KERNEL_TC_PAIR = 0, 1, 2
 
 _SUPPORTED_ACTIVATIONS = ("silu", "swigluoai_uninterleave")
 _ALL_ACTIVATIONS = ("silu", "gelu", "relu2", "swigluoai", "swigluoai_uninterleave", "swiglustep",
@@ -48,6 +51,24 @@ def _no_mark(_name):
 
 def _force_generic() -> bool:
     return os.environ.get("FLAGGEMS_B200_GENERIC_GEMM", "0").lower() in ("1", "true", "yes", "on")
+
+
+def _pair_policy() -> str:
+    """FLAGGEMS_B200_TC_PAIR = 0 (never), 1 (always when the tensor-core kernel runs), auto."""
+    v = os.environ.get("FLAGGEMS_B200_TC_PAIR", "auto").lower()
+    return {"0": "off", "off": "off", "1": "on", "on": "on"}.get(v, "auto")
+
+
+def _choose_kernel(mode, act_dtype, H, I, numel, num_experts):
+    if _force_generic() or not _tc_eligible(mode, act_dtype, H, I):
+        return KERNEL_GENERIC
+    policy = _pair_policy()
+    if policy == "on":
+        return KERNEL_TC_PAIR
+    if policy == "off":
+        return KERNEL_TC
+    # CTA pairs (256-row align blocks) pay off once an expert sees well over 128 rows
+    return KERNEL_TC_PAIR if numel >= 160 * num_experts else KERNEL_TC
 
 
 def _tc_eligible(mode: int, act_dtype: torch.dtype, H: int, I: int) -> bool:
@@ -112,8 +133,10 @@ def route_pipeline(a_rows, a_scales_t, w1, w2, route_weight, topk_ids, *, mode, 
     numel = M * k
     act_code = _lib.dtype_code(act_dtype)
     if use_tensor_cores is None:
-        use_tensor_cores = _tc_eligible(mode, act_dtype, H, I) and not _force_generic()
-    block_m = TC_BLOCK_M if use_tensor_cores else GENERIC_BLOCK_M
+        kernel = _choose_kernel(mode, act_dtype, H, I, numel, global_num_experts)
+    else:
+        kernel = int(use_tensor_cores)
+    block_m = {KERNEL_GENERIC: GENERIC_BLOCK_M, KERNEL_TC: TC_BLOCK_M, KERNEL_TC_PAIR: TC_PAIR_BLOCK_M}[kernel]
 
     # every expert that owns at least one route pads by < block_m
     rows_cap = round_up(numel + min(numel, global_num_experts) * (block_m - 1), block_m)
@@ -139,7 +162,7 @@ def route_pipeline(a_rows, a_scales_t, w1, w2, route_weight, topk_ids, *, mode, 
         act_scales = None
     rw = route_weight if route_weight.dtype == torch.float32 else route_weight.float()
     rw = rw if rw.is_contiguous() else rw.contiguous()
-    tc = int(bool(use_tensor_cores))
+    tc = kernel
     _lib.check(L.moe_gemm1(mode, act_code, a_rows.data_ptr(), _lib.ptr(a_scales_t), M, k, w1.data_ptr(),
                            _lib.ptr(w1_scale), expert_ids.data_ptr(), sorted_ids.data_ptr(), npp.data_ptr(),
                            rw.data_ptr(), int(apply_router_weight_on_input), rows_cap, block_m, E_local, H, I,
@@ -154,7 +177,7 @@ def route_pipeline(a_rows, a_scales_t, w1, w2, route_weight, topk_ids, *, mode, 
     if keep is not None:
         keep.update(sorted_ids=sorted_ids, expert_ids=expert_ids, num_post_pad=npp, a_rows=a_rows,
                     a_scales_t=a_scales_t, act=act, act_scales_t=act_scales, y=y, block_m=block_m,
-                    rows_cap=rows_cap, used_tensor_cores=bool(use_tensor_cores))
+                    rows_cap=rows_cap, used_tensor_cores=kernel != KERNEL_GENERIC, kernel=kernel)
     return y
 
 

@@ -118,9 +118,12 @@ int moe_widen_int8(const void* src, void* dst, int dst_dtype, int64_t n, void* s
  *   out [rows_cap, I] in sorted order: act dtype, or e4m3 with
  *     out_scales_t [I/128, rows_cap] in FP8 mode (the activation is rounded to
  *     act dtype, then quantised 1x128, as the reference does between its GEMMs)
- * use_tensor_cores: 1 = tcgen05 kernel (block_m must be 128, rows_cap % 128 == 0,
- *   I % 128 == 0, H % 128 == 0 for FP8 / H % 64 == 0 for half), 0 = generic
- *   kernel (block_m % 16 == 0, any mode).
+ * use_tensor_cores: 0 = generic kernel (block_m % 16 == 0, any mode);
+ *   1 = tcgen05 kernel, one CTA per 128-row align block (block_m must be 128,
+ *   rows_cap % 128 == 0, I % 128 == 0, H % 128 == 0 for FP8 / H % 64 == 0 for half);
+ *   2 = tcgen05 kernel, a cta_group::2 CTA pair per 256-row align block
+ *   (block_m must be 256, rows_cap % 256 == 0): each weight tile is fetched once
+ *   per 256 rows.  GEMM1 and GEMM2 of one layer must use the same block_m.
  */
 int moe_gemm1(int mode, int act_dtype, const void* a, const float* a_scales_t, int64_t num_tokens,
               int topk, const void* w1, const float* w1_scale, const int32_t* expert_ids,

@@ -35,17 +35,27 @@ def _route(M, E, k, dtype, seed=0):
 
 
 def _both_kernels(run):
-    """Runs ``run()`` with the generic kernels and with the tensor-core kernels."""
+    """Runs ``run()`` with each GEMM kernel: the generic one, the tensor-core
+    kernel with one CTA per 128-row block, and the CTA-pair (cta_group::2) one.
+    MOE_TEST_KERNELS = generic | tensor | pair | both (default: all three)."""
     outs = {}
-    which = os.environ.get("MOE_TEST_KERNELS", "both")  # generic | tensor | both
-    for name, val in (("generic", "1"), ("tensor", "0")):
+    which = os.environ.get("MOE_TEST_KERNELS", "both")
+    variants = (("generic", {"FLAGGEMS_B200_GENERIC_GEMM": "1"}),
+                ("tensor", {"FLAGGEMS_B200_GENERIC_GEMM": "0", "FLAGGEMS_B200_TC_PAIR": "0"}),
+                ("pair", {"FLAGGEMS_B200_GENERIC_GEMM": "0", "FLAGGEMS_B200_TC_PAIR": "1"}))
+    for name, env in variants:
         if which not in ("both", name):
             continue
-        os.environ["FLAGGEMS_B200_GENERIC_GEMM"] = val
+        saved = {k: os.environ.get(k) for k in env}
+        os.environ.update(env)
         try:
             outs[name] = run()
         finally:
-            os.environ.pop("FLAGGEMS_B200_GENERIC_GEMM", None)
+            for k, v in saved.items():
+                if v is None:
+                    os.environ.pop(k, None)
+                else:
+                    os.environ[k] = v
     return outs
 
 
@@ -179,7 +189,11 @@ def _sampled_oracle_fp8(x, w1, s1, w2, s2, tw, ti, rows):
 
 
 @pytest.mark.parametrize("M", [1, 32, 1024, 8192])
-def test_config3_full_size_sampled_parity_and_properties(M):
+@pytest.mark.parametrize("pair", ["0", "1"])
+def test_config3_full_size_sampled_parity_and_properties(M, pair, monkeypatch):
+    if os.environ.get("MOE_TEST_KERNELS", "both") not in ("both", "pair" if pair == "1" else "tensor"):
+        pytest.skip("kernel variant not selected")
+    monkeypatch.setenv("FLAGGEMS_B200_TC_PAIR", pair)
     E, H, I, k = 256, 7168, 2048, 8
     x = T.make_activations(M, H, DEV)
     w1, s1 = T.make_fp8_block_weights(E, 2 * I, H, DEV, seed=1)
@@ -309,7 +323,8 @@ def test_intermediates_follow_the_documented_layout():
     fused_moe.run_chunk(x, w1, w2, tw, ti, out, mode=_lib.MODE_FP8_BLOCK, w1_scale=s1, w2_scale=s2,
                         global_num_experts=E, expert_map=None, apply_router_weight_on_input=False, keep=keep)
     torch.cuda.synchronize()
-    assert keep["used_tensor_cores"] and keep["block_m"] == 128
+    assert keep["used_tensor_cores"] and keep["block_m"] in (128, 256)
+    bm = keep["block_m"]
     xq, xs = O.per_token_group_quant_fp8_oracle(x, 128)
     assert torch.equal(keep["a_rows"].cpu().view(torch.uint8), xq.view(torch.uint8))
     assert torch.equal(keep["a_scales_t"].cpu().t(), xs)
@@ -317,7 +332,7 @@ def test_intermediates_follow_the_documented_layout():
     n = int(keep["num_post_pad"].item())
     sid = keep["sorted_ids"][:n].cpu()
     valid = sid < M * k
-    os_, oe, on = O.moe_align_block_size_oracle(ti, 128, E, pad_sorted_ids=True)
+    os_, oe, on = O.moe_align_block_size_oracle(ti, bm, E, pad_sorted_ids=True)
     assert n == int(on[0]) and torch.equal(sid, torch.from_numpy(os_[:n]))
     act = keep["act"][:n].cpu().float() * keep["act_scales_t"][:, :n].cpu().t().repeat_interleave(128, dim=1)
     assert torch.isfinite(act[valid]).all()
