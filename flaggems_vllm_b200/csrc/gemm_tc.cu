@@ -149,11 +149,14 @@ __device__ __forceinline__ uint32_t cluster_ctarank() {
   return r;
 }
 // Arrive on the barrier at the same shared-memory offset in CTA `rank` of the cluster.
+// Relaxed: what the leader consumes after this arrival is not generic-proxy data of this
+// thread (TMA / cp.async results fenced to the async proxy, or TMEM already read back by
+// tcgen05.wait::ld), and a release at cluster scope costs about a microsecond per call.
 __device__ __forceinline__ void mbar_arrive_remote(uint64_t* bar, uint32_t rank) {
   asm volatile(
       "{\n\t.reg .b32 ra;\n\t"
       "mapa.shared::cluster.u32 ra, %0, %1;\n\t"
-      "mbarrier.arrive.release.cluster.shared::cluster.b64 _, [ra];\n\t}"
+      "mbarrier.arrive.relaxed.cluster.shared::cluster.b64 _, [ra];\n\t}"
       ::"r"(smem_u32(bar)), "r"(rank)
       : "memory");
 }

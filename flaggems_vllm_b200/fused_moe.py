@@ -67,8 +67,13 @@ def _choose_kernel(mode, act_dtype, H, I, numel, num_experts):
         return KERNEL_TC_PAIR
     if policy == "off":
         return KERNEL_TC
-    # CTA pairs (256-row align blocks) pay off once an expert sees well over 128 rows
-    return KERNEL_TC_PAIR if numel >= 160 * num_experts else KERNEL_TC
+    # CTA pairs (cta_group::2, 256-row align blocks) halve the L2 -> shared-memory weight
+    # traffic.  Measured on B200: a gain for the half-precision GEMMs from ~512 rows per
+    # expert on (Mixtral shape M=4096: 781 -> 812 TFLOP/s, M=16384: 715 -> 786); a loss
+    # for FP8 block scales, whose per-K-block accumulator hand-off then crosses two SMs.
+    if mode == _lib.MODE_HALF and numel >= 512 * num_experts:
+        return KERNEL_TC_PAIR
+    return KERNEL_TC
 
 
 def _tc_eligible(mode: int, act_dtype: torch.dtype, H: int, I: int) -> bool:
