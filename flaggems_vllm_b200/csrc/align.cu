@@ -15,7 +15,8 @@
 //            golden (tests/test_moe_align_block_size.py:293-388); the
 //            reference kernels rank by atomic arrival order instead
 //            (src/flaggems_vllm/ops/moe_align_block_size.py:505-527).
-// Ids outside [0, num_experts) are skipped and flagged in the status word.
+// Ids outside [0, num_experts) are skipped; ids >= num_experts are also flagged in the
+// status word (negative ids are the conventional "no route" marker and stay silent).
 //
 // Large inputs (thousands of ids) use the same algorithm spread over a
 // thread-block cluster of 8 CTAs: each CTA owns a contiguous eighth of the ids,
@@ -67,7 +68,7 @@ __global__ void __launch_bounds__(kAlignThreads) align_kernel(
     for (int i = begin + lane; i < end; i += 32) {
       long long e = (long long)ids[i];
       if (e >= 0 && e < E) atomicAdd(&h[(int)e], 1);
-      else bad = true;
+      else if (e >= E) bad = true;  // negative ids mean "no route" (padding rows, other ranks' slots)
     }
   }
   if (bad) set_status(status, MOE_ST_BAD_EXPERT_ID);
@@ -200,7 +201,7 @@ align_cluster_kernel(const IdT* __restrict__ ids, int numel, int E, int block_si
     for (int i = begin + lane; i < end; i += 32) {
       long long e = (long long)ids[i];
       if (e >= 0 && e < E) atomicAdd(&h[(int)e], 1);
-      else bad = true;
+      else if (e >= E) bad = true;  // negative ids mean "no route" (padding rows, other ranks' slots)
     }
   }
   if (bad) set_status(status, MOE_ST_BAD_EXPERT_ID);

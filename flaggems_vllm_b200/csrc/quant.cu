@@ -101,7 +101,8 @@ __global__ void __launch_bounds__(256) moe_sum_kernel(
           }
           if (use[u]) {
             const int64_t src_row = row_index != nullptr ? (int64_t)row_index[m * topk + j] : m * topk + j;
-            raw[u] = *reinterpret_cast<const uint4*>(in + src_row * H + h0);
+            use[u] = src_row >= 0;
+            if (use[u]) raw[u] = *reinterpret_cast<const uint4*>(in + src_row * H + h0);
           }
         }
 #pragma unroll
@@ -121,6 +122,7 @@ __global__ void __launch_bounds__(256) moe_sum_kernel(
           if (expert_map != nullptr && expert_map[e] < 0) continue;
         }
         const int64_t src_row = row_index != nullptr ? (int64_t)row_index[m * topk + j] : m * topk + j;
+        if (src_row < 0) continue;
         const T* src = in + src_row * H + h0;
         for (int i = 0; i < V && h0 + i < H; ++i) acc[i] += ToF32<T>::get(src[i]);
       }

@@ -2,17 +2,23 @@
 
 Experts are partitioned across ranks (rank r owns experts
 [r*E/R, (r+1)*E/R)); tokens are data-parallel.  Every rank routes its own
-tokens with the full score matrix, then
+tokens with the full score matrix.  The unit that travels is a
+(token, destination rank) pair, not a route: a token whose k experts live on
+fewer than k ranks is sent once per rank (DeepSeek-V3's group-limited routing
+keeps a token's 8 experts inside 4 of 8 groups, so with one group per rank
+dispatch and combine move half the rows a per-route exchange would).
 
-    dispatch   all-to-all of the routed rows to the rank that owns the expert
-               (FP8 mode: the e4m3 row and its 1x128 scales travel, half the
-               bytes of the bf16 row; plus local expert id and route weight)
-    compute    align -> GEMM1 -> GEMM2 over the received rows (top-k = 1); the
-               GEMM2 epilogue applies the route weight and writes rows in
-               receive order, which IS the combine send order: no pack kernel
-    combine    all-to-all of the bf16 rows back to their source rank
-    sum        fixed-order fp32 sum over each token's k routes, reading the
-               returned rows through an index (no un-permute pass)
+    plan       which ranks each token visits (a [M, R] mask), counts all-to-all
+    dispatch   all-to-all of the rows (FP8 mode: e4m3 row + 1x128 scales, half
+               the bytes of a bf16 row) and of k (local expert id, weight)
+               slots per row, -1 marking slots that belong to other ranks
+    compute    align -> GEMM1 -> GEMM2 over the received rows with their k
+               slots, then the fixed-order sum of each row's local routes: the
+               result is already the per-(token, rank) partial output, in
+               receive order, which IS the combine send order
+    combine    all-to-all of those bf16 rows back to their source rank
+    sum        fixed-order fp32 sum over the ranks each token visited, reading
+               the returned rows through an index
 
 Collectives are NCCL ``all_to_all_single`` over NVLink/NVSwitch; every payload
 lands in the rank's own HBM before a kernel touches it.  The reference's own
@@ -30,13 +36,23 @@ from . import _lib
 from .fused_moe import combine_routes, quantize_rows, route_pipeline
 
 
-def partition_routes(topk_ids: torch.Tensor, experts_per_rank: int, world: int):
-    """Host-side plan of the dispatch: routes ordered by destination rank
-    (stable), and how many go to each rank.  Works on CPU tensors too."""
-    dest = torch.div(topk_ids.reshape(-1), experts_per_rank, rounding_mode="floor").clamp_(0, world - 1)
-    order = torch.sort(dest, stable=True)[1]
-    counts = torch.bincount(dest, minlength=world)[:world]
-    return order, counts
+def plan_dispatch(topk_ids: torch.Tensor, experts_per_rank: int, world: int):
+    """Which (token, rank) pairs exist.  Returns
+    ``tok`` [P] token of each pair, ``dst`` [P] its rank (pairs ordered by rank,
+    then token), ``counts`` [R] pairs per rank, ``index`` [M, R] position of the
+    pair of (token, rank) in that order or -1.  Works on CPU tensors too."""
+    M = topk_ids.shape[0]
+    ids = topk_ids.long()
+    valid = ids >= 0
+    dest = torch.div(ids.clamp_min(0), experts_per_rank, rounding_mode="floor").clamp_(max=world - 1)
+    visits = torch.zeros((M, world), dtype=torch.bool, device=topk_ids.device)
+    visits.scatter_(1, dest, valid)
+    counts = visits.sum(0)
+    pairs = visits.t().nonzero(as_tuple=False)  # sorted by rank, then token
+    dst, tok = pairs[:, 0], pairs[:, 1]
+    index = torch.full((M, world), -1, dtype=torch.int32, device=topk_ids.device)
+    index[tok, dst] = torch.arange(pairs.shape[0], device=topk_ids.device, dtype=torch.int32)
+    return tok, dst, counts, index, dest
 
 
 class ExpertParallelMoE:
@@ -44,9 +60,9 @@ class ExpertParallelMoE:
 
     def __init__(self, w1, w2, w1_scale, w2_scale, num_experts_global: int, group=None, *,
                  mode: int = _lib.MODE_FP8_BLOCK, compute_fn=None, combine_fn=None):
-        """``compute_fn(a_rows, a_scales_t, route_weight, local_ids) -> y`` and
-        ``combine_fn(y_back, out, topk_ids, row_index)`` replace the CUDA steps;
-        the CPU (gloo) tests of the dispatch/combine plumbing inject them."""
+        """``compute_fn(a_rows, a_scales_t, slot_weights, slot_ids, act_dtype) -> rows``
+        and ``combine_fn(rows_back, out, index)`` replace the CUDA steps; the CPU
+        (gloo) tests of the dispatch/combine plumbing inject them."""
         self.group = group if group is not None else dist.group.WORLD
         self.world = dist.get_world_size(self.group)
         self.rank = dist.get_rank(self.group)
@@ -60,14 +76,18 @@ class ExpertParallelMoE:
         self.compute_fn = compute_fn or self._compute_cuda
         self.combine_fn = combine_fn or self._combine_cuda
 
-    def _compute_cuda(self, a_rows, a_scales_t, route_weight, local_ids, act_dtype):
-        return route_pipeline(a_rows, a_scales_t, self.w1, self.w2, route_weight, local_ids, mode=self.mode,
-                              act_dtype=act_dtype, w1_scale=self.s1, w2_scale=self.s2,
-                              global_num_experts=self.E_local, expert_map=None,
-                              apply_router_weight_on_input=False)
+    def _compute_cuda(self, a_rows, a_scales_t, slot_weights, slot_ids, act_dtype):
+        y = route_pipeline(a_rows, a_scales_t, self.w1, self.w2, slot_weights, slot_ids, mode=self.mode,
+                           act_dtype=act_dtype, w1_scale=self.s1, w2_scale=self.s2,
+                           global_num_experts=self.E_local, expert_map=None,
+                           apply_router_weight_on_input=False)
+        rows = torch.empty((a_rows.shape[0], y.shape[1]), dtype=act_dtype, device=y.device)
+        combine_routes(y, rows, slot_ids, self.E_local)  # slots of other ranks (-1) are skipped
+        return rows
 
-    def _combine_cuda(self, y_back, out, topk_ids, row_index):
-        combine_routes(y_back, out, topk_ids, self.E, None, row_index=row_index)
+    def _combine_cuda(self, rows_back, out, index):
+        # one slot per rank; ranks the token did not visit have index -1
+        combine_routes(rows_back, out, None, 0, None, row_index=index)
 
     def _a2a(self, out, inp, out_splits, in_splits):
         dist.all_to_all_single(out, inp, output_split_sizes=out_splits, input_split_sizes=in_splits,
@@ -79,8 +99,8 @@ class ExpertParallelMoE:
         dev = x.device
         fp8 = self.mode == _lib.MODE_FP8_BLOCK
 
-        # ---- plan: routes by destination rank, counts to/from every rank
-        order, send_counts = partition_routes(topk_ids, self.E_local, self.world)
+        # ---- plan and counts
+        tok, dst, send_counts, index, dest = plan_dispatch(topk_ids, self.E_local, self.world)
         recv_counts = torch.empty_like(send_counts)
         dist.all_to_all_single(recv_counts, send_counts, group=self.group)
         counts = torch.stack([send_counts, recv_counts]).tolist()  # the one host sync of the step
@@ -88,41 +108,41 @@ class ExpertParallelMoE:
         n_send, n_recv = sum(send_splits), sum(recv_splits)
         self.last_counts = (send_splits, recv_splits)
 
-        # ---- dispatch payload, in send order
-        src_tok = torch.div(order, k, rounding_mode="floor")
-        flat_ids = topk_ids.reshape(-1)[order]
-        meta_send = torch.stack([(flat_ids % self.E_local).float(),
-                                 topk_weights.reshape(-1)[order].float()], dim=1).contiguous()
-        meta_recv = torch.empty((n_recv, 2), dtype=torch.float32, device=dev)
+        # ---- slots of each pair: (local expert id, weight) for routes that live on its rank, else (-1, 0)
+        mine = dest[tok] == dst[:, None]
+        slot_ids = torch.where(mine, topk_ids[tok].long() % self.E_local, torch.full_like(dest[tok], -1))
+        slot_w = torch.where(mine, topk_weights[tok].float(), torch.zeros((), device=dev))
+        meta_send = torch.cat([slot_ids.float(), slot_w], dim=1).contiguous()  # ids < 2^24: exact in fp32
+        meta_recv = torch.empty((n_recv, 2 * k), dtype=torch.float32, device=dev)
         self._a2a(meta_recv, meta_send, recv_splits, send_splits)
+
+        # ---- rows, in send order
         if fp8:
             xq, xs_t = quantize_rows(x)
-            rows_send = xq.view(torch.uint8)[src_tok]
-            sc_send = xs_t.t()[src_tok].contiguous()
-            rows_recv = torch.empty((n_recv, H), dtype=torch.uint8, device=dev)
-            sc_recv = torch.empty((n_recv, H // 128), dtype=torch.float32, device=dev)
-            self._a2a(rows_recv, rows_send, recv_splits, send_splits)
-            self._a2a(sc_recv, sc_send, recv_splits, send_splits)
-            a_rows = rows_recv.view(torch.float8_e4m3fn)
-            a_scales_t = sc_recv.t().contiguous()
+            g = H // 128
+            pay_send = torch.empty((n_send, H + 4 * g), dtype=torch.uint8, device=dev)
+            pay_send[:, :H] = xq.view(torch.uint8)[tok]
+            pay_send[:, H:] = xs_t.t()[tok].contiguous().view(torch.uint8)
+            pay_recv = torch.empty((n_recv, H + 4 * g), dtype=torch.uint8, device=dev)
+            self._a2a(pay_recv, pay_send, recv_splits, send_splits)
+            a_rows = pay_recv[:, :H].contiguous().view(torch.float8_e4m3fn)
+            a_scales_t = pay_recv[:, H:].contiguous().view(torch.float32).t().contiguous()
         else:
-            rows_send = x[src_tok]
-            rows_recv = torch.empty((n_recv, H), dtype=x.dtype, device=dev)
-            self._a2a(rows_recv, rows_send, recv_splits, send_splits)
-            a_rows, a_scales_t = rows_recv, None
+            rows_send = x[tok]
+            a_rows = torch.empty((n_recv, H), dtype=x.dtype, device=dev)
+            self._a2a(a_rows, rows_send, recv_splits, send_splits)
+            a_scales_t = None
 
-        # ---- local experts over the received rows (top-k = 1)
+        # ---- local experts over the received rows
         if n_recv > 0:
-            local_ids = meta_recv[:, 0].to(torch.int32).view(n_recv, 1)
-            y = self.compute_fn(a_rows, a_scales_t, meta_recv[:, 1].contiguous(), local_ids, x.dtype)
+            rows = self.compute_fn(a_rows, a_scales_t, meta_recv[:, k:].contiguous(),
+                                   meta_recv[:, :k].to(torch.int32).contiguous(), x.dtype)
         else:
-            y = torch.empty((0, H), dtype=x.dtype, device=dev)
+            rows = torch.empty((0, H), dtype=x.dtype, device=dev)
 
-        # ---- combine: rows return in send order; sum through the inverse permutation
-        y_back = torch.empty((n_send, H), dtype=x.dtype, device=dev)
-        self._a2a(y_back, y, send_splits, recv_splits)
-        inverse = torch.empty_like(order, dtype=torch.int32)
-        inverse[order] = torch.arange(order.numel(), device=dev, dtype=torch.int32)
+        # ---- combine
+        rows_back = torch.empty((n_send, H), dtype=x.dtype, device=dev)
+        self._a2a(rows_back, rows, send_splits, recv_splits)
         out = torch.empty_like(x)
-        self.combine_fn(y_back, out, topk_ids, inverse)
+        self.combine_fn(rows_back, out, index)
         return out

@@ -187,18 +187,28 @@ def route_pipeline(a_rows, a_scales_t, w1, w2, route_weight, topk_ids, *, mode, 
 
 
 def combine_routes(y, out, topk_ids, global_num_experts, expert_map=None, row_index=None):
-    """out[m] = sum over the k routes of token m (fp32, fixed order), skipping
-    routes whose expert id is invalid or not local."""
-    M, k = topk_ids.shape
-    H = out.shape[1]
-    ids = topk_ids if topk_ids.is_contiguous() else topk_ids.contiguous()
+    """out[m] = fp32 sum, in fixed slot order, of the rows of token m.
+
+    With ``topk_ids`` [M, k]: slot (m, j) is row m*k + j of ``y`` (or
+    ``row_index[m, j]``), skipped when its expert id is negative, >= the expert
+    count, or not local under ``expert_map``.  With ``topk_ids=None``:
+    ``row_index`` [M, S] alone names the rows; negative entries are skipped."""
+    M, H = out.shape
+    ids = None
+    if topk_ids is not None:
+        k = topk_ids.shape[1]
+        ids = topk_ids if topk_ids.is_contiguous() else topk_ids.contiguous()
+    else:
+        k = row_index.shape[1]
     emap = None
     if expert_map is not None:
         emap = expert_map if expert_map.dtype == torch.int32 else expert_map.to(torch.int32)
         emap = emap.contiguous()
-    _lib.check(_lib.lib().moe_sum(y.data_ptr(), out.data_ptr(), _lib.dtype_code(out.dtype), M, k, H, ids.data_ptr(),
-                                  int(ids.dtype == torch.int64), global_num_experts, _lib.ptr(emap),
-                                  _lib.ptr(row_index), _lib.stream_of(out)))
+    if row_index is not None:
+        row_index = row_index.contiguous()
+    _lib.check(_lib.lib().moe_sum(y.data_ptr(), out.data_ptr(), _lib.dtype_code(out.dtype), M, k, H, _lib.ptr(ids),
+                                  int(ids is not None and ids.dtype == torch.int64), global_num_experts,
+                                  _lib.ptr(emap), _lib.ptr(row_index), _lib.stream_of(out)))
 
 
 def run_chunk(x, w1, w2, topk_weights, topk_ids, out, *, mode, w1_scale, w2_scale, global_num_experts,

@@ -40,7 +40,7 @@ enum {
 };
 
 enum {
-  MOE_ST_BAD_EXPERT_ID = 1,  /* an expert id outside [0, num_experts) was skipped */
+  MOE_ST_BAD_EXPERT_ID = 1,  /* an expert id >= num_experts was skipped (negative ids = no route, silent) */
   MOE_ST_WAIT_TIMEOUT = 2,   /* a bounded barrier wait ran out; results invalid */
   MOE_ST_BAD_ROW = 4         /* a sorted row index outside its buffer was skipped */
 };
@@ -152,8 +152,9 @@ int moe_gemm2(int mode, int act_dtype, const void* act_sorted, const float* act_
  * When topk_ids is given, slot j is skipped if its id is outside
  * [0, num_experts) or expert_map[id] < 0 (expert-parallel ranks).
  * When row_index is given, the row of slot (m, j) is in[row_index[m*topk + j]]
- * instead of in[m*topk + j] (used after the expert-parallel combine, where the
- * returned rows are ordered by the rank that computed them).
+ * instead of in[m*topk + j], and a negative index skips the slot (used after the
+ * expert-parallel combine, where the returned rows are ordered by the rank that
+ * computed them and a token has no row from ranks it sent nothing to).
  */
 int moe_sum(const void* in, void* out, int dtype, int64_t M, int topk, int64_t H,
             const void* topk_ids, int ids_int64, int num_experts, const int32_t* expert_map,

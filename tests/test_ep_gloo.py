@@ -11,15 +11,16 @@ import torch.distributed as dist
 import torch.multiprocessing as mp
 
 from flaggems_vllm_b200 import _lib
-from flaggems_vllm_b200.ep import ExpertParallelMoE, partition_routes
+from flaggems_vllm_b200.ep import ExpertParallelMoE, plan_dispatch
 from oracle import moe_oracle as O
 
 
-def test_partition_routes_orders_by_destination_rank():
-    ids = torch.tensor([[5, 0], [2, 7], [4, 1]], dtype=torch.int32)
-    order, counts = partition_routes(ids, 4, 2)
-    assert counts.tolist() == [3, 3]
-    assert order.tolist() == [1, 2, 5, 0, 3, 4]  # stable inside a destination
+def test_plan_dispatch_sends_a_token_once_per_rank():
+    ids = torch.tensor([[5, 0], [2, 3], [4, 1], [-1, 6]], dtype=torch.int32)
+    tok, dst, counts, index, dest = plan_dispatch(ids, 4, 2)
+    assert counts.tolist() == [3, 3]                      # token 1 visits rank 0 once although both routes go there
+    assert dst.tolist() == [0, 0, 0, 1, 1, 1] and tok.tolist() == [0, 1, 2, 0, 2, 3]
+    assert index.tolist() == [[0, 3], [1, -1], [2, 4], [-1, 5]]
 
 
 def _free_port():
@@ -42,14 +43,15 @@ def _worker(rank, world, port, M, E, H, I, k, ret):
         El = E // world
         lw1, lw2 = w1[rank * El:(rank + 1) * El], w2[rank * El:(rank + 1) * El]
 
-        def compute(a_rows, a_scales_t, route_weight, local_ids, act_dtype):
-            # one route per received row
-            y = O.fused_moe_half_oracle(a_rows, lw1, lw2, route_weight.view(-1, 1), local_ids)
-            return y.to(act_dtype)
+        def compute(a_rows, a_scales_t, slot_w, slot_ids, act_dtype):
+            # slots with id -1 belong to other ranks: route them to expert 0 with weight 0
+            ids = slot_ids.clamp_min(0)
+            w = torch.where(slot_ids >= 0, slot_w, torch.zeros(()))
+            return O.fused_moe_half_oracle(a_rows, lw1, lw2, w, ids).to(act_dtype)
 
-        def combine(y_back, out, topk_ids, row_index):
-            Mloc, kk = topk_ids.shape
-            out.copy_(y_back.float()[row_index.long()].view(Mloc, kk, out.shape[1]).sum(1).to(out.dtype))
+        def combine(rows_back, out, index):
+            padded = torch.cat([rows_back.float(), torch.zeros(1, out.shape[1])])
+            out.copy_(padded[index.long()].sum(1).to(out.dtype))  # index -1 picks the zero row
 
         layer = ExpertParallelMoE(lw1, lw2, None, None, E, mode=_lib.MODE_HALF, compute_fn=compute,
                                   combine_fn=combine)
@@ -69,7 +71,7 @@ def test_two_rank_dispatch_combine_matches_single_process(M):
     assert len(ret) == world
     for rank in range(world):
         rl2, cs, counts = ret[rank]
-        assert sum(counts[0]) == M * k
+        assert sum(counts[0]) <= M * k
         if M:
             assert rl2 < 1e-2 and cs > 0.9999, f"rank {rank}: rel_l2={rl2} cos={cs}"
     # what rank 0 sends to rank 1 is what rank 1 receives from rank 0
