@@ -51,7 +51,9 @@ def main():
         a, b = out.float(), full.float()
         rl2 = ((a - b).norm() / b.norm().clamp_min(1e-20)).item()
         st = fg.read_status(dev)
-        good = rl2 < 2e-3 and st == 0
+        # the per-rank partial sums are rounded to the activation dtype before the final sum,
+        # one rounding more than the single-GPU layer: allow 5e-3 (the layer tolerance is 1e-2)
+        good = rl2 < 5e-3 and st == 0
         ok = ok and good
         print(f"rank {rank} {mode} M={M}: rel_l2 vs single-GPU layer {rl2:.2e} status {st} {'OK' if good else 'FAIL'}",
               flush=True)
