@@ -402,27 +402,81 @@ def main():
     status = fg.read_status(dev)
 
     # ---- end to end with host buffers through the public API
+    # Every step copies its activations and router logits from pinned host memory, runs the
+    # public ops, and copies the layer output back to pinned host memory.  Two figures:
+    #   serial    - copy in, compute, copy out on one stream (latency of an isolated step)
+    #   pipelined - the same three phases on three streams with double-buffered device
+    #               inputs, so step i+1's H2D and step i-1's D2H overlap step i's kernels
+    #               (how a serving loop would drive it); reported as `e2e`.
     hx = torch.empty((M, H), dtype=torch.bfloat16).pin_memory()
     hl = torch.empty((M, E), dtype=torch.float32).pin_memory()
     hx.copy_(x.cpu())
     hl.copy_(logits.cpu())
-    hout = torch.empty((M, H), dtype=torch.bfloat16).pin_memory()
-    dx, dl = torch.empty_like(x), torch.empty_like(logits)
+    hout = [torch.empty((M, H), dtype=torch.bfloat16).pin_memory() for _ in range(2)]
+    dx = [torch.empty_like(x) for _ in range(2)]
+    dl = [torch.empty_like(logits) for _ in range(2)]
 
-    def e2e_step():
-        dx.copy_(hx, non_blocking=True)
-        dl.copy_(hl, non_blocking=True)
-        tw, ti = fg.grouped_topk(dl, c["n_group"], c["topk_group"], k, True, c["rsf"], bias, 1)
+    def layer_call(xi, li):
+        tw, ti = fg.grouped_topk(li, c["n_group"], c["topk_group"], k, True, c["rsf"], bias, 1)
         if layer is not None:
-            out = layer.forward(dx, tw, ti)
-        else:
-            out = fg.fused_experts_impl(dx, w1, w2, tw, ti, use_fp8_w8a8=True, w1_scale=s1, w2_scale=s2,
-                                        block_shape=[128, 128])
-        hout.copy_(out, non_blocking=True)
+            return layer.forward(xi, tw, ti)
+        return fg.fused_experts_impl(xi, w1, w2, tw, ti, use_fp8_w8a8=True, w1_scale=s1, w2_scale=s2,
+                                     block_shape=[128, 128])
+
+    def e2e_serial_step():
+        dx[0].copy_(hx, non_blocking=True)
+        dl[0].copy_(hl, non_blocking=True)
+        hout[0].copy_(layer_call(dx[0], dl[0]), non_blocking=True)
 
     for _ in range(3):
-        e2e_step()
-    e2e_ms = timed(e2e_step, max(3, args.steps // 2))
+        e2e_serial_step()
+    e2e_serial_ms = timed(e2e_serial_step, max(3, args.steps // 2))
+
+    s_in, s_out = torch.cuda.Stream(), torch.cuda.Stream()
+    s_comp = torch.cuda.current_stream()
+
+    def e2e_pipelined(steps):
+        """Returns total milliseconds for `steps` pipelined steps (device clock)."""
+        in_ready = [torch.cuda.Event() for _ in range(2)]
+        comp_done = [torch.cuda.Event() for _ in range(2)]
+        out_done = [torch.cuda.Event() for _ in range(2)]
+        keep = [None, None]
+        barrier()
+        t0, t1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        t0.record(s_comp)
+        s_in.wait_event(t0)
+        s_out.wait_event(t0)
+        for i in range(steps):
+            b = i % 2
+            with torch.cuda.stream(s_in):
+                if i >= 2:
+                    s_in.wait_event(comp_done[b])      # step i-2 has finished reading these inputs
+                dx[b].copy_(hx, non_blocking=True)
+                dl[b].copy_(hl, non_blocking=True)
+                in_ready[b].record(s_in)
+            s_comp.wait_event(in_ready[b])
+            out = layer_call(dx[b], dl[b])
+            comp_done[b].record(s_comp)
+            with torch.cuda.stream(s_out):
+                s_out.wait_event(comp_done[b])
+                if i >= 2:
+                    s_out.wait_event(out_done[b])
+                out.record_stream(s_out)
+                hout[b].copy_(out, non_blocking=True)
+                out_done[b].record(s_out)
+            keep[b] = out
+        s_comp.wait_stream(s_out)
+        s_comp.wait_stream(s_in)
+        t1.record(s_comp)
+        barrier()
+        tt = torch.tensor([t0.elapsed_time(t1)], dtype=torch.float64, device=dev)
+        if dist is not None:
+            dist.all_reduce(tt, op=dist.ReduceOp.MAX)
+        return float(tt.item())
+
+    e2e_pipelined(3)
+    e2e_steps = max(4, args.steps)
+    e2e_ms = e2e_pipelined(e2e_steps) / e2e_steps
 
     total_tokens = M * world
     flops = 6.0 * total_tokens * k * H * I
@@ -436,7 +490,9 @@ def main():
                    "l2": "flushed between iterations (252 MB memset); weights 11.3 GB >> L2"},
         "tflops": flops / (ms * 1e-3) / 1e12,
         "e2e": {"value": total_tokens / (e2e_ms * 1e-3), "unit": "tokens/s", "ms_per_step": e2e_ms,
-                "h2d_bytes_per_step": hx.numel() * 2 + hl.numel() * 4, "d2h_bytes_per_step": hout.numel() * 2},
+                "h2d_bytes_per_step": hx.numel() * 2 + hl.numel() * 4, "d2h_bytes_per_step": hout[0].numel() * 2,
+                "mode": "three streams, double-buffered: H2D / kernels / D2H of neighbouring steps overlap",
+                "serial_ms_per_step": e2e_serial_ms, "serial_value": total_tokens / (e2e_serial_ms * 1e-3)},
         "gpu_launches": 6 * args.steps,
         "clocks": clocks, "kernel_status": status,
     }

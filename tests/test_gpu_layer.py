@@ -354,3 +354,30 @@ def test_quant_and_sum_wrappers():
             fg.moe_sum(inp, o)
             torch.testing.assert_close(o.float().cpu(), O.moe_sum_oracle(inp).to(dt).float(),
                                        rtol=1.6e-2 if dt != torch.float32 else 1.3e-6, atol=1e-4 * k)
+
+
+def test_layer_under_cuda_graph_replay_with_new_inputs():
+    M, E, H, I, k = 32, 32, 512, 256, 4
+    w1, s1 = T.make_fp8_block_weights(E, 2 * I, H, DEV, seed=1, std=H**-0.5)
+    w2, s2 = T.make_fp8_block_weights(E, H, I, DEV, seed=2, std=I**-0.5)
+    x = T.make_activations(M, H, DEV, seed=3)
+    logits, bias = T.make_router_inputs(M, E, DEV, seed=4)
+
+    def step():
+        tw, ti = fg.grouped_topk(logits, 8, 4, k, True, 2.5, bias, 1)
+        return tw, ti, fg.fused_experts_impl(x, w1, w2, tw, ti, use_fp8_w8a8=True, w1_scale=s1, w2_scale=s2,
+                                             block_shape=[128, 128])
+
+    step()
+    torch.cuda.synchronize()
+    graph = torch.cuda.CUDAGraph()
+    with torch.cuda.graph(graph):
+        tw, ti, out = step()
+    for seed in (5, 6):
+        x.copy_(T.make_activations(M, H, DEV, seed=seed))
+        logits.copy_(T.make_router_inputs(M, E, DEV, seed=seed)[0])
+        graph.replay()
+        torch.cuda.synchronize()
+        ow, oi = O.grouped_topk_oracle(logits, 8, 4, k, True, 2.5, bias, 1)
+        assert torch.equal(ti.cpu(), oi)
+        _assert_parity(out, O.fused_moe_fp8_block_oracle(x, w1, w2, s1, s2, ow, oi), f"replay {seed}")
