@@ -11,7 +11,7 @@ int tc_gemm(bool gemm1, int mode, int act_dtype, const void* a, const float* a_s
             const float* w_scale, const int32_t* expert_ids, const int32_t* sorted_ids, const int32_t* npp,
             const float* route_weight, int mul_weight, int64_t numel, int64_t rows_cap, int64_t a_tokens, int topk,
             int block_m, int E, int K, int Nout, void* out, float* out_scales_t, int32_t* status, cudaStream_t st,
-            bool pair);
+            int variant);
 
 static int check_common(const char* who, int mode, const void* a, const float* a_scales, const void* w,
                         const float* w_scale, const int32_t* expert_ids, const int32_t* sorted_ids,
@@ -43,7 +43,7 @@ extern "C" int moe_gemm1(int mode, int act_dtype, const void* a, const float* a_
   if (use_tensor_cores)
     return tc_gemm(true, mode, act_dtype, a, a_scales_t, w1, w1_scale, expert_ids, sorted_ids, num_post_pad,
                    route_weight, mul_weight, numel, rows_cap, num_tokens, topk, block_m, E, H, I, out, out_scales_t,
-                   status, (cudaStream_t)stream, use_tensor_cores == 2);
+                   status, (cudaStream_t)stream, use_tensor_cores);
   return simt_gemm(true, mode, act_dtype, a, a_scales_t, w1, w1_scale, expert_ids, sorted_ids, num_post_pad,
                    route_weight, mul_weight, numel, rows_cap, num_tokens, topk, block_m, E, H, I, out, out_scales_t,
                    status, (cudaStream_t)stream);
@@ -62,7 +62,7 @@ extern "C" int moe_gemm2(int mode, int act_dtype, const void* act_sorted, const 
   if (use_tensor_cores)
     return tc_gemm(false, mode, act_dtype, act_sorted, act_scales_t, w2, w2_scale, expert_ids, sorted_ids,
                    num_post_pad, route_weight, mul_weight, numel, rows_cap, 0, 1, block_m, E, I, H, y, nullptr, status,
-                   (cudaStream_t)stream, use_tensor_cores == 2);
+                   (cudaStream_t)stream, use_tensor_cores);
   return simt_gemm(false, mode, act_dtype, act_sorted, act_scales_t, w2, w2_scale, expert_ids, sorted_ids,
                    num_post_pad, route_weight, mul_weight, numel, rows_cap, 0, 1, block_m, E, I, H, y, nullptr, status,
                    (cudaStream_t)stream);

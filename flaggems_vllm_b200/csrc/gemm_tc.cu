@@ -53,10 +53,13 @@ constexpr int A_STAGE_BYTES = BM * 128;
 constexpr int B_STAGE_BYTES = BN * 128;       // whole B tile (single-CTA kernel)
 constexpr int B_HALF_BYTES = B_STAGE_BYTES / 2;  // what each CTA of a pair holds
 constexpr int MAX_STAGES = 6;
-// single CTA: 4 stages of A + B; CTA pair (cta_group::2): 6 stages of A + half of B
-template <bool PAIR> struct Cfg {
-  static constexpr int STAGES = PAIR ? 6 : 4;
-  static constexpr int STAGE_BYTES = A_STAGE_BYTES + (PAIR ? B_HALF_BYTES : B_STAGE_BYTES);
+// single CTA: 4 stages of A + B; CTA pair (cta_group::2): 6 stages of A + half of B;
+// wide tile (RB = 2, half precision only): 3 stages of two A blocks + B, i.e. a 256x256
+// output tile whose two accumulators fill TMEM, each B tile fetched once per 256 rows
+template <bool PAIR, int RB> struct Cfg {
+  static constexpr int STAGES = PAIR ? 6 : (RB == 2 ? 3 : 4);
+  static constexpr int A_LOCAL = RB * A_STAGE_BYTES;
+  static constexpr int STAGE_BYTES = A_LOCAL + (PAIR ? B_HALF_BYTES : B_STAGE_BYTES);
 };
 constexpr int B_BOX_ROWS = 64;
 constexpr int THREADS = 384;
@@ -93,7 +96,7 @@ struct SmemAux {
   float sc_a[SCALE_SLOTS][BM];  // activation scale of each tile row
   float sc_w[SCALE_SLOTS][4];   // weight scales of the two column halves
 };
-template <bool PAIR> constexpr size_t smem_bytes() { return (size_t)Cfg<PAIR>::STAGES * Cfg<PAIR>::STAGE_BYTES + sizeof(SmemAux) + 1024; }
+template <bool PAIR, int RB> constexpr size_t smem_bytes() { return (size_t)Cfg<PAIR, RB>::STAGES * Cfg<PAIR, RB>::STAGE_BYTES + sizeof(SmemAux) + 1024; }
 
 struct Params {
   const uint8_t* a_rows;    // GEMM1: activations [tokens, K] in token order (gathered by cp.async)
@@ -343,25 +346,35 @@ __device__ __forceinline__ float round_act(float v) {
 // landed" to the leader with a remote mbarrier arrive, and the leader's
 // tcgen05.commit signals the stage-free / accumulator-ready barriers of both
 // CTAs.
-template <bool FP8, typename AT, bool GEMM1, bool PAIR>
+//
+// RB = 2 (half precision, single CTA): the tile is 256 rows x 256 columns; both TMEM
+// accumulators belong to it (rows 0-127 and 128-255), so every B stage is used by two
+// instruction groups and each weight tile crosses L2 -> shared memory once per 256 rows
+// without any cross-CTA traffic.  FP8 cannot use it: its fp32 fold accumulators live in
+// registers and two blocks would need the whole register file.
+template <bool FP8, typename AT, bool GEMM1, bool PAIR, int RB>
 __global__ void __launch_bounds__(THREADS, 1)
 tc_gemm_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant__ CUtensorMap map_b, const Params P) {
-  constexpr int STAGES = Cfg<PAIR>::STAGES;
+  static_assert(RB == 1 || (RB == 2 && !FP8 && !PAIR), "wide tiles: half precision, single CTA");
+  constexpr int STAGES = Cfg<PAIR, RB>::STAGES;
+  constexpr int A_LOCAL_BYTES = Cfg<PAIR, RB>::A_LOCAL;
   constexpr int B_LOCAL_BYTES = PAIR ? B_HALF_BYTES : B_STAGE_BYTES;
   extern __shared__ uint8_t smem_raw[];
   uint8_t* smem = reinterpret_cast<uint8_t*>(((uintptr_t)smem_raw + 1023) & ~(uintptr_t)1023);
   uint8_t* sA = smem;
-  uint8_t* sB = smem + (size_t)STAGES * A_STAGE_BYTES;
-  SmemAux* aux = reinterpret_cast<SmemAux*>(smem + (size_t)STAGES * Cfg<PAIR>::STAGE_BYTES);
+  uint8_t* sB = smem + (size_t)STAGES * A_LOCAL_BYTES;
+  SmemAux* aux = reinterpret_cast<SmemAux*>(smem + (size_t)STAGES * Cfg<PAIR, RB>::STAGE_BYTES);
 
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
   constexpr int KBE = FP8 ? 128 : 64;  // elements of K per stage
   const int KB = (P.K + KBE - 1) / KBE;
   const int npp = min((int64_t)P.num_post_pad[0], P.rows_cap);
-  // work unit: one CTA and a 128-row align block, or a CTA pair and a 256-row align block
-  constexpr int UNIT = PAIR ? 2 : 1;
+  // work unit: one CTA and a 128-row align block; a CTA pair and a 256-row block; or one
+  // CTA and a 256-row block (RB = 2).  UNIT = 128-row blocks per align block.
+  constexpr int UNIT = PAIR ? 2 : RB;
+  constexpr int CTAS = PAIR ? 2 : 1;
   const int cr = PAIR ? (int)cluster_ctarank() : 0;  // rank inside the pair; 0 leads
-  const int tile0 = blockIdx.x / UNIT, tile_step = gridDim.x / UNIT;
+  const int tile0 = blockIdx.x / CTAS, tile_step = gridDim.x / CTAS;
   const int total_tiles = ((npp + UNIT * BM - 1) / (UNIT * BM)) * P.n_tiles;
   // tile -> expert_ids index (blk), this CTA's 128-row block (mb), column tile (nt)
 #define MOE_TILE_COORDS(tile)                      \
@@ -420,8 +433,11 @@ tc_gemm_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant_
           if constexpr (GEMM1) {
             mbar_expect_tx(&aux->full[s], B_LOCAL_BYTES);  // A rows arrive by cp.async (warps 2-3)
           } else {
-            mbar_expect_tx(&aux->full[s], A_STAGE_BYTES + B_LOCAL_BYTES);
-            tma_load_2d(&map_a, &aux->full[s], sA + (size_t)s * A_STAGE_BYTES, kb * KBE, row0);
+            mbar_expect_tx(&aux->full[s], A_LOCAL_BYTES + B_LOCAL_BYTES);
+#pragma unroll
+            for (int j = 0; j < RB; ++j)
+              tma_load_2d(&map_a, &aux->full[s], sA + (size_t)s * A_LOCAL_BYTES + j * A_STAGE_BYTES, kb * KBE,
+                          row0 + j * BM);
           }
           // 64-row boxes of the B tile: all four, or (pair) the two of this CTA's column half
           constexpr int NBOX = PAIR ? 2 : 4;
@@ -440,9 +456,12 @@ tc_gemm_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant_
         MOE_TILE_COORDS(tile)
         if (e < 0 || e >= P.E) continue;
         for (int kb = 0; kb < KB; ++kb, ++it) {
-          const uint32_t a = acc_it & 1;
+          // accumulator barrier and phase: the two accumulators alternate (per K block in FP8
+          // mode, per tile in half mode); a wide tile owns both and uses barrier 0
+          const uint32_t a = RB == 2 ? 0u : (acc_it & 1);
+          const uint32_t aph = RB == 2 ? (acc_it & 1) : ((acc_it >> 1) & 1);
           if (FP8 || kb == 0) {
-            if (!mbar_wait<PAIR>(&aux->tmem_empty[a], ((acc_it >> 1) & 1) ^ 1, P.status)) { alive = false; break; }
+            if (!mbar_wait<PAIR>(&aux->tmem_empty[a], aph ^ 1, P.status)) { alive = false; break; }
             tc_fence_after();
           }
           const int s = it % STAGES;
@@ -452,15 +471,18 @@ tc_gemm_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant_
           }
           if constexpr (GEMM1) asm volatile("fence.proxy.async.shared::cta;" ::: "memory");  // cp.async writes -> tensor core reads
           tc_fence_after();
-          const uint64_t adesc = make_smem_desc(smem_u32(sA + (size_t)s * A_STAGE_BYTES));
           const uint64_t bdesc = make_smem_desc(smem_u32(sB + (size_t)s * B_LOCAL_BYTES));
-          const uint32_t d = tmem_base + a * BN;
 #pragma unroll
-          for (int k4 = 0; k4 < 4; ++k4) {
-            // 32 bytes of K per instruction: start address advances by 32 B >> 4
-            const uint32_t accum = FP8 ? (k4 > 0) : (kb > 0 || k4 > 0);
-            if constexpr (PAIR) tc_mma_pair<FP8>(d, adesc + (uint64_t)(k4 * 2), bdesc + (uint64_t)(k4 * 2), idesc, accum);
-            else tc_mma<FP8>(d, adesc + (uint64_t)(k4 * 2), bdesc + (uint64_t)(k4 * 2), idesc, accum);
+          for (int j = 0; j < RB; ++j) {
+            const uint64_t adesc = make_smem_desc(smem_u32(sA + (size_t)s * A_LOCAL_BYTES + j * A_STAGE_BYTES));
+            const uint32_t d = tmem_base + (RB == 2 ? (uint32_t)j : a) * BN;
+#pragma unroll
+            for (int k4 = 0; k4 < 4; ++k4) {
+              // 32 bytes of K per instruction: start address advances by 32 B >> 4
+              const uint32_t accum = FP8 ? (k4 > 0) : (kb > 0 || k4 > 0);
+              if constexpr (PAIR) tc_mma_pair<FP8>(d, adesc + (uint64_t)(k4 * 2), bdesc + (uint64_t)(k4 * 2), idesc, accum);
+              else tc_mma<FP8>(d, adesc + (uint64_t)(k4 * 2), bdesc + (uint64_t)(k4 * 2), idesc, accum);
+            }
           }
           if constexpr (PAIR) tc_commit_pair(&aux->empty[s]); else tc_commit(&aux->empty[s]);
           if (FP8 || kb == KB - 1) {
@@ -492,10 +514,11 @@ tc_gemm_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant_
       for (int tile = tile0; tile < total_tiles && alive; tile += tile_step) {
         MOE_TILE_COORDS(tile)
         if (e < 0 || e >= P.E) continue;
-        const uint8_t* src[2];
-        [[maybe_unused]] const float* as_src[2];
-        uint32_t dst_off[2];
-        bool ok[2];
+        constexpr int RPT = 2 * RB;  // rows per gather thread
+        const uint8_t* src[RPT];
+        [[maybe_unused]] const float* as_src[RPT];
+        uint32_t dst_off[RPT];
+        bool ok[RPT];
         // weight-scale row of this thread (g = 0: gate rows nt*128.., g = 1: up rows I + nt*128..)
         [[maybe_unused]] const float* ws_src = nullptr;
         if constexpr (FP8) {
@@ -503,8 +526,8 @@ tc_gemm_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant_
           ws_src = P.w_scale + ((int64_t)e * sblk_per_e + (g == 1 ? (P.Nout >> 7) + nt : nt)) * KB;
         }
 #pragma unroll
-        for (int j = 0; j < 2; ++j) {
-          const int r = g + 64 * j;
+        for (int j = 0; j < RPT; ++j) {
+          const int r = g + 64 * j;  // row inside the (RB x 128)-row tile
           const int64_t p = (int64_t)mb * BM + r;
           const int64_t sid = p < P.rows_cap ? (int64_t)P.sorted_ids[p] : P.numel;
           ok[j] = sid >= 0 && sid < P.numel;  // padding slot: the row keeps stale bytes, its results are never stored
@@ -516,9 +539,9 @@ tc_gemm_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant_
         for (int kb = 0; kb < KB; ++kb, ++it) {
           const int s = it % STAGES;
           if (!mbar_wait(&aux->empty[s], ((it / STAGES) & 1) ^ 1, P.status)) { alive = false; break; }
-          const uint32_t base = smem_u32(sA + (size_t)s * A_STAGE_BYTES);
+          const uint32_t base = smem_u32(sA + (size_t)s * A_LOCAL_BYTES);
 #pragma unroll
-          for (int j = 0; j < 2; ++j) {
+          for (int j = 0; j < RPT; ++j) {
             if (ok[j]) {
               const int r = g + 64 * j;
               const uint8_t* sp = src[j] + (int64_t)kb * 128;
@@ -579,7 +602,8 @@ tc_gemm_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant_
     for (int tile = tile0; tile < total_tiles && alive; tile += tile_step) {
       MOE_TILE_COORDS(tile)
       if (e < 0 || e >= P.E) continue;
-      const int64_t p = (int64_t)mb * BM + row;
+      for (int sub = 0; sub < RB && alive; ++sub) {  // the 128-row blocks of this tile (two for wide tiles)
+      const int64_t p = (int64_t)(mb + sub) * BM + row;
       int64_t sid = P.numel;
       if (p < P.rows_cap) sid = (int64_t)P.sorted_ids[p];
       const bool row_ok = sid >= 0 && sid < P.numel;
@@ -622,15 +646,20 @@ tc_gemm_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant_
         }
         if (!alive) break;
       } else {
-        const uint32_t a = acc_it & 1;
-        if (!mbar_wait(&aux->tmem_full[a], (acc_it >> 1) & 1, P.status)) { alive = false; break; }
-        tc_fence_after();
-        const uint32_t t0 = t_lane + a * BN;
+        const uint32_t a = RB == 2 ? 0u : (acc_it & 1);
+        const uint32_t aph = RB == 2 ? (acc_it & 1) : ((acc_it >> 1) & 1);
+        if (sub == 0) {
+          if (!mbar_wait(&aux->tmem_full[a], aph, P.status)) { alive = false; break; }
+          tc_fence_after();
+        }
+        const uint32_t t0 = t_lane + (RB == 2 ? (uint32_t)sub : a) * BN;
         uint32_t* r = reinterpret_cast<uint32_t*>(acc);
         tmem_ld64_sync(t0, r, r + 32);
         tmem_ld64_sync(t0 + 64, r + 64, r + 96);
-        release_acc(a);
-        ++acc_it;
+        if (sub == RB - 1) {  // everything of this tile is in registers (or already stored)
+          release_acc(a);
+          ++acc_it;
+        }
       }
 
       // ---------------------------------------------------------- tile epilogue
@@ -718,6 +747,7 @@ tc_gemm_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant_
                               pack2<AT>(acc[v * 8 + 6] * rw, acc[v * 8 + 7] * rw));
         }
       }
+      }  // sub
       ++tile_it;
     }
   }
@@ -774,10 +804,10 @@ static int make_map(CUtensorMap* m, const void* base, CUtensorMapDataType dt, in
   return 0;
 }
 
-template <bool FP8, typename AT, bool GEMM1, bool PAIR>
+template <bool FP8, typename AT, bool GEMM1, bool PAIR, int RB>
 static int launch(const CUtensorMap& ma, const CUtensorMap& mb, const Params& P, int grid, cudaStream_t st) {
-  auto kern = tc_gemm_kernel<FP8, AT, GEMM1, PAIR>;
-  constexpr size_t smem = smem_bytes<PAIR>();
+  auto kern = tc_gemm_kernel<FP8, AT, GEMM1, PAIR, RB>;
+  constexpr size_t smem = smem_bytes<PAIR, RB>();
   cudaFuncAttributes fa;
   cudaError_t ce = cudaFuncGetAttributes(&fa, kern);
   if (ce != cudaSuccess) return fail((int)ce, "tensor-core GEMM: cudaFuncGetAttributes: %s", cudaGetErrorString(ce));
@@ -812,14 +842,19 @@ int tc_gemm(bool gemm1, int mode, int act_dtype, const void* a, const float* a_s
             const float* w_scale, const int32_t* expert_ids, const int32_t* sorted_ids, const int32_t* npp,
             const float* route_weight, int mul_weight, int64_t numel, int64_t rows_cap, int64_t a_tokens, int topk,
             int block_m, int E, int K, int Nout, void* out, float* out_scales_t, int32_t* status, cudaStream_t st,
-            bool pair) {
+            int variant) {
+  // variant: 1 = one CTA per 128-row block, 2 = cta_group::2 CTA pair per 256-row block,
+  //          3 = one CTA per 256-row block with a 256x256 tile (half precision only)
   using namespace tc;
+  const bool pair = variant == 2, wide = variant == 3;
+  if (variant < 1 || variant > 3) return fail(MOE_E_BADARG, "tensor-core GEMM: unknown kernel variant %d", variant);
+  if (wide && mode != MOE_MODE_HALF) return fail(MOE_E_SHAPE, "tensor-core GEMM: the 256x256 tile serves half precision only");
   const bool fp8 = mode == MOE_MODE_FP8_BLOCK;
   if (mode != MOE_MODE_FP8_BLOCK && mode != MOE_MODE_HALF)
     return fail(MOE_E_SHAPE, "tensor-core GEMM: mode %d is served by the generic kernel", mode);
   if (act_dtype != MOE_BF16 && act_dtype != MOE_F16)
     return fail(MOE_E_DTYPE, "tensor-core GEMM: activations must be f16 or bf16");
-  const int unit_rows = pair ? 2 * BM : BM;
+  const int unit_rows = (pair || wide) ? 2 * BM : BM;
   if (block_m != unit_rows) return fail(MOE_E_SHAPE, "tensor-core GEMM: align block must be %d", unit_rows);
   if (rows_cap % unit_rows != 0 || rows_cap <= 0)
     return fail(MOE_E_SHAPE, "tensor-core GEMM: row capacity must be a positive multiple of %d", unit_rows);
@@ -862,9 +897,17 @@ int tc_gemm(bool gemm1, int mode, int act_dtype, const void* a, const float* a_s
   const int units = pair ? sms / 2 : sms;  // work units resident at once: CTAs, or CTA pairs
   const int grid = (int)(cap_tiles < units ? cap_tiles : units) * (pair ? 2 : 1);
 
-#define MOE_TC_LAUNCH2(F, T, G) (pair ? launch<F, T, G, true>(ma, mb, P, grid, st) : launch<F, T, G, false>(ma, mb, P, grid, st))
+#define MOE_TC_LAUNCH2(F, T, G) \
+  (pair ? launch<F, T, G, true, 1>(ma, mb, P, grid, st) : launch<F, T, G, false, 1>(ma, mb, P, grid, st))
 #define MOE_TC_LAUNCH(F, T) (gemm1 ? MOE_TC_LAUNCH2(F, T, true) : MOE_TC_LAUNCH2(F, T, false))
   if (fp8) return act_dtype == MOE_BF16 ? MOE_TC_LAUNCH(true, __nv_bfloat16) : MOE_TC_LAUNCH(true, __half);
+  if (wide) {
+    if (act_dtype == MOE_BF16)
+      return gemm1 ? launch<false, __nv_bfloat16, true, false, 2>(ma, mb, P, grid, st)
+                   : launch<false, __nv_bfloat16, false, false, 2>(ma, mb, P, grid, st);
+    return gemm1 ? launch<false, __half, true, false, 2>(ma, mb, P, grid, st)
+                 : launch<false, __half, false, false, 2>(ma, mb, P, grid, st);
+  }
   return act_dtype == MOE_BF16 ? MOE_TC_LAUNCH(false, __nv_bfloat16) : MOE_TC_LAUNCH(false, __half);
 #undef MOE_TC_LAUNCH
 #undef MOE_TC_LAUNCH2

@@ -34,7 +34,7 @@ TC_BLOCK_M = 128
 TC_PAIR_BLOCK_M = 256
 GENERIC_BLOCK_M = 16
 # kernel selector passed to moe_gemm1 / moe_gemm2
-KERNEL_GENERIC, KERNEL_TC, KERNEL_TC_PAIR = 0, 1, 2
+KERNEL_GENERIC, KERNEL_TC, KERNEL_TC_PAIR, KERNEL_TC_WIDE = 0, 1, 2, 3
 
 _SUPPORTED_ACTIVATIONS = ("silu", "swigluoai_uninterleave")
 _ALL_ACTIVATIONS = ("silu", "gelu", "relu2", "swigluoai", "swigluoai_uninterleave", "swiglustep",
@@ -53,26 +53,31 @@ def _force_generic() -> bool:
     return os.environ.get("FLAGGEMS_B200_GENERIC_GEMM", "0").lower() in ("1", "true", "yes", "on")
 
 
-def _pair_policy() -> str:
-    """FLAGGEMS_B200_TC_PAIR = 0 (never), 1 (always when the tensor-core kernel runs), auto."""
-    v = os.environ.get("FLAGGEMS_B200_TC_PAIR", "auto").lower()
+def _policy(var: str) -> str:
+    """Environment switch: 0 / off, 1 / on, anything else = auto."""
+    v = os.environ.get(var, "auto").lower()
     return {"0": "off", "off": "off", "1": "on", "on": "on"}.get(v, "auto")
 
 
 def _choose_kernel(mode, act_dtype, H, I, numel, num_experts):
+    """Which GEMM kernel serves the call.  FLAGGEMS_B200_GENERIC_GEMM=1 forces the generic
+    kernel, FLAGGEMS_B200_TC_WIDE / FLAGGEMS_B200_TC_PAIR = 0/1 force the 256-row variants
+    off/on (tests and experiments); otherwise:
+
+    * FP8 block scales: one CTA per 128-row block.  (The cta_group::2 pair loses there: the
+      per-K-block accumulator hand-off would cross two SMs; GEMM1 3.6 -> 4.2 ms at M=8192.)
+    * half precision / widened int8 with >= 512 rows per expert: the 256x256 single-CTA tile,
+      which fetches each weight tile once per 256 rows.
+    """
     if _force_generic() or not _tc_eligible(mode, act_dtype, H, I):
         return KERNEL_GENERIC
-    policy = _pair_policy()
-    if policy == "on":
+    wide, pair = _policy("FLAGGEMS_B200_TC_WIDE"), _policy("FLAGGEMS_B200_TC_PAIR")
+    if wide == "on" and mode == _lib.MODE_HALF:
+        return KERNEL_TC_WIDE
+    if pair == "on":
         return KERNEL_TC_PAIR
-    if policy == "off":
-        return KERNEL_TC
-    # CTA pairs (cta_group::2, 256-row align blocks) halve the L2 -> shared-memory weight
-    # traffic.  Measured on B200: a gain for the half-precision GEMMs from ~512 rows per
-    # expert on (Mixtral shape M=4096: 781 -> 812 TFLOP/s, M=16384: 715 -> 786); a loss
-    # for FP8 block scales, whose per-K-block accumulator hand-off then crosses two SMs.
-    if mode == _lib.MODE_HALF and numel >= 512 * num_experts:
-        return KERNEL_TC_PAIR
+    if mode == _lib.MODE_HALF and numel >= 512 * num_experts and wide != "off":
+        return KERNEL_TC_WIDE
     return KERNEL_TC
 
 
@@ -141,7 +146,8 @@ def route_pipeline(a_rows, a_scales_t, w1, w2, route_weight, topk_ids, *, mode, 
         kernel = _choose_kernel(mode, act_dtype, H, I, numel, global_num_experts)
     else:
         kernel = int(use_tensor_cores)
-    block_m = {KERNEL_GENERIC: GENERIC_BLOCK_M, KERNEL_TC: TC_BLOCK_M, KERNEL_TC_PAIR: TC_PAIR_BLOCK_M}[kernel]
+    block_m = {KERNEL_GENERIC: GENERIC_BLOCK_M, KERNEL_TC: TC_BLOCK_M, KERNEL_TC_PAIR: TC_PAIR_BLOCK_M,
+               KERNEL_TC_WIDE: TC_PAIR_BLOCK_M}[kernel]
 
     # every expert that owns at least one route pads by < block_m
     rows_cap = round_up(numel + min(numel, global_num_experts) * (block_m - 1), block_m)

@@ -123,7 +123,10 @@ int moe_widen_int8(const void* src, void* dst, int dst_dtype, int64_t n, void* s
  *   rows_cap % 128 == 0, I % 128 == 0, H % 128 == 0 for FP8 / H % 64 == 0 for half);
  *   2 = tcgen05 kernel, a cta_group::2 CTA pair per 256-row align block
  *   (block_m must be 256, rows_cap % 256 == 0): each weight tile is fetched once
- *   per 256 rows.  GEMM1 and GEMM2 of one layer must use the same block_m.
+ *   per 256 rows;
+ *   3 = tcgen05 kernel, one CTA per 256-row align block with a 256x256 tile whose two
+ *   accumulators fill TMEM (half precision only, block_m 256).
+ *   GEMM1 and GEMM2 of one layer must use the same block_m.
  */
 int moe_gemm1(int mode, int act_dtype, const void* a, const float* a_scales_t, int64_t num_tokens,
               int topk, const void* w1, const float* w1_scale, const int32_t* expert_ids,
