@@ -391,7 +391,7 @@ tc_gemm_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant_
     }
     for (int a = 0; a < 2; ++a) {
       mbar_init(&aux->tmem_full[a], 1);
-      mbar_init(&aux->tmem_empty[a], UNIT * (EPI_THREADS / 32));  // the leader also collects the partner's warps
+      mbar_init(&aux->tmem_empty[a], CTAS * (EPI_THREADS / 32));  // a pair's leader also collects the partner's warps
     }
     mbar_init(&aux->xch_bar, EPI_THREADS);
     asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
