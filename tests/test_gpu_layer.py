@@ -383,3 +383,16 @@ def test_layer_under_cuda_graph_replay_with_new_inputs():
         ow, oi = O.grouped_topk_oracle(logits, 8, 4, k, True, 2.5, bias, 1)
         assert torch.equal(ti.cpu(), oi)
         _assert_parity(out, O.fused_moe_fp8_block_oracle(x, w1, w2, s1, s2, ow, oi), f"replay {seed}")
+
+
+def test_empty_batch_and_single_token():
+    E, H, I, k = 8, 128, 256, 2
+    w1 = T.make_half_weights(E, 2 * I, H, DEV, seed=1, std=H**-0.5)
+    w2 = T.make_half_weights(E, H, I, DEV, seed=2, std=I**-0.5)
+    x0 = torch.empty((0, H), device=DEV, dtype=torch.bfloat16)
+    out0 = fg.fused_experts_impl(x0, w1, w2, torch.empty((0, k), device=DEV), torch.empty((0, k), device=DEV,
+                                                                                           dtype=torch.int32))
+    assert out0.shape == (0, H)
+    x1 = T.make_activations(1, H, DEV)
+    tw, ti = _route(1, E, k, torch.bfloat16)
+    _assert_parity(fg.fused_experts_impl(x1, w1, w2, tw, ti), O.fused_moe_half_oracle(x1, w1, w2, tw, ti))
