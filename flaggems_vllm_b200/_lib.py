@@ -25,6 +25,8 @@ SYMBOLS = {
     "moe_last_error": (c_char_p, []),
     "moe_grouped_topk": (c_int, [c_void_p, c_int, c_int64, c_int64, c_void_p, c_int, c_void_p, c_int64, c_int,
                                  c_int, c_int, c_int, c_int, c_float, c_int, c_void_p, c_void_p, c_void_p]),
+    "moe_topk_route": (c_int, [c_void_p, c_int, c_void_p, c_void_p, c_int64, c_int, c_int, c_int, c_int, c_float,
+                               c_void_p, c_void_p, c_int, c_void_p, c_void_p]),
     "moe_align_block_size": (c_int, [c_void_p, c_int, c_int64, c_int, c_int, c_void_p, c_int64, c_void_p,
                                      c_int64, c_void_p, c_void_p, c_void_p]),
     "moe_per_token_group_quant_fp8": (c_int, [c_void_p, c_int, c_int64, c_int64, c_int, c_void_p, c_void_p,

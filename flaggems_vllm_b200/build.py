@@ -15,7 +15,7 @@ HERE = os.path.dirname(os.path.abspath(__file__))
 CSRC = os.path.join(HERE, "csrc")
 LIB = os.path.join(HERE, "libmoe_sm100.so")
 STAMP = LIB + ".srchash"
-SOURCES = ["common.cu", "grouped_topk.cu", "align.cu", "quant.cu", "gemm_simt.cu", "gemm_tc.cu",
+SOURCES = ["common.cu", "grouped_topk.cu", "topk_route.cu", "align.cu", "quant.cu", "gemm_simt.cu", "gemm_tc.cu",
            "gemm_api.cu"]
 
 

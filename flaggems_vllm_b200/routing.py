@@ -95,3 +95,82 @@ def grouped_topk(
         ids.data_ptr(), _lib.stream_of(scores))
     _lib.check(rc)
     return weights, ids
+
+
+def _launch_topk_route(topk_weights, topk_indices, token_expert_indices, gating_output, renormalize,
+                       e_score_correction_bias, is_padding, *, sigmoid: bool, scale: float) -> None:
+    # argument contract of the reference (src/flaggems_vllm/ops/topk_sigmoid.py:86-126)
+    assert gating_output.ndim == 2 and topk_weights.ndim == 2
+    if gating_output.device.type != "cuda":
+        raise NotImplementedError("Extended top-k routing requires a CUDA device")
+    m, e = gating_output.shape
+    k = topk_weights.shape[1]
+    assert gating_output.is_contiguous()
+    assert gating_output.dtype in (torch.float32, torch.float16, torch.bfloat16)
+    assert topk_weights.dtype == torch.float32 and topk_weights.shape == (m, k)
+    kinds = {torch.int32: 0, torch.int64: 1}
+    if not sigmoid:
+        kinds[torch.uint32] = 2
+    if topk_indices.dtype not in kinds:
+        raise TypeError("topk_indices must be int32/int64/uint32")
+    assert token_expert_indices.dtype == torch.int32
+    assert topk_indices.shape == token_expert_indices.shape == (m, k)
+    assert all(t.is_contiguous() and t.device == gating_output.device
+               for t in (topk_weights, topk_indices, token_expert_indices))
+    assert 0 < k <= min(32, e)
+    if e > 1024:
+        raise NotImplementedError("Top-k routing supports at most 1024 experts")
+    if e_score_correction_bias is not None:
+        assert e_score_correction_bias.shape == (e,)
+        assert e_score_correction_bias.dtype == torch.float32
+        assert e_score_correction_bias.is_contiguous()
+        assert e_score_correction_bias.device == gating_output.device
+    if is_padding is not None:
+        assert is_padding.shape == (m,) and is_padding.dtype == torch.bool
+        assert is_padding.is_contiguous() and is_padding.device == gating_output.device
+    if not m:
+        return
+    pad = is_padding.view(torch.uint8) if is_padding is not None else None
+    rc = _lib.lib().moe_topk_route(
+        gating_output.data_ptr(), _lib.dtype_code(gating_output.dtype), _lib.ptr(e_score_correction_bias),
+        _lib.ptr(pad), m, e, k, int(sigmoid), int(bool(renormalize)), float(scale), topk_weights.data_ptr(),
+        topk_indices.data_ptr(), kinds[topk_indices.dtype], token_expert_indices.data_ptr(),
+        _lib.stream_of(gating_output))
+    _lib.check(rc)
+
+
+def topk_softmax(
+    topk_weights: torch.Tensor,
+    topk_indices: torch.Tensor,
+    token_expert_indices: torch.Tensor,
+    gating_output: torch.Tensor,
+    renormalize: bool = False,
+    e_score_correction_bias: torch.Tensor | None = None,
+    is_padding: torch.Tensor | None = None,
+) -> None:
+    """Route with softmax scores, optionally using bias for expert selection.
+
+    Returned weights are unbiased.  Padded rows have zero weights and expert
+    id -1, with valid expanded token row indices.  Outputs are written in place
+    (src/flaggems_vllm/ops/topk_softmax.py:126-140)."""
+    logger.debug("GEMS TOPK SOFTMAX")
+    _launch_topk_route(topk_weights, topk_indices, token_expert_indices, gating_output, renormalize,
+                       e_score_correction_bias, is_padding, sigmoid=False, scale=1.0)
+
+
+def topk_sigmoid(
+    topk_weights: torch.Tensor,
+    topk_indices: torch.Tensor,
+    token_expert_indices: torch.Tensor,
+    gating_output: torch.Tensor,
+    renormalize: bool = False,
+    e_score_correction_bias: torch.Tensor | None = None,
+    routed_scaling_factor: float = 1.0,
+    is_padding: torch.Tensor | None = None,
+) -> None:
+    """Route with sigmoid scores, then scale the optionally normalised weights.
+
+    Bias affects expert selection only (src/flaggems_vllm/ops/topk_sigmoid.py:203-226)."""
+    logger.debug("GEMS TOPK SIGMOID")
+    _launch_topk_route(topk_weights, topk_indices, token_expert_indices, gating_output, renormalize,
+                       e_score_correction_bias, is_padding, sigmoid=True, scale=routed_scaling_factor)

@@ -66,6 +66,21 @@ int moe_grouped_topk(const void* scores, int scores_dtype, int64_t stride0, int6
                      float* topk_weights, int32_t* topk_ids, void* stream);
 
 /*
+ * Non-grouped routers: softmax (sigmoid = 0) or sigmoid (1) scores of logits[M,E]
+ * (contiguous), optional fp32 selection bias[E], optional padding mask, top-k
+ * with ties to the lower expert id; weights are the unbiased scores, divided by
+ * their sum when renormalize (if the sum is positive), times `scale`.  Outputs
+ * are caller-owned: topk_weights[M,topk] fp32, topk_indices[M,topk] (index_kind
+ * 0 int32, 1 int64, 2 uint32), token_expert_indices[M,topk] int32 = slot*M + token.
+ * Stands in for topk_softmax (src/flaggems_vllm/ops/topk_softmax.py:126-202) and
+ * topk_sigmoid (src/flaggems_vllm/ops/topk_sigmoid.py:92-226).  Limits: E <= 1024, topk <= 32.
+ */
+int moe_topk_route(const void* logits, int logits_dtype, const float* bias, const uint8_t* is_padding,
+                   int64_t M, int E, int topk, int sigmoid, int renormalize, float scale,
+                   float* topk_weights, void* topk_indices, int index_kind,
+                   int32_t* token_expert_indices, void* stream);
+
+/*
  * Stable counting sort of the flat expert-id array with per-expert padding to
  * block_size.  Stands in for moe_align_block_size_triton
  * (src/flaggems_vllm/ops/moe_align_block_size.py:607-718; stages :414-527).

@@ -155,6 +155,32 @@ def routing_margin_ulps(
     return m
 
 
+def topk_route_oracle(logits, bias, k, renormalize, sigmoid, scale=1.0, is_padding=None):
+    """Non-grouped routers (tests/test_topk_sigmoid.py:11-24, tests/test_topk_softmax.py:146-164):
+    p = sigmoid or softmax of the logits with NaN -> 0 (a softmax row holding NaN or +inf
+    is all zeros), choice = p + bias, stable descending top-k of choice, weights = p
+    gathered, divided by their sum when renormalising (if positive), times ``scale``;
+    padded rows give weight 0 and id -1; source[m, j] = j * M + m.  Scores are the
+    double-precision values rounded once to fp32 (see ``_sigmoid_f32``)."""
+    x = logits.detach().cpu().double()
+    p = (torch.sigmoid(x) if sigmoid else torch.softmax(x, dim=-1)).float()
+    p = torch.nan_to_num(p, nan=0.0)
+    choice = p if bias is None else p + bias.detach().cpu().float()
+    ids = torch.argsort(choice, dim=-1, descending=True, stable=True)[:, :k]
+    w = p.gather(1, ids)
+    if renormalize:
+        den = w.sum(-1, keepdim=True)
+        w = w / torch.where(den > 0, den, torch.ones_like(den))
+    w = w * scale
+    m = x.shape[0]
+    source = (torch.arange(k)[None, :] * m + torch.arange(m)[:, None]).int()
+    if is_padding is not None:
+        pad = is_padding.detach().cpu().bool()
+        w = w.masked_fill(pad[:, None], 0.0)
+        ids = ids.masked_fill(pad[:, None], -1)
+    return w, ids, source
+
+
 def softmax_topk_oracle(gating: torch.Tensor, topk: int, dtype: torch.dtype):
     """softmax -> top-k -> renormalise, ids int32
     (tests/test_fused_experts_impl.py:142-146)."""

@@ -199,6 +199,17 @@ def main(ref_root: str):
         save(f"layer_w8a16_{i}.npz", x=x, w1=w1, w2=w2, w1_scale=s1.squeeze(-1),
              w2_scale=s2.squeeze(-1), topk_weights=tw.float(), topk_ids=ti, out=ref.float())
 
+    # ------------------------------------------------------------ non-grouped routers
+    ts = lift(os.path.join(tests, "test_topk_sigmoid.py"), ["reference"], base)
+    g = torch.Generator().manual_seed(31)
+    for i, (m, e, k, ren, bias_on) in enumerate([(7, 128, 8, True, True), (64, 256, 4, False, False),
+                                                 (5, 64, 8, True, False)]):
+        logits = torch.randn((m, e), generator=g)
+        bias = torch.randn((e,), generator=g) * 0.1 if bias_on else None
+        w, ids, src = ts["reference"](logits, bias, k, ren)
+        save(f"topk_sigmoid_{i}.npz", logits=logits, bias=bias if bias is not None else torch.zeros(0),
+             params=np.array([k, int(ren), int(bias_on)]), weights=w, ids=ids.int(), source=src)
+
     # ------------------------------------------------------------ fp8 quant
     qt = lift(os.path.join(tests, "test_per_token_group_quant_fp8.py"),
               ["native_per_token_group_quant_fp8"], base)

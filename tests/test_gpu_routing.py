@@ -135,3 +135,84 @@ def test_cuda_graph_replay_with_new_scores():
         ow, oi = O.grouped_topk_oracle(fresh, 8, 4, 8, True, 2.5, bias, 1)
         assert torch.equal(ids.cpu(), oi)
         torch.testing.assert_close(w.cpu(), ow, rtol=2e-6, atol=2e-6)
+
+
+# ---------------------------------------------------------------- non-grouped routers
+def _route_outputs(m, k, index_dtype=torch.int32):
+    return (torch.empty((m, k), device=DEV), torch.empty((m, k), device=DEV, dtype=index_dtype),
+            torch.empty((m, k), device=DEV, dtype=torch.int32))
+
+
+@pytest.mark.parametrize("name", golden_files("topk_sigmoid_"))
+def test_topk_sigmoid_golden_vectors(name):
+    g = load_golden(name)
+    k, ren, bias_on = [int(v) for v in g["params"]]
+    logits = g["logits"].to(DEV)
+    w, ids, src = _route_outputs(logits.shape[0], k)
+    fg.topk_sigmoid(w, ids, src, logits, bool(ren), g["bias"].to(DEV) if bias_on else None)
+    assert torch.equal(ids.cpu(), g["ids"]) and torch.equal(src.cpu(), g["source"])
+    torch.testing.assert_close(w.cpu(), g["weights"], atol=2e-7, rtol=2e-6)
+
+
+@pytest.mark.parametrize("dtype", [torch.float16, torch.bfloat16, torch.float32])
+@pytest.mark.parametrize("shape", [(0, 32, 4), (1, 64, 8), (7, 128, 8), (64, 256, 4), (4096, 128, 8), (33, 1000, 32)])
+@pytest.mark.parametrize("renormalize", [False, True])
+@pytest.mark.parametrize("bias_on", [False, True])
+@pytest.mark.parametrize("sigmoid", [False, True])
+def test_topk_routers_match_oracle(dtype, shape, renormalize, bias_on, sigmoid):
+    m, e, k = shape
+    logits = (torch.randn((m, e), generator=torch.Generator().manual_seed(31)) * 2).to(dtype).to(DEV)
+    bias = (torch.randn((e,), generator=torch.Generator().manual_seed(5)) * 0.1).to(DEV) if bias_on else None
+    for idt in (torch.int32, torch.int64):
+        w, ids, src = _route_outputs(m, k, idt)
+        if sigmoid:
+            fg.topk_sigmoid(w, ids, src, logits, renormalize, bias, 2.5)
+        else:
+            fg.topk_softmax(w, ids, src, logits, renormalize, bias)
+        ow, oi, osrc = O.topk_route_oracle(logits, bias, k, renormalize, sigmoid, 2.5 if sigmoid else 1.0)
+        assert torch.equal(ids.cpu().long(), oi) and torch.equal(src.cpu(), osrc)
+        torch.testing.assert_close(w.cpu(), ow, atol=2e-7, rtol=2e-6)
+
+
+@pytest.mark.parametrize("normalize", [False, True])
+@pytest.mark.parametrize("expert_count", [5, 256, 257, 512])
+@pytest.mark.parametrize("sigmoid", [False, True])
+def test_topk_routers_bias_padding_and_nonfinite(normalize, expert_count, sigmoid):
+    # the fixture of tests/test_topk_softmax.py:121-164 in the reference
+    logits = torch.tensor([[2, 1, 0, 1, 4], [4, 3, 2, 1, 0], [1, 3, 2, 3, 0], [float("nan"), 1, 2, 3, 4],
+                           [float("inf"), 1, 2, 3, 4], [float("-inf")] * 5], device=DEV)
+    bias = torch.tensor([0.0, 0.75, 0.0, 0.75, -0.5], device=DEV)
+    if expert_count > 5:
+        extra = torch.arange(expert_count - 5, device=DEV)
+        logits = torch.cat((logits, (extra.remainder(13).float() / 5 - 2).expand(6, -1)), dim=1).contiguous()
+        bias = torch.cat((bias, (extra.remainder(7).float() - 3) * 0.03125))
+    padding = torch.tensor([False, True, False, False, False, False], device=DEV)
+    w, ids, src = _route_outputs(6, 3, torch.int64)
+    if sigmoid:
+        fg.topk_sigmoid(w, ids, src, logits, normalize, bias, 1.0, padding)
+    else:
+        fg.topk_softmax(w, ids, src, logits, normalize, bias, padding)
+    ow, oi, osrc = O.topk_route_oracle(logits, bias, 3, normalize, sigmoid, is_padding=padding)
+    assert torch.equal(ids.cpu(), oi) and torch.equal(src.cpu(), osrc)
+    torch.testing.assert_close(w.cpu(), ow, atol=2e-7, rtol=2e-6)
+    assert torch.all(w[1] == 0) and torch.all(ids[1] == -1)
+
+
+def test_topk_sigmoid_ties_nan_and_graph_replay():
+    logits = torch.zeros((3, 128), device=DEV)
+    logits[1] = float("nan")
+    logits[2] = -float("inf")
+    w, ids, src = _route_outputs(3, 8)
+    fg.topk_sigmoid(w, ids, src, logits, True)
+    ow, oi, _ = O.topk_route_oracle(logits, None, 8, True, True)
+    assert torch.equal(ids.cpu().long(), oi)
+    torch.testing.assert_close(w.cpu(), ow)
+    graph = torch.cuda.CUDAGraph()
+    with torch.cuda.graph(graph):
+        fg.topk_sigmoid(w, ids, src, logits, True)
+    logits.copy_(torch.randn_like(logits))
+    graph.replay()
+    torch.cuda.synchronize()
+    ow, oi, _ = O.topk_route_oracle(logits, None, 8, True, True)
+    assert torch.equal(ids.cpu().long(), oi)
+    torch.testing.assert_close(w.cpu(), ow, atol=2e-7, rtol=2e-6)

@@ -178,3 +178,31 @@ def test_block_matmul_oracle_against_plain_dequant():
     ad = aq.float() * as_.repeat_interleave(128, dim=1)
     bd = bq[0].float() * bs[0].repeat_interleave(128, 0).repeat_interleave(128, 1)
     torch.testing.assert_close(c, ad @ bd.t(), rtol=1e-4, atol=1e-4)
+
+
+@pytest.mark.parametrize("name", golden_files("topk_sigmoid_"))
+def test_topk_sigmoid_matches_reference_golden(name):
+    g = load_golden(name)
+    k, ren, bias_on = [int(v) for v in g["params"]]
+    w, ids, src = O.topk_route_oracle(g["logits"], g["bias"] if bias_on else None, k, bool(ren), True)
+    assert torch.equal(ids.int(), g["ids"]) and torch.equal(src, g["source"])
+    torch.testing.assert_close(w, g["weights"], atol=2e-7, rtol=2e-6)
+
+
+def test_topk_softmax_known_answer_bias_padding_nonfinite():
+    # reference: tests/test_topk_softmax.py:121-164
+    logits = torch.tensor([[2, 1, 0, 1, 4], [4, 3, 2, 1, 0], [1, 3, 2, 3, 0], [float("nan"), 1, 2, 3, 4],
+                           [float("inf"), 1, 2, 3, 4], [float("-inf")] * 5])
+    bias = torch.tensor([0.0, 0.75, 0.0, 0.75, -0.5])
+    padding = torch.tensor([False, True, False, False, False, False])
+    for ren in (False, True):
+        w, ids, src = O.topk_route_oracle(logits, bias, 3, ren, False, is_padding=padding)
+        probabilities = torch.softmax(logits.float(), dim=-1).nan_to_num()
+        exp_ids = torch.argsort(probabilities + bias, dim=-1, descending=True, stable=True)[:, :3]
+        exp_w = probabilities.gather(1, exp_ids)
+        if ren:
+            den = exp_w.sum(-1, keepdim=True)
+            exp_w = exp_w / torch.where(den > 0, den, torch.ones_like(den))
+        assert torch.equal(ids, exp_ids.masked_fill(padding[:, None], -1))
+        torch.testing.assert_close(w, exp_w.masked_fill(padding[:, None], 0))
+        assert torch.equal(src, (torch.arange(3)[None, :] * 6 + torch.arange(6)[:, None]).int())
