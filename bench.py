@@ -305,6 +305,9 @@ def main():
     ap.add_argument("--ref-tokens", type=int, default=4, help="tokens per step of the CPU reference arm")
     ap.add_argument("--cpu-baseline-tokens", type=int, default=16)
     ap.add_argument("--no-cpu-baseline", action="store_true")
+    ap.add_argument("--router-bias-std", type=float, default=0.02,
+                    help="spread of the synthetic score-correction bias; the scores are i.i.d., so a small "
+                         "spread gives the balanced expert load a trained bias produces")
     ap.add_argument("--experts", type=int, default=DSV3["E"],
                     help="expert count (smaller values give the small case used for ncu captures)")
     ap.add_argument("--sweep", default="", help="comma list of dsv3,mixtral,qwen3,align,routing: print one line per point")
@@ -342,7 +345,7 @@ def main():
     w1, s1 = T.make_fp8_block_weights(E_local, 2 * I, H, dev, seed=100 + rank)
     w2, s2 = T.make_fp8_block_weights(E_local, H, I, dev, seed=200 + rank)
     x = T.make_activations(M, H, dev, seed=300 + rank)
-    logits, bias = T.make_router_inputs(M, E, dev, seed=400 + rank)
+    logits, bias = T.make_router_inputs(M, E, dev, seed=400 + rank, bias_std=args.router_bias_std)
     if world > 1:
         dist.broadcast(bias, 0)
     flush = torch.empty(2 * L2_BYTES, dtype=torch.uint8, device=dev)
@@ -486,7 +489,7 @@ def main():
         "steps": args.steps, "warmup": args.warmup, "ms_per_step": ms, "higher_is_better": True,
         "scaling": "weak", "vs_baseline": None, "dtype": "fp8_e4m3", "data": "synthetic",
         "config": {"workload": "deepseek_v3_fp8_block_moe_layer", "tokens_per_gpu": M, "global_tokens": total_tokens,
-                   **c, "experts_per_gpu": E_local, "parallelism": f"ep{world}" if world > 1 else "single",
+                   **c, "experts_per_gpu": E_local, "router_bias_std": args.router_bias_std, "parallelism": f"ep{world}" if world > 1 else "single",
                    "l2": "flushed between iterations (252 MB memset); weights 11.3 GB >> L2"},
         "tflops": flops / (ms * 1e-3) / 1e12,
         "e2e": {"value": total_tokens / (e2e_ms * 1e-3), "unit": "tokens/s", "ms_per_step": e2e_ms,

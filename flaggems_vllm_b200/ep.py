@@ -9,9 +9,10 @@ keeps a token's 8 experts inside 4 of 8 groups, so with one group per rank
 dispatch and combine move half the rows a per-route exchange would).
 
     plan       which ranks each token visits (a [M, R] mask), counts all-to-all
-    dispatch   all-to-all of the rows (FP8 mode: e4m3 row + 1x128 scales, half
-               the bytes of a bf16 row) and of k (local expert id, weight)
-               slots per row, -1 marking slots that belong to other ranks
+    dispatch   all-to-all of the rows (FP8 mode: e4m3, half the bytes of a bf16
+               row) and of one fp32 side row per pair (the token's k expert ids
+               and weights, plus its 1x128 scales in FP8 mode); the receiver
+               marks the slots that belong to other ranks with -1
     compute    align -> GEMM1 -> GEMM2 over the received rows with their k
                slots, then the fixed-order sum of each row's local routes: the
                result is already the per-(token, rank) partial output, in
@@ -33,7 +34,8 @@ import torch
 import torch.distributed as dist
 
 from . import _lib
-from .fused_moe import combine_routes, quantize_rows, route_pipeline
+from .fused_moe import combine_routes, route_pipeline
+from .quant import per_token_group_quant_fp8
 
 
 def plan_dispatch(topk_ids: torch.Tensor, experts_per_rank: int, world: int):
@@ -108,35 +110,32 @@ class ExpertParallelMoE:
         n_send, n_recv = sum(send_splits), sum(recv_splits)
         self.last_counts = (send_splits, recv_splits)
 
-        # ---- slots of each pair: (local expert id, weight) for routes that live on its rank, else (-1, 0)
-        mine = dest[tok] == dst[:, None]
-        slot_ids = torch.where(mine, topk_ids[tok].long() % self.E_local, torch.full_like(dest[tok], -1))
-        slot_w = torch.where(mine, topk_weights[tok].float(), torch.zeros((), device=dev))
-        meta_send = torch.cat([slot_ids.float(), slot_w], dim=1).contiguous()  # ids < 2^24: exact in fp32
-        meta_recv = torch.empty((n_recv, 2 * k), dtype=torch.float32, device=dev)
-        self._a2a(meta_recv, meta_send, recv_splits, send_splits)
-
-        # ---- rows, in send order
+        # ---- side data of each pair: the token's k global expert ids and weights (and, in FP8 mode,
+        # its 1x128 scales) travel as one fp32 row; the receiver keeps the ids it owns
+        g = H // 128 if fp8 else 0
         if fp8:
-            xq, xs_t = quantize_rows(x)
-            g = H // 128
-            pay_send = torch.empty((n_send, H + 4 * g), dtype=torch.uint8, device=dev)
-            pay_send[:, :H] = xq.view(torch.uint8)[tok]
-            pay_send[:, H:] = xs_t.t()[tok].contiguous().view(torch.uint8)
-            pay_recv = torch.empty((n_recv, H + 4 * g), dtype=torch.uint8, device=dev)
-            self._a2a(pay_recv, pay_send, recv_splits, send_splits)
-            a_rows = pay_recv[:, :H].contiguous().view(torch.float8_e4m3fn)
-            a_scales_t = pay_recv[:, H:].contiguous().view(torch.float32).t().contiguous()
+            xq, xs = per_token_group_quant_fp8(x, 128)
+            side_send = torch.cat([xs[tok], topk_ids[tok].float(), topk_weights[tok].float()], dim=1)
+            rows_send = xq.view(torch.uint8)[tok]
         else:
+            side_send = torch.cat([topk_ids[tok].float(), topk_weights[tok].float()], dim=1)  # ids < 2^24: exact
             rows_send = x[tok]
-            a_rows = torch.empty((n_recv, H), dtype=x.dtype, device=dev)
-            self._a2a(a_rows, rows_send, recv_splits, send_splits)
+        side_recv = torch.empty((n_recv, g + 2 * k), dtype=torch.float32, device=dev)
+        self._a2a(side_recv, side_send, recv_splits, send_splits)
+        a_rows = torch.empty((n_recv, H), dtype=rows_send.dtype, device=dev)
+        self._a2a(a_rows, rows_send, recv_splits, send_splits)
+        if fp8:
+            a_rows = a_rows.view(torch.float8_e4m3fn)
+            a_scales_t = side_recv[:, :g].t().contiguous()
+        else:
             a_scales_t = None
+        local = side_recv[:, g:g + k].to(torch.int32) - self.rank * self.E_local
+        slot_ids = torch.where((local >= 0) & (local < self.E_local), local, -1)  # -1: another rank's route
+        slot_w = side_recv[:, g + k:].contiguous()
 
         # ---- local experts over the received rows
         if n_recv > 0:
-            rows = self.compute_fn(a_rows, a_scales_t, meta_recv[:, k:].contiguous(),
-                                   meta_recv[:, :k].to(torch.int32).contiguous(), x.dtype)
+            rows = self.compute_fn(a_rows, a_scales_t, slot_w, slot_ids, x.dtype)
         else:
             rows = torch.empty((0, H), dtype=x.dtype, device=dev)
 
