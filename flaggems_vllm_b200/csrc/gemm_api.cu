@@ -12,6 +12,10 @@ int tc_gemm(bool gemm1, int mode, int act_dtype, const void* a, const float* a_s
             const float* route_weight, int mul_weight, int64_t numel, int64_t rows_cap, int64_t a_tokens, int topk,
             int block_m, int E, int K, int Nout, void* out, float* out_scales_t, int32_t* status, cudaStream_t st,
             int variant);
+int w8_gemm(bool gemm1, int act_dtype, const void* a, const void* w, const float* w_scale, const int32_t* expert_ids,
+            const int32_t* sorted_ids, const int32_t* npp, const float* route_weight, int mul_weight, int64_t numel,
+            int64_t rows_cap, int64_t a_tokens, int topk, int block_m, int E, int K, int Nout, void* out,
+            int32_t* status, cudaStream_t st);
 
 static int check_common(const char* who, int mode, const void* a, const float* a_scales, const void* w,
                         const float* w_scale, const int32_t* expert_ids, const int32_t* sorted_ids,
@@ -40,6 +44,9 @@ extern "C" int moe_gemm1(int mode, int act_dtype, const void* a, const float* a_
   if (rc) return rc;
   if (mode == MOE_MODE_FP8_BLOCK && !out_scales_t) return fail(MOE_E_BADARG, "gemm1: output scale buffer missing");
   if (rows_cap == 0 || numel == 0) return 0;
+  if (use_tensor_cores && mode == MOE_MODE_W8A16)  // int8 weights widened inside the kernel
+    return w8_gemm(true, act_dtype, a, w1, w1_scale, expert_ids, sorted_ids, num_post_pad, route_weight, mul_weight,
+                   numel, rows_cap, num_tokens, topk, block_m, E, H, I, out, status, (cudaStream_t)stream);
   if (use_tensor_cores)
     return tc_gemm(true, mode, act_dtype, a, a_scales_t, w1, w1_scale, expert_ids, sorted_ids, num_post_pad,
                    route_weight, mul_weight, numel, rows_cap, num_tokens, topk, block_m, E, H, I, out, out_scales_t,
@@ -59,6 +66,9 @@ extern "C" int moe_gemm2(int mode, int act_dtype, const void* act_sorted, const 
                         route_weight, mul_weight, numel, rows_cap, block_m, E, H, I, y);
   if (rc) return rc;
   if (rows_cap == 0 || numel == 0) return 0;
+  if (use_tensor_cores && mode == MOE_MODE_W8A16)
+    return w8_gemm(false, act_dtype, act_sorted, w2, w2_scale, expert_ids, sorted_ids, num_post_pad, route_weight,
+                   mul_weight, numel, rows_cap, 0, 1, block_m, E, I, H, y, status, (cudaStream_t)stream);
   if (use_tensor_cores)
     return tc_gemm(false, mode, act_dtype, act_sorted, act_scales_t, w2, w2_scale, expert_ids, sorted_ids,
                    num_post_pad, route_weight, mul_weight, numel, rows_cap, 0, 1, block_m, E, I, H, y, nullptr, status,

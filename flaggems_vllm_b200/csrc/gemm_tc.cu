@@ -9,11 +9,14 @@
 //             token sorted_ids[p] / topk, copied by 64 producer threads with
 //             16-byte cp.async into the same 128-byte-swizzled layout TMA
 //             would produce, so no sorted copy of the activations ever exists.
-//   B stage : 256 rows x 128 B  (four TMA boxes of 64 weight rows each)
-// GEMM1 picks the four boxes as {gate lo, up lo, gate hi, up hi} of a 128-wide
-// output tile, so one accumulator holds gate and up of the same output column
-// in the same thread and SiLU(gate)*up plus the 1x128 re-quantisation are done
-// in registers.  GEMM2 uses four consecutive 64-row boxes (256 output columns).
+//             (A lane owns whole rows.  Giving the eight chunks of a row to eight
+//             lanes, so that a warp instruction touches four 128-byte lines instead
+//             of 32, was measured 45 % slower for the whole GEMM.)
+//   B stage : 256 rows x 128 B
+// GEMM1 fetches it as two TMA boxes, 128 gate rows and the 128 up rows of the same
+// 128 outputs, so one accumulator holds gate (columns 0-127) and up (128-255) of
+// an output column in the same thread and SiLU(gate)*up plus the 1x128
+// re-quantisation are done in registers.  GEMM2 fetches one box of 256 rows.
 //
 // Warp roles (384 threads):
 //   warp 0      TMA producer (one lane)
@@ -21,7 +24,8 @@
 //   warp 2      TMEM allocation (512 columns = two 256-column accumulators)
 //   warps 2-3   GEMM1 only: cp.async gather of the A rows (2 rows per thread)
 //   warps 4-11  accumulator consumers, two groups of four warps; group h owns
-//               accumulator columns [128h, 128h+128), warp w lanes 32*(w%4)...
+//               accumulator columns [128h, 128h+128) (GEMM1: gate [64h, 64h+64) and
+//               up [128+64h, 128+64h+64)), warp w lanes 32*(w%4)...
 // FP8 block-scaled mode: the tensor core cannot apply fp32 128x128 / 1x128
 // scales, so every 128-wide K block is multiplied into a fresh TMEM
 // accumulator (the two accumulators alternate) and the consumer warps fold it
@@ -37,12 +41,7 @@
 //
 // Every barrier wait is bounded (wall-clock limit); on expiry the kernel sets
 // MOE_ST_WAIT_TIMEOUT, leaves its loops, frees TMEM and returns.
-#include <cuda.h>
-
-#include <cstring>
-#include <type_traits>
-
-#include "moe_common.cuh"
+#include "tc_common.cuh"
 
 namespace moe {
 namespace tc {
@@ -61,7 +60,6 @@ template <bool PAIR, int RB> struct Cfg {
   static constexpr int A_LOCAL = RB * A_STAGE_BYTES;
   static constexpr int STAGE_BYTES = A_LOCAL + (PAIR ? B_HALF_BYTES : B_STAGE_BYTES);
 };
-constexpr int B_BOX_ROWS = 64;
 constexpr int THREADS = 384;
 constexpr int EPI_THREADS = 256;
 constexpr int GATHER_THREADS = 64;  // warps 2-3 (GEMM1)
@@ -77,7 +75,6 @@ constexpr int CONSUMER_REGS = 224;
 static_assert((THREADS - EPI_THREADS) * PRODUCER_REGS + EPI_THREADS * CONSUMER_REGS <= THREADS * LAUNCH_REGS,
               "register redistribution exceeds the CTA's allocation");
 static_assert(THREADS * LAUNCH_REGS <= 65536, "CTA does not fit the register file");
-constexpr unsigned long long WAIT_LIMIT_NS = 2000000000ull;  // 2 s
 
 struct SmemAux {
   uint64_t full[MAX_STAGES];       // this CTA's operands (and scales) of the stage have landed
@@ -121,180 +118,6 @@ struct Params {
   int n_tiles;  // column tiles per align block
 };
 
-// ------------------------------------------------------------------ PTX wrappers
-__device__ __forceinline__ uint32_t smem_u32(const void* p) {
-  return (uint32_t)__cvta_generic_to_shared(p);
-}
-__device__ __forceinline__ void mbar_init(uint64_t* bar, uint32_t count) {
-  asm volatile("mbarrier.init.shared::cta.b64 [%0], %1;" ::"r"(smem_u32(bar)), "r"(count));
-}
-__device__ __forceinline__ void mbar_expect_tx(uint64_t* bar, uint32_t bytes) {
-  asm volatile("mbarrier.arrive.expect_tx.shared::cta.b64 _, [%0], %1;" ::"r"(smem_u32(bar)), "r"(bytes)
-               : "memory");
-}
-__device__ __forceinline__ void mbar_arrive(uint64_t* bar) {
-  asm volatile("mbarrier.arrive.shared::cta.b64 _, [%0];" ::"r"(smem_u32(bar)) : "memory");
-}
-__device__ __forceinline__ bool mbar_try(uint64_t* bar, uint32_t parity) {
-  uint32_t ok;
-  asm volatile(
-      "{\n\t.reg .pred p;\n\t"
-      "mbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2;\n\t"
-      "selp.u32 %0, 1, 0, p;\n\t}"
-      : "=r"(ok)
-      : "r"(smem_u32(bar)), "r"(parity)
-      : "memory");
-  return ok != 0;
-}
-__device__ __forceinline__ uint32_t cluster_ctarank() {
-  uint32_t r;
-  asm volatile("mov.u32 %0, %%cluster_ctarank;" : "=r"(r));
-  return r;
-}
-// Arrive on the barrier at the same shared-memory offset in CTA `rank` of the cluster.
-// Relaxed: what the leader consumes after this arrival is not generic-proxy data of this
-// thread (TMA / cp.async results fenced to the async proxy, or TMEM already read back by
-// tcgen05.wait::ld), and a release at cluster scope costs about a microsecond per call.
-__device__ __forceinline__ void mbar_arrive_remote(uint64_t* bar, uint32_t rank) {
-  asm volatile(
-      "{\n\t.reg .b32 ra;\n\t"
-      "mapa.shared::cluster.u32 ra, %0, %1;\n\t"
-      "mbarrier.arrive.relaxed.cluster.shared::cluster.b64 _, [ra];\n\t}"
-      ::"r"(smem_u32(bar)), "r"(rank)
-      : "memory");
-}
-__device__ __forceinline__ bool mbar_try_cluster(uint64_t* bar, uint32_t parity) {
-  uint32_t ok;
-  asm volatile(
-      "{\n\t.reg .pred p;\n\t"
-      "mbarrier.try_wait.parity.acquire.cluster.shared::cta.b64 p, [%1], %2;\n\t"
-      "selp.u32 %0, 1, 0, p;\n\t}"
-      : "=r"(ok)
-      : "r"(smem_u32(bar)), "r"(parity)
-      : "memory");
-  return ok != 0;
-}
-__device__ __forceinline__ void cluster_sync_all() {
-  asm volatile("barrier.cluster.arrive.release.aligned;\n\tbarrier.cluster.wait.acquire.aligned;" ::: "memory");
-}
-__device__ __forceinline__ unsigned long long now_ns() {
-  unsigned long long t;
-  asm volatile("mov.u64 %0, %globaltimer;" : "=l"(t));
-  return t;
-}
-// Bounded wait: false when the limit ran out (status word is set).
-// CLUSTER: the barrier is also arrived on by the partner CTA (acquire at cluster scope).
-template <bool CLUSTER = false>
-__device__ __forceinline__ bool mbar_wait(uint64_t* bar, uint32_t parity, int32_t* status) {
-  auto probe = [&]() { return CLUSTER ? mbar_try_cluster(bar, parity) : mbar_try(bar, parity); };
-  if (probe()) return true;
-  const unsigned long long t0 = now_ns();
-  uint32_t spins = 0;
-  while (!probe()) {
-    if ((++spins & 0x3FF) == 0 && now_ns() - t0 > WAIT_LIMIT_NS) {
-      set_status(status, MOE_ST_WAIT_TIMEOUT);
-      return false;
-    }
-  }
-  return true;
-}
-__device__ __forceinline__ void tma_load_2d(const CUtensorMap* map, uint64_t* bar, void* dst, int c0, int c1) {
-  asm volatile(
-      "cp.async.bulk.tensor.2d.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1, {%3, %4}], [%2];"
-      ::"r"(smem_u32(dst)), "l"(map), "r"(smem_u32(bar)), "r"(c0), "r"(c1)
-      : "memory");
-}
-__device__ __forceinline__ void tc_fence_before() { asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory"); }
-__device__ __forceinline__ void tc_fence_after() { asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory"); }
-__device__ __forceinline__ void tc_commit(uint64_t* bar) {
-  asm volatile("tcgen05.commit.cta_group::1.mbarrier::arrive::one.shared::cluster.b64 [%0];" ::"r"(smem_u32(bar))
-               : "memory");
-}
-// cta_group::2: completion is signalled on the barrier at this offset in BOTH CTAs of the pair
-__device__ __forceinline__ void tc_commit_pair(uint64_t* bar) {
-  asm volatile(
-      "tcgen05.commit.cta_group::2.mbarrier::arrive::one.shared::cluster.multicast::cluster.b64 [%0], %1;"
-      ::"r"(smem_u32(bar)), "h"((uint16_t)3)
-      : "memory");
-}
-// One instruction for the pair: M = 256 (128 rows from each CTA), N = 256 (128 B rows from each CTA)
-template <bool FP8>
-__device__ __forceinline__ void tc_mma_pair(uint32_t tmem_d, uint64_t adesc, uint64_t bdesc, uint32_t idesc, uint32_t acc) {
-  if constexpr (FP8) {
-    asm volatile(
-        "{\n\t.reg .pred p;\n\tsetp.ne.b32 p, %4, 0;\n\t"
-        "tcgen05.mma.cta_group::2.kind::f8f6f4 [%0], %1, %2, %3, p;\n\t}"
-        ::"r"(tmem_d), "l"(adesc), "l"(bdesc), "r"(idesc), "r"(acc)
-        : "memory");
-  } else {
-    asm volatile(
-        "{\n\t.reg .pred p;\n\tsetp.ne.b32 p, %4, 0;\n\t"
-        "tcgen05.mma.cta_group::2.kind::f16 [%0], %1, %2, %3, p;\n\t}"
-        ::"r"(tmem_d), "l"(adesc), "l"(bdesc), "r"(idesc), "r"(acc)
-        : "memory");
-  }
-}
-template <bool FP8>
-__device__ __forceinline__ void tc_mma(uint32_t tmem_d, uint64_t adesc, uint64_t bdesc, uint32_t idesc, uint32_t acc) {
-  if constexpr (FP8) {
-    asm volatile(
-        "{\n\t.reg .pred p;\n\tsetp.ne.b32 p, %4, 0;\n\t"
-        "tcgen05.mma.cta_group::1.kind::f8f6f4 [%0], %1, %2, %3, p;\n\t}"
-        ::"r"(tmem_d), "l"(adesc), "l"(bdesc), "r"(idesc), "r"(acc)
-        : "memory");
-  } else {
-    asm volatile(
-        "{\n\t.reg .pred p;\n\tsetp.ne.b32 p, %4, 0;\n\t"
-        "tcgen05.mma.cta_group::1.kind::f16 [%0], %1, %2, %3, p;\n\t}"
-        ::"r"(tmem_d), "l"(adesc), "l"(bdesc), "r"(idesc), "r"(acc)
-        : "memory");
-  }
-}
-// Two 32-column loads and the wait in ONE asm statement: the 64 results only
-// become visible to the compiler after the wait, so nothing can be scheduled
-// between the loads and the wait, and no extra register copies are needed.
-__device__ __forceinline__ void tmem_ld64_sync(uint32_t taddr, uint32_t* a, uint32_t* b) {
-  asm volatile(
-      "tcgen05.ld.sync.aligned.32x32b.x32.b32 "
-      "{%0, %1, %2, %3, %4, %5, %6, %7, %8, %9, %10, %11, %12, %13, %14, %15, "
-      "%16, %17, %18, %19, %20, %21, %22, %23, %24, %25, %26, %27, %28, %29, %30, %31}, [%64];\n\t"
-      "tcgen05.ld.sync.aligned.32x32b.x32.b32 "
-      "{%32, %33, %34, %35, %36, %37, %38, %39, %40, %41, %42, %43, %44, %45, %46, %47, "
-      "%48, %49, %50, %51, %52, %53, %54, %55, %56, %57, %58, %59, %60, %61, %62, %63}, [%65];\n\t"
-      "tcgen05.wait::ld.sync.aligned;"
-      : "=r"(a[0]), "=r"(a[1]), "=r"(a[2]), "=r"(a[3]), "=r"(a[4]), "=r"(a[5]), "=r"(a[6]), "=r"(a[7]),
-        "=r"(a[8]), "=r"(a[9]), "=r"(a[10]), "=r"(a[11]), "=r"(a[12]), "=r"(a[13]), "=r"(a[14]), "=r"(a[15]),
-        "=r"(a[16]), "=r"(a[17]), "=r"(a[18]), "=r"(a[19]), "=r"(a[20]), "=r"(a[21]), "=r"(a[22]), "=r"(a[23]),
-        "=r"(a[24]), "=r"(a[25]), "=r"(a[26]), "=r"(a[27]), "=r"(a[28]), "=r"(a[29]), "=r"(a[30]), "=r"(a[31]),
-        "=r"(b[0]), "=r"(b[1]), "=r"(b[2]), "=r"(b[3]), "=r"(b[4]), "=r"(b[5]), "=r"(b[6]), "=r"(b[7]),
-        "=r"(b[8]), "=r"(b[9]), "=r"(b[10]), "=r"(b[11]), "=r"(b[12]), "=r"(b[13]), "=r"(b[14]), "=r"(b[15]),
-        "=r"(b[16]), "=r"(b[17]), "=r"(b[18]), "=r"(b[19]), "=r"(b[20]), "=r"(b[21]), "=r"(b[22]), "=r"(b[23]),
-        "=r"(b[24]), "=r"(b[25]), "=r"(b[26]), "=r"(b[27]), "=r"(b[28]), "=r"(b[29]), "=r"(b[30]), "=r"(b[31])
-      : "r"(taddr), "r"(taddr + 32)
-      : "memory");
-}
-__device__ __forceinline__ void cp_async16(uint32_t dst_smem, const void* src) {
-  asm volatile("cp.async.cg.shared.global [%0], [%1], 16;" ::"r"(dst_smem), "l"(src) : "memory");
-}
-__device__ __forceinline__ void cp_async4(uint32_t dst_smem, const void* src) {
-  asm volatile("cp.async.ca.shared.global [%0], [%1], 4;" ::"r"(dst_smem), "l"(src) : "memory");
-}
-// The barrier receives one arrival when all earlier cp.async of this thread have landed.
-__device__ __forceinline__ void cp_async_arrive_noinc(uint64_t* bar) {
-  asm volatile("cp.async.mbarrier.arrive.noinc.shared::cta.b64 [%0];" ::"r"(smem_u32(bar)) : "memory");
-}
-// K-major operand tile with 128-byte swizzle: rows are 128 B apart, groups of
-// 8 rows 1024 B apart (stride byte offset), descriptor version 1 (sm_100).
-__device__ __forceinline__ uint64_t make_smem_desc(uint32_t saddr) {
-  uint64_t d = 0;
-  d |= (uint64_t)((saddr & 0x3FFFFu) >> 4);
-  d |= (uint64_t)1 << 16;            // leading byte offset (unused for swizzled K-major)
-  d |= (uint64_t)(1024 >> 4) << 32;  // stride byte offset
-  d |= (uint64_t)1 << 46;            // descriptor version
-  d |= (uint64_t)2 << 61;            // SWIZZLE_128B
-  return d;
-}
-
 // Instruction descriptor: fp32 accumulator (bits 4-5 = 1), A/B element format
 // (bits 7-9 / 10-12: e4m3 = 0 for kind::f8f6f4; f16 = 0, bf16 = 1 for
 // kind::f16), both operands K-major, N >> 3 at bit 17, M >> 4 at bit 24.
@@ -306,34 +129,20 @@ struct IDesc {
       (1u << 4) | (fmt << 7) | (fmt << 10) | ((uint32_t)(BN >> 3) << 17) | ((uint32_t)(m >> 4) << 24);
 };
 
-// weight row (inside the expert) of the first row of B box `c` of column tile `nt`
-template <bool GEMM1>
-__device__ __forceinline__ int box_row(int nt, int c, int Nout) {
-  if constexpr (GEMM1) return nt * 128 + (c >> 1) * 64 + (c & 1) * Nout;  // gate/up interleaved
-  else return nt * BN + c * 64;
-}
-
-template <typename AT>
-__device__ __forceinline__ uint32_t pack2(float a, float b);
-template <>
-__device__ __forceinline__ uint32_t pack2<__nv_bfloat16>(float a, float b) {
-  __nv_bfloat162 v = __floats2bfloat162_rn(a, b);
-  return *reinterpret_cast<uint32_t*>(&v);
-}
-template <>
-__device__ __forceinline__ uint32_t pack2<__half>(float a, float b) {
-  __half2 v = __floats2half2_rn(a, b);
-  return *reinterpret_cast<uint32_t*>(&v);
-}
-// SiLU(g) * u with the fast exponential and division; like the reference kernel
-// (tl.exp / tl.fdiv, src/flaggems_vllm/ops/fused_moe.py:1795) it is accurate
-// to a couple of ulp, far inside the layer tolerance.
-__device__ __forceinline__ float silu_mul_fast(float g, float u) {
-  return __fdividef(g, 1.0f + __expf(-g)) * u;
-}
-template <typename AT>
-__device__ __forceinline__ float round_act(float v) {
-  return ToF32<AT>::get(from_f32<AT>(v));
+// B tile = 256 accumulator columns = 256 weight rows, fetched with as few TMA instructions
+// as the weight layout allows (every instruction costs the single producer thread issue
+// time, whatever the box size).  GEMM1: columns [0,128) are gate rows nt*128.., columns
+// [128,256) the up rows of the same outputs: two boxes of 128 rows (a CTA pair: one each).
+// GEMM2: 256 consecutive rows, one box (a pair: 128 rows each).
+template <bool GEMM1, bool PAIR> struct BBox {
+  static constexpr int COUNT = (GEMM1 && !PAIR) ? 2 : 1;  // boxes per CTA and stage
+  static constexpr int ROWS = (GEMM1 || PAIR) ? 128 : 256;
+};
+// weight row (inside the expert) of the first row of this CTA's box `c` of column tile `nt`
+template <bool GEMM1, bool PAIR>
+__device__ __forceinline__ int box_row(int nt, int c, int cr, int Nout) {
+  if constexpr (GEMM1) return nt * 128 + (PAIR ? cr : c) * Nout;
+  else return nt * BN + (PAIR ? cr * 128 : 0);
 }
 
 // PAIR = true: two CTAs of a cluster work as one cta_group::2 unit on a 256-row
@@ -439,12 +248,10 @@ tc_gemm_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant_
               tma_load_2d(&map_a, &aux->full[s], sA + (size_t)s * A_LOCAL_BYTES + j * A_STAGE_BYTES, kb * KBE,
                           row0 + j * BM);
           }
-          // 64-row boxes of the B tile: all four, or (pair) the two of this CTA's column half
-          constexpr int NBOX = PAIR ? 2 : 4;
 #pragma unroll
-          for (int c = 0; c < NBOX; ++c)
-            tma_load_2d(&map_b, &aux->full[s], sB + (size_t)s * B_LOCAL_BYTES + c * (B_BOX_ROWS * 128), kb * KBE,
-                        wrow0 + box_row<GEMM1>(nt, NBOX * cr + c, P.Nout));
+          for (int c = 0; c < BBox<GEMM1, PAIR>::COUNT; ++c)
+            tma_load_2d(&map_b, &aux->full[s], sB + (size_t)s * B_LOCAL_BYTES + c * (BBox<GEMM1, PAIR>::ROWS * 128),
+                        kb * KBE, wrow0 + box_row<GEMM1, PAIR>(nt, c, cr, P.Nout));
         }
       }
     } else if (warp == 1 && lane == 0 && cr == 0) {
@@ -587,7 +394,8 @@ tc_gemm_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant_
     asm volatile("setmaxnreg.inc.sync.aligned.u32 %0;" ::"n"(CONSUMER_REGS));
     const int h = (warp - 4) >> 2;                  // column half owned by this group
     const int row = ((warp & 3) << 5) + lane;       // accumulator lane = tile row
-    const uint32_t t_lane = tmem_base + ((uint32_t)((warp & 3) << 5) << 16) + (uint32_t)(h * 128);
+    const uint32_t t_lane = tmem_base + ((uint32_t)((warp & 3) << 5) << 16) + (uint32_t)(h * (GEMM1 ? 64 : 128));
+    constexpr uint32_t SECOND = GEMM1 ? 128 : 64;  // column distance of the group's second 64-column chunk
     uint32_t acc_it = 0, tile_it = 0;
     bool alive = true;
     // releasing an accumulator: the pair's leader collects the arrivals of both CTAs
@@ -625,7 +433,7 @@ tc_gemm_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant_
           for (int i = 0; i < 32; ++i) acc[i] = fmaf(__uint_as_float(ra[i]), s_lo, acc[i]);
 #pragma unroll
           for (int i = 0; i < 32; ++i) acc[32 + i] = fmaf(__uint_as_float(rb[i]), s_lo, acc[32 + i]);
-          tmem_ld64_sync(t0 + 64, ra, rb);
+          tmem_ld64_sync(t0 + SECOND, ra, rb);
           release_acc(a);
 #pragma unroll
           for (int i = 0; i < 32; ++i) acc[64 + i] = fmaf(__uint_as_float(ra[i]), s_hi, acc[64 + i]);
@@ -655,7 +463,7 @@ tc_gemm_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant_
         const uint32_t t0 = t_lane + (RB == 2 ? (uint32_t)sub : a) * BN;
         uint32_t* r = reinterpret_cast<uint32_t*>(acc);
         tmem_ld64_sync(t0, r, r + 32);
-        tmem_ld64_sync(t0 + 64, r + 64, r + 96);
+        tmem_ld64_sync(t0 + SECOND, r + 64, r + 96);
         if (sub == RB - 1) {  // everything of this tile is in registers (or already stored)
           release_acc(a);
           ++acc_it;
@@ -767,43 +575,6 @@ tc_gemm_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant_
 }
 
 // ------------------------------------------------------------------ host side
-typedef CUresult (*EncodeTiledFn)(CUtensorMap*, CUtensorMapDataType, cuuint32_t, void*, const cuuint64_t*,
-                                  const cuuint64_t*, const cuuint32_t*, const cuuint32_t*, CUtensorMapInterleave,
-                                  CUtensorMapSwizzle, CUtensorMapL2promotion, CUtensorMapFloatOOBfill);
-
-static EncodeTiledFn get_encode() {
-  static EncodeTiledFn fn = nullptr;
-  static bool tried = false;
-  if (!tried) {
-    tried = true;
-    void* p = nullptr;
-    cudaDriverEntryPointQueryResult q;
-    if (cudaGetDriverEntryPoint("cuTensorMapEncodeTiled", &p, cudaEnableDefault, &q) == cudaSuccess &&
-        q == cudaDriverEntryPointSuccess)
-      fn = (EncodeTiledFn)p;
-  }
-  return fn;
-}
-
-// 2-D row-major [rows, cols] tensor, box = 128 bytes of a row x box_rows rows, 128B swizzle.
-static int make_map(CUtensorMap* m, const void* base, CUtensorMapDataType dt, int elem_bytes, uint64_t rows,
-                    uint64_t cols, uint32_t box_rows, bool weights) {
-  EncodeTiledFn enc = get_encode();
-  if (!enc) return fail(MOE_E_DRIVER, "cuTensorMapEncodeTiled is not available from the driver");
-  if (((uintptr_t)base & 15) != 0) return fail(MOE_E_BADARG, "tensor-core GEMM: operand not 16-byte aligned");
-  if ((cols * elem_bytes) % 16 != 0) return fail(MOE_E_SHAPE, "tensor-core GEMM: row pitch must be a multiple of 16 bytes");
-  cuuint64_t gdim[2] = {cols, rows};
-  cuuint64_t gstr[1] = {cols * (uint64_t)elem_bytes};
-  cuuint32_t box[2] = {(cuuint32_t)(128 / elem_bytes), box_rows};
-  cuuint32_t estr[2] = {1, 1};
-  CUresult r = enc(m, dt, 2, const_cast<void*>(base), gdim, gstr, box, estr, CU_TENSOR_MAP_INTERLEAVE_NONE,
-                   CU_TENSOR_MAP_SWIZZLE_128B,
-                   weights ? CU_TENSOR_MAP_L2_PROMOTION_L2_256B : CU_TENSOR_MAP_L2_PROMOTION_L2_128B,
-                   CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
-  if (r != CUDA_SUCCESS) return fail(MOE_E_DRIVER, "cuTensorMapEncodeTiled failed with CUresult %d", (int)r);
-  return 0;
-}
-
 template <bool FP8, typename AT, bool GEMM1, bool PAIR, int RB>
 static int launch(const CUtensorMap& ma, const CUtensorMap& mb, const Params& P, int grid, cudaStream_t st) {
   auto kern = tc_gemm_kernel<FP8, AT, GEMM1, PAIR, RB>;
@@ -879,7 +650,7 @@ int tc_gemm(bool gemm1, int mode, int act_dtype, const void* a, const float* a_s
     rc = make_map(&ma, a, dt, eb, (uint64_t)rows_cap, (uint64_t)K, BM, false);
     if (rc) return rc;
   }
-  rc = make_map(&mb, w, dt, eb, (uint64_t)E * rows_w, (uint64_t)K, B_BOX_ROWS, true);
+  rc = make_map(&mb, w, dt, eb, (uint64_t)E * rows_w, (uint64_t)K, (gemm1 || pair) ? 128 : 256, true);
   if (rc) return rc;
 
   Params P;

@@ -66,12 +66,15 @@ def _choose_kernel(mode, act_dtype, H, I, numel, num_experts):
 
     * FP8 block scales: one CTA per 128-row block.  (The cta_group::2 pair loses there: the
       per-K-block accumulator hand-off would cross two SMs; GEMM1 3.6 -> 4.2 ms at M=8192.)
-    * half precision / widened int8 with >= 512 rows per expert: the 256x256 single-CTA tile,
+    * weight-only int8: the kernel that widens the weights in shared memory.
+    * half precision with >= 512 rows per expert: the 256x256 single-CTA tile,
       which fetches each weight tile once per 256 rows.
     """
     if _force_generic() or not _tc_eligible(mode, act_dtype, H, I):
         return KERNEL_GENERIC
     wide, pair = _policy("FLAGGEMS_B200_TC_WIDE"), _policy("FLAGGEMS_B200_TC_PAIR")
+    if mode == _lib.MODE_W8A16:
+        return KERNEL_TC  # int8 weights widened in shared memory, one CTA per 128-row block
     if wide == "on" and mode == _lib.MODE_HALF:
         return KERNEL_TC_WIDE
     if pair == "on":
@@ -86,7 +89,7 @@ def _tc_eligible(mode: int, act_dtype: torch.dtype, H: int, I: int) -> bool:
         return False
     if mode == _lib.MODE_FP8_BLOCK:
         return H % 128 == 0 and I % 128 == 0
-    if mode == _lib.MODE_HALF:
+    if mode in (_lib.MODE_HALF, _lib.MODE_W8A16):
         return H % 64 == 0 and I % 128 == 0
     return False
 
@@ -332,10 +335,11 @@ def fused_experts_impl(
         s1 = w1_scale.to(torch.float32).contiguous()
         s2 = w2_scale.to(torch.float32).contiguous()
 
-    if (mode == _lib.MODE_W8A16 and not _force_generic()
+    if (mode == _lib.MODE_W8A16 and os.environ.get("FLAGGEMS_B200_W8_WIDEN", "0") == "1" and not _force_generic()
             and _tc_eligible(_lib.MODE_HALF, hidden_states.dtype, K, N // 2)):
-        # tensor-core route for weight-only int8: widen the weights exactly to the
-        # activation dtype, per-channel scales go to the GEMM epilogues
+        # experiment switch: widen the int8 weights to the activation dtype in global memory
+        # first (one extra pass over them per call) and run the half-precision kernels; the
+        # default is the kernel that widens them in shared memory
         w1c, w2c = _widen_int8(w1c, hidden_states.dtype), _widen_int8(w2c, hidden_states.dtype)
         mode = _lib.MODE_HALF
 

@@ -37,12 +37,14 @@ def _route(M, E, k, dtype, seed=0):
 def _both_kernels(run):
     """Runs ``run()`` with each GEMM kernel: the generic one, the tensor-core
     kernel with one CTA per 128-row block, and the CTA-pair (cta_group::2) one.
-    MOE_TEST_KERNELS = generic | tensor | pair | wide | both (default: all)."""
+    MOE_TEST_KERNELS = generic | tensor | widen | pair | wide | both (default: all)."""
     outs = {}
     which = os.environ.get("MOE_TEST_KERNELS", "both")
-    off = {"FLAGGEMS_B200_GENERIC_GEMM": "0", "FLAGGEMS_B200_TC_PAIR": "0", "FLAGGEMS_B200_TC_WIDE": "0"}
+    off = {"FLAGGEMS_B200_GENERIC_GEMM": "0", "FLAGGEMS_B200_TC_PAIR": "0", "FLAGGEMS_B200_TC_WIDE": "0",
+           "FLAGGEMS_B200_W8_WIDEN": "0"}
     variants = (("generic", dict(off, FLAGGEMS_B200_GENERIC_GEMM="1")),
                 ("tensor", off),
+                ("widen", dict(off, FLAGGEMS_B200_W8_WIDEN="1")),  # weight-only int8: widening pass + half kernels
                 ("pair", dict(off, FLAGGEMS_B200_TC_PAIR="1")),
                 ("wide", dict(off, FLAGGEMS_B200_TC_WIDE="1")))  # half precision only; FP8 falls back to "tensor"
     for name, env in variants:
@@ -138,13 +140,15 @@ def test_fp8_block_shapes(cfg, dtype):
         _assert_parity(out, ref, name)
 
 
-@pytest.mark.parametrize("cfg", QUANT_SHAPES[:6] + [(64, 128, 2048, 768, 8)])
-def test_w8a16_shapes(cfg):
+@pytest.mark.parametrize("cfg", QUANT_SHAPES + [(64, 128, 2048, 768, 8), (700, 4, 320, 640, 2)])
+@pytest.mark.parametrize("dtype", [torch.bfloat16, torch.float16])
+def test_w8a16_shapes(cfg, dtype):
     M, E, H, I, k = cfg
-    x = T.make_activations(M, H, DEV)
+    x = T.make_activations(M, H, DEV, dtype=dtype)
     w1, s1 = T.make_int8_channel_weights(E, 2 * I, H, DEV, seed=1, std=H**-0.5)
     w2, s2 = T.make_int8_channel_weights(E, H, I, DEV, seed=2, std=I**-0.5)
-    tw, ti = _route(M, E, k, torch.bfloat16)
+    w1[0, 0, :8] = torch.tensor([-128, 127, 0, -1, 1, -127, 64, -64], dtype=torch.int8, device=DEV)  # range ends
+    tw, ti = _route(M, E, k, dtype)
     ref = O.fused_moe_w8a16_oracle(x, w1, w2, s1, s2, tw, ti)
     run = lambda: fg.fused_experts_impl(x, w1, w2, tw, ti, use_int8_w8a16=True, per_channel_quant=True,
                                         w1_scale=s1, w2_scale=s2)
