@@ -216,14 +216,20 @@ def run_sweep(args):
         print(json.dumps(line), flush=True)
 
     which = args.sweep.split(",")
+    keep_m = {int(v) for v in args.sweep_m.split(",")} if args.sweep_m else None
+
+    def sizes(all_m):
+        return tuple(m for m in all_m if keep_m is None or m in keep_m)
+
+    iters = lambda default: args.sweep_iters or default
     if "dsv3" in which:
         c = DSV3
         E, H, I, k = c["E"], c["H"], c["I"], c["topk"]
         w1, s1 = T.make_fp8_block_weights(E, 2 * I, H, dev, seed=100)
         w2, s2 = T.make_fp8_block_weights(E, H, I, dev, seed=200)
-        for M in (1, 32, 128, 1024, 8192):
+        for M in sizes((1, 32, 128, 1024, 8192)):
             x = T.make_activations(M, H, dev)
-            logits, bias = T.make_router_inputs(M, E, dev)
+            logits, bias = T.make_router_inputs(M, E, dev, bias_std=args.router_bias_std)
 
             def step():
                 tw, ti = fg.grouped_topk(logits, c["n_group"], c["topk_group"], k, True, c["rsf"], bias, 1)
@@ -237,13 +243,13 @@ def run_sweep(args):
             extra = {"distinct_experts": e_act}
             if M <= 128:
                 extra["cuda_graph_replay_ms"] = graph_ms(step)
-            report("dsv3_fp8", M, timeit(step, 10), 6.0 * M * k * H * I, nbytes, 2 * peaks["bf16_tflops"], extra)
+            report("dsv3_fp8", M, timeit(step, iters(10)), 6.0 * M * k * H * I, nbytes, 2 * peaks["bf16_tflops"], extra)
         del w1, w2, s1, s2
     if "mixtral" in which:
         E, H, I, k = 8, 4096, 14336, 2
         w1 = T.make_half_weights(E, 2 * I, H, dev, seed=1, chunk=1)
         w2 = T.make_half_weights(E, H, I, dev, seed=2, chunk=1)
-        for M in (1, 16, 64, 256, 1024, 4096, 16384):
+        for M in sizes((1, 16, 64, 256, 1024, 4096, 16384)):
             x = T.make_activations(M, H, dev)
             logits, _ = T.make_router_inputs(M, E, dev)
             zero = torch.zeros(E, device=dev)
@@ -255,14 +261,14 @@ def run_sweep(args):
             _, ti = fg.grouped_topk(torch.softmax(logits, -1), 1, 1, k, True, 1.0, zero, 0)
             e_act = int(torch.unique(ti).numel())
             nbytes = e_act * 3 * H * I * 2 + M * H * 2 * 2 + M * E * 4 + k * 8 * M
-            report("mixtral_bf16", M, timeit(step, 6), 6.0 * M * k * H * I, nbytes, peaks["bf16_tflops"],
+            report("mixtral_bf16", M, timeit(step, iters(6)), 6.0 * M * k * H * I, nbytes, peaks["bf16_tflops"],
                    {"distinct_experts": e_act})
         del w1, w2
     if "qwen3" in which:
         E, H, I, k = 128, 2048, 768, 8
         w1, s1 = T.make_int8_channel_weights(E, 2 * I, H, dev, seed=1)
         w2, s2 = T.make_int8_channel_weights(E, H, I, dev, seed=2)
-        for M in (1, 64, 512, 4096):
+        for M in sizes((1, 64, 512, 4096)):
             x = T.make_activations(M, H, dev)
             logits, _ = T.make_router_inputs(M, E, dev)
             zero = torch.zeros(E, device=dev)
@@ -275,7 +281,7 @@ def run_sweep(args):
             _, ti = fg.grouped_topk(torch.softmax(logits, -1), 1, 1, k, True, 1.0, zero, 0)
             e_act = int(torch.unique(ti).numel())
             nbytes = e_act * (3 * H * I + 3 * I * 4 + H * 4) + M * H * 2 * 2 + M * E * 4 + k * 8 * M
-            report("qwen3_w8a16", M, timeit(step, 6), 6.0 * M * k * H * I, nbytes, peaks["bf16_tflops"],
+            report("qwen3_w8a16", M, timeit(step, iters(6)), 6.0 * M * k * H * I, nbytes, peaks["bf16_tflops"],
                    {"distinct_experts": e_act})
     if "align" in which:
         for M in (1, 128, 2048, 8192):
@@ -310,6 +316,8 @@ def main():
                          "spread gives the balanced expert load a trained bias produces")
     ap.add_argument("--experts", type=int, default=DSV3["E"],
                     help="expert count (smaller values give the small case used for ncu captures)")
+    ap.add_argument("--sweep-m", default="", help="comma list: keep only these token counts of a --sweep")
+    ap.add_argument("--sweep-iters", type=int, default=0, help="timed iterations per --sweep point (0: default)")
     ap.add_argument("--sweep", default="", help="comma list of dsv3,mixtral,qwen3,align,routing: print one line per point")
     args = ap.parse_args()
     args.warmup = max(args.warmup, 3) if args.impl == "b200" else args.warmup

@@ -9,9 +9,7 @@
 //             token sorted_ids[p] / topk, copied by 64 producer threads with
 //             16-byte cp.async into the same 128-byte-swizzled layout TMA
 //             would produce, so no sorted copy of the activations ever exists.
-//             (A lane owns whole rows.  Giving the eight chunks of a row to eight
-//             lanes, so that a warp instruction touches four 128-byte lines instead
-//             of 32, was measured 45 % slower for the whole GEMM.)
+//             Two lanes share a row, so every 32-byte sector is requested once.
 //   B stage : 256 rows x 128 B
 // GEMM1 fetches it as two TMA boxes, 128 gate rows and the 128 up rows of the same
 // 128 outputs, so one accumulator holds gate (columns 0-127) and up (128-255) of
@@ -54,9 +52,11 @@ constexpr int B_HALF_BYTES = B_STAGE_BYTES / 2;  // what each CTA of a pair hold
 constexpr int MAX_STAGES = 6;
 // single CTA: 4 stages of A + B; CTA pair (cta_group::2): 6 stages of A + half of B;
 // wide tile (RB = 2, half precision only): 3 stages of two A blocks + B, i.e. a 256x256
-// output tile whose two accumulators fill TMEM, each B tile fetched once per 256 rows
+// output tile whose two accumulators fill TMEM, each B tile fetched once per 256 rows;
+// wide pair: 4 stages of two A blocks + half of B, a 512x256 tile per pair, each B tile
+// fetched once per 512 rows and each CTA loading only half of it
 template <bool PAIR, int RB> struct Cfg {
-  static constexpr int STAGES = PAIR ? 6 : (RB == 2 ? 3 : 4);
+  static constexpr int STAGES = PAIR ? (RB == 2 ? 4 : 6) : (RB == 2 ? 3 : 4);
   static constexpr int A_LOCAL = RB * A_STAGE_BYTES;
   static constexpr int STAGE_BYTES = A_LOCAL + (PAIR ? B_HALF_BYTES : B_STAGE_BYTES);
 };
@@ -164,7 +164,7 @@ __device__ __forceinline__ int box_row(int nt, int c, int cr, int Nout) {
 template <bool FP8, typename AT, bool GEMM1, bool PAIR, int RB>
 __global__ void __launch_bounds__(THREADS, 1)
 tc_gemm_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant__ CUtensorMap map_b, const Params P) {
-  static_assert(RB == 1 || (RB == 2 && !FP8 && !PAIR), "wide tiles: half precision, single CTA");
+  static_assert(RB == 1 || (RB == 2 && !FP8), "wide tiles: half precision only");
   constexpr int STAGES = Cfg<PAIR, RB>::STAGES;
   constexpr int A_LOCAL_BYTES = Cfg<PAIR, RB>::A_LOCAL;
   constexpr int B_LOCAL_BYTES = PAIR ? B_HALF_BYTES : B_STAGE_BYTES;
@@ -180,7 +180,7 @@ tc_gemm_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant_
   const int npp = min((int64_t)P.num_post_pad[0], P.rows_cap);
   // work unit: one CTA and a 128-row align block; a CTA pair and a 256-row block; or one
   // CTA and a 256-row block (RB = 2).  UNIT = 128-row blocks per align block.
-  constexpr int UNIT = PAIR ? 2 : RB;
+  constexpr int UNIT = PAIR ? 2 * RB : RB;
   constexpr int CTAS = PAIR ? 2 : 1;
   const int cr = PAIR ? (int)cluster_ctarank() : 0;  // rank inside the pair; 0 leads
   const int tile0 = blockIdx.x / CTAS, tile_step = gridDim.x / CTAS;
@@ -189,7 +189,7 @@ tc_gemm_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant_
 #define MOE_TILE_COORDS(tile)                      \
   const int blk = (tile) / P.n_tiles;              \
   [[maybe_unused]] const int nt = (tile) % P.n_tiles; \
-  [[maybe_unused]] const int mb = UNIT * blk + cr; \
+  [[maybe_unused]] const int mb = UNIT * blk + RB * cr; \
   const int e = P.expert_ids[blk];
 
   if (threadIdx.x == 0) {
@@ -314,34 +314,44 @@ tc_gemm_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant_
       }
     } else if (GEMM1 && warp >= 2) {
       // ------------------------------------------------------------ A-row gather (cp.async)
-      const int g = threadIdx.x - 64;  // 0..63: rows g and g + 64 of every tile
+      // Two lanes share a row: lane pair q copies the 32-byte sector {2c, 2c+1} of rows
+      // q + 32 j in step c, so every warp instruction fetches 16 whole sectors (one lane per row
+      // would touch 32 sectors per instruction and fetch every sector twice).
+      const int g = threadIdx.x - 64;  // 0..63
+      const int q = g >> 1, half = g & 1;
       const int64_t pitch = (int64_t)P.K * (FP8 ? 1 : 2);
       uint32_t it = 0;
       bool alive = true;
       for (int tile = tile0; tile < total_tiles && alive; tile += tile_step) {
         MOE_TILE_COORDS(tile)
         if (e < 0 || e >= P.E) continue;
-        constexpr int RPT = 2 * RB;  // rows per gather thread
+        constexpr int RPT = 4 * RB;  // rows per lane pair
         const uint8_t* src[RPT];
-        [[maybe_unused]] const float* as_src[RPT];
-        uint32_t dst_off[RPT];
         bool ok[RPT];
-        // weight-scale row of this thread (g = 0: gate rows nt*128.., g = 1: up rows I + nt*128..)
+        // FP8: thread g also stages the activation scales of rows g and g + 64 and (g < 2) the
+        // weight scale of the gate (g = 0: rows nt*128..) or up (g = 1: rows I + nt*128..) block
         [[maybe_unused]] const float* ws_src = nullptr;
+        [[maybe_unused]] const float* as_src[2] = {nullptr, nullptr};
+        auto row_token = [&](int r, bool& valid) -> int64_t {
+          const int64_t p = (int64_t)mb * BM + r;
+          const int64_t sid = p < P.rows_cap ? (int64_t)P.sorted_ids[p] : P.numel;
+          valid = sid >= 0 && sid < P.numel;  // padding slot: the row keeps stale bytes, its results are never stored
+          return valid ? sid / P.topk : 0;
+        };
         if constexpr (FP8) {
           const int sblk_per_e = (P.rows_w + 127) / 128;
           ws_src = P.w_scale + ((int64_t)e * sblk_per_e + (g == 1 ? (P.Nout >> 7) + nt : nt)) * KB;
+#pragma unroll
+          for (int j = 0; j < 2; ++j) {
+            bool valid;
+            const int64_t tok = row_token(g + 64 * j, valid);
+            if (valid) as_src[j] = P.a_scales_t + tok;
+          }
         }
 #pragma unroll
         for (int j = 0; j < RPT; ++j) {
-          const int r = g + 64 * j;  // row inside the (RB x 128)-row tile
-          const int64_t p = (int64_t)mb * BM + r;
-          const int64_t sid = p < P.rows_cap ? (int64_t)P.sorted_ids[p] : P.numel;
-          ok[j] = sid >= 0 && sid < P.numel;  // padding slot: the row keeps stale bytes, its results are never stored
-          const int64_t tok = ok[j] ? sid / P.topk : 0;
-          src[j] = P.a_rows + tok * pitch;
-          if constexpr (FP8) as_src[j] = P.a_scales_t + tok;
-          dst_off[j] = (uint32_t)r * 128u;
+          const int64_t tok = row_token(q + 32 * j, ok[j]);
+          src[j] = P.a_rows + tok * pitch + half * 16;
         }
         for (int kb = 0; kb < KB; ++kb, ++it) {
           const int s = it % STAGES;
@@ -350,18 +360,18 @@ tc_gemm_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant_
 #pragma unroll
           for (int j = 0; j < RPT; ++j) {
             if (ok[j]) {
-              const int r = g + 64 * j;
+              const int r = q + 32 * j;  // row inside the (RB x 128)-row tile
               const uint8_t* sp = src[j] + (int64_t)kb * 128;
 #pragma unroll
-              for (int c = 0; c < 8; ++c)  // 128-byte swizzle: 16-byte chunk index XOR (row mod 8)
-                cp_async16(base + dst_off[j] + (uint32_t)((c ^ (r & 7)) << 4), sp + c * 16);
+              for (int c = 0; c < 4; ++c)  // 128-byte swizzle: 16-byte chunk index XOR (row mod 8)
+                cp_async16(base + (uint32_t)r * 128u + (uint32_t)(((2 * c + half) ^ (r & 7)) << 4), sp + c * 32);
             }
           }
           if constexpr (FP8) {
             const int slot = it % SCALE_SLOTS;
 #pragma unroll
             for (int j = 0; j < 2; ++j)
-              if (ok[j]) cp_async4(smem_u32(&aux->sc_a[slot][g + 64 * j]), as_src[j] + (int64_t)kb * P.a_scale_ld);
+              if (as_src[j] != nullptr) cp_async4(smem_u32(&aux->sc_a[slot][g + 64 * j]), as_src[j] + (int64_t)kb * P.a_scale_ld);
             if (g < 2) cp_async4(smem_u32(&aux->sc_w[slot][g]), ws_src + kb);
           }
           cp_async_arrive_noinc(&aux->full[s]);
@@ -615,17 +625,18 @@ int tc_gemm(bool gemm1, int mode, int act_dtype, const void* a, const float* a_s
             int block_m, int E, int K, int Nout, void* out, float* out_scales_t, int32_t* status, cudaStream_t st,
             int variant) {
   // variant: 1 = one CTA per 128-row block, 2 = cta_group::2 CTA pair per 256-row block,
-  //          3 = one CTA per 256-row block with a 256x256 tile (half precision only)
+  //          3 = one CTA per 256-row block with a 256x256 tile (half precision only),
+  //          4 = CTA pair per 512-row block, 256x256 per CTA (half precision only)
   using namespace tc;
-  const bool pair = variant == 2, wide = variant == 3;
-  if (variant < 1 || variant > 3) return fail(MOE_E_BADARG, "tensor-core GEMM: unknown kernel variant %d", variant);
-  if (wide && mode != MOE_MODE_HALF) return fail(MOE_E_SHAPE, "tensor-core GEMM: the 256x256 tile serves half precision only");
+  const bool pair = variant == 2 || variant == 4, wide = variant == 3 || variant == 4;
+  if (variant < 1 || variant > 4) return fail(MOE_E_BADARG, "tensor-core GEMM: unknown kernel variant %d", variant);
+  if (wide && mode != MOE_MODE_HALF) return fail(MOE_E_SHAPE, "tensor-core GEMM: the 256-row-per-CTA tiles serve half precision only");
   const bool fp8 = mode == MOE_MODE_FP8_BLOCK;
   if (mode != MOE_MODE_FP8_BLOCK && mode != MOE_MODE_HALF)
     return fail(MOE_E_SHAPE, "tensor-core GEMM: mode %d is served by the generic kernel", mode);
   if (act_dtype != MOE_BF16 && act_dtype != MOE_F16)
     return fail(MOE_E_DTYPE, "tensor-core GEMM: activations must be f16 or bf16");
-  const int unit_rows = (pair || wide) ? 2 * BM : BM;
+  const int unit_rows = BM * (pair ? 2 : 1) * (wide ? 2 : 1);
   if (block_m != unit_rows) return fail(MOE_E_SHAPE, "tensor-core GEMM: align block must be %d", unit_rows);
   if (rows_cap % unit_rows != 0 || rows_cap <= 0)
     return fail(MOE_E_SHAPE, "tensor-core GEMM: row capacity must be a positive multiple of %d", unit_rows);
@@ -672,13 +683,13 @@ int tc_gemm(bool gemm1, int mode, int act_dtype, const void* a, const float* a_s
   (pair ? launch<F, T, G, true, 1>(ma, mb, P, grid, st) : launch<F, T, G, false, 1>(ma, mb, P, grid, st))
 #define MOE_TC_LAUNCH(F, T) (gemm1 ? MOE_TC_LAUNCH2(F, T, true) : MOE_TC_LAUNCH2(F, T, false))
   if (fp8) return act_dtype == MOE_BF16 ? MOE_TC_LAUNCH(true, __nv_bfloat16) : MOE_TC_LAUNCH(true, __half);
+#define MOE_TC_WIDE(T, G) \
+  (pair ? launch<false, T, G, true, 2>(ma, mb, P, grid, st) : launch<false, T, G, false, 2>(ma, mb, P, grid, st))
   if (wide) {
-    if (act_dtype == MOE_BF16)
-      return gemm1 ? launch<false, __nv_bfloat16, true, false, 2>(ma, mb, P, grid, st)
-                   : launch<false, __nv_bfloat16, false, false, 2>(ma, mb, P, grid, st);
-    return gemm1 ? launch<false, __half, true, false, 2>(ma, mb, P, grid, st)
-                 : launch<false, __half, false, false, 2>(ma, mb, P, grid, st);
+    if (act_dtype == MOE_BF16) return gemm1 ? MOE_TC_WIDE(__nv_bfloat16, true) : MOE_TC_WIDE(__nv_bfloat16, false);
+    return gemm1 ? MOE_TC_WIDE(__half, true) : MOE_TC_WIDE(__half, false);
   }
+#undef MOE_TC_WIDE
   return act_dtype == MOE_BF16 ? MOE_TC_LAUNCH(false, __nv_bfloat16) : MOE_TC_LAUNCH(false, __half);
 #undef MOE_TC_LAUNCH
 #undef MOE_TC_LAUNCH2

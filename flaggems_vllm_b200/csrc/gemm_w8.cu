@@ -254,34 +254,37 @@ w8_gemm_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant_
       }
     } else if (GEMM1 && warp >= 2) {
       // ------------------------------------------------------------ A-row gather (cp.async)
-      const int g = threadIdx.x - 64;  // 0..63: rows g and g + 64 of every tile
+      // Two lanes share a row: lane pair q copies the 32-byte sector {2c, 2c+1} of rows
+      // q + 32 j in step c, so every warp instruction fetches 16 whole sectors.
+      const int g = threadIdx.x - 64;  // 0..63
+      const int q = g >> 1, half = g & 1;
       const int64_t pitch = (int64_t)P.K * 2;
       uint32_t it = 0;
       bool alive = true;
       for (int tile = tile0; tile < total_tiles && alive; tile += tile_step) {
         MOE_TILE_COORDS(tile)
         if (e < 0 || e >= P.E) continue;
-        const uint8_t* src[2];
-        bool ok[2];
+        const uint8_t* src[4];
+        bool ok[4];
 #pragma unroll
-        for (int j = 0; j < 2; ++j) {
-          const int64_t p = (int64_t)blk * BM + g + 64 * j;
+        for (int j = 0; j < 4; ++j) {
+          const int64_t p = (int64_t)blk * BM + q + 32 * j;
           const int64_t sid = p < P.rows_cap ? (int64_t)P.sorted_ids[p] : P.numel;
           ok[j] = sid >= 0 && sid < P.numel;  // padding slot: the row keeps stale bytes, its results are never stored
-          src[j] = P.a_rows + (ok[j] ? sid / P.topk : 0) * pitch;
+          src[j] = P.a_rows + (ok[j] ? sid / P.topk : 0) * pitch + half * 16;
         }
         for (int kb = 0; kb < KB; ++kb, ++it) {
           const int s = it % SA;
           if (!mbar_wait(&aux->a_empty[s], ((it / SA) & 1) ^ 1, P.status)) { alive = false; break; }
           const uint32_t base = smem_u32(sA + (size_t)s * A_BYTES);
 #pragma unroll
-          for (int j = 0; j < 2; ++j) {
+          for (int j = 0; j < 4; ++j) {
             if (ok[j]) {
-              const int r = g + 64 * j;
+              const int r = q + 32 * j;
               const uint8_t* sp = src[j] + (int64_t)kb * 128;
 #pragma unroll
-              for (int c = 0; c < 8; ++c)  // 128-byte swizzle: 16-byte chunk index XOR (row mod 8)
-                cp_async16(base + (uint32_t)r * 128u + (uint32_t)((c ^ (r & 7)) << 4), sp + c * 16);
+              for (int c = 0; c < 4; ++c)  // 128-byte swizzle: 16-byte chunk index XOR (row mod 8)
+                cp_async16(base + (uint32_t)r * 128u + (uint32_t)(((2 * c + half) ^ (r & 7)) << 4), sp + c * 32);
             }
           }
           cp_async_arrive_noinc(&aux->a_full[s]);

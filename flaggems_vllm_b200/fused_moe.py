@@ -32,9 +32,10 @@ logger = logging.getLogger(__name__)
 CHUNK_SIZE = 32 * 1024
 TC_BLOCK_M = 128
 TC_PAIR_BLOCK_M = 256
+TC_PAIR_WIDE_BLOCK_M = 512
 GENERIC_BLOCK_M = 16
 # kernel selector passed to moe_gemm1 / moe_gemm2
-KERNEL_GENERIC, KERNEL_TC, KERNEL_TC_PAIR, KERNEL_TC_WIDE = 0, 1, 2, 3
+KERNEL_GENERIC, KERNEL_TC, KERNEL_TC_PAIR, KERNEL_TC_WIDE, KERNEL_TC_PAIR_WIDE = 0, 1, 2, 3, 4
 
 _SUPPORTED_ACTIVATIONS = ("silu", "swigluoai_uninterleave")
 _ALL_ACTIVATIONS = ("silu", "gelu", "relu2", "swigluoai", "swigluoai_uninterleave", "swiglustep",
@@ -73,8 +74,11 @@ def _choose_kernel(mode, act_dtype, H, I, numel, num_experts):
     if _force_generic() or not _tc_eligible(mode, act_dtype, H, I):
         return KERNEL_GENERIC
     wide, pair = _policy("FLAGGEMS_B200_TC_WIDE"), _policy("FLAGGEMS_B200_TC_PAIR")
+    pair_wide = _policy("FLAGGEMS_B200_TC_PAIR_WIDE")
     if mode == _lib.MODE_W8A16:
         return KERNEL_TC  # int8 weights widened in shared memory, one CTA per 128-row block
+    if pair_wide == "on" and mode == _lib.MODE_HALF:
+        return KERNEL_TC_PAIR_WIDE
     if wide == "on" and mode == _lib.MODE_HALF:
         return KERNEL_TC_WIDE
     if pair == "on":
@@ -150,7 +154,7 @@ def route_pipeline(a_rows, a_scales_t, w1, w2, route_weight, topk_ids, *, mode, 
     else:
         kernel = int(use_tensor_cores)
     block_m = {KERNEL_GENERIC: GENERIC_BLOCK_M, KERNEL_TC: TC_BLOCK_M, KERNEL_TC_PAIR: TC_PAIR_BLOCK_M,
-               KERNEL_TC_WIDE: TC_PAIR_BLOCK_M}[kernel]
+               KERNEL_TC_WIDE: TC_PAIR_BLOCK_M, KERNEL_TC_PAIR_WIDE: TC_PAIR_WIDE_BLOCK_M}[kernel]
 
     # every expert that owns at least one route pads by < block_m
     rows_cap = round_up(numel + min(numel, global_num_experts) * (block_m - 1), block_m)

@@ -140,7 +140,10 @@ int moe_widen_int8(const void* src, void* dst, int dst_dtype, int64_t n, void* s
  *   (block_m must be 256, rows_cap % 256 == 0): each weight tile is fetched once
  *   per 256 rows;
  *   3 = tcgen05 kernel, one CTA per 256-row align block with a 256x256 tile whose two
- *   accumulators fill TMEM (half precision only, block_m 256).
+ *   accumulators fill TMEM (half precision only, block_m 256);
+ *   4 = tcgen05 kernel, a cta_group::2 CTA pair per 512-row align block, 256x256 per
+ *   CTA, each CTA loading half of every weight tile (half precision only, block_m 512).
+ *   MOE_MODE_W8A16 accepts 0 and 1; 1 widens the int8 weights in shared memory.
  *   GEMM1 and GEMM2 of one layer must use the same block_m.
  */
 int moe_gemm1(int mode, int act_dtype, const void* a, const float* a_scales_t, int64_t num_tokens,
