@@ -58,7 +58,7 @@ class ClockSampler:
     def start(self):
         try:
             self.proc = subprocess.Popen(
-                ["nvidia-smi", f"--query-gpu={self.Q}", "--format=csv,noheader,nounits", "-lms", "100",
+                ["nvidia-smi", f"--query-gpu={self.Q}", "--format=csv,noheader,nounits", "-lms", "20",
                  "-i", str(self.gpu)], stdout=subprocess.PIPE, stderr=subprocess.DEVNULL, text=True)
         except OSError:
             self.proc = None
@@ -73,23 +73,27 @@ class ClockSampler:
         except subprocess.TimeoutExpired:
             self.proc.kill()
             out, _ = self.proc.communicate()
-        sm, mx, reasons = [], [], set()
+        rows, mx, reasons = [], [], set()
         names = ["hw_slowdown", "hw_thermal_slowdown", "sw_thermal_slowdown", "sw_power_cap"]
         for line in out.strip().splitlines():
             f = [x.strip() for x in line.split(",")]
             if len(f) < 9:
                 continue
             try:
-                sm.append(float(f[1]))
+                rows.append((float(f[1]), float(f[3])))
                 mx.append(float(f[2]))
             except ValueError:
                 continue
             for nm, v in zip(names, f[5:9]):
                 if v.lower().startswith("active"):
                     reasons.add(nm)
-        sm.sort()
-        return {"sm_mhz": sm[len(sm) // 2] if sm else None, "sm_max_mhz": max(mx) if mx else None,
-                "samples": len(sm), "reasons": sorted(reasons)}
+        # "under load" = samples drawing at least 60 % of the highest power seen: the sampler also
+        # runs a little before and after the timed region, where the clock is back at its maximum
+        pmax = max((p for _, p in rows), default=0.0)
+        load = sorted(c for c, p in rows if p >= 0.6 * pmax) or sorted(c for c, _ in rows)
+        return {"sm_mhz": load[len(load) // 2] if load else None, "sm_max_mhz": max(mx) if mx else None,
+                "samples": len(rows), "samples_under_load": len(load), "power_w_max": pmax,
+                "reasons": sorted(reasons)}
 
 
 def dist_env():
@@ -525,6 +529,7 @@ def main():
         alg1 = e_act * (2 * I * H + (2 * I // 128) * (H // 128) * 4) + M * H + M * (H // 128) * 4 + M * k * I
         line["roofline"] = {"kernel": "tc_gemm_kernel<fp8,gemm1>", "bound": "tensor", "achieved": f1 / (g1 * 1e-3) / 1e12,
                             "peak": peak, "unit": "TFLOP/s", "frac": f1 / (g1 * 1e-3) / 1e12 / peak,
+                            "frac_of_sustained": f1 / (g1 * 1e-3) / 1e12 / (2.0 * peaks["bf16_tflops_sustained"]),
                             "traffic": 1.41 * alg1, "traffic_source": "ncu small-case DRAM bytes scaled by algorithmic bytes (x1.41)",
                             "algorithmic_bytes": alg1, "peak_source": f"2 x bf16_tflops of {peaks['source']} peaks",
                             "ms_per_launch": g1, "experts_in_use": e_act}

@@ -11,7 +11,7 @@ int tc_gemm(bool gemm1, int mode, int act_dtype, const void* a, const float* a_s
             const float* w_scale, const int32_t* expert_ids, const int32_t* sorted_ids, const int32_t* npp,
             const float* route_weight, int mul_weight, int64_t numel, int64_t rows_cap, int64_t a_tokens, int topk,
             int block_m, int E, int K, int Nout, void* out, float* out_scales_t, int32_t* status, cudaStream_t st,
-            int variant);
+            int variant, int a_sorted);
 int w8_gemm(bool gemm1, int act_dtype, const void* a, const void* w, const float* w_scale, const int32_t* expert_ids,
             const int32_t* sorted_ids, const int32_t* npp, const float* route_weight, int mul_weight, int64_t numel,
             int64_t rows_cap, int64_t a_tokens, int topk, int block_m, int E, int K, int Nout, void* out,
@@ -31,7 +31,8 @@ static int check_common(const char* who, int mode, const void* a, const float* a
 }
 }  // namespace moe
 
-extern "C" int moe_gemm1(int mode, int act_dtype, const void* a, const float* a_scales_t, int64_t num_tokens,
+extern "C" int moe_gemm1(int mode, int act_dtype, const void* a, int a_sorted, const float* a_scales_t,
+                         int64_t num_tokens,
                          int topk, const void* w1, const float* w1_scale, const int32_t* expert_ids,
                          const int32_t* sorted_ids, const int32_t* num_post_pad, const float* route_weight,
                          int mul_weight, int64_t rows_cap, int block_m, int E, int H, int I, void* out,
@@ -44,13 +45,15 @@ extern "C" int moe_gemm1(int mode, int act_dtype, const void* a, const float* a_
   if (rc) return rc;
   if (mode == MOE_MODE_FP8_BLOCK && !out_scales_t) return fail(MOE_E_BADARG, "gemm1: output scale buffer missing");
   if (rows_cap == 0 || numel == 0) return 0;
+  if (a_sorted && (mode != MOE_MODE_HALF || (use_tensor_cores != 1 && use_tensor_cores != 3)))
+    return fail(MOE_E_SHAPE, "gemm1: pre-sorted rows are read by the half-precision tensor-core kernels 1 and 3 only");
   if (use_tensor_cores && mode == MOE_MODE_W8A16)  // int8 weights widened inside the kernel
     return w8_gemm(true, act_dtype, a, w1, w1_scale, expert_ids, sorted_ids, num_post_pad, route_weight, mul_weight,
                    numel, rows_cap, num_tokens, topk, block_m, E, H, I, out, status, (cudaStream_t)stream);
   if (use_tensor_cores)
     return tc_gemm(true, mode, act_dtype, a, a_scales_t, w1, w1_scale, expert_ids, sorted_ids, num_post_pad,
                    route_weight, mul_weight, numel, rows_cap, num_tokens, topk, block_m, E, H, I, out, out_scales_t,
-                   status, (cudaStream_t)stream, use_tensor_cores);
+                   status, (cudaStream_t)stream, use_tensor_cores, a_sorted);
   return simt_gemm(true, mode, act_dtype, a, a_scales_t, w1, w1_scale, expert_ids, sorted_ids, num_post_pad,
                    route_weight, mul_weight, numel, rows_cap, num_tokens, topk, block_m, E, H, I, out, out_scales_t,
                    status, (cudaStream_t)stream);
@@ -72,7 +75,7 @@ extern "C" int moe_gemm2(int mode, int act_dtype, const void* act_sorted, const 
   if (use_tensor_cores)
     return tc_gemm(false, mode, act_dtype, act_sorted, act_scales_t, w2, w2_scale, expert_ids, sorted_ids,
                    num_post_pad, route_weight, mul_weight, numel, rows_cap, 0, 1, block_m, E, I, H, y, nullptr, status,
-                   (cudaStream_t)stream, use_tensor_cores);
+                   (cudaStream_t)stream, use_tensor_cores, 0);
   return simt_gemm(false, mode, act_dtype, act_sorted, act_scales_t, w2, w2_scale, expert_ids, sorted_ids,
                    num_post_pad, route_weight, mul_weight, numel, rows_cap, 0, 1, block_m, E, I, H, y, nullptr, status,
                    (cudaStream_t)stream);

@@ -161,9 +161,17 @@ __device__ __forceinline__ int box_row(int nt, int c, int cr, int Nout) {
 // instruction groups and each weight tile crosses L2 -> shared memory once per 256 rows
 // without any cross-CTA traffic.  FP8 cannot use it: its fp32 fold accumulators live in
 // registers and two blocks would need the whole register file.
-template <bool FP8, typename AT, bool GEMM1, bool PAIR, int RB>
+//
+// SORTED (GEMM1, half precision): the token rows were copied into sorted order beforehand
+// (moe_gather_rows), so A arrives as one TMA box per 128 rows like in GEMM2 and warps 2-3 idle.
+// With many rows per expert the in-kernel cp.async gather is the limiter of GEMM1 (its
+// per-lane requests keep the load/store unit busier than the tensor core: 1.07 against
+// 1.37 PFLOP/s for the TMA-fed GEMM2 on the Mixtral shape), and the copy costs far less.
+template <bool FP8, typename AT, bool GEMM1, bool PAIR, int RB, bool SORTED = false>
 __global__ void __launch_bounds__(THREADS, 1)
 tc_gemm_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant__ CUtensorMap map_b, const Params P) {
+  static_assert(!SORTED || (GEMM1 && !FP8), "pre-sorted A rows: half-precision GEMM1 only");
+  constexpr bool GATHER = GEMM1 && !SORTED;  // A rows gathered inside the kernel
   static_assert(RB == 1 || (RB == 2 && !FP8), "wide tiles: half precision only");
   constexpr int STAGES = Cfg<PAIR, RB>::STAGES;
   constexpr int A_LOCAL_BYTES = Cfg<PAIR, RB>::A_LOCAL;
@@ -194,7 +202,7 @@ tc_gemm_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant_
 
   if (threadIdx.x == 0) {
     for (int s = 0; s < STAGES; ++s) {
-      mbar_init(&aux->full[s], GEMM1 ? 1 + GATHER_THREADS : (FP8 ? 1 + SCALE_THREADS : 1));
+      mbar_init(&aux->full[s], GATHER ? 1 + GATHER_THREADS : (FP8 ? 1 + SCALE_THREADS : 1));
       mbar_init(&aux->empty[s], 1);
       mbar_init(&aux->peer_full[s], 1);
     }
@@ -226,7 +234,7 @@ tc_gemm_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant_
     asm volatile("setmaxnreg.dec.sync.aligned.u32 %0;" ::"n"(PRODUCER_REGS));
     if (warp == 0 && lane == 0) {
       // ------------------------------------------------------------ TMA producer
-      if constexpr (!GEMM1) asm volatile("prefetch.tensormap [%0];" ::"l"(&map_a) : "memory");
+      if constexpr (!GATHER) asm volatile("prefetch.tensormap [%0];" ::"l"(&map_a) : "memory");
       asm volatile("prefetch.tensormap [%0];" ::"l"(&map_b) : "memory");
       uint32_t it = 0;
       bool alive = true;
@@ -239,7 +247,7 @@ tc_gemm_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant_
           const int s = it % STAGES;
           const uint32_t ph = (it / STAGES) & 1;
           if (!mbar_wait(&aux->empty[s], ph ^ 1, P.status)) { alive = false; break; }
-          if constexpr (GEMM1) {
+          if constexpr (GATHER) {
             mbar_expect_tx(&aux->full[s], B_LOCAL_BYTES);  // A rows arrive by cp.async (warps 2-3)
           } else {
             mbar_expect_tx(&aux->full[s], A_LOCAL_BYTES + B_LOCAL_BYTES);
@@ -276,7 +284,7 @@ tc_gemm_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant_
           if constexpr (PAIR) {
             if (!mbar_wait<true>(&aux->peer_full[s], (it / STAGES) & 1, P.status)) { alive = false; break; }
           }
-          if constexpr (GEMM1) asm volatile("fence.proxy.async.shared::cta;" ::: "memory");  // cp.async writes -> tensor core reads
+          if constexpr (GATHER) asm volatile("fence.proxy.async.shared::cta;" ::: "memory");  // cp.async writes -> tensor core reads
           tc_fence_after();
           const uint64_t bdesc = make_smem_desc(smem_u32(sB + (size_t)s * B_LOCAL_BYTES));
 #pragma unroll
@@ -312,7 +320,7 @@ tc_gemm_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant_
           mbar_arrive_remote(&aux->peer_full[s], 0);
         }
       }
-    } else if (GEMM1 && warp >= 2) {
+    } else if (GATHER && warp >= 2) {
       // ------------------------------------------------------------ A-row gather (cp.async)
       // Two lanes share a row: lane pair q copies the 32-byte sector {2c, 2c+1} of rows
       // q + 32 j in step c, so every warp instruction fetches 16 whole sectors (one lane per row
@@ -585,9 +593,9 @@ tc_gemm_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant_
 }
 
 // ------------------------------------------------------------------ host side
-template <bool FP8, typename AT, bool GEMM1, bool PAIR, int RB>
+template <bool FP8, typename AT, bool GEMM1, bool PAIR, int RB, bool SORTED = false>
 static int launch(const CUtensorMap& ma, const CUtensorMap& mb, const Params& P, int grid, cudaStream_t st) {
-  auto kern = tc_gemm_kernel<FP8, AT, GEMM1, PAIR, RB>;
+  auto kern = tc_gemm_kernel<FP8, AT, GEMM1, PAIR, RB, SORTED>;
   constexpr size_t smem = smem_bytes<PAIR, RB>();
   cudaFuncAttributes fa;
   cudaError_t ce = cudaFuncGetAttributes(&fa, kern);
@@ -623,7 +631,8 @@ int tc_gemm(bool gemm1, int mode, int act_dtype, const void* a, const float* a_s
             const float* w_scale, const int32_t* expert_ids, const int32_t* sorted_ids, const int32_t* npp,
             const float* route_weight, int mul_weight, int64_t numel, int64_t rows_cap, int64_t a_tokens, int topk,
             int block_m, int E, int K, int Nout, void* out, float* out_scales_t, int32_t* status, cudaStream_t st,
-            int variant) {
+            int variant, int a_sorted) {
+  // a_sorted (gemm1): `a` holds [rows_cap, K] rows already in sorted order (moe_gather_rows)
   // variant: 1 = one CTA per 128-row block, 2 = cta_group::2 CTA pair per 256-row block,
   //          3 = one CTA per 256-row block with a 256x256 tile (half precision only),
   //          4 = CTA pair per 512-row block, 256x256 per CTA (half precision only)
@@ -632,6 +641,9 @@ int tc_gemm(bool gemm1, int mode, int act_dtype, const void* a, const float* a_s
   if (variant < 1 || variant > 4) return fail(MOE_E_BADARG, "tensor-core GEMM: unknown kernel variant %d", variant);
   if (wide && mode != MOE_MODE_HALF) return fail(MOE_E_SHAPE, "tensor-core GEMM: the 256-row-per-CTA tiles serve half precision only");
   const bool fp8 = mode == MOE_MODE_FP8_BLOCK;
+  const bool sorted = gemm1 && a_sorted != 0;
+  if (sorted && (fp8 || pair))
+    return fail(MOE_E_SHAPE, "tensor-core GEMM1: pre-sorted rows are served by the single-CTA half-precision kernels");
   if (mode != MOE_MODE_FP8_BLOCK && mode != MOE_MODE_HALF)
     return fail(MOE_E_SHAPE, "tensor-core GEMM: mode %d is served by the generic kernel", mode);
   if (act_dtype != MOE_BF16 && act_dtype != MOE_F16)
@@ -653,7 +665,7 @@ int tc_gemm(bool gemm1, int mode, int act_dtype, const void* a, const float* a_s
                                      : (act_dtype == MOE_BF16 ? CU_TENSOR_MAP_DATA_TYPE_BFLOAT16 : CU_TENSOR_MAP_DATA_TYPE_FLOAT16);
   CUtensorMap ma, mb;
   int rc = 0;
-  if (gemm1) {
+  if (gemm1 && !sorted) {
     memset(&ma, 0, sizeof(ma));  // A rows are gathered with cp.async, no tensor map
     if (((uintptr_t)a & 15) != 0) return fail(MOE_E_BADARG, "tensor-core GEMM1: activations not 16-byte aligned");
     if (topk <= 0 || a_tokens * topk != numel) return fail(MOE_E_BADARG, "tensor-core GEMM1: tokens * topk != numel");
@@ -665,6 +677,7 @@ int tc_gemm(bool gemm1, int mode, int act_dtype, const void* a, const float* a_s
   if (rc) return rc;
 
   Params P;
+  if (sorted && (topk <= 0 || a_tokens * topk != numel)) return fail(MOE_E_BADARG, "tensor-core GEMM1: tokens * topk != numel");
   P.a_rows = (const uint8_t*)a; P.a_scale_ld = gemm1 ? a_tokens : rows_cap; P.topk = gemm1 ? topk : 1;
   P.a_scales_t = a_scales_t; P.w_scale = w_scale; P.expert_ids = expert_ids; P.sorted_ids = sorted_ids;
   P.num_post_pad = npp; P.route_weight = route_weight; P.out = out; P.out_scales_t = out_scales_t;
@@ -683,6 +696,13 @@ int tc_gemm(bool gemm1, int mode, int act_dtype, const void* a, const float* a_s
   (pair ? launch<F, T, G, true, 1>(ma, mb, P, grid, st) : launch<F, T, G, false, 1>(ma, mb, P, grid, st))
 #define MOE_TC_LAUNCH(F, T) (gemm1 ? MOE_TC_LAUNCH2(F, T, true) : MOE_TC_LAUNCH2(F, T, false))
   if (fp8) return act_dtype == MOE_BF16 ? MOE_TC_LAUNCH(true, __nv_bfloat16) : MOE_TC_LAUNCH(true, __half);
+  if (sorted) {
+    if (act_dtype == MOE_BF16)
+      return wide ? launch<false, __nv_bfloat16, true, false, 2, true>(ma, mb, P, grid, st)
+                  : launch<false, __nv_bfloat16, true, false, 1, true>(ma, mb, P, grid, st);
+    return wide ? launch<false, __half, true, false, 2, true>(ma, mb, P, grid, st)
+                : launch<false, __half, true, false, 1, true>(ma, mb, P, grid, st);
+  }
 #define MOE_TC_WIDE(T, G) \
   (pair ? launch<false, T, G, true, 2>(ma, mb, P, grid, st) : launch<false, T, G, false, 2>(ma, mb, P, grid, st))
   if (wide) {

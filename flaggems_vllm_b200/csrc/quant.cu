@@ -164,8 +164,47 @@ int launch_sum(const void* in, void* out, int64_t M, int topk, int64_t H, const 
   return check_launch("moe_sum");
 }
 
+// out[p] = x[sorted_ids[p] / topk] for the occupied slots p < num_post_pad; one warp per row,
+// 16-byte copies.  Padding slots and the unused tail are left untouched.
+__global__ void gather_rows_kernel(const uint4* __restrict__ x, const int32_t* __restrict__ sorted_ids,
+                                   const int32_t* __restrict__ num_post_pad, int64_t numel, int topk,
+                                   int64_t rows_cap, int64_t row_vec, uint4* __restrict__ out) {
+  const int lane = threadIdx.x & 31;
+  const int64_t warp = ((int64_t)blockIdx.x * blockDim.x + threadIdx.x) >> 5;
+  const int64_t warps = ((int64_t)gridDim.x * blockDim.x) >> 5;
+  const int64_t npp = min((int64_t)num_post_pad[0], rows_cap);
+  for (int64_t p = warp; p < npp; p += warps) {
+    const int64_t sid = sorted_ids[p];
+    if (sid < 0 || sid >= numel) continue;
+    const uint4* src = x + (sid / topk) * row_vec;
+    uint4* dst = out + p * row_vec;
+    int64_t c = lane;
+    for (; c + 96 < row_vec; c += 128) {  // four loads in flight
+      const uint4 v0 = src[c], v1 = src[c + 32], v2 = src[c + 64], v3 = src[c + 96];
+      dst[c] = v0; dst[c + 32] = v1; dst[c + 64] = v2; dst[c + 96] = v3;
+    }
+    for (; c < row_vec; c += 32) dst[c] = src[c];
+  }
+}
+
 }  // namespace
 }  // namespace moe
+
+extern "C" int moe_gather_rows(const void* x, int64_t num_tokens, int topk, int64_t row_bytes,
+                               const int32_t* sorted_ids, const int32_t* num_post_pad, int64_t rows_cap, void* out,
+                               void* stream) {
+  using namespace moe;
+  if (num_tokens < 0 || topk <= 0 || row_bytes <= 0 || rows_cap < 0) return fail(MOE_E_BADARG, "gather_rows: bad extent");
+  if (num_tokens == 0 || rows_cap == 0) return 0;
+  if (!x || !sorted_ids || !num_post_pad || !out) return fail(MOE_E_BADARG, "gather_rows: null pointer");
+  if (row_bytes % 16 != 0 || ((uintptr_t)x & 15) || ((uintptr_t)out & 15))
+    return fail(MOE_E_SHAPE, "gather_rows: row size and pointers must be multiples of 16 bytes");
+  const int grid = grid_for((rows_cap + 7) / 8, 16);
+  gather_rows_kernel<<<grid, 256, 0, (cudaStream_t)stream>>>((const uint4*)x, sorted_ids, num_post_pad,
+                                                            num_tokens * topk, topk, rows_cap, row_bytes / 16,
+                                                            (uint4*)out);
+  return check_launch("gather_rows");
+}
 
 extern "C" int moe_per_token_group_quant_fp8(const void* x, int x_dtype, int64_t rows, int64_t cols,
                                              int group, void* q, float* scales,

@@ -117,12 +117,27 @@ int moe_per_token_group_quant_fp8(const void* x, int x_dtype, int64_t rows, int6
 int moe_widen_int8(const void* src, void* dst, int dst_dtype, int64_t n, void* stream);
 
 /*
+ * Copy of the token rows into sorted order: out[p] = x[sorted_ids[p] / topk] for
+ * the occupied slots p < num_post_pad (padding slots and the tail are left
+ * untouched).  Optional first step of GEMM 1 (a_sorted = 1): with many rows per
+ * expert the tensor-core kernel is faster fed by TMA boxes of this copy than by
+ * its own row gather.  The reference gathers inside its GEMM kernel
+ * (src/flaggems_vllm/ops/fused_moe.py:1559); this copy has no counterpart there.
+ *   x [num_tokens, row_bytes] any dtype, out [rows_cap, row_bytes]; row_bytes % 16 == 0
+ */
+int moe_gather_rows(const void* x, int64_t num_tokens, int topk, int64_t row_bytes, const int32_t* sorted_ids,
+                    const int32_t* num_post_pad, int64_t rows_cap, void* out, void* stream);
+
+/*
  * Expert grouped GEMM 1: act[p] = SiLU(x_t Wg^T) * (x_t Wu^T) for every sorted
  * row p, where t = sorted_ids[p] / topk is the token of that route.  The kernel
- * gathers the token rows itself; no sorted copy of the activations is needed.
+ * gathers the token rows itself; no sorted copy of the activations is needed
+ * (a_sorted = 0), or reads rows already copied into sorted order (a_sorted = 1).
  * Stands in for fused_moe_kernel with FUSE_SILU, including its row gather
  * (src/flaggems_vllm/ops/fused_moe.py:1559, 1634-1795, launch :2078-2220).
- *   a [num_tokens, H]        activations in token order (act dtype, or e4m3 in FP8 mode)
+ *   a [num_tokens, H]        activations in token order (act dtype, or e4m3 in FP8 mode);
+ *     with a_sorted != 0: [rows_cap, H] rows in sorted order from moe_gather_rows
+ *     (half-precision modes with use_tensor_cores 1 or 3 only)
  *   a_scales_t [H/128, num_tokens]  1x128 activation scales, transposed (FP8 mode)
  *   w1 [E, 2I, H] contiguous (act dtype, e4m3 or int8), gate rows first
  *   w1_scale: FP8 [E, 2I/128, H/128]; W8A16 [E, 2I]; HALF: NULL, or [E, 2I]
@@ -146,7 +161,7 @@ int moe_widen_int8(const void* src, void* dst, int dst_dtype, int64_t n, void* s
  *   MOE_MODE_W8A16 accepts 0 and 1; 1 widens the int8 weights in shared memory.
  *   GEMM1 and GEMM2 of one layer must use the same block_m.
  */
-int moe_gemm1(int mode, int act_dtype, const void* a, const float* a_scales_t, int64_t num_tokens,
+int moe_gemm1(int mode, int act_dtype, const void* a, int a_sorted, const float* a_scales_t, int64_t num_tokens,
               int topk, const void* w1, const float* w1_scale, const int32_t* expert_ids,
               const int32_t* sorted_ids, const int32_t* num_post_pad, const float* route_weight,
               int mul_weight, int64_t rows_cap, int block_m, int E, int H, int I, void* out,

@@ -37,17 +37,20 @@ def _route(M, E, k, dtype, seed=0):
 def _both_kernels(run):
     """Runs ``run()`` with each GEMM kernel: the generic one, the tensor-core
     kernel with one CTA per 128-row block, and the CTA-pair (cta_group::2) one.
-    MOE_TEST_KERNELS = generic | tensor | widen | pair | wide | pairwide | both (default: all)."""
+    MOE_TEST_KERNELS = generic | tensor | widen | pair | wide | pairwide | presort | presortwide | both
+    (default: all)."""
     outs = {}
     which = os.environ.get("MOE_TEST_KERNELS", "both")
     off = {"FLAGGEMS_B200_GENERIC_GEMM": "0", "FLAGGEMS_B200_TC_PAIR": "0", "FLAGGEMS_B200_TC_WIDE": "0",
-           "FLAGGEMS_B200_TC_PAIR_WIDE": "0", "FLAGGEMS_B200_W8_WIDEN": "0"}
+           "FLAGGEMS_B200_TC_PAIR_WIDE": "0", "FLAGGEMS_B200_W8_WIDEN": "0", "FLAGGEMS_B200_PRESORT": "0"}
     variants = (("generic", dict(off, FLAGGEMS_B200_GENERIC_GEMM="1")),
                 ("tensor", off),
                 ("widen", dict(off, FLAGGEMS_B200_W8_WIDEN="1")),  # weight-only int8: widening pass + half kernels
                 ("pair", dict(off, FLAGGEMS_B200_TC_PAIR="1")),
                 ("wide", dict(off, FLAGGEMS_B200_TC_WIDE="1")),  # half precision only; FP8 falls back to "tensor"
-                ("pairwide", dict(off, FLAGGEMS_B200_TC_PAIR_WIDE="1")))  # half precision only
+                ("pairwide", dict(off, FLAGGEMS_B200_TC_PAIR_WIDE="1")),  # half precision only
+                ("presort", dict(off, FLAGGEMS_B200_PRESORT="1")),  # half precision: GEMM1 reads a sorted copy
+                ("presortwide", dict(off, FLAGGEMS_B200_PRESORT="1", FLAGGEMS_B200_TC_WIDE="1")))
     for name, env in variants:
         if which not in ("both", name):
             continue
