@@ -303,6 +303,13 @@ def run_sweep(args):
             ms = timeit(lambda: fg.grouped_topk(logits, 8, 4, 8, True, 2.5, bias, 1), 20)
             print(json.dumps({"sweep": "grouped_topk_dsv3", "M": M, "ms": ms, "tokens_per_s": M / (ms * 1e-3)}),
                   flush=True)
+        wr = torch.randn((256, 7168), device=dev).to(torch.bfloat16)
+        for M in (1, 8, 32, 128, 256):
+            xr = torch.randn((M, 7168), device=dev).to(torch.bfloat16)
+            ms = timeit(lambda: fg.router_gemm(xr, wr), 20)
+            nbytes = (256 + M) * 7168 * 2 + M * 256 * 4
+            print(json.dumps({"sweep": "router_gemm_dsv3", "M": M, "ms": ms, "gbs": nbytes / (ms * 1e-3) / 1e9,
+                              "tokens_per_s": M / (ms * 1e-3)}), flush=True)
 
 
 def main():

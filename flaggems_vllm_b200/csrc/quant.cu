@@ -12,7 +12,7 @@ namespace {
 constexpr int kRowThreads = 256;
 
 // One warp quantises one 128-wide group: 4 consecutive elements per lane.
-template <typename T>
+template <typename T, bool UE8M0>
 __device__ __forceinline__ void quant_group_128(const T* __restrict__ src, uint8_t* __restrict__ dst,
                                                 float* __restrict__ scale_out, int lane) {
   float v[4];
@@ -28,7 +28,10 @@ __device__ __forceinline__ void quant_group_128(const T* __restrict__ src, uint8
   float amax = fmaxf(fmaxf(fabsf(v[0]), fabsf(v[1])), fmaxf(fabsf(v[2]), fabsf(v[3])));
 #pragma unroll
   for (int off = 16; off > 0; off >>= 1) amax = fmaxf(amax, __shfl_xor_sync(0xFFFFFFFFu, amax, off));
-  const float s = fmaxf(amax, kQuantEps) * (1.0f / kFp8Max);
+  float s = fmaxf(amax, kQuantEps) * (1.0f / kFp8Max);
+  // power-of-two (UE8M0) scales: exp2(ceil(log2(max(|s|, 1e-10)))), the reference's expression
+  // (src/flaggems_vllm/ops/per_token_group_quant_fp8.py:153-154)
+  if (UE8M0) s = exp2f(ceilf(log2f(fmaxf(fabsf(s), 1e-10f))));
   uint32_t packed = 0;
 #pragma unroll
   for (int i = 0; i < 4; ++i) {
@@ -54,7 +57,7 @@ __global__ void __launch_bounds__(256) widen_int8_kernel(const int8_t* __restric
   }
 }
 
-template <typename T>
+template <typename T, bool UE8M0>
 __global__ void __launch_bounds__(kRowThreads) quant_rows_kernel(
     const T* __restrict__ x, int64_t rows, int64_t cols, uint8_t* __restrict__ q,
     float* __restrict__ scales, int transposed, int64_t scale_ld) {
@@ -66,7 +69,7 @@ __global__ void __launch_bounds__(kRowThreads) quant_rows_kernel(
   for (int64_t w = warp0; w < total; w += stride) {
     const int64_t r = w / groups_per_row, g = w % groups_per_row;
     float* so = transposed ? scales + g * scale_ld + r : scales + r * groups_per_row + g;
-    quant_group_128<T>(x + r * cols + g * 128, q + r * cols + g * 128, so, lane);
+    quant_group_128<T, UE8M0>(x + r * cols + g * 128, q + r * cols + g * 128, so, lane);
   }
 }
 
@@ -217,18 +220,20 @@ extern "C" int moe_per_token_group_quant_fp8(const void* x, int x_dtype, int64_t
   if (!x || !q || !scales) return fail(MOE_E_BADARG, "quant_fp8: null pointer");
   cudaStream_t st = (cudaStream_t)stream;
   const int grid = grid_for((rows * (cols / 128) + 7) / 8, 8);
+  const int transposed = scales_transposed & 1;
+  const bool ue8m0 = (scales_transposed & 2) != 0;
+#define MOE_QUANT_LAUNCH(T)                                                                                        \
+  (ue8m0 ? quant_rows_kernel<T, true><<<grid, kRowThreads, 0, st>>>((const T*)x, rows, cols, (uint8_t*)q, scales,  \
+                                                                    transposed, scale_ld)                          \
+         : quant_rows_kernel<T, false><<<grid, kRowThreads, 0, st>>>((const T*)x, rows, cols, (uint8_t*)q, scales, \
+                                                                     transposed, scale_ld))
   switch (x_dtype) {
-    case MOE_F32:
-      quant_rows_kernel<float><<<grid, kRowThreads, 0, st>>>((const float*)x, rows, cols, (uint8_t*)q, scales, scales_transposed, scale_ld);
-      break;
-    case MOE_F16:
-      quant_rows_kernel<__half><<<grid, kRowThreads, 0, st>>>((const __half*)x, rows, cols, (uint8_t*)q, scales, scales_transposed, scale_ld);
-      break;
-    case MOE_BF16:
-      quant_rows_kernel<__nv_bfloat16><<<grid, kRowThreads, 0, st>>>((const __nv_bfloat16*)x, rows, cols, (uint8_t*)q, scales, scales_transposed, scale_ld);
-      break;
+    case MOE_F32: MOE_QUANT_LAUNCH(float); break;
+    case MOE_F16: MOE_QUANT_LAUNCH(__half); break;
+    case MOE_BF16: MOE_QUANT_LAUNCH(__nv_bfloat16); break;
     default: return fail(MOE_E_DTYPE, "quant_fp8: unsupported dtype %d", x_dtype);
   }
+#undef MOE_QUANT_LAUNCH
   return check_launch("per_token_group_quant_fp8");
 }
 

@@ -38,8 +38,6 @@ def per_token_group_quant_fp8(
     _lib.require_cuda(x, "per_token_group_quant_fp8")
     if fp8_dtype != torch.float8_e4m3fn:
         raise NotImplementedError("only float8_e4m3fn output is implemented")
-    if scale_ue8m0:
-        raise NotImplementedError("UE8M0 scales are not implemented")
     if group_size != 128:
         raise NotImplementedError("only group_size=128 is implemented")
     if abs(eps - 1e-10) > 1e-16:
@@ -57,7 +55,7 @@ def per_token_group_quant_fp8(
         x_s = torch.empty(tuple(xc.shape[:-1]) + (groups,), device=x.device, dtype=torch.float32)
     rc = _lib.lib().moe_per_token_group_quant_fp8(
         xc.data_ptr(), _lib.dtype_code(xc.dtype), rows, cols, group_size, x_q.data_ptr(), x_s.data_ptr(),
-        int(column_major_scales), rows, _lib.stream_of(x))
+        int(column_major_scales) | (2 if scale_ue8m0 else 0), rows, _lib.stream_of(x))
     _lib.check(rc)
     if column_major_scales:
         x_s = x_s.permute(-1, -2)

@@ -100,8 +100,9 @@ int moe_align_block_size(const void* topk_ids, int ids_int64, int64_t numel, int
  * q = clamp(x / scale).  Stands in for per_token_group_quant_fp8
  * (src/flaggems_vllm/ops/per_token_group_quant_fp8.py:226-335, kernel :115-162).
  * x[rows, cols] contiguous (F32/F16/BF16); q[rows, cols]; scales row-major
- * [rows, cols/group] (scales_transposed = 0) or [cols/group, scale_ld]
- * (scales_transposed = 1).  group must be 128.
+ * [rows, cols/group] or, with bit 0 of scales_transposed set, [cols/group, scale_ld].
+ * Bit 1 of scales_transposed rounds every scale up to a power of two (the
+ * reference's scale_ue8m0 option, :153-154).  group must be 128.
  */
 int moe_per_token_group_quant_fp8(const void* x, int x_dtype, int64_t rows, int64_t cols, int group,
                                   void* q, float* scales, int scales_transposed, int64_t scale_ld,
@@ -115,6 +116,17 @@ int moe_per_token_group_quant_fp8(const void* x, int x_dtype, int64_t rows, int6
  * every call (src/flaggems_vllm/ops/fused_moe.py:2493-2500).
  */
 int moe_widen_int8(const void* src, void* dst, int dst_dtype, int64_t n, void* stream);
+
+/*
+ * Router GEMM: logits[M, N] = x[M, K] . w[N, K]^T with fp32 products, fp32
+ * accumulation in a fixed order (deterministic) and fp32 output, for decode-sized
+ * M.  Stands in for router_gemm (src/flaggems_vllm/ops/router_gemm.py:207-237) and
+ * fp32_router_gemm (src/flaggems_vllm/ops/fp32_router_gemm.py:108-145).
+ *   x [M, K] F32/F16/BF16, rows x_ld elements apart (x_ld % 8 == 0, K % 8 == 0)
+ *   w [N, K] contiguous F32/F16/BF16; out [M, N] fp32
+ */
+int moe_router_gemm(const void* x, int x_dtype, int64_t x_ld, const void* w, int w_dtype, int64_t M, int N, int K,
+                    float* out, void* stream);
 
 /*
  * Copy of the token rows into sorted order: out[p] = x[sorted_ids[p] / topk] for

@@ -252,7 +252,7 @@ def moe_align_block_size_oracle(
 # Quantisation helpers
 # ----------------------------------------------------------------------------
 def per_token_group_quant_fp8_oracle(x: torch.Tensor, group_size: int = 128, eps: float = 1e-10,
-                                     reciprocal: bool = True):
+                                     reciprocal: bool = True, scale_ue8m0: bool = False):
     """1 x ``group_size`` e4m3 quantisation of the last dimension.
 
     ``reciprocal=True`` multiplies amax by fp32(1/448) like the reference kernel
@@ -272,8 +272,19 @@ def per_token_group_quant_fp8_oracle(x: torch.Tensor, group_size: int = 128, eps
         s = amax * torch.tensor(1.0 / FP8_MAX, dtype=torch.float32)
     else:
         s = amax / FP8_MAX
+    if scale_ue8m0:
+        # power-of-two scales, the expression of the reference kernel and of its golden
+        # (per_token_group_quant_fp8.py:153-154, tests/test_per_token_group_quant_fp8.py:88-91)
+        s = torch.exp2(torch.ceil(torch.log2(torch.maximum(s.abs(), torch.tensor(1e-10)))))
     q = (xr.float() / s).clamp(min=-FP8_MAX, max=FP8_MAX).to(FP8)
     return q.reshape(x.shape), s.reshape(x.shape[:-1] + (x.shape[-1] // group_size,))
+
+
+def router_gemm_oracle(x: torch.Tensor, weight: torch.Tensor) -> torch.Tensor:
+    """fp32 logits ``x @ weight.T`` with both operands upcast first, the reference the
+    project's own tests compare against (tests/test_router_gemm.py:46-50,
+    tests/test_fp32_router_gemm.py)."""
+    return torch.mm(x.detach().cpu().float(), weight.detach().cpu().float().t())
 
 
 def block_scaled_matmul_oracle(a_q, a_s, b_q, b_s, block_n: int, block_k: int):

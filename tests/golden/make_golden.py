@@ -218,6 +218,8 @@ def main(ref_root: str):
     x[0, :128] = 0
     q, s = qt["native_per_token_group_quant_fp8"](x, 128, dtype=torch.float8_e4m3fn)
     save("quant_fp8_0.npz", x=x, q=q, s=s)
+    q, s = qt["native_per_token_group_quant_fp8"](x, 128, dtype=torch.float8_e4m3fn, scale_ue8m0=True)
+    save("quant_fp8_ue8m0_0.npz", x=x, q=q, s=s)
 
 
 if __name__ == "__main__":

@@ -357,6 +357,17 @@ def test_quant_and_sum_wrappers():
     q2, s2 = fg.per_token_group_quant_fp8(x, 128, column_major_scales=True)
     assert s2.shape == s.shape and s2.stride(0) == 1 and torch.equal(s2.contiguous(), s) and torch.equal(
         q2.view(torch.uint8), q.view(torch.uint8))
+    # power-of-two scales: the same expression as the oracle; log2 of a value a few ulps above a
+    # power of two may round either way, so a scale may differ by exactly one binade, rarely
+    xb = torch.randn(257, 1024, device=DEV, dtype=torch.bfloat16) * 5
+    q3, s3 = fg.per_token_group_quant_fp8(xb, 128, scale_ue8m0=True)
+    oq3, os3 = O.per_token_group_quant_fp8_oracle(xb, 128, scale_ue8m0=True)
+    s3c = s3.cpu()
+    assert torch.equal(torch.exp2(torch.round(torch.log2(s3c))), s3c)
+    same = s3c == os3
+    assert same.float().mean() > 0.999 and torch.all((s3c[~same] == 2 * os3[~same]) | (2 * s3c[~same] == os3[~same]))
+    rows_same = same.repeat_interleave(128, dim=1)
+    assert torch.equal(q3.cpu().view(torch.uint8)[rows_same], oq3.view(torch.uint8)[rows_same])
     for dt in (torch.float32, torch.float16, torch.bfloat16):
         for (m, k, h) in [(1, 2, 128), (33, 6, 511), (222, 2, 1024)]:
             inp = torch.randn(m, k, h, device=DEV, dtype=dt)
@@ -364,6 +375,23 @@ def test_quant_and_sum_wrappers():
             fg.moe_sum(inp, o)
             torch.testing.assert_close(o.float().cpu(), O.moe_sum_oracle(inp).to(dt).float(),
                                        rtol=1.6e-2 if dt != torch.float32 else 1.3e-6, atol=1e-4 * k)
+
+
+def test_gather_rows_matches_index_select():
+    from flaggems_vllm_b200 import _lib
+    M, k, E, H, bm = 77, 4, 16, 256, 128
+    x = T.make_activations(M, H, DEV)
+    ids = T.make_align_ids(M, k, E, DEV)
+    sorted_ids, expert_ids, npp = fg.moe_align_block_size(ids, bm, E)
+    rows_cap = sorted_ids.numel()
+    out = torch.full((rows_cap, H), -7.0, device=DEV, dtype=x.dtype)
+    _lib.check(_lib.lib().moe_gather_rows(x.data_ptr(), M, k, H * 2, sorted_ids.data_ptr(), npp.data_ptr(), rows_cap,
+                                          out.data_ptr(), _lib.stream_of(x)))
+    n = int(npp.item())
+    sid = sorted_ids[:n].long()
+    valid = sid < M * k
+    assert torch.equal(out[:n][valid], x[sid[valid] // k])
+    assert torch.all(out[:n][~valid] == -7.0) and torch.all(out[n:] == -7.0)  # padding and tail untouched
 
 
 def test_layer_under_cuda_graph_replay_with_new_inputs():

@@ -216,3 +216,59 @@ def test_topk_sigmoid_ties_nan_and_graph_replay():
     ow, oi, _ = O.topk_route_oracle(logits, None, 8, True, True)
     assert torch.equal(ids.cpu().long(), oi)
     torch.testing.assert_close(w.cpu(), ow, atol=2e-7, rtol=2e-6)
+
+
+# ---------------------------------------------------------------- router GEMMs
+# shapes of the reference's tests/test_router_gemm.py:22-37 plus a prefill size served by cuBLAS
+@pytest.mark.parametrize("shape", [(1, 256, 7168), (8, 256, 7168), (16, 256, 7168), (32, 256, 7168), (128, 256, 7168),
+                                   (1, 64, 4096), (16, 128, 4096), (64, 384, 7168), (0, 256, 7168),
+                                   (1000, 256, 7168)])
+def test_router_gemm_matches_oracle(shape):
+    M, N, K = shape
+    g = torch.Generator(device="cpu").manual_seed(M + N)
+    x = torch.randn((M, K), generator=g).to(torch.bfloat16).to(DEV)
+    w = torch.randn((N, K), generator=g).to(torch.bfloat16).to(DEV)
+    out = fg.router_gemm(x, w)
+    assert out.shape == (M, N) and out.dtype == torch.float32
+    torch.testing.assert_close(out.cpu(), O.router_gemm_oracle(x, w), rtol=1e-4, atol=2e-3)
+    if 0 < M <= 256:  # the CUDA kernel reduces in a fixed order: bitwise repeatable
+        assert torch.equal(out, fg.router_gemm(x, w))
+
+
+# tests/test_fp32_router_gemm.py:14-38 (same sizes, value scales, strides and tolerances)
+@pytest.mark.parametrize("m", [0, 1, 3, 4, 8, 16, 32])
+@pytest.mark.parametrize("dtype", [torch.bfloat16, torch.float32])
+@pytest.mark.parametrize("strided", [False, True])
+def test_fp32_router_gemm_matches_oracle(m, dtype, strided):
+    g = torch.Generator(device="cpu").manual_seed(29)
+    cols = 12288 if strided else 6144
+    x = torch.randn((m, cols), generator=g).to(dtype).to(DEV)
+    w = (torch.randn((128, cols), generator=g) * 0.01).to(DEV)
+    if strided:
+        x, w = x[:, ::2], w[:, ::2]
+    out = fg.fp32_router_gemm(x, w)
+    assert out.shape == (m, 128) and out.dtype == torch.float32
+    expected = torch.mm(x.cpu().double(), w.cpu().double().t()).float()  # correctly rounded fp32 logits
+    torch.testing.assert_close(out.cpu(), expected, atol=3e-6, rtol=2e-5)
+    torch.testing.assert_close(out.cpu(), O.router_gemm_oracle(x, w), atol=3e-6, rtol=2e-5)
+    if m:
+        assert torch.equal(out.cpu().argmax(-1), expected.argmax(-1))
+        assert torch.equal(out, fg.fp32_router_gemm(x, w))
+    with pytest.raises(NotImplementedError):
+        fg.fp32_router_gemm(torch.zeros((33, 6144), device=DEV, dtype=dtype), w)
+    with pytest.raises(NotImplementedError):
+        fg.fp32_router_gemm(torch.zeros((2, 7168), device=DEV, dtype=dtype), torch.zeros((128, 7168), device=DEV))
+
+
+def test_fp32_router_gemm_under_graph_replay():
+    x = torch.randn((4, 6144), device=DEV, dtype=torch.bfloat16)
+    w = torch.randn((128, 6144), device=DEV) * 0.01
+    fg.fp32_router_gemm(x, w)
+    torch.cuda.synchronize()
+    graph = torch.cuda.CUDAGraph()
+    with torch.cuda.graph(graph):
+        out = fg.fp32_router_gemm(x, w)
+    x.mul_(-1)
+    graph.replay()
+    torch.cuda.synchronize()
+    assert torch.equal(out, fg.fp32_router_gemm(x, w))

@@ -66,6 +66,12 @@ def test_signatures_match_reference():
     assert flaggems_vllm.grouped_topk is fg.grouped_topk
     assert flaggems_vllm.ops_experts_impl is fg.fused_experts_impl
     assert "inplace" not in inspect.signature(fg.inplace_fused_experts).parameters
+    # src/flaggems_vllm/ops/router_gemm.py:207, src/flaggems_vllm/ops/fp32_router_gemm.py:17,143
+    assert [n for n, _, _ in _sig(fg.router_gemm)] == ["x", "weight"]
+    assert [n for n, _, _ in _sig(fg.fp32_router_gemm)] == ["input", "router_weight"]
+    assert [n for n, _, _ in _sig(fg.supports_fp32_router_gemm)] == [
+        "hidden_size", "num_experts", "input_dtype", "weight_dtype"]
+    assert flaggems_vllm.router_gemm is fg.router_gemm
 
 
 def test_grouped_topk_validation_errors():
@@ -115,6 +121,19 @@ def test_fused_experts_validation_errors():
         fg.fused_experts_impl(x, w1, w2, tw, ti, use_fp8_w8a8=True)
     with pytest.raises(RuntimeError, match="no CPU path"):
         fg.fused_experts_impl(x, w1, w2, tw, ti)
+
+
+def test_router_gemm_validation_errors():
+    x, w = torch.zeros(2, 16, dtype=torch.bfloat16), torch.zeros(4, 16, dtype=torch.bfloat16)
+    with pytest.raises(ValueError, match="2D"):
+        fg.router_gemm(x[0], w)
+    with pytest.raises(ValueError, match="shape"):
+        fg.router_gemm(x, w[:, :8])
+    with pytest.raises(ValueError, match="CUDA device"):
+        fg.fp32_router_gemm(x, w.float())
+    assert fg.supports_fp32_router_gemm(6144, 128, torch.bfloat16, torch.float32)
+    assert not fg.supports_fp32_router_gemm(7168, 256, torch.bfloat16, torch.float32)
+    assert not fg.supports_fp32_router_gemm(6144, 128, torch.bfloat16, torch.bfloat16)
 
 
 def test_align_rejects_cpu_tensors_and_bad_dtypes():

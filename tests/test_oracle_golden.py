@@ -129,6 +129,15 @@ def test_quant_fp8_matches_reference_golden():
     assert torch.equal(q.view(torch.uint8), g["q"].view(torch.uint8))
 
 
+def test_quant_fp8_power_of_two_scales_match_reference_golden():
+    g = load_golden("quant_fp8_ue8m0_0.npz")
+    q, s = O.per_token_group_quant_fp8_oracle(g["x"], 128, reciprocal=True, scale_ue8m0=True)
+    nz = g["x"].float().reshape(-1, 128).abs().amax(dim=1).reshape(s.shape) > 0
+    assert torch.equal(s[nz], g["s"][nz])
+    assert torch.equal(torch.exp2(torch.round(torch.log2(s))), s)  # powers of two
+    assert torch.equal(q.view(torch.uint8), g["q"].view(torch.uint8))
+
+
 @pytest.mark.parametrize("name", golden_files("layer_half_"))
 def test_layer_half_matches_reference_golden(name):
     g = load_golden(name)
