@@ -116,6 +116,7 @@ struct Params {
   int Nout;     // output columns (I for GEMM1, H for GEMM2)
   int rows_w;   // weight rows per expert (2I or H)
   int n_tiles;  // column tiles per align block
+  bool wide_store;  // the output is 32-byte aligned: rows are written with 32-byte stores
 };
 
 // Instruction descriptor: fp32 accumulator (bits 4-5 = 1), A/B element format
@@ -536,7 +537,7 @@ tc_gemm_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant_
           const float s = fmaxf(amax, kQuantEps) * (1.0f / kFp8Max);
           const float inv_s = 1.0f / s;  // one reciprocal per row instead of 64 divisions
           if (row_ok) {
-            uint4* o = reinterpret_cast<uint4*>(reinterpret_cast<uint8_t*>(P.out) + p * P.Nout + col0);
+            uint4 pieces[4];
 #pragma unroll
             for (int v = 0; v < 4; ++v) {
               uint32_t w[4];
@@ -550,27 +551,34 @@ tc_gemm_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant_
                 }
                 w[q] = pk;
               }
-              o[v] = make_uint4(w[0], w[1], w[2], w[3]);
+              pieces[v] = make_uint4(w[0], w[1], w[2], w[3]);
             }
+            store_row_pieces(reinterpret_cast<uint8_t*>(P.out) + p * P.Nout + col0, pieces, P.wide_store);
             if (h == 0) P.out_scales_t[(int64_t)nt * P.rows_cap + p] = s;
           }
         } else if (row_ok) {
-          uint4* o = reinterpret_cast<uint4*>(reinterpret_cast<AT*>(P.out) + p * P.Nout + col0);
+          uint4 pieces[8];
 #pragma unroll
           for (int v = 0; v < 8; ++v)
-            o[v] = make_uint4(pack2<AT>(acc[v * 8 + 0], acc[v * 8 + 1]), pack2<AT>(acc[v * 8 + 2], acc[v * 8 + 3]),
-                              pack2<AT>(acc[v * 8 + 4], acc[v * 8 + 5]), pack2<AT>(acc[v * 8 + 6], acc[v * 8 + 7]));
+            pieces[v] = make_uint4(pack2<AT>(acc[v * 8 + 0], acc[v * 8 + 1]), pack2<AT>(acc[v * 8 + 2], acc[v * 8 + 3]),
+                                   pack2<AT>(acc[v * 8 + 4], acc[v * 8 + 5]), pack2<AT>(acc[v * 8 + 6], acc[v * 8 + 7]));
+          store_row_pieces(reinterpret_cast<AT*>(P.out) + p * P.Nout + col0, pieces, P.wide_store);
         }
       } else if (row_ok) {
         const int col0 = nt * BN + 128 * h;
-        uint4* o = reinterpret_cast<uint4*>(reinterpret_cast<AT*>(P.out) + sid * P.Nout + col0);
+        AT* o = reinterpret_cast<AT*>(P.out) + sid * P.Nout + col0;
 #pragma unroll
-        for (int v = 0; v < 16; ++v) {
-          if (col0 + v * 8 < P.Nout)
-            o[v] = make_uint4(pack2<AT>(acc[v * 8 + 0] * rw, acc[v * 8 + 1] * rw),
-                              pack2<AT>(acc[v * 8 + 2] * rw, acc[v * 8 + 3] * rw),
-                              pack2<AT>(acc[v * 8 + 4] * rw, acc[v * 8 + 5] * rw),
-                              pack2<AT>(acc[v * 8 + 6] * rw, acc[v * 8 + 7] * rw));
+        for (int v = 0; v < 16; v += 2) {
+          if (col0 + v * 8 < P.Nout) {  // Nout is a multiple of 64: the two pieces are in or out together
+            uint4 pieces[2];
+#pragma unroll
+            for (int u = 0; u < 2; ++u)
+              pieces[u] = make_uint4(pack2<AT>(acc[(v + u) * 8 + 0] * rw, acc[(v + u) * 8 + 1] * rw),
+                                     pack2<AT>(acc[(v + u) * 8 + 2] * rw, acc[(v + u) * 8 + 3] * rw),
+                                     pack2<AT>(acc[(v + u) * 8 + 4] * rw, acc[(v + u) * 8 + 5] * rw),
+                                     pack2<AT>(acc[(v + u) * 8 + 6] * rw, acc[(v + u) * 8 + 7] * rw));
+            store_row_pieces(o + v * 8, pieces, P.wide_store);
+          }
         }
       }
       }  // sub
@@ -684,6 +692,7 @@ int tc_gemm(bool gemm1, int mode, int act_dtype, const void* a, const float* a_s
   P.status = status; P.numel = numel; P.rows_cap = rows_cap; P.mul_weight = mul_weight; P.E = E; P.K = K;
   P.Nout = Nout; P.rows_w = rows_w;
   P.n_tiles = gemm1 ? Nout / 128 : (Nout + BN - 1) / BN;
+  P.wide_store = ((uintptr_t)out & 31) == 0;
 
   int dev = 0, sms = 148;
   cudaGetDevice(&dev);

@@ -85,6 +85,7 @@ struct Params {
   int Nout;     // output columns (I for GEMM1, H for GEMM2)
   int rows_w;   // weight rows per expert (2I or H)
   int n_tiles;  // column tiles per align block
+  bool wide_store;  // the output is 32-byte aligned: rows are written with 32-byte stores
 };
 
 // The raw tile is fetched with as few TMA instructions as the weight layout allows: GEMM1
@@ -357,23 +358,29 @@ w8_gemm_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant_
             for (int q = 0; q < 4; ++q)
               acc[4 * j4 + q] = silu_mul_fast(acc[4 * j4 + q] * gs[q] * rw, acc[64 + 4 * j4 + q] * us[q] * rw);
           }
-          uint4* o = reinterpret_cast<uint4*>(reinterpret_cast<AT*>(P.out) + p * P.Nout + n0);
+          uint4 pieces[8];
 #pragma unroll
           for (int v = 0; v < 8; ++v)
-            o[v] = make_uint4(pack2<AT>(acc[v * 8 + 0], acc[v * 8 + 1]), pack2<AT>(acc[v * 8 + 2], acc[v * 8 + 3]),
-                              pack2<AT>(acc[v * 8 + 4], acc[v * 8 + 5]), pack2<AT>(acc[v * 8 + 6], acc[v * 8 + 7]));
+            pieces[v] = make_uint4(pack2<AT>(acc[v * 8 + 0], acc[v * 8 + 1]), pack2<AT>(acc[v * 8 + 2], acc[v * 8 + 3]),
+                                   pack2<AT>(acc[v * 8 + 4], acc[v * 8 + 5]), pack2<AT>(acc[v * 8 + 6], acc[v * 8 + 7]));
+          store_row_pieces(reinterpret_cast<AT*>(P.out) + p * P.Nout + n0, pieces, P.wide_store);
         } else {
           const int n0 = nt * BN + 128 * h;
           const float4* s4 = reinterpret_cast<const float4*>(cs + 128 * h);
-          uint4* o = reinterpret_cast<uint4*>(reinterpret_cast<AT*>(P.out) + sid * P.Nout + n0);
+          AT* o = reinterpret_cast<AT*>(P.out) + sid * P.Nout + n0;
 #pragma unroll
-          for (int v = 0; v < 16; ++v) {
-            if (n0 + v * 8 < P.Nout) {
-              const float4 s0 = s4[2 * v], s1 = s4[2 * v + 1];
-              o[v] = make_uint4(pack2<AT>(acc[v * 8 + 0] * s0.x * rw, acc[v * 8 + 1] * s0.y * rw),
-                                pack2<AT>(acc[v * 8 + 2] * s0.z * rw, acc[v * 8 + 3] * s0.w * rw),
-                                pack2<AT>(acc[v * 8 + 4] * s1.x * rw, acc[v * 8 + 5] * s1.y * rw),
-                                pack2<AT>(acc[v * 8 + 6] * s1.z * rw, acc[v * 8 + 7] * s1.w * rw));
+          for (int v = 0; v < 16; v += 2) {
+            if (n0 + v * 8 < P.Nout) {  // Nout is a multiple of 64: the two pieces are in or out together
+              uint4 pieces[2];
+#pragma unroll
+              for (int u = 0; u < 2; ++u) {
+                const float4 s0 = s4[2 * (v + u)], s1 = s4[2 * (v + u) + 1];
+                pieces[u] = make_uint4(pack2<AT>(acc[(v + u) * 8 + 0] * s0.x * rw, acc[(v + u) * 8 + 1] * s0.y * rw),
+                                       pack2<AT>(acc[(v + u) * 8 + 2] * s0.z * rw, acc[(v + u) * 8 + 3] * s0.w * rw),
+                                       pack2<AT>(acc[(v + u) * 8 + 4] * s1.x * rw, acc[(v + u) * 8 + 5] * s1.y * rw),
+                                       pack2<AT>(acc[(v + u) * 8 + 6] * s1.z * rw, acc[(v + u) * 8 + 7] * s1.w * rw));
+              }
+              store_row_pieces(o + v * 8, pieces, P.wide_store);
             }
           }
         }
@@ -498,6 +505,7 @@ int w8_gemm(bool gemm1, int act_dtype, const void* a, const void* w, const float
   P.num_post_pad = npp; P.route_weight = route_weight; P.out = out; P.status = status; P.numel = numel;
   P.rows_cap = rows_cap; P.topk = gemm1 ? topk : 1; P.mul_weight = mul_weight; P.E = E; P.K = K; P.Nout = Nout;
   P.rows_w = rows_w; P.n_tiles = gemm1 ? Nout / 128 : (Nout + BN - 1) / BN;
+  P.wide_store = ((uintptr_t)out & 31) == 0;
 
   int dev = 0, sms = 148;
   cudaGetDevice(&dev);

@@ -177,6 +177,25 @@ __device__ __forceinline__ void cp_async4(uint32_t dst_smem, const void* src) {
 __device__ __forceinline__ void cp_async_arrive_noinc(uint64_t* bar) {
   asm volatile("cp.async.mbarrier.arrive.noinc.shared::cta.b64 [%0];" ::"r"(smem_u32(bar)) : "memory");
 }
+// 32 bytes per lane: a whole sector per store, so a row segment written by one thread costs
+// half the sector writes of two 16-byte stores.  The address must be 32-byte aligned.
+__device__ __forceinline__ void st_global_32(void* p, const uint4& a, const uint4& b) {
+  asm volatile("st.global.v8.b32 [%0], {%1, %2, %3, %4, %5, %6, %7, %8};" ::"l"(p), "r"(a.x), "r"(a.y), "r"(a.z), "r"(a.w),
+               "r"(b.x), "r"(b.y), "r"(b.z), "r"(b.w)
+               : "memory");
+}
+// stores 2n 16-byte pieces v[0..2n) to consecutive addresses, as n 32-byte stores when `wide`
+template <int N2>
+__device__ __forceinline__ void store_row_pieces(void* dst, const uint4 (&v)[N2], bool wide) {
+  static_assert(N2 % 2 == 0, "pairs of 16-byte pieces");
+  if (wide) {
+#pragma unroll
+    for (int i = 0; i < N2; i += 2) st_global_32(reinterpret_cast<uint8_t*>(dst) + 16 * i, v[i], v[i + 1]);
+  } else {
+#pragma unroll
+    for (int i = 0; i < N2; ++i) reinterpret_cast<uint4*>(dst)[i] = v[i];
+  }
+}
 // K-major operand tile with 128-byte swizzle: rows are 128 B apart, groups of
 // 8 rows 1024 B apart (stride byte offset), descriptor version 1 (sm_100).
 __device__ __forceinline__ uint64_t make_smem_desc(uint32_t saddr) {
