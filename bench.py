@@ -527,8 +527,8 @@ def main():
         f1 = 2.0 * M * k * (2 * I) * H
         peak = 2.0 * peaks["bf16_tflops"]
         # DRAM traffic of one GEMM1 launch: ncu (dram__bytes_read+write) on the 32-expert /
-        # 1024-token capture gave 1.341 GB for 0.951 GB of algorithmic bytes (weights of the
-        # experts in use + e4m3 activations + scales + the e4m3 intermediate), a ratio of 1.41;
+        # 1024-token capture gave 1.134 GB for 0.964 GB of algorithmic bytes (weights of the
+        # experts in use + e4m3 activations + scales + the e4m3 intermediate), a ratio of 1.18;
         # both grow with the number of experts in use, so the full-size figure is that ratio
         # times this launch's algorithmic bytes.
         _, ti0 = fg.grouped_topk(logits, c["n_group"], c["topk_group"], k, True, c["rsf"], bias, 1)
@@ -537,7 +537,7 @@ def main():
         line["roofline"] = {"kernel": "tc_gemm_kernel<fp8,gemm1>", "bound": "tensor", "achieved": f1 / (g1 * 1e-3) / 1e12,
                             "peak": peak, "unit": "TFLOP/s", "frac": f1 / (g1 * 1e-3) / 1e12 / peak,
                             "frac_of_sustained": f1 / (g1 * 1e-3) / 1e12 / (2.0 * peaks["bf16_tflops_sustained"]),
-                            "traffic": 1.41 * alg1, "traffic_source": "ncu small-case DRAM bytes scaled by algorithmic bytes (x1.41)",
+                            "traffic": 1.18 * alg1, "traffic_source": "ncu small-case DRAM bytes scaled by algorithmic bytes (x1.18)",
                             "algorithmic_bytes": alg1, "peak_source": f"2 x bf16_tflops of {peaks['source']} peaks",
                             "ms_per_launch": g1, "experts_in_use": e_act}
         wbytes = E * 3 * H * I + (E * (2 * I // 128) * (H // 128) + E * (H // 128) * (I // 128)) * 4
