@@ -68,7 +68,7 @@ def _choose_kernel(mode, act_dtype, H, I, numel, num_experts):
     * FP8 block scales: one CTA per 128-row block.  (The cta_group::2 pair loses there: the
       per-K-block accumulator hand-off would cross two SMs; GEMM1 3.6 -> 4.2 ms at M=8192.)
     * weight-only int8: the kernel that widens the weights in shared memory.
-    * half precision with >= 512 rows per expert: the 256x256 single-CTA tile,
+    * half precision with >= 256 rows per expert: the 256x256 single-CTA tile,
       which fetches each weight tile once per 256 rows.
     """
     if _force_generic() or not _tc_eligible(mode, act_dtype, H, I):
@@ -83,7 +83,7 @@ def _choose_kernel(mode, act_dtype, H, I, numel, num_experts):
         return KERNEL_TC_WIDE
     if pair == "on":
         return KERNEL_TC_PAIR
-    if mode == _lib.MODE_HALF and numel >= 512 * num_experts and wide != "off":
+    if mode == _lib.MODE_HALF and numel >= 256 * num_experts and wide != "off":
         return KERNEL_TC_WIDE
     return KERNEL_TC
 
