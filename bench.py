@@ -409,10 +409,12 @@ def main():
             dist.all_reduce(t, op=dist.ReduceOp.MAX)
         return float(t.item()) / steps
 
-    for _ in range(args.warmup):
-        device_step()
+    # the clock sampler starts before the warm-up (nvidia-smi needs a moment to produce its first
+    # line, more so with eight GPUs in the box); only its samples under load are used
     sampler = ClockSampler(local)
     sampler.start()
+    for _ in range(args.warmup):
+        device_step()
     ms = timed(device_step, args.steps, record_stages=(world == 1))
     clocks = sampler.stop()
     if world == 1:
