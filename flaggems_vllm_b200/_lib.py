@@ -32,6 +32,11 @@ SYMBOLS = {
     "moe_per_token_group_quant_fp8": (c_int, [c_void_p, c_int, c_int64, c_int64, c_int, c_void_p, c_void_p,
                                               c_int, c_int64, c_void_p]),
     "moe_widen_int8": (c_int, [c_void_p, c_void_p, c_int, c_int64, c_void_p]),
+    "moe_ep_plan": (c_int, [c_void_p, c_int64, c_int, c_int, c_int, c_void_p, c_void_p, c_void_p, c_void_p]),
+    "moe_ep_pack": (c_int, [c_void_p, c_int64, c_void_p, c_int, c_void_p, c_void_p, c_int, c_void_p, c_int64,
+                            c_void_p, c_void_p, c_void_p]),
+    "moe_ep_unpack": (c_int, [c_void_p, c_int64, c_int, c_int, c_int, c_int, c_void_p, c_void_p, c_void_p,
+                              c_void_p]),
     "moe_router_gemm": (c_int, [c_void_p, c_int, c_int64, c_void_p, c_int, c_int64, c_int, c_int, c_void_p, c_void_p]),
     "moe_gather_rows": (c_int, [c_void_p, c_int64, c_int, c_int64, c_void_p, c_void_p, c_int64, c_void_p, c_void_p]),
     "moe_gemm1": (c_int, [c_int, c_int, c_void_p, c_int, c_void_p, c_int64, c_int, c_void_p, c_void_p, c_void_p,

@@ -47,8 +47,11 @@ def plan_dispatch(topk_ids: torch.Tensor, experts_per_rank: int, world: int):
     ids = topk_ids.long()
     valid = ids >= 0
     dest = torch.div(ids.clamp_min(0), experts_per_rank, rounding_mode="floor").clamp_(max=world - 1)
-    visits = torch.zeros((M, world), dtype=torch.bool, device=topk_ids.device)
-    visits.scatter_(1, dest, valid)
+    # a rank is visited when ANY route goes there (a plain scatter of the validity flags would let
+    # a padded route, which also maps to rank 0, overwrite a real one)
+    visits = torch.zeros((M, world), dtype=torch.int32, device=topk_ids.device)
+    visits.scatter_add_(1, dest, valid.to(torch.int32))
+    visits = visits > 0
     counts = visits.sum(0)
     pairs = visits.t().nonzero(as_tuple=False)  # sorted by rank, then token
     dst, tok = pairs[:, 0], pairs[:, 1]
@@ -96,6 +99,66 @@ class ExpertParallelMoE:
                                group=self.group)
 
     def forward(self, x: torch.Tensor, topk_weights: torch.Tensor, topk_ids: torch.Tensor) -> torch.Tensor:
+        if x.is_cuda and self.compute_fn == self._compute_cuda:
+            return self._forward_cuda(x, topk_weights, topk_ids)
+        return self._forward_torch(x, topk_weights, topk_ids)
+
+    def _forward_cuda(self, x, topk_weights, topk_ids):
+        """The same step with the bookkeeping done by three kernels (plan, pack, unpack) instead
+        of some thirty small tensor operations; one host read (the pair counts) remains."""
+        M, H = x.shape
+        k = topk_ids.shape[1]
+        dev = x.device
+        L, st = _lib.lib(), _lib.stream_of(x)
+        fp8 = self.mode == _lib.MODE_FP8_BLOCK
+        R = self.world
+        ids = topk_ids if topk_ids.dtype == torch.int32 and topk_ids.is_contiguous() else topk_ids.to(torch.int32).contiguous()
+        tw = topk_weights if topk_weights.dtype == torch.float32 and topk_weights.is_contiguous() \
+            else topk_weights.float().contiguous()
+        index = torch.empty((M, R), dtype=torch.int32, device=dev)
+        both = torch.empty((2, R), dtype=torch.int32, device=dev)  # [send counts; receive counts]
+        tok = torch.empty((max(M * R, 1),), dtype=torch.int32, device=dev)
+        _lib.check(L.moe_ep_plan(ids.data_ptr(), M, k, self.E_local, R, index.data_ptr(), both[0].data_ptr(),
+                                 tok.data_ptr(), st))
+        dist.all_to_all_single(both[1], both[0], group=self.group)
+        counts = both.tolist()  # the one host sync of the step
+        send_splits, recv_splits = counts[0], counts[1]
+        n_send, n_recv = sum(send_splits), sum(recv_splits)
+        self.last_counts = (send_splits, recv_splits)
+
+        g = H // 128 if fp8 else 0
+        if fp8:
+            xq, xs = per_token_group_quant_fp8(x, 128)
+            rows_src, row_bytes, rows_dtype = xq, H, torch.float8_e4m3fn
+        else:
+            xs = None
+            rows_src, row_bytes, rows_dtype = x if x.is_contiguous() else x.contiguous(), H * x.element_size(), x.dtype
+        rows_send = torch.empty((n_send, H), dtype=rows_dtype, device=dev)
+        side_send = torch.empty((n_send, g + 2 * k), dtype=torch.float32, device=dev)
+        _lib.check(L.moe_ep_pack(rows_src.data_ptr(), row_bytes, _lib.ptr(xs), g, ids.data_ptr(), tw.data_ptr(), k,
+                                 tok.data_ptr(), n_send, rows_send.data_ptr(), side_send.data_ptr(), st))
+        side_recv = torch.empty((n_recv, g + 2 * k), dtype=torch.float32, device=dev)
+        a_rows = torch.empty((n_recv, H), dtype=rows_dtype, device=dev)
+        # the fp8 rows travel as bytes (NCCL has no e4m3 all-to-all on every version)
+        self._a2a(side_recv, side_send, recv_splits, send_splits)
+        self._a2a(a_rows.view(torch.uint8) if fp8 else a_rows, rows_send.view(torch.uint8) if fp8 else rows_send,
+                  recv_splits, send_splits)
+        a_scales_t = torch.empty((g, n_recv), dtype=torch.float32, device=dev) if fp8 else None
+        slot_ids = torch.empty((n_recv, k), dtype=torch.int32, device=dev)
+        slot_w = torch.empty((n_recv, k), dtype=torch.float32, device=dev)
+        _lib.check(L.moe_ep_unpack(side_recv.data_ptr(), n_recv, g, k, self.rank, self.E_local, _lib.ptr(a_scales_t),
+                                   slot_ids.data_ptr(), slot_w.data_ptr(), st))
+        if n_recv > 0:
+            rows = self.compute_fn(a_rows, a_scales_t, slot_w, slot_ids, x.dtype)
+        else:
+            rows = torch.empty((0, H), dtype=x.dtype, device=dev)
+        rows_back = torch.empty((n_send, H), dtype=x.dtype, device=dev)
+        self._a2a(rows_back, rows, send_splits, recv_splits)
+        out = torch.empty_like(x)
+        self.combine_fn(rows_back, out, index)
+        return out
+
+    def _forward_torch(self, x: torch.Tensor, topk_weights: torch.Tensor, topk_ids: torch.Tensor) -> torch.Tensor:
         M, H = x.shape
         k = topk_ids.shape[1]
         dev = x.device

@@ -208,6 +208,31 @@ int moe_sum(const void* in, void* out, int dtype, int64_t M, int topk, int64_t H
             const void* topk_ids, int ids_int64, int num_experts, const int32_t* expert_map,
             const int32_t* row_index, void* stream);
 
+/*
+ * Expert-parallel bookkeeping (experts partitioned over `world` ranks, rank r owning experts
+ * [r * experts_per_rank, (r + 1) * experts_per_rank); tokens data-parallel).  The reference
+ * has no all-to-all path (its hook is expert_map with replicated tokens,
+ * src/flaggems_vllm/ops/fused_moe.py:2553-2560); these three calls have no counterpart there.
+ *
+ * moe_ep_plan: the (token, destination rank) pairs of topk_ids [M, k] int32 (negative ids are
+ *   no route), ordered by rank, then token.  index [M, world]: position of the pair or -1;
+ *   counts [world]: pairs per rank; tok [M * world]: token of every pair (first sum(counts)
+ *   entries).  world <= 16.
+ * moe_ep_pack: send buffers of the dispatch: rows_out [pairs, row_bytes] = rows[tok[p]] and
+ *   side_out [pairs, groups + 2k] fp32 = [scales[tok[p]] (groups) | expert ids | weights].
+ *   scales [M, groups] row-major (groups = 0: none); topk_weights fp32.
+ * moe_ep_unpack: the receiver's view of side rows: scales_t [groups, rows] (transposed),
+ *   slot_ids [rows, k] = id - rank * experts_per_rank when this rank owns the expert, else -1,
+ *   slot_w [rows, k].
+ */
+int moe_ep_plan(const int32_t* topk_ids, int64_t M, int k, int experts_per_rank, int world, int32_t* index,
+                int32_t* counts, int32_t* tok, void* stream);
+int moe_ep_pack(const void* rows, int64_t row_bytes, const float* scales, int groups, const int32_t* topk_ids,
+                const float* topk_weights, int k, const int32_t* tok, int64_t pairs, void* rows_out, float* side_out,
+                void* stream);
+int moe_ep_unpack(const float* side, int64_t rows, int groups, int k, int rank, int experts_per_rank,
+                  float* scales_t, int32_t* slot_ids, float* slot_w, void* stream);
+
 #ifdef __cplusplus
 }
 #endif
