@@ -11,11 +11,10 @@ namespace {
 
 constexpr int kRowThreads = 256;
 
-// One warp quantises one 128-wide group: 4 consecutive elements per lane.
-template <typename T, bool UE8M0>
-__device__ __forceinline__ void quant_group_128(const T* __restrict__ src, uint8_t* __restrict__ dst,
-                                                float* __restrict__ scale_out, int lane) {
-  float v[4];
+// One warp quantises one 128-wide group: 4 consecutive elements per lane.  The load is a
+// separate step so that a warp can have the loads of several groups in flight.
+template <typename T>
+__device__ __forceinline__ void load_group_128(const T* __restrict__ src, int lane, float (&v)[4]) {
   if constexpr (sizeof(T) == 2) {
     uint2 raw = *reinterpret_cast<const uint2*>(src + lane * 4);
     const T* p = reinterpret_cast<const T*>(&raw);
@@ -25,6 +24,10 @@ __device__ __forceinline__ void quant_group_128(const T* __restrict__ src, uint8
     float4 raw = *reinterpret_cast<const float4*>(src + lane * 4);
     v[0] = raw.x; v[1] = raw.y; v[2] = raw.z; v[3] = raw.w;
   }
+}
+template <bool UE8M0>
+__device__ __forceinline__ void quant_group_128(const float (&v)[4], uint8_t* __restrict__ dst,
+                                                float* __restrict__ scale_out, int lane) {
   float amax = fmaxf(fmaxf(fabsf(v[0]), fabsf(v[1])), fmaxf(fabsf(v[2]), fabsf(v[3])));
 #pragma unroll
   for (int off = 16; off > 0; off >>= 1) amax = fmaxf(amax, __shfl_xor_sync(0xFFFFFFFFu, amax, off));
@@ -66,10 +69,23 @@ __global__ void __launch_bounds__(kRowThreads) quant_rows_kernel(
   const int64_t total = rows * groups_per_row;
   const int64_t warp0 = (int64_t)blockIdx.x * (kRowThreads / 32) + (threadIdx.x >> 5);
   const int64_t stride = (int64_t)gridDim.x * (kRowThreads / 32);
-  for (int64_t w = warp0; w < total; w += stride) {
-    const int64_t r = w / groups_per_row, g = w % groups_per_row;
-    float* so = transposed ? scales + g * scale_ld + r : scales + r * groups_per_row + g;
-    quant_group_128<T, UE8M0>(x + r * cols + g * 128, q + r * cols + g * 128, so, lane);
+  constexpr int U = 4;  // groups in flight per warp
+  for (int64_t w = warp0; w < total; w += U * stride) {
+    float v[U][4];
+#pragma unroll
+    for (int u = 0; u < U; ++u) {
+      const int64_t wu = w + u * stride;
+      if (wu < total) load_group_128<T>(x + wu * 128, lane, v[u]);  // rows are contiguous: group wu starts at wu * 128
+    }
+#pragma unroll
+    for (int u = 0; u < U; ++u) {
+      const int64_t wu = w + u * stride;
+      if (wu < total) {
+        const int64_t r = wu / groups_per_row, g = wu % groups_per_row;
+        float* so = transposed ? scales + g * scale_ld + r : scales + r * groups_per_row + g;
+        quant_group_128<UE8M0>(v[u], q + wu * 128, so, lane);
+      }
+    }
   }
 }
 
