@@ -377,6 +377,18 @@ def test_quant_and_sum_wrappers():
                                        rtol=1.6e-2 if dt != torch.float32 else 1.3e-6, atol=1e-4 * k)
 
 
+def test_moe_sum_accepts_strided_tensors():
+    # the reference's general kernel is stride-aware (src/flaggems_vllm/ops/moe_sum.py:295-310)
+    big = torch.randn(40, 6, 512, device=DEV, dtype=torch.bfloat16)
+    inp = big[::2, 1:5, ::2]                      # non-contiguous in every dimension
+    out_big = torch.zeros(20, 512, device=DEV, dtype=torch.bfloat16)
+    out = out_big[:, ::2]
+    fg.moe_sum(inp, out)
+    torch.testing.assert_close(out.float().cpu(), O.moe_sum_oracle(inp.contiguous()).to(torch.bfloat16).float(),
+                               rtol=1.6e-2, atol=1e-3)
+    assert torch.all(out_big[:, 1::2] == 0)       # the gaps of the strided output stay untouched
+
+
 def test_gather_rows_matches_index_select():
     from flaggems_vllm_b200 import _lib
     M, k, E, H, bm = 77, 4, 16, 256, 128
