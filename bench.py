@@ -541,7 +541,9 @@ def main():
                 "mode": "three streams, double-buffered: H2D / kernels / D2H of neighbouring steps overlap",
                 "serial_ms_per_step": e2e_serial_ms, "serial_value": total_tokens / (e2e_serial_ms * 1e-3),
                 "cpus_bound": numa},
-        "gpu_launches": 6 * args.steps,
+        # kernels of this library per timed step: routing, quantiser, align, GEMM1, GEMM2, sum on one
+        # GPU; the expert-parallel step adds plan, pack, unpack and the combine sum
+        "gpu_launches": (10 if world > 1 else 6) * args.steps,
         "clocks": clocks, "kernel_status": status,
     }
     if world == 1:
