@@ -329,7 +329,7 @@ w8_gemm_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant_
       }
       if (!alive) continue;
       const uint32_t a = acc_it & 1;
-      if (!mbar_wait(&aux->tmem_full[a], (acc_it >> 1) & 1, P.status)) { alive = false; continue; }
+      if (!mbar_wait_idle(&aux->tmem_full[a], (acc_it >> 1) & 1, P.status)) { alive = false; continue; }
       tc_fence_after();
 #pragma unroll 1
       for (int h = 0; h < 2; ++h) {

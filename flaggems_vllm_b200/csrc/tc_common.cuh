@@ -92,6 +92,22 @@ __device__ __forceinline__ bool mbar_wait(uint64_t* bar, uint32_t parity, int32_
   }
   return true;
 }
+// The same bounded wait for warps that expect to wait long (an epilogue warp waiting for a
+// whole K loop): they sleep between probes, so their polling does not take issue slots from
+// the warps that feed the tensor core.
+__device__ __forceinline__ bool mbar_wait_idle(uint64_t* bar, uint32_t parity, int32_t* status) {
+  if (mbar_try(bar, parity)) return true;
+  const unsigned long long t0 = now_ns();
+  uint32_t spins = 0;
+  while (!mbar_try(bar, parity)) {
+    __nanosleep(128);
+    if ((++spins & 0xFF) == 0 && now_ns() - t0 > WAIT_LIMIT_NS) {
+      set_status(status, MOE_ST_WAIT_TIMEOUT);
+      return false;
+    }
+  }
+  return true;
+}
 __device__ __forceinline__ void tma_load_2d(const CUtensorMap* map, uint64_t* bar, void* dst, int c0, int c1) {
   asm volatile(
       "cp.async.bulk.tensor.2d.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1, {%3, %4}], [%2];"
