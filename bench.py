@@ -159,32 +159,72 @@ def cpu_oracle_run(M_sample, seed_shift=0, E_used=None, threads=None):
     return step, threads, len(used)
 
 
+def fit_reference_tokens(want, steps, warmup, budget_s, seed_shift=0):
+    """Largest power-of-two fraction of `want` tokens whose `steps + warmup` CPU passes fit
+    `budget_s` seconds, judged from one timed pass.  Returns (tokens, step, threads,
+    distinct experts, seconds of that first pass)."""
+    M_s = want
+    while True:
+        step, threads, n_used = cpu_oracle_run(M_s, seed_shift)
+        t0 = time.perf_counter()
+        step()
+        first = time.perf_counter() - t0
+        if first * (steps + warmup) <= budget_s or M_s <= 16:
+            return M_s, step, threads, n_used, first
+        M_s //= 2
+
+
 def run_reference(args):
     """--impl reference: the reference's torch-native path (CPU oracle port) on host cores."""
     rank, world, _ = dist_env()
     if rank != 0:
         return
-    M_s = args.ref_tokens
-    step, threads, n_used = cpu_oracle_run(M_s)
-    for _ in range(max(1, min(args.warmup, 1))):
+    M_s, step, threads, n_used, _ = fit_reference_tokens(args.ref_tokens, args.steps, args.warmup,
+                                                         args.ref_budget_s)
+    for _ in range(max(0, args.warmup - 1)):  # the sizing pass above was the first warm-up pass
         step()
     t0 = time.perf_counter()
     for _ in range(args.steps):
         step()
     dt = (time.perf_counter() - t0) / args.steps
     val = M_s / dt
+    sample = (f"{M_s} tokens per step of the DSV3 FP8 layer ({n_used} distinct experts; the GPU arm runs "
+              f"{args.tokens} tokens per step: the CPU sample is the largest that keeps {args.steps}+{args.warmup} "
+              f"passes inside {args.ref_budget_s:.0f} s), CPU oracle restating the reference's torch goldens")
     line = {
         "impl": "reference", "metric": "fused_moe_layer_tokens_per_s", "value": val, "unit": "tokens/s",
-        "n_gpus": args.gpus, "steps": args.steps, "warmup": min(args.warmup, 1), "ms_per_step": dt * 1e3,
+        "n_gpus": args.gpus, "steps": args.steps, "warmup": args.warmup, "ms_per_step": dt * 1e3,
         "higher_is_better": True, "scaling": "weak", "vs_baseline": None, "dtype": "fp8_e4m3", "data": "synthetic",
         "config": {"workload": "deepseek_v3_fp8_block_moe_layer", "tokens": M_s, **DSV3},
-        "cpu_baseline": {"value": val, "unit": "tokens/s", "cores": threads, "kind": "port",
-                         "sample": f"{M_s} tokens per step of the DSV3 FP8 layer ({n_used} distinct experts), "
-                                   "CPU oracle restating the reference's torch goldens"},
+        "cpu_baseline": {"value": val, "unit": "tokens/s", "cores": threads, "kind": "port", "sample": sample},
         "e2e": {"value": val, "unit": "tokens/s", "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0},
         "tflops": 6.0 * M_s * DSV3["topk"] * DSV3["H"] * DSV3["I"] / dt / 1e12,
     }
     print(json.dumps(line), flush=True)
+
+
+def measure_fp8_peak(dev, n=8192, reps=10):
+    """Dense e4m3 x e4m3 -> bf16 library GEMM (torch._scaled_mm, per-tensor scales) of n^3,
+    best of `reps`, CUDA events: the denominator of the FP8 roofline.  Runs once, outside
+    every timed region.  Returns TFLOP/s or None when the library call is unavailable."""
+    try:
+        a = torch.randn((n, n), device=dev, dtype=torch.bfloat16).to(torch.float8_e4m3fn)
+        b = torch.randn((n, n), device=dev, dtype=torch.bfloat16).to(torch.float8_e4m3fn).t()
+        one = torch.ones((), device=dev, dtype=torch.float32)
+        for _ in range(3):
+            torch._scaled_mm(a, b, scale_a=one, scale_b=one, out_dtype=torch.bfloat16)
+        best = None
+        for _ in range(reps):
+            e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+            e0.record()
+            torch._scaled_mm(a, b, scale_a=one, scale_b=one, out_dtype=torch.bfloat16)
+            e1.record()
+            torch.cuda.synchronize()
+            ms = e0.elapsed_time(e1)
+            best = ms if best is None or ms < best else best
+        return 2.0 * n ** 3 / (best * 1e-3) / 1e12
+    except Exception:
+        return None
 
 
 def run_sweep(args):
@@ -334,6 +374,97 @@ def run_sweep(args):
                               "tokens_per_s": M / (ms * 1e-3)}), flush=True)
 
 
+def ep_parity_check(dist, dev, rank, world, layer, x, logits, bias, c, sample_tokens):
+    """Expert-parallel correctness, run before the timed region at N > 1.
+
+    (a) Three small layers (FP8 M=96, half precision M=64, FP8 M=1): every rank holds the full
+        seeded weights, runs the expert-parallel step on its own tokens and compares with the
+        single-GPU layer of the same tokens.
+    (b) `sample_tokens` tokens per rank of the full-size step against the CPU oracle; only the
+        experts those tokens use are broadcast from their owners.
+    Returns {"max_rel_l2", "min_cos", "ok", ...}; limits are the layer tolerance (relative L2
+    <= 1e-2, cosine >= 0.9999).  The per-rank partial sums are rounded to bf16 before the final
+    sum, one rounding more than the single-GPU layer."""
+    import flaggems_vllm_b200 as fg
+    from flaggems_vllm_b200 import _lib, ep
+    from flaggems_vllm_b200 import testing as T
+    from oracle import moe_oracle as O
+
+    worst, mincos, status = 0.0, 1.0, 0
+    cases = []
+    for mode, (M, E, H, I, k) in (("fp8", (96, 32, 512, 256, 8)), ("half", (64, 16, 256, 256, 4)),
+                                  ("fp8", (1, 32, 512, 256, 8))):
+        xs = T.make_activations(M, H, dev, seed=50 + rank)
+        lg, bs = T.make_router_inputs(M, E, dev, seed=60 + rank)
+        El = E // world
+        sl = slice(rank * El, (rank + 1) * El)
+        if mode == "fp8":
+            w1, s1 = T.make_fp8_block_weights(E, 2 * I, H, dev, seed=1, std=H ** -0.5)
+            w2, s2 = T.make_fp8_block_weights(E, H, I, dev, seed=2, std=I ** -0.5)
+            tw, ti = fg.grouped_topk(lg, 8, 4, k, True, 2.5, torch.zeros_like(bs), 1)
+            full = fg.fused_experts_impl(xs, w1, w2, tw, ti, use_fp8_w8a8=True, w1_scale=s1, w2_scale=s2,
+                                         block_shape=[128, 128])
+            small = ep.ExpertParallelMoE(w1[sl].contiguous(), w2[sl].contiguous(), s1[sl].contiguous(),
+                                         s2[sl].contiguous(), E, mode=_lib.MODE_FP8_BLOCK)
+        else:
+            w1 = T.make_half_weights(E, 2 * I, H, dev, seed=1, std=H ** -0.5)
+            w2 = T.make_half_weights(E, H, I, dev, seed=2, std=I ** -0.5)
+            tw, ti = fg.grouped_topk(torch.softmax(lg, -1), 1, 1, k, True, 1.0, torch.zeros_like(bs), 0)
+            full = fg.fused_experts_impl(xs, w1, w2, tw, ti)
+            small = ep.ExpertParallelMoE(w1[sl].contiguous(), w2[sl].contiguous(), None, None, E, mode=_lib.MODE_HALF)
+        got = small.forward(xs, tw, ti)
+        torch.cuda.synchronize()
+        rl2, cs = O.rel_l2(got.float().cpu(), full.float().cpu()), O.cosine(got.float().cpu(), full.float().cpu())
+        worst, mincos = max(worst, rl2), min(mincos, cs)
+        cases.append(rl2)
+    status |= fg.read_status(dev)
+
+    # ---- (b) sampled tokens of the full-size step against the CPU oracle
+    E, k, M = c["E"], c["topk"], x.shape[0]
+    El = E // world
+    tw, ti = fg.grouped_topk(logits, c["n_group"], c["topk_group"], k, True, c["rsf"], bias, 1)
+    out = layer.forward(x, tw, ti)
+    torch.cuda.synchronize()
+    status |= fg.read_status(dev)
+    n_s = min(sample_tokens, M)
+    idx = torch.linspace(0, M - 1, n_s, device=dev).long()
+    ids_s = ti[idx]
+    need = torch.zeros(E, dtype=torch.int32, device=dev)
+    need[ids_s.reshape(-1).long()] = 1
+    union = need.clone()
+    dist.all_reduce(union, op=dist.ReduceOp.MAX)
+    mine = need.cpu().bool()
+    tabs = {"w1": [], "s1": [], "w2": [], "s2": []}
+    remap = torch.full((E,), -1, dtype=torch.int64)
+    for e in torch.nonzero(union.cpu()).reshape(-1).tolist():
+        owner, el = divmod(e, El)
+        parts = {}
+        for name, t in (("w1", layer.w1), ("s1", layer.s1), ("w2", layer.w2), ("s2", layer.s2)):
+            buf = t[el].clone() if rank == owner else torch.empty_like(t[0])
+            flat = buf.view(torch.uint8) if buf.dtype == torch.float8_e4m3fn else buf
+            dist.broadcast(flat, owner)
+            parts[name] = buf
+        if mine[e]:
+            remap[e] = len(tabs["w1"])
+            for name in tabs:
+                tabs[name].append(parts[name].cpu())
+    torch.set_num_threads(max(1, (os.cpu_count() or 1) // world))
+    w1t, s1t, w2t, s2t = (torch.stack(tabs[n]) for n in ("w1", "s1", "w2", "s2"))
+    ref = O.fused_moe_fp8_block_oracle(x[idx].cpu(), w1t, w2t, s1t, s2t, tw[idx].cpu(),
+                                       remap[ids_s.cpu().long()].to(torch.int32))
+    got = out[idx].float().cpu()
+    rl2, cs = O.rel_l2(got, ref), O.cosine(got, ref)
+    worst_t = torch.tensor([max(worst, rl2), -min(mincos, cs), float(status)], dtype=torch.float64, device=dev)
+    dist.all_reduce(worst_t, op=dist.ReduceOp.MAX)
+    w, mc, stt = float(worst_t[0]), -float(worst_t[1]), int(worst_t[2])
+    return {"max_rel_l2": w, "min_cos": mc, "ok": bool(w <= 1e-2 and mc >= 0.9999 and stt == 0),
+            "kernel_status": stt, "rank0_small_cases_rel_l2": cases, "rank0_full_size_sample_rel_l2": rl2,
+            "full_size_sample_tokens_per_rank": n_s,
+            "what": "max over ranks: 3 small layers vs the single-GPU layer, and sampled tokens of the "
+                    "full-size step vs the CPU oracle (limits 1e-2 / 0.9999; the per-rank partial sums are "
+                    "rounded to bf16 once more than on one GPU)"}
+
+
 def main():
     ap = argparse.ArgumentParser()
     ap.add_argument("--gpus", type=int, default=1)
@@ -341,9 +472,13 @@ def main():
     ap.add_argument("--warmup", type=int, default=5)
     ap.add_argument("--impl", default="b200", choices=["b200", "reference"])
     ap.add_argument("--tokens", type=int, default=8192, help="tokens per GPU per step")
-    ap.add_argument("--ref-tokens", type=int, default=4, help="tokens per step of the CPU reference arm")
-    ap.add_argument("--cpu-baseline-tokens", type=int, default=16)
+    ap.add_argument("--ref-tokens", type=int, default=256,
+                    help="tokens per step of the CPU reference arm (halved until the run fits --ref-budget-s)")
+    ap.add_argument("--ref-budget-s", type=float, default=240.0, help="wall-clock budget of the CPU reference arm")
+    ap.add_argument("--cpu-baseline-tokens", type=int, default=256)
     ap.add_argument("--no-cpu-baseline", action="store_true")
+    ap.add_argument("--ep-check-tokens", type=int, default=16,
+                    help="tokens per rank of the full-size expert-parallel step checked against the CPU oracle (0: skip)")
     ap.add_argument("--router-bias-std", type=float, default=0.02,
                     help="spread of the synthetic score-correction bias; the scores are i.i.d., so a small "
                          "spread gives the balanced expert load a trained bias produces")
@@ -391,6 +526,10 @@ def main():
         dist.broadcast(bias, 0)
     flush = torch.empty(2 * L2_BYTES, dtype=torch.uint8, device=dev)
     layer = ep.ExpertParallelMoE(w1, w2, s1, s2, E, dist.group.WORLD) if world > 1 else None
+    ep_parity = None
+    if world > 1 and args.ep_check_tokens > 0:
+        ep_parity = ep_parity_check(dist, dev, rank, world, layer, x, logits, bias, c, args.ep_check_tokens)
+    fp8_peak = measure_fp8_peak(dev) if world == 1 else None
 
     def device_step():
         tw, ti = fg.grouped_topk(logits, c["n_group"], c["topk_group"], k, True, c["rsf"], bias, 1)
@@ -435,9 +574,13 @@ def main():
     # line, more so with eight GPUs in the box); only its samples under load are used
     sampler = ClockSampler(local)
     sampler.start()
+    from flaggems_vllm_b200 import _lib as _native
+
     for _ in range(args.warmup):
         device_step()
+    launches0 = _native.LAUNCHES
     ms = timed(device_step, args.steps, record_stages=(world == 1))
+    launches = _native.LAUNCHES - launches0
     clocks = sampler.stop()
     if world == 1:
         prev = None
@@ -541,9 +684,8 @@ def main():
                 "mode": "three streams, double-buffered: H2D / kernels / D2H of neighbouring steps overlap",
                 "serial_ms_per_step": e2e_serial_ms, "serial_value": total_tokens / (e2e_serial_ms * 1e-3),
                 "cpus_bound": numa},
-        # kernels of this library per timed step: routing, quantiser, align, GEMM1, GEMM2, sum on one
-        # GPU; the expert-parallel step adds plan, pack, unpack and the combine sum
-        "gpu_launches": (10 if world > 1 else 6) * args.steps,
+        # kernel-launching calls into libmoe_sm100.so counted inside the timed region on this rank
+        "gpu_launches": launches,
         "clocks": clocks, "kernel_status": status,
     }
     if world == 1:
@@ -553,7 +695,8 @@ def main():
         # MEASURED_PEAKS.json, so 2x the measured bf16 burst figure is used
         g1 = sum(stage_ms["gemm1"]) / len(stage_ms["gemm1"])
         f1 = 2.0 * M * k * (2 * I) * H
-        peak = 2.0 * peaks["bf16_tflops"]
+        peak2x = 2.0 * peaks["bf16_tflops"]
+        peak = fp8_peak if fp8_peak else peak2x
         # DRAM traffic of one GEMM1 launch: ncu (dram__bytes_read+write) on the 32-expert /
         # 1024-token capture gave 1.134 GB for 0.964 GB of algorithmic bytes (weights of the
         # experts in use + e4m3 activations + scales + the e4m3 intermediate), a ratio of 1.18;
@@ -562,30 +705,44 @@ def main():
         _, ti0 = fg.grouped_topk(logits, c["n_group"], c["topk_group"], k, True, c["rsf"], bias, 1)
         e_act = int(torch.unique(ti0).numel())
         alg1 = e_act * (2 * I * H + (2 * I // 128) * (H // 128) * 4) + M * H + M * (H // 128) * 4 + M * k * I
-        line["roofline"] = {"kernel": "tc_gemm_kernel<fp8,gemm1>", "bound": "tensor", "achieved": f1 / (g1 * 1e-3) / 1e12,
-                            "peak": peak, "unit": "TFLOP/s", "frac": f1 / (g1 * 1e-3) / 1e12 / peak,
-                            "frac_of_sustained": f1 / (g1 * 1e-3) / 1e12 / (2.0 * peaks["bf16_tflops_sustained"]),
+        ach = f1 / (g1 * 1e-3) / 1e12
+        line["roofline"] = {"kernel": "tc_gemm_kernel<fp8,gemm1>", "bound": "tensor", "achieved": ach,
+                            "peak": peak, "unit": "TFLOP/s", "frac": ach / peak,
+                            "peak_fp8_measured": fp8_peak, "frac_vs_2x_bf16": ach / peak2x,
+                            "frac_of_sustained": ach / (2.0 * peaks["bf16_tflops_sustained"]),
                             "traffic": 1.18 * alg1, "traffic_source": "ncu small-case DRAM bytes scaled by algorithmic bytes (x1.18)",
-                            "algorithmic_bytes": alg1, "peak_source": f"2 x bf16_tflops of {peaks['source']} peaks",
-                            "ms_per_launch": g1, "experts_in_use": e_act}
+                            "algorithmic_bytes": alg1,
+                            "peak_source": ("torch._scaled_mm e4m3 8192^3, best of 10, CUDA events, measured in this run"
+                                            if fp8_peak else f"2 x bf16_tflops of {peaks['source']} peaks"),
+                            "ms_per_launch": g1, "experts_in_use": e_act,
+                            "layer_tflops": flops / (ms * 1e-3) / 1e12, "layer_frac": flops / (ms * 1e-3) / 1e12 / peak}
         wbytes = E * 3 * H * I + (E * (2 * I // 128) * (H // 128) + E * (H // 128) * (I // 128)) * 4
         B = wbytes + M * H * 2 * 2 + M * E * 4 + k * 8 * M
         line["layer_hbm"] = {"algorithmic_bytes": B, "achieved_gbs": B / (ms * 1e-3) / 1e9,
                              "peak_gbs": peaks["hbm_gbs"], "frac": B / (ms * 1e-3) / 1e9 / peaks["hbm_gbs"]}
+    if ep_parity is not None:
+        line["ep_parity"] = ep_parity
     if rank == 0 and world == 1 and not args.no_cpu_baseline and E == DSV3["E"]:
-        Ms = args.cpu_baseline_tokens
-        step, threads, n_used = cpu_oracle_run(Ms)
-        step()
+        # same sample size as the reference arm; one sizing/warm-up pass, one timed pass
+        Ms, step, threads, n_used, _ = fit_reference_tokens(args.cpu_baseline_tokens, 1, 1, 60.0)
         t0 = time.perf_counter()
         step()
         dt = time.perf_counter() - t0
         line["cpu_baseline"] = {"value": Ms / dt, "unit": "tokens/s", "cores": threads, "kind": "port",
-                                "sample": f"{Ms} tokens of the same layer ({n_used} distinct experts), one timed pass "
-                                          "after one warm-up, CPU oracle (torch-native restatement of the reference goldens)"}
+                                "ms_per_step": dt * 1e3,
+                                "sample": f"{Ms} tokens of the same layer ({n_used} distinct experts; the GPU step is {M} "
+                                          "tokens), one timed pass after one warm-up, CPU oracle (torch-native "
+                                          "restatement of the reference goldens)"}
     if rank == 0:
         print(json.dumps(line), flush=True)
     if dist is not None:
         dist.destroy_process_group()
+    if status != 0:
+        print(f"kernel status word = {status} (a kernel reported a failure)", file=sys.stderr)
+        sys.exit(3)
+    if ep_parity is not None and not ep_parity["ok"]:
+        print(f"expert-parallel parity check failed: {ep_parity}", file=sys.stderr)
+        sys.exit(4)
 
 
 if __name__ == "__main__":

@@ -39,6 +39,7 @@ SYMBOLS = {
                               c_void_p]),
     "moe_router_gemm": (c_int, [c_void_p, c_int, c_int64, c_void_p, c_int, c_int64, c_int, c_int, c_void_p, c_void_p]),
     "moe_gather_rows": (c_int, [c_void_p, c_int64, c_int, c_int64, c_void_p, c_void_p, c_int64, c_void_p, c_void_p]),
+    "moe_gather_scales_t": (c_int, [c_void_p, c_int, c_int64, c_int, c_void_p, c_void_p, c_int64, c_void_p, c_void_p]),
     "moe_gemm1": (c_int, [c_int, c_int, c_void_p, c_int, c_void_p, c_int64, c_int, c_void_p, c_void_p, c_void_p,
                           c_void_p, c_void_p, c_void_p, c_int, c_int64, c_int, c_int, c_int, c_int, c_void_p,
                           c_void_p, c_int, c_void_p, c_void_p]),
@@ -51,13 +52,34 @@ SYMBOLS = {
 
 _lib = None
 _status = {}
+# calls of entry points that enqueue a kernel (bench.py reports the count of its timed region)
+LAUNCHES = 0
+_NO_KERNEL = ("moe_abi_version", "moe_last_error")
+
+
+class _Counted:
+    """The library handle with a call counter in front of every kernel-launching entry point."""
+
+    def __init__(self, handle):
+        for name in SYMBOLS:
+            fn = getattr(handle, name)
+            setattr(self, name, fn if name in _NO_KERNEL else self._wrap(fn))
+
+    @staticmethod
+    def _wrap(fn):
+        def call(*args):
+            global LAUNCHES
+            LAUNCHES += 1
+            return fn(*args)
+
+        return call
 
 
 class MoeKernelError(RuntimeError):
     """A launch was rejected or failed; the message is the library's text."""
 
 
-def lib() -> ctypes.CDLL:
+def lib():
     global _lib
     if _lib is None:
         if not os.path.exists(LIB_PATH):
@@ -70,7 +92,7 @@ def lib() -> ctypes.CDLL:
             fn = getattr(handle, name)
             fn.restype = res
             fn.argtypes = args
-        _lib = handle
+        _lib = _Counted(handle)
     return _lib
 
 
@@ -96,7 +118,9 @@ def require_cuda(t: torch.Tensor, who: str) -> None:
 
 def status_word(device) -> torch.Tensor:
     """Per-device int32 word the kernels OR failure bits into."""
-    key = torch.device(device).index or 0
+    key = torch.device(device).index
+    if key is None:
+        key = torch.cuda.current_device()
     if key not in _status:
         _status[key] = torch.zeros(1, dtype=torch.int32, device=torch.device("cuda", key))
     return _status[key]

@@ -40,6 +40,9 @@
 // Every barrier wait is bounded (wall-clock limit); on expiry the kernel sets
 // MOE_ST_WAIT_TIMEOUT, leaves its loops, frees TMEM and returns.
 #include "tc_common.cuh"
+#ifdef MOE_TC_TRACE
+#include <cstdlib>
+#endif
 
 namespace moe {
 namespace tc {
@@ -117,7 +120,19 @@ struct Params {
   int rows_w;   // weight rows per expert (2I or H)
   int n_tiles;  // column tiles per align block
   bool wide_store;  // the output is 32-byte aligned: rows are written with 32-byte stores
+#ifdef MOE_TC_TRACE
+  long long* trace;  // [4 roles][64 K blocks][8 events] cycle stamps of CTA 0, third tile (experiment builds)
+#endif
 };
+#ifdef MOE_TC_TRACE
+#define MOE_TR(role, kb, ev) \
+  do { if (blockIdx.x == 0 && tile == tile0 + 2 * tile_step && P.trace && (kb) < 64) P.trace[((role) * 64 + (kb)) * 8 + (ev)] = clock64(); } while (0)
+#define MOE_TRN(role, slot, ev) \
+  do { if (blockIdx.x == 0 && tile == tile0 + 3 * tile_step && P.trace) P.trace[((role) * 64 + (slot)) * 8 + (ev)] = clock64(); } while (0)
+#else
+#define MOE_TR(role, kb, ev) do {} while (0)
+#define MOE_TRN(role, slot, ev) do {} while (0)
+#endif
 
 // Instruction descriptor: fp32 accumulator (bits 4-5 = 1), A/B element format
 // (bits 7-9 / 10-12: e4m3 = 0 for kind::f8f6f4; f16 = 0, bf16 = 1 for
@@ -171,7 +186,7 @@ __device__ __forceinline__ int box_row(int nt, int c, int cr, int Nout) {
 template <bool FP8, typename AT, bool GEMM1, bool PAIR, int RB, bool SORTED = false>
 __global__ void __launch_bounds__(THREADS, 1)
 tc_gemm_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant__ CUtensorMap map_b, const Params P) {
-  static_assert(!SORTED || (GEMM1 && !FP8), "pre-sorted A rows: half-precision GEMM1 only");
+  static_assert(!SORTED || (GEMM1 && !PAIR), "pre-sorted A rows: single-CTA GEMM1 only");
   constexpr bool GATHER = GEMM1 && !SORTED;  // A rows gathered inside the kernel
   static_assert(RB == 1 || (RB == 2 && !FP8), "wide tiles: half precision only");
   constexpr int STAGES = Cfg<PAIR, RB>::STAGES;
@@ -194,13 +209,20 @@ tc_gemm_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant_
   const int cr = PAIR ? (int)cluster_ctarank() : 0;  // rank inside the pair; 0 leads
   const int tile0 = blockIdx.x / CTAS, tile_step = gridDim.x / CTAS;
   const int total_tiles = ((npp + UNIT * BM - 1) / (UNIT * BM)) * P.n_tiles;
-  // tile -> expert_ids index (blk), this CTA's 128-row block (mb), column tile (nt)
+  // tile -> expert_ids index (blk), this CTA's 128-row block (mb), column tile (nt).  The expert of
+  // the NEXT tile is fetched while the current one is worked on: a tile starts without waiting
+  // for a global load (every role walks the same tile list with its own copy of e_next).
 #define MOE_TILE_COORDS(tile)                      \
   const int blk = (tile) / P.n_tiles;              \
   [[maybe_unused]] const int nt = (tile) % P.n_tiles; \
   [[maybe_unused]] const int mb = UNIT * blk + RB * cr; \
-  const int e = P.expert_ids[blk];
+  const int e = e_next;                            \
+  e_next = (tile) + tile_step < total_tiles ? P.expert_ids[((tile) + tile_step) / P.n_tiles] : -1;
+  int e_next = tile0 < total_tiles ? P.expert_ids[tile0 / P.n_tiles] : -1;
 
+#ifdef MOE_TC_TRACE
+  if (threadIdx.x == 0 && blockIdx.x == 0 && P.trace) { P.trace[2048] = clock64(); P.trace[2049] = (long long)now_ns(); P.trace[2052] = total_tiles; }
+#endif
   if (threadIdx.x == 0) {
     for (int s = 0; s < STAGES; ++s) {
       mbar_init(&aux->full[s], GATHER ? 1 + GATHER_THREADS : (FP8 ? 1 + SCALE_THREADS : 1));
@@ -247,7 +269,9 @@ tc_gemm_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant_
         for (int kb = 0; kb < KB; ++kb, ++it) {
           const int s = it % STAGES;
           const uint32_t ph = (it / STAGES) & 1;
+          MOE_TR(0, kb, 0);
           if (!mbar_wait(&aux->empty[s], ph ^ 1, P.status)) { alive = false; break; }
+          MOE_TR(0, kb, 1);
           if constexpr (GATHER) {
             mbar_expect_tx(&aux->full[s], B_LOCAL_BYTES);  // A rows arrive by cp.async (warps 2-3)
           } else {
@@ -261,13 +285,71 @@ tc_gemm_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant_
           for (int c = 0; c < BBox<GEMM1, PAIR>::COUNT; ++c)
             tma_load_2d(&map_b, &aux->full[s], sB + (size_t)s * B_LOCAL_BYTES + c * (BBox<GEMM1, PAIR>::ROWS * 128),
                         kb * KBE, wrow0 + box_row<GEMM1, PAIR>(nt, c, cr, P.Nout));
+          MOE_TR(0, kb, 2);
         }
       }
     } else if (warp == 1 && lane == 0 && cr == 0) {
       // ------------------------------------------------------------ MMA issuer (pair: leader only)
       constexpr uint32_t idesc = IDesc<FP8, AT, PAIR>::value;
-      uint32_t it = 0, acc_it = 0;
+      [[maybe_unused]] uint32_t it = 0;
+      uint32_t acc_it = 0;
       bool alive = true;
+      if constexpr (!PAIR) {
+        // This thread shares its scheduler with two consumer warps that stream FMAs, and every
+        // instruction it needs between "accumulator released" and "MMAs issued" waits for an issue
+        // slot behind them.  So everything that does not depend on the release is done before the
+        // wait for it: stage index and phase are carried (no division), the descriptors are one
+        // add away from a base, and the operands' barrier (which completed long before) is waited
+        // for first.  After the release only the fence, the four MMAs and the commits remain.
+        const uint64_t adesc0 = make_smem_desc(smem_u32(sA));
+        const uint64_t bdesc0 = make_smem_desc(smem_u32(sB));
+        uint32_t s = 0, sph = 0;
+        for (int tile = tile0; tile < total_tiles && alive; tile += tile_step) {
+          MOE_TRN(1, 61, 0);
+          MOE_TILE_COORDS(tile)
+          if (e < 0 || e >= P.E) continue;
+          MOE_TRN(1, 61, 1);
+          for (int kb = 0; kb < KB; ++kb) {
+            const uint32_t a = RB == 2 ? 0u : (acc_it & 1);
+            const uint32_t aph = RB == 2 ? (acc_it & 1) : ((acc_it >> 1) & 1);
+            const uint64_t bdesc = bdesc0 + (uint64_t)(s * (uint32_t)(B_LOCAL_BYTES >> 4));
+            const uint64_t adesc = adesc0 + (uint64_t)(s * (uint32_t)(A_LOCAL_BYTES >> 4));
+            const uint32_t d0 = tmem_base + a * BN;
+            MOE_TR(1, kb, 0);
+            if (!mbar_wait(&aux->full[s], sph, P.status)) { alive = false; break; }
+            MOE_TR(1, kb, 1);
+            if constexpr (GATHER) asm volatile("fence.proxy.async.shared::cta;" ::: "memory");  // cp.async writes -> tensor core reads
+            if (FP8 || kb == 0) {
+              if (!mbar_wait(&aux->tmem_empty[a], aph ^ 1, P.status)) { alive = false; break; }
+            }
+            MOE_TR(1, kb, 2);
+            tc_fence_after();
+#pragma unroll
+            for (int j = 0; j < RB; ++j) {
+              const uint64_t aj = adesc + (uint64_t)(j * (A_STAGE_BYTES >> 4));
+              const uint32_t d = RB == 2 ? tmem_base + (uint32_t)j * BN : d0;
+              if (FP8) {
+                tc_mma_const<FP8, false>(d, aj, bdesc, idesc);
+              } else {
+                tc_mma<FP8>(d, aj, bdesc, idesc, kb > 0);
+              }
+#pragma unroll
+              for (int k4 = 1; k4 < 4; ++k4)  // 32 bytes of K per instruction: start address advances by 32 B >> 4
+                tc_mma_const<FP8, true>(d, aj + (uint64_t)(k4 * 2), bdesc + (uint64_t)(k4 * 2), idesc);
+            }
+            if (FP8 || kb == KB - 1) {
+              tc_commit(&aux->tmem_full[a]);
+              ++acc_it;
+            }
+            tc_commit(&aux->empty[s]);
+            MOE_TR(1, kb, 3);
+            if (kb == 0) MOE_TRN(1, 61, 2);
+            if (kb == 1) MOE_TRN(1, 61, 3);
+            if (kb == 2) MOE_TRN(1, 61, 4);
+            if (++s == STAGES) { s = 0; sph ^= 1; }
+          }
+        }
+      } else {
       for (int tile = tile0; tile < total_tiles && alive; tile += tile_step) {
         MOE_TILE_COORDS(tile)
         if (e < 0 || e >= P.E) continue;
@@ -282,9 +364,7 @@ tc_gemm_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant_
           }
           const int s = it % STAGES;
           if (!mbar_wait(&aux->full[s], (it / STAGES) & 1, P.status)) { alive = false; break; }
-          if constexpr (PAIR) {
-            if (!mbar_wait<true>(&aux->peer_full[s], (it / STAGES) & 1, P.status)) { alive = false; break; }
-          }
+          if (!mbar_wait<true>(&aux->peer_full[s], (it / STAGES) & 1, P.status)) { alive = false; break; }
           if constexpr (GATHER) asm volatile("fence.proxy.async.shared::cta;" ::: "memory");  // cp.async writes -> tensor core reads
           tc_fence_after();
           const uint64_t bdesc = make_smem_desc(smem_u32(sB + (size_t)s * B_LOCAL_BYTES));
@@ -296,16 +376,16 @@ tc_gemm_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant_
             for (int k4 = 0; k4 < 4; ++k4) {
               // 32 bytes of K per instruction: start address advances by 32 B >> 4
               const uint32_t accum = FP8 ? (k4 > 0) : (kb > 0 || k4 > 0);
-              if constexpr (PAIR) tc_mma_pair<FP8>(d, adesc + (uint64_t)(k4 * 2), bdesc + (uint64_t)(k4 * 2), idesc, accum);
-              else tc_mma<FP8>(d, adesc + (uint64_t)(k4 * 2), bdesc + (uint64_t)(k4 * 2), idesc, accum);
+              tc_mma_pair<FP8>(d, adesc + (uint64_t)(k4 * 2), bdesc + (uint64_t)(k4 * 2), idesc, accum);
             }
           }
-          if constexpr (PAIR) tc_commit_pair(&aux->empty[s]); else tc_commit(&aux->empty[s]);
+          tc_commit_pair(&aux->empty[s]);
           if (FP8 || kb == KB - 1) {
-            if constexpr (PAIR) tc_commit_pair(&aux->tmem_full[a]); else tc_commit(&aux->tmem_full[a]);
+            tc_commit_pair(&aux->tmem_full[a]);
             ++acc_it;
           }
         }
+      }
       }
     } else if (PAIR && warp == 1 && lane == 0 && cr == 1) {
       // ------------------------------------------------------------ partner CTA: tell the leader a stage has landed
@@ -364,7 +444,9 @@ tc_gemm_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant_
         }
         for (int kb = 0; kb < KB; ++kb, ++it) {
           const int s = it % STAGES;
+          if (g == 0) MOE_TR(2, kb, 0);
           if (!mbar_wait(&aux->empty[s], ((it / STAGES) & 1) ^ 1, P.status)) { alive = false; break; }
+          if (g == 0) MOE_TR(2, kb, 1);
           const uint32_t base = smem_u32(sA + (size_t)s * A_LOCAL_BYTES);
 #pragma unroll
           for (int j = 0; j < RPT; ++j) {
@@ -384,11 +466,12 @@ tc_gemm_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant_
             if (g < 2) cp_async4(smem_u32(&aux->sc_w[slot][g]), ws_src + kb);
           }
           cp_async_arrive_noinc(&aux->full[s]);
+          if (g == 0) MOE_TR(2, kb, 2);
         }
       }
       asm volatile("cp.async.wait_all;" ::: "memory");
-    } else if (FP8 && !GEMM1 && warp == 3) {
-      // ------------------------------------------------------------ scale staging (FP8 GEMM2)
+    } else if (FP8 && !GATHER && warp == 3) {
+      // ------------------------------------------------------------ scale staging (FP8, A rows read by TMA)
       uint32_t it = 0;
       bool alive = true;
       const int sblk_per_e = (P.rows_w + 127) / 128;
@@ -396,7 +479,9 @@ tc_gemm_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant_
         MOE_TILE_COORDS(tile)
         if (e < 0 || e >= P.E) continue;
         const float* as_row = P.a_scales_t + (int64_t)mb * BM + 4 * lane;
-        const float* ws_src = P.w_scale + ((int64_t)e * sblk_per_e + min(2 * nt + lane, sblk_per_e - 1)) * KB;
+        // GEMM2: the two 128-column weight blocks of the tile; GEMM1: the gate block and the up block
+        const int wblk = GEMM1 ? (lane == 1 ? (P.Nout >> 7) + nt : nt) : min(2 * nt + lane, sblk_per_e - 1);
+        const float* ws_src = P.w_scale + ((int64_t)e * sblk_per_e + wblk) * KB;
         for (int kb = 0; kb < KB; ++kb, ++it) {
           const int s = it % STAGES;
           if (!mbar_wait(&aux->empty[s], ((it / STAGES) & 1) ^ 1, P.status)) { alive = false; break; }
@@ -427,54 +512,70 @@ tc_gemm_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant_
       }
     };
     for (int tile = tile0; tile < total_tiles && alive; tile += tile_step) {
+      if (threadIdx.x == 128) MOE_TRN(3, 61, 0);
       MOE_TILE_COORDS(tile)
       if (e < 0 || e >= P.E) continue;
+      if (threadIdx.x == 128) MOE_TRN(3, 61, 1);
       for (int sub = 0; sub < RB && alive; ++sub) {  // the 128-row blocks of this tile (two for wide tiles)
       const int64_t p = (int64_t)(mb + sub) * BM + row;
       int64_t sid = P.numel;
       if (p < P.rows_cap) sid = (int64_t)P.sorted_ids[p];
       const bool row_ok = sid >= 0 && sid < P.numel;
       float acc[128];
+      float rw = 1.0f;  // route weight of this row, fetched early: the epilogue must not wait for it
       if constexpr (FP8) {
 #pragma unroll
         for (int i = 0; i < 128; ++i) acc[i] = 0.0f;
         // one K block: wait for its accumulator, fold it into acc, release it
-        auto fold_block = [&](float s_lo, float s_hi) -> bool {
+        auto fold_block = [&](float s_lo, float s_hi, [[maybe_unused]] int kb) {
           const uint32_t a = acc_it & 1;
-          if (!mbar_wait(&aux->tmem_full[a], (acc_it >> 1) & 1, P.status)) return false;
           tc_fence_after();
           const uint32_t t0 = t_lane + a * BN;
           uint32_t ra[32], rb[32];
-          // two loads in flight, one wait; the second pair is issued after the first
-          // pair has been folded, and the accumulator is released before the last FMAs
+          unsigned long long* acc2 = reinterpret_cast<unsigned long long*>(acc);
+          const unsigned long long lo2 = splat2(s_lo), hi2 = splat2(s_hi);
+          // The accumulator is held from the first load to the release, and the tensor core's next
+          // K block into it waits for that.  The second half is therefore reloaded into each
+          // 32-register staging set as soon as its FMAs have consumed it, under the FMAs of the
+          // other set, and the FMAs of the second half run after the release.  Packed pair FMAs:
+          // the fold's issue slots are what the MMA-issuing thread on the same scheduler competes with.
           tmem_ld64_sync(t0, ra, rb);
+          if (threadIdx.x == 128) MOE_TR(3, kb, 2);
 #pragma unroll
-          for (int i = 0; i < 32; ++i) acc[i] = fmaf(__uint_as_float(ra[i]), s_lo, acc[i]);
+          for (int i = 0; i < 16; ++i) fma2(acc2[i], ra[2 * i], ra[2 * i + 1], lo2);
+          tmem_ld32_async(t0 + SECOND, ra);
 #pragma unroll
-          for (int i = 0; i < 32; ++i) acc[32 + i] = fmaf(__uint_as_float(rb[i]), s_lo, acc[32 + i]);
-          tmem_ld64_sync(t0 + SECOND, ra, rb);
+          for (int i = 0; i < 16; ++i) fma2(acc2[16 + i], rb[2 * i], rb[2 * i + 1], lo2);
+          tmem_ld32_async(t0 + SECOND + 32, rb);
+          tmem_wait64(ra, rb);
           release_acc(a);
+          if (threadIdx.x == 128) MOE_TR(3, kb, 3);
 #pragma unroll
-          for (int i = 0; i < 32; ++i) acc[64 + i] = fmaf(__uint_as_float(ra[i]), s_hi, acc[64 + i]);
+          for (int i = 0; i < 16; ++i) fma2(acc2[32 + i], ra[2 * i], ra[2 * i + 1], hi2);
 #pragma unroll
-          for (int i = 0; i < 32; ++i) acc[96 + i] = fmaf(__uint_as_float(rb[i]), s_hi, acc[96 + i]);
+          for (int i = 0; i < 16; ++i) fma2(acc2[48 + i], rb[2 * i], rb[2 * i + 1], hi2);
           ++acc_it;
-          return true;
         };
         // scales come from the shared-memory ring filled by the producer side:
         // GEMM1 halves are (gate, up) -> sc_w[0], sc_w[1]; GEMM2 group h owns one weight block
         for (int kb = 0; kb < KB; ++kb) {
           const int slot = acc_it % SCALE_SLOTS;
+          if (threadIdx.x == 128) MOE_TR(3, kb, 0);
           if (!mbar_wait(&aux->tmem_full[acc_it & 1], (acc_it >> 1) & 1, P.status)) { alive = false; break; }
+          if (threadIdx.x == 128) MOE_TR(3, kb, 1);
+          if (threadIdx.x == 128 && kb == 0) MOE_TRN(3, 61, 2);
           const float sa = aux->sc_a[slot][row];
           const float s_lo = sa * aux->sc_w[slot][GEMM1 ? 0 : h];
           const float s_hi = sa * aux->sc_w[slot][GEMM1 ? 1 : h];
-          if (!fold_block(s_lo, s_hi)) { alive = false; break; }
+          fold_block(s_lo, s_hi, kb);
+          if (kb == 0 && P.mul_weight && row_ok) rw = P.route_weight[sid];  // sid arrived during the first fold
+          if (threadIdx.x == 128) MOE_TR(3, kb, 4);
         }
         if (!alive) break;
       } else {
         const uint32_t a = RB == 2 ? 0u : (acc_it & 1);
         const uint32_t aph = RB == 2 ? (acc_it & 1) : ((acc_it >> 1) & 1);
+        if (P.mul_weight && row_ok) rw = P.route_weight[sid];
         if (sub == 0) {
           if (!mbar_wait(&aux->tmem_full[a], aph, P.status)) { alive = false; break; }
           tc_fence_after();
@@ -489,6 +590,7 @@ tc_gemm_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant_
         }
       }
 
+      if (threadIdx.x == 128) MOE_TR(3, 60, 0);
       // ---------------------------------------------------------- tile epilogue
       if constexpr (!FP8) {
         if (P.w_scale != nullptr) {
@@ -517,8 +619,6 @@ tc_gemm_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant_
           }
         }
       }
-      float rw = 1.0f;
-      if (P.mul_weight && row_ok) rw = P.route_weight[sid];
       if constexpr (GEMM1) {
         // acc[0..63] gate, acc[64..127] up of output columns nt*128 + 64h + j
         float amax = 0.0f;
@@ -581,6 +681,7 @@ tc_gemm_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant_
           }
         }
       }
+      if (threadIdx.x == 128) MOE_TR(3, 60, 1);
       }  // sub
       ++tile_it;
     }
@@ -597,6 +698,9 @@ tc_gemm_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant_
     else
       asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" ::"r"(tmem_base), "r"(512));
   }
+#ifdef MOE_TC_TRACE
+  if (threadIdx.x == 0 && blockIdx.x == 0 && P.trace) { P.trace[2050] = clock64(); P.trace[2051] = (long long)now_ns(); }
+#endif
 #undef MOE_TILE_COORDS
 }
 
@@ -650,8 +754,8 @@ int tc_gemm(bool gemm1, int mode, int act_dtype, const void* a, const float* a_s
   if (wide && mode != MOE_MODE_HALF) return fail(MOE_E_SHAPE, "tensor-core GEMM: the 256-row-per-CTA tiles serve half precision only");
   const bool fp8 = mode == MOE_MODE_FP8_BLOCK;
   const bool sorted = gemm1 && a_sorted != 0;
-  if (sorted && (fp8 || pair))
-    return fail(MOE_E_SHAPE, "tensor-core GEMM1: pre-sorted rows are served by the single-CTA half-precision kernels");
+  if (sorted && (pair || (fp8 && wide)))
+    return fail(MOE_E_SHAPE, "tensor-core GEMM1: pre-sorted rows are served by the single-CTA kernels");
   if (mode != MOE_MODE_FP8_BLOCK && mode != MOE_MODE_HALF)
     return fail(MOE_E_SHAPE, "tensor-core GEMM: mode %d is served by the generic kernel", mode);
   if (act_dtype != MOE_BF16 && act_dtype != MOE_F16)
@@ -686,13 +790,16 @@ int tc_gemm(bool gemm1, int mode, int act_dtype, const void* a, const float* a_s
 
   Params P;
   if (sorted && (topk <= 0 || a_tokens * topk != numel)) return fail(MOE_E_BADARG, "tensor-core GEMM1: tokens * topk != numel");
-  P.a_rows = (const uint8_t*)a; P.a_scale_ld = gemm1 ? a_tokens : rows_cap; P.topk = gemm1 ? topk : 1;
+  P.a_rows = (const uint8_t*)a; P.a_scale_ld = (gemm1 && !sorted) ? a_tokens : rows_cap; P.topk = gemm1 ? topk : 1;
   P.a_scales_t = a_scales_t; P.w_scale = w_scale; P.expert_ids = expert_ids; P.sorted_ids = sorted_ids;
   P.num_post_pad = npp; P.route_weight = route_weight; P.out = out; P.out_scales_t = out_scales_t;
   P.status = status; P.numel = numel; P.rows_cap = rows_cap; P.mul_weight = mul_weight; P.E = E; P.K = K;
   P.Nout = Nout; P.rows_w = rows_w;
   P.n_tiles = gemm1 ? Nout / 128 : (Nout + BN - 1) / BN;
   P.wide_store = ((uintptr_t)out & 31) == 0;
+#ifdef MOE_TC_TRACE
+  { const char* t = getenv(gemm1 ? "MOE_TRACE1" : "MOE_TRACE2"); P.trace = t ? (long long*)strtoull(t, nullptr, 0) : nullptr; }
+#endif
 
   int dev = 0, sms = 148;
   cudaGetDevice(&dev);
@@ -704,6 +811,9 @@ int tc_gemm(bool gemm1, int mode, int act_dtype, const void* a, const float* a_s
 #define MOE_TC_LAUNCH2(F, T, G) \
   (pair ? launch<F, T, G, true, 1>(ma, mb, P, grid, st) : launch<F, T, G, false, 1>(ma, mb, P, grid, st))
 #define MOE_TC_LAUNCH(F, T) (gemm1 ? MOE_TC_LAUNCH2(F, T, true) : MOE_TC_LAUNCH2(F, T, false))
+  if (fp8 && sorted)
+    return act_dtype == MOE_BF16 ? launch<true, __nv_bfloat16, true, false, 1, true>(ma, mb, P, grid, st)
+                                 : launch<true, __half, true, false, 1, true>(ma, mb, P, grid, st);
   if (fp8) return act_dtype == MOE_BF16 ? MOE_TC_LAUNCH(true, __nv_bfloat16) : MOE_TC_LAUNCH(true, __half);
   if (sorted) {
     if (act_dtype == MOE_BF16)

@@ -206,8 +206,34 @@ __global__ void gather_rows_kernel(const uint4* __restrict__ x, const int32_t* _
   }
 }
 
+// out_t[g][p] = scales_t[g][sorted_ids[p] / topk] for the occupied slots p < num_post_pad
+__global__ void gather_scales_kernel(const float* __restrict__ scales_t, int groups, int64_t tokens,
+                                     const int32_t* __restrict__ sorted_ids, const int32_t* __restrict__ num_post_pad,
+                                     int64_t numel, int topk, int64_t rows_cap, float* __restrict__ out_t) {
+  const int64_t npp = min((int64_t)num_post_pad[0], rows_cap);
+  for (int64_t p = (int64_t)blockIdx.x * blockDim.x + threadIdx.x; p < npp; p += (int64_t)gridDim.x * blockDim.x) {
+    const int64_t sid = sorted_ids[p];
+    if (sid < 0 || sid >= numel) continue;
+    const int64_t tok = sid / topk;
+    for (int g = 0; g < groups; ++g) out_t[(int64_t)g * rows_cap + p] = scales_t[(int64_t)g * tokens + tok];
+  }
+}
+
 }  // namespace
 }  // namespace moe
+
+extern "C" int moe_gather_scales_t(const float* scales_t, int groups, int64_t num_tokens, int topk,
+                                   const int32_t* sorted_ids, const int32_t* num_post_pad, int64_t rows_cap,
+                                   float* out_t, void* stream) {
+  using namespace moe;
+  if (num_tokens < 0 || topk <= 0 || groups <= 0 || rows_cap < 0) return fail(MOE_E_BADARG, "gather_scales_t: bad extent");
+  if (num_tokens == 0 || rows_cap == 0) return 0;
+  if (!scales_t || !sorted_ids || !num_post_pad || !out_t) return fail(MOE_E_BADARG, "gather_scales_t: null pointer");
+  const int grid = grid_for((rows_cap + 255) / 256, 8);
+  gather_scales_kernel<<<grid, 256, 0, (cudaStream_t)stream>>>(scales_t, groups, num_tokens, sorted_ids, num_post_pad,
+                                                              num_tokens * topk, topk, rows_cap, out_t);
+  return check_launch("gather_scales_t");
+}
 
 extern "C" int moe_gather_rows(const void* x, int64_t num_tokens, int topk, int64_t row_bytes,
                                const int32_t* sorted_ids, const int32_t* num_post_pad, int64_t rows_cap, void* out,

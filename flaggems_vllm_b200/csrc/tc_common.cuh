@@ -160,6 +160,36 @@ __device__ __forceinline__ void tc_mma(uint32_t tmem_d, uint64_t adesc, uint64_t
         : "memory");
   }
 }
+// The same with a compile-time accumulate flag: no predicate has to be computed at run time.
+template <bool FP8, bool ACC>
+__device__ __forceinline__ void tc_mma_const(uint32_t tmem_d, uint64_t adesc, uint64_t bdesc, uint32_t idesc) {
+  if constexpr (FP8) {
+    asm volatile(
+        "{\n\t.reg .pred p;\n\tsetp.ne.b32 p, %4, 0;\n\t"
+        "tcgen05.mma.cta_group::1.kind::f8f6f4 [%0], %1, %2, %3, p;\n\t}"
+        ::"r"(tmem_d), "l"(adesc), "l"(bdesc), "r"(idesc), "n"(ACC ? 1 : 0)
+        : "memory");
+  } else {
+    asm volatile(
+        "{\n\t.reg .pred p;\n\tsetp.ne.b32 p, %4, 0;\n\t"
+        "tcgen05.mma.cta_group::1.kind::f16 [%0], %1, %2, %3, p;\n\t}"
+        ::"r"(tmem_d), "l"(adesc), "l"(bdesc), "r"(idesc), "n"(ACC ? 1 : 0)
+        : "memory");
+  }
+}
+// Packed fp32 pair FMA: d = a * b + d on two lanes of a 64-bit register pair.  Half the issue
+// slots of two scalar FMAs, which matters for warps that share a scheduler with the thread
+// that feeds the tensor core.
+__device__ __forceinline__ void fma2(unsigned long long& d, uint32_t a_lo, uint32_t a_hi, unsigned long long b2) {
+  unsigned long long a2;
+  asm("mov.b64 %0, {%1, %2};" : "=l"(a2) : "r"(a_lo), "r"(a_hi));
+  asm("fma.rn.f32x2 %0, %1, %2, %0;" : "+l"(d) : "l"(a2), "l"(b2));
+}
+__device__ __forceinline__ unsigned long long splat2(float v) {
+  unsigned long long r;
+  asm("mov.b64 %0, {%1, %1};" : "=l"(r) : "r"(__float_as_uint(v)));
+  return r;
+}
 // Two 32-column loads and the wait in ONE asm statement: the 64 results only
 // become visible to the compiler after the wait, so nothing can be scheduled
 // between the loads and the wait, and no extra register copies are needed.
@@ -183,6 +213,26 @@ __device__ __forceinline__ void tmem_ld64_sync(uint32_t taddr, uint32_t* a, uint
       : "r"(taddr), "r"(taddr + 32)
       : "memory");
 }
+// One 32-column load WITHOUT the wait, and the wait as a statement that "rewrites" the
+// destination registers, so that no use of them can be scheduled above it.
+#define MOE_R8(a, o) "=r"(a[o]), "=r"(a[o + 1]), "=r"(a[o + 2]), "=r"(a[o + 3]), "=r"(a[o + 4]), "=r"(a[o + 5]), "=r"(a[o + 6]), "=r"(a[o + 7])
+#define MOE_RW8(a, o) "+r"(a[o]), "+r"(a[o + 1]), "+r"(a[o + 2]), "+r"(a[o + 3]), "+r"(a[o + 4]), "+r"(a[o + 5]), "+r"(a[o + 6]), "+r"(a[o + 7])
+__device__ __forceinline__ void tmem_ld32_async(uint32_t taddr, uint32_t* a) {
+  asm volatile(
+      "tcgen05.ld.sync.aligned.32x32b.x32.b32 "
+      "{%0, %1, %2, %3, %4, %5, %6, %7, %8, %9, %10, %11, %12, %13, %14, %15, "
+      "%16, %17, %18, %19, %20, %21, %22, %23, %24, %25, %26, %27, %28, %29, %30, %31}, [%32];"
+      : MOE_R8(a, 0), MOE_R8(a, 8), MOE_R8(a, 16), MOE_R8(a, 24)
+      : "r"(taddr)
+      : "memory");
+}
+__device__ __forceinline__ void tmem_wait64(uint32_t* a, uint32_t* b) {
+  asm volatile("tcgen05.wait::ld.sync.aligned;"
+               : MOE_RW8(a, 0), MOE_RW8(a, 8), MOE_RW8(a, 16), MOE_RW8(a, 24), MOE_RW8(b, 0), MOE_RW8(b, 8), MOE_RW8(b, 16),
+                 MOE_RW8(b, 24)::"memory");
+}
+#undef MOE_R8
+#undef MOE_RW8
 __device__ __forceinline__ void cp_async16(uint32_t dst_smem, const void* src) {
   asm volatile("cp.async.cg.shared.global [%0], [%1], 16;" ::"r"(dst_smem), "l"(src) : "memory");
 }

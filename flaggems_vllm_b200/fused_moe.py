@@ -90,14 +90,18 @@ def _choose_kernel(mode, act_dtype, H, I, numel, num_experts):
 
 def _presort_rows(mode, kernel, numel, num_experts) -> bool:
     """GEMM1 reads a sorted copy of the token rows (TMA) instead of gathering them itself:
-    half precision on the single-CTA tensor-core kernels with >= 256 rows per expert.
+    half precision on the single-CTA tensor-core kernels with >= 256 rows per expert, FP8
+    (e4m3 rows and their transposed scales) on the 128-row kernel with >= 128 rows per expert.
     FLAGGEMS_B200_PRESORT = 0/1 forces it off/on."""
-    if mode != _lib.MODE_HALF or kernel not in (KERNEL_TC, KERNEL_TC_WIDE):
+    if mode == _lib.MODE_FP8_BLOCK:
+        if kernel != KERNEL_TC:
+            return False
+    elif mode != _lib.MODE_HALF or kernel not in (KERNEL_TC, KERNEL_TC_WIDE):
         return False
     force = _policy("FLAGGEMS_B200_PRESORT")
     if force != "auto":
         return force == "on"
-    return numel >= 256 * num_experts
+    return numel >= (128 if mode == _lib.MODE_FP8_BLOCK else 256) * num_experts
 
 
 def _tc_eligible(mode: int, act_dtype: torch.dtype, H: int, I: int) -> bool:
@@ -193,16 +197,21 @@ def route_pipeline(a_rows, a_scales_t, w1, w2, route_weight, topk_ids, *, mode, 
     rw = route_weight if route_weight.dtype == torch.float32 else route_weight.float()
     rw = rw if rw.is_contiguous() else rw.contiguous()
     tc = kernel
-    a_in, a_sorted = a_rows, 0
+    a_in, a_sorted, a_scales_in = a_rows, 0, a_scales_t
     if _presort_rows(mode, kernel, numel, global_num_experts):
         # many rows per expert: copy the token rows into sorted order once and let GEMM1 read
         # them with TMA boxes instead of gathering them inside the kernel
         a_in = torch.empty((rows_cap, H), dtype=a_rows.dtype, device=dev)
         _lib.check(L.moe_gather_rows(a_rows.data_ptr(), M, k, H * a_rows.element_size(), sorted_ids.data_ptr(),
                                      npp.data_ptr(), rows_cap, a_in.data_ptr(), st))
+        if fp8:
+            sc_in = torch.empty((H // 128, rows_cap), dtype=torch.float32, device=dev)
+            _lib.check(L.moe_gather_scales_t(a_scales_t.data_ptr(), H // 128, M, k, sorted_ids.data_ptr(),
+                                             npp.data_ptr(), rows_cap, sc_in.data_ptr(), st))
+            a_scales_in = sc_in
         a_sorted = 1
         mark("gather")
-    _lib.check(L.moe_gemm1(mode, act_code, a_in.data_ptr(), a_sorted, _lib.ptr(a_scales_t), M, k, w1.data_ptr(),
+    _lib.check(L.moe_gemm1(mode, act_code, a_in.data_ptr(), a_sorted, _lib.ptr(a_scales_in), M, k, w1.data_ptr(),
                            _lib.ptr(w1_scale), expert_ids.data_ptr(), sorted_ids.data_ptr(), npp.data_ptr(),
                            rw.data_ptr(), int(apply_router_weight_on_input), rows_cap, block_m, E_local, H, I,
                            act.data_ptr(), _lib.ptr(act_scales), tc, status.data_ptr(), st))

@@ -141,6 +141,14 @@ int moe_gather_rows(const void* x, int64_t num_tokens, int topk, int64_t row_byt
                     const int32_t* num_post_pad, int64_t rows_cap, void* out, void* stream);
 
 /*
+ * The companion of moe_gather_rows for FP8 activations: the transposed 1x128 scales
+ * [groups, num_tokens] copied into sorted order, out_t[g][p] = scales_t[g][sorted_ids[p] / topk]
+ * with out_t [groups, rows_cap].  Like the row copy it has no counterpart in the reference.
+ */
+int moe_gather_scales_t(const float* scales_t, int groups, int64_t num_tokens, int topk, const int32_t* sorted_ids,
+                        const int32_t* num_post_pad, int64_t rows_cap, float* out_t, void* stream);
+
+/*
  * Expert grouped GEMM 1: act[p] = SiLU(x_t Wg^T) * (x_t Wu^T) for every sorted
  * row p, where t = sorted_ids[p] / topk is the token of that route.  The kernel
  * gathers the token rows itself; no sorted copy of the activations is needed

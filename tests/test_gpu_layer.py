@@ -187,6 +187,25 @@ def test_config3_deepseek_shape_reduced_expert_count():
     _assert_parity(out, O.fused_moe_fp8_block_oracle(x, w1, w2, s1, s2, tw, ti))
 
 
+def _sample_tokens(ti, E, n=64, seed=0):
+    """At most ``n`` distinct tokens that include the first and the last expert-sorted row of the
+    fullest and of the emptiest expert in use (rows inside an expert are ordered by flat route
+    index), filled up with a seeded random choice."""
+    M, k = ti.shape
+    flat = ti.reshape(-1).long().cpu()
+    counts = torch.bincount(flat, minlength=E)
+    used = torch.nonzero(counts).flatten()
+    fullest = int(used[counts[used].argmax()])
+    emptiest = int(used[counts[used].argmin()])
+    picked = []
+    for e in (fullest, emptiest):
+        routes = torch.nonzero(flat == e).flatten()
+        picked += [int(routes[0]) // k, int(routes[-1]) // k]
+    extra = torch.randperm(M, generator=torch.Generator().manual_seed(seed))[:n].tolist()
+    rows = list(dict.fromkeys(picked + extra))[: min(M, n)]
+    return torch.tensor(sorted(rows), device=ti.device)
+
+
 def _sampled_oracle_fp8(x, w1, s1, w2, s2, tw, ti, rows):
     """Oracle on a sample of tokens: only the experts those tokens use are copied to the host."""
     xs, tws, tis = x[rows].cpu(), tw[rows].cpu(), ti[rows].cpu()
@@ -198,7 +217,7 @@ def _sampled_oracle_fp8(x, w1, s1, w2, s2, tw, ti, rows):
     return O.fused_moe_fp8_block_oracle(xs, lw1, lw2, ls1, ls2, tws, lti)
 
 
-@pytest.mark.parametrize("M", [1, 32, 1024, 8192])
+@pytest.mark.parametrize("M", [1, 32, 128, 1024, 8192])
 @pytest.mark.parametrize("pair", ["0", "1"])
 def test_config3_full_size_sampled_parity_and_properties(M, pair, monkeypatch):
     if os.environ.get("MOE_TEST_KERNELS", "both") not in ("both", "pair" if pair == "1" else "tensor"):
@@ -212,7 +231,7 @@ def test_config3_full_size_sampled_parity_and_properties(M, pair, monkeypatch):
     tw, ti = fg.grouped_topk(logits, 8, 4, k, True, 2.5, bias, 1)
     kw = dict(use_fp8_w8a8=True, w1_scale=s1, w2_scale=s2, block_shape=[128, 128])
     out = fg.fused_experts_impl(x, w1, w2, tw, ti, **kw)
-    rows = torch.randperm(M, generator=torch.Generator().manual_seed(0))[: min(M, 8)].to(DEV)
+    rows = _sample_tokens(ti, E, 64 if pair == "0" else 16)
     _assert_parity(out[rows], _sampled_oracle_fp8(x, w1, s1, w2, s2, tw, ti, rows), f"M={M}")
     # run-to-run determinism (bitwise)
     assert torch.equal(out, fg.fused_experts_impl(x, w1, w2, tw, ti, **kw))
@@ -225,27 +244,43 @@ def test_config3_full_size_sampled_parity_and_properties(M, pair, monkeypatch):
     assert O.rel_l2(out2.float(), out.float() * 2.0) < 5e-3
 
 
-def test_config2_mixtral_shape_sampled():
-    M, E, H, I, k = 1024, 8, 4096, 14336, 2
-    x = T.make_activations(M, H, DEV)
+@pytest.fixture(scope="module")
+def mixtral_weights():
+    E, H, I = 8, 4096, 14336
     w1 = T.make_half_weights(E, 2 * I, H, DEV, seed=1, chunk=1)
     w2 = T.make_half_weights(E, H, I, DEV, seed=2, chunk=1)
+    yield w1, w2
+    del w1, w2
+    torch.cuda.empty_cache()
+
+
+@pytest.mark.parametrize("M", [1, 16, 64, 256, 1024, 4096, 16384])
+def test_config2_mixtral_shape_sampled(M, mixtral_weights):
+    """Every token count of the Mixtral-shape sweep with the kernel the layer picks for it
+    (small-batch schedule, 128-row tiles, 256-row tiles with pre-sorted rows)."""
+    E, H, I, k = 8, 4096, 14336, 2
+    w1, w2 = mixtral_weights
+    x = T.make_activations(M, H, DEV)
     tw, ti = _route(M, E, k, torch.bfloat16)
     out = fg.fused_experts_impl(x, w1, w2, tw, ti)
-    rows = torch.arange(0, M, 64, device=DEV)
+    rows = _sample_tokens(ti, E, 64)
     ref = O.fused_moe_half_oracle(x[rows], w1, w2, tw[rows], ti[rows])
-    _assert_parity(out[rows], ref)
+    _assert_parity(out[rows], ref, f"M={M}")
+    assert torch.equal(out, fg.fused_experts_impl(x, w1, w2, tw, ti))  # bitwise run-to-run
 
 
-def test_config4_qwen3_shape():
-    M, E, H, I, k = 64, 128, 2048, 768, 8
+@pytest.mark.parametrize("M", [1, 64, 512, 4096])
+def test_config4_qwen3_shape(M):
+    E, H, I, k = 128, 2048, 768, 8
     x = T.make_activations(M, H, DEV)
     w1, s1 = T.make_int8_channel_weights(E, 2 * I, H, DEV, seed=1)
     w2, s2 = T.make_int8_channel_weights(E, H, I, DEV, seed=2)
     tw, ti = _route(M, E, k, torch.bfloat16)
-    out = fg.fused_experts_impl(x, w1, w2, tw, ti, use_int8_w8a16=True, per_channel_quant=True, w1_scale=s1,
-                                w2_scale=s2)
-    _assert_parity(out, O.fused_moe_w8a16_oracle(x, w1, w2, s1, s2, tw, ti))
+    kw = dict(use_int8_w8a16=True, per_channel_quant=True, w1_scale=s1, w2_scale=s2)
+    out = fg.fused_experts_impl(x, w1, w2, tw, ti, **kw)
+    rows = _sample_tokens(ti, E, 64)
+    _assert_parity(out[rows], O.fused_moe_w8a16_oracle(x[rows], w1, w2, s1, s2, tw[rows], ti[rows]), f"M={M}")
+    assert torch.equal(out, fg.fused_experts_impl(x, w1, w2, tw, ti, **kw))
 
 
 # ---------------------------------------------------------------- API behaviour
