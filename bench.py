@@ -307,7 +307,7 @@ def run_sweep(args):
             nbytes = e_act * (3 * H * I + (2 * I // 128) * (H // 128) * 4 + (H // 128) * (I // 128) * 4) \
                 + M * H * 2 * 2 + M * E * 4 + k * 8 * M
             extra = {"distinct_experts": e_act}
-            if M <= 128:
+            if M <= 128 and not args.no_graph:
                 extra["cuda_graph_replay_ms"] = graph_ms(step)
             report("dsv3_fp8", M, timeit(step, iters(10)), 6.0 * M * k * H * I, nbytes, 2 * peaks["bf16_tflops"], extra)
         del w1, w2, s1, s2
@@ -327,8 +327,10 @@ def run_sweep(args):
             _, ti = fg.grouped_topk(torch.softmax(logits, -1), 1, 1, k, True, 1.0, zero, 0)
             e_act = int(torch.unique(ti).numel())
             nbytes = e_act * 3 * H * I * 2 + M * H * 2 * 2 + M * E * 4 + k * 8 * M
-            report("mixtral_bf16", M, timeit(step, iters(6)), 6.0 * M * k * H * I, nbytes, peaks["bf16_tflops"],
-                   {"distinct_experts": e_act})
+            extra = {"distinct_experts": e_act}
+            if M <= 128 and not args.no_graph:
+                extra["cuda_graph_replay_ms"] = graph_ms(step)
+            report("mixtral_bf16", M, timeit(step, iters(6)), 6.0 * M * k * H * I, nbytes, peaks["bf16_tflops"], extra)
         del w1, w2
     if "qwen3" in which:
         E, H, I, k = 128, 2048, 768, 8
@@ -347,8 +349,10 @@ def run_sweep(args):
             _, ti = fg.grouped_topk(torch.softmax(logits, -1), 1, 1, k, True, 1.0, zero, 0)
             e_act = int(torch.unique(ti).numel())
             nbytes = e_act * (3 * H * I + 3 * I * 4 + H * 4) + M * H * 2 * 2 + M * E * 4 + k * 8 * M
-            report("qwen3_w8a16", M, timeit(step, iters(6)), 6.0 * M * k * H * I, nbytes, peaks["bf16_tflops"],
-                   {"distinct_experts": e_act})
+            extra = {"distinct_experts": e_act}
+            if M <= 128 and not args.no_graph:
+                extra["cuda_graph_replay_ms"] = graph_ms(step)
+            report("qwen3_w8a16", M, timeit(step, iters(6)), 6.0 * M * k * H * I, nbytes, peaks["bf16_tflops"], extra)
     if "align" in which:
         for M in (1, 128, 2048, 8192):
             for skewed in (False, True):
@@ -486,6 +490,7 @@ def main():
                     help="expert count (smaller values give the small case used for ncu captures)")
     ap.add_argument("--sweep-m", default="", help="comma list: keep only these token counts of a --sweep")
     ap.add_argument("--sweep-iters", type=int, default=0, help="timed iterations per --sweep point (0: default)")
+    ap.add_argument("--no-graph", action="store_true", help="--sweep: skip the CUDA-graph replay timing of small M")
     ap.add_argument("--sweep", default="", help="comma list of dsv3,mixtral,qwen3,align,routing: print one line per point")
     args = ap.parse_args()
     args.warmup = max(args.warmup, 3) if args.impl == "b200" else args.warmup

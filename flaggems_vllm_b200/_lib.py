@@ -46,6 +46,10 @@ SYMBOLS = {
     "moe_gemm2": (c_int, [c_int, c_int, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p,
                           c_void_p, c_int, c_int64, c_int64, c_int, c_int, c_int, c_int, c_void_p, c_int,
                           c_void_p, c_void_p]),
+    "moe_small_m_plan": (c_int, [c_int, c_int, c_int, c_int, c_int64, c_int64, c_int, c_void_p, c_void_p, c_void_p]),
+    "moe_small_m_gemm": (c_int, [c_int, c_int, c_int, c_void_p, c_int64, c_int, c_void_p, c_void_p, c_void_p, c_void_p,
+                                 c_void_p, c_void_p, c_int, c_void_p, c_int, c_void_p, c_int, c_int64, c_int, c_int,
+                                 c_int, c_void_p, c_void_p, c_int, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p]),
     "moe_sum": (c_int, [c_void_p, c_void_p, c_int, c_int64, c_int, c_int64, c_void_p, c_int, c_int, c_void_p,
                         c_void_p, c_void_p]),
 }
@@ -54,7 +58,7 @@ _lib = None
 _status = {}
 # calls of entry points that enqueue a kernel (bench.py reports the count of its timed region)
 LAUNCHES = 0
-_NO_KERNEL = ("moe_abi_version", "moe_last_error")
+_NO_KERNEL = ("moe_abi_version", "moe_last_error", "moe_small_m_plan")
 
 
 class _Counted:

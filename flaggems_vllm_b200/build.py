@@ -16,7 +16,7 @@ CSRC = os.path.join(HERE, "csrc")
 LIB = os.path.join(HERE, "libmoe_sm100.so")
 STAMP = LIB + ".srchash"
 SOURCES = ["common.cu", "grouped_topk.cu", "topk_route.cu", "align.cu", "quant.cu", "gemm_simt.cu", "gemm_tc.cu",
-           "gemm_w8.cu", "gemm_api.cu", "router_gemm.cu", "ep_pack.cu"]
+           "gemm_w8.cu", "gemm_small.cu", "gemm_api.cu", "router_gemm.cu", "ep_pack.cu"]
 
 
 def _nvcc() -> str:

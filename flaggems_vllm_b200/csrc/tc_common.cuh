@@ -297,6 +297,34 @@ __device__ __forceinline__ float round_act(float v) {
   return ToF32<AT>::get(from_f32<AT>(v));
 }
 
+// Four int8 (one 32-bit word, lowest byte = lowest K index) -> four AT values in two words.
+template <typename AT>
+__device__ __forceinline__ void widen4(uint32_t w, uint32_t& lo, uint32_t& hi);
+// bf16: with x = m - 128 s (m = low seven bits, s = sign bit), 0x4300 | m is 128 + m and
+// 0x4300 | (s << 7) is 128 (1 + s), both exact, and so is their difference x
+template <>
+__device__ __forceinline__ void widen4<__nv_bfloat16>(uint32_t w, uint32_t& lo, uint32_t& hi) {
+  const uint32_t m = w & 0x7F7F7F7Fu, sg = w & 0x80808080u;
+  uint32_t a01 = __byte_perm(m, 0x43434343u, 0x4140), a23 = __byte_perm(m, 0x43434343u, 0x4342);
+  uint32_t b01 = __byte_perm(sg, 0x43434343u, 0x4140), b23 = __byte_perm(sg, 0x43434343u, 0x4342);
+  const __nv_bfloat162 r01 = __hsub2(*reinterpret_cast<__nv_bfloat162*>(&a01), *reinterpret_cast<__nv_bfloat162*>(&b01));
+  const __nv_bfloat162 r23 = __hsub2(*reinterpret_cast<__nv_bfloat162*>(&a23), *reinterpret_cast<__nv_bfloat162*>(&b23));
+  lo = *reinterpret_cast<const uint32_t*>(&r01);
+  hi = *reinterpret_cast<const uint32_t*>(&r23);
+}
+// f16: 0x6400 | u is 1024 + u; subtracting 1152 leaves x exactly
+template <>
+__device__ __forceinline__ void widen4<__half>(uint32_t w, uint32_t& lo, uint32_t& hi) {
+  const uint32_t u = w ^ 0x80808080u;
+  uint32_t h01 = __byte_perm(u, 0x64646464u, 0x4140);
+  uint32_t h23 = __byte_perm(u, 0x64646464u, 0x4342);
+  const uint32_t bias = 0x64806480u;  // (1152, 1152)
+  const __half2 r01 = __hsub2(*reinterpret_cast<__half2*>(&h01), *reinterpret_cast<const __half2*>(&bias));
+  const __half2 r23 = __hsub2(*reinterpret_cast<__half2*>(&h23), *reinterpret_cast<const __half2*>(&bias));
+  lo = *reinterpret_cast<const uint32_t*>(&r01);
+  hi = *reinterpret_cast<const uint32_t*>(&r23);
+}
+
 // ------------------------------------------------------------------ host side
 typedef CUresult (*EncodeTiledFn)(CUtensorMap*, CUtensorMapDataType, cuuint32_t, void*, const cuuint64_t*,
                                   const cuuint64_t*, const cuuint32_t*, const cuuint32_t*, CUtensorMapInterleave,

@@ -203,6 +203,40 @@ int moe_gemm2(int mode, int act_dtype, const void* act_sorted, const float* act_
               void* y, int use_tensor_cores, int32_t* status, void* stream);
 
 /*
+ * Small-batch schedule of the two expert GEMMs (weight streaming, split-K): align blocks of
+ * 8 routes, every routed expert's weights read once, K cut into slices whose fp32 partial
+ * tiles are added in slice order by whichever CTA finishes a tile last (no floating-point
+ * atomics, bitwise reproducible).  GEMM 2 also joins the top-k routes of every token in
+ * slot order and writes the layer output, so no separate moe_sum pass runs.
+ * Stands in for the reference's small-batch route (naive_block_assignment,
+ * src/flaggems_vllm/ops/fused_moe.py:2542-2568, kernel branch :1541-1548) and, for the
+ * combine, moe_sum (src/flaggems_vllm/ops/moe_sum.py:250-310).
+ *
+ * moe_small_m_plan: scratch sizes of one GEMM for (K, Nout, rows_cap): fp32 elements of the
+ *   partial-sum buffer (0 when one K slice suffices), int32 unit counters, int32 token counters
+ *   (GEMM 2 only).  k_slices >= 1 asks for at least that many K slices (more units of work
+ *   when few experts are routed to).  Counters must be zero before the first launch; every
+ *   launch leaves them zero.  Launches that share scratch must not overlap on the GPU.
+ * moe_small_m_gemm (gemm1 = 1): a = x [num_tokens, K] in act dtype (FP8 mode: quantised
+ *   1 x 128 inside the kernel), w = w1 [E, 2*Nout, K], out = intermediate [rows_cap, Nout] in
+ *   act dtype, sorted order.  (gemm1 = 0): a = that intermediate (K = intermediate size),
+ *   w = w2 [E, Nout, K], out = y [num_tokens * topk, Nout] scratch in act dtype,
+ *   final_out = layer output [num_tokens, Nout]; rows of tokens without a valid route are
+ *   zeroed.  sorted_ids / expert_ids / num_post_pad come from moe_align_block_size with
+ *   block_size 8 and the GLOBAL expert count; expert_map (or NULL) maps global to local ids.
+ *   w_scale as in moe_gemm1 / moe_gemm2.  Limits: topk <= 32, Nout % 64 (GEMM 1) / % 128
+ *   (GEMM 2), K a multiple of 128 bytes of weights (and of 128 elements in FP8 mode).
+ */
+int moe_small_m_plan(int gemm1, int mode, int K, int Nout, int64_t rows_cap, int64_t num_tokens, int k_slices,
+                     int64_t* partial_floats, int64_t* unit_counters, int64_t* token_counters);
+int moe_small_m_gemm(int gemm1, int mode, int act_dtype, const void* a, int64_t num_tokens, int topk,
+                     const void* w, const float* w_scale, const int32_t* expert_ids, const int32_t* sorted_ids,
+                     const int32_t* num_post_pad, const int32_t* expert_map, int num_experts_global,
+                     const float* route_weight, int mul_weight, const void* topk_ids, int ids_int64,
+                     int64_t rows_cap, int E, int K, int Nout, void* out, void* final_out, int k_slices,
+                     float* partial, int32_t* unit_counters, int32_t* token_counters, int32_t* status, void* stream);
+
+/*
  * out[m, :] = sum_j in[m, j, :] in fp32, fixed order j = 0..topk-1, stored in
  * the io dtype.  Stands in for moe_sum (src/flaggems_vllm/ops/moe_sum.py:250-310).
  * When topk_ids is given, slot j is skipped if its id is outside

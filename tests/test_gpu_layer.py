@@ -283,6 +283,82 @@ def test_config4_qwen3_shape(M):
     assert torch.equal(out, fg.fused_experts_impl(x, w1, w2, tw, ti, **kw))
 
 
+# ---------------------------------------------------------------- small-batch schedule
+@pytest.mark.parametrize("M", [1, 2, 7, 16, 32, 64])
+@pytest.mark.parametrize("fmt", ["half", "fp8", "w8a16"])
+@pytest.mark.parametrize("dtype", [torch.bfloat16, torch.float16])
+def test_small_batch_schedule_matches_the_oracle(M, fmt, dtype, monkeypatch):
+    """The weight-streaming split-K kernels, forced on: H = 2304 needs two K slices in GEMM 1
+    (three with the slice hint), so the ordered partial-sum reduction runs; k = 4 routes per
+    token exercise the in-kernel top-k combine."""
+    monkeypatch.setenv("FLAGGEMS_B200_SMALL_M", "1")
+    E, H, I, k = 16, 2304, 384, 4
+    x = T.make_activations(M, H, DEV, dtype=dtype)
+    tw, ti = _route(M, E, k, dtype)
+    if fmt == "half":
+        w1 = T.make_half_weights(E, 2 * I, H, DEV, seed=1, dtype=dtype, std=H**-0.5)
+        w2 = T.make_half_weights(E, H, I, DEV, seed=2, dtype=dtype, std=I**-0.5)
+        kw = {}
+        ref = O.fused_moe_half_oracle(x, w1, w2, tw, ti)
+    elif fmt == "fp8":
+        w1, s1 = T.make_fp8_block_weights(E, 2 * I, H, DEV, seed=1, std=H**-0.5)
+        w2, s2 = T.make_fp8_block_weights(E, H, I, DEV, seed=2, std=I**-0.5)
+        kw = dict(use_fp8_w8a8=True, w1_scale=s1, w2_scale=s2, block_shape=[128, 128])
+        ref = O.fused_moe_fp8_block_oracle(x, w1, w2, s1, s2, tw, ti)
+    else:
+        w1, s1 = T.make_int8_channel_weights(E, 2 * I, H, DEV, seed=1, std=H**-0.5)
+        w2, s2 = T.make_int8_channel_weights(E, H, I, DEV, seed=2, std=I**-0.5)
+        kw = dict(use_int8_w8a16=True, per_channel_quant=True, w1_scale=s1, w2_scale=s2)
+        ref = O.fused_moe_w8a16_oracle(x, w1, w2, s1, s2, tw, ti)
+    keep = {}
+    out = torch.empty_like(x)
+    mode = {"half": _lib.MODE_HALF, "fp8": _lib.MODE_FP8_BLOCK, "w8a16": _lib.MODE_W8A16}[fmt]
+    fused_moe.run_chunk(x, w1, w2, tw, ti, out, mode=mode, w1_scale=kw.get("w1_scale"), w2_scale=kw.get("w2_scale"),
+                        global_num_experts=E, expert_map=None, apply_router_weight_on_input=False, keep=keep)
+    assert keep["kernel"] == "small"
+    _assert_parity(out, ref, f"{fmt} M={M}")
+    again = fg.fused_experts_impl(x, w1, w2, tw, ti, **kw)
+    assert torch.equal(out, again)                      # bitwise run to run, and the counters were left clean
+    perm = torch.randperm(M, device=DEV)
+    assert torch.equal(fg.fused_experts_impl(x[perm].contiguous(), w1, w2, tw[perm].contiguous(),
+                                             ti[perm].contiguous(), **kw), out[perm])
+    buf = x.clone()
+    fg.fused_experts_impl(buf, w1, w2, tw, ti, inplace=True, **kw)
+    assert torch.equal(buf, out)
+
+
+def test_small_batch_schedule_expert_map_and_weight_on_input(monkeypatch):
+    monkeypatch.setenv("FLAGGEMS_B200_SMALL_M", "1")
+    M, E, H, I, k = 12, 16, 256, 256, 4
+    x = T.make_activations(M, H, DEV)
+    w1 = T.make_half_weights(E, 2 * I, H, DEV, seed=1, std=H**-0.5)
+    w2 = T.make_half_weights(E, H, I, DEV, seed=2, std=I**-0.5)
+    tw, ti = _route(M, E, k, torch.bfloat16)
+    full = fg.fused_experts_impl(x, w1, w2, tw, ti)
+    total = torch.zeros_like(full, dtype=torch.float32)
+    for r in range(2):
+        lo, hi = r * 8, (r + 1) * 8
+        emap = torch.full((E,), -1, dtype=torch.int32, device=DEV)
+        emap[lo:hi] = torch.arange(8, dtype=torch.int32, device=DEV)
+        part = fg.fused_experts_impl(x, w1[lo:hi].contiguous(), w2[lo:hi].contiguous(), tw, ti,
+                                     global_num_experts=E, expert_map=emap)
+        total += part.float()
+    assert O.rel_l2(total, full.float()) < 5e-3
+    # a token whose routes all belong to the other rank gets a zero row
+    ti2 = ti.clone()
+    ti2[0] = torch.tensor([8, 9, 10, 11], dtype=ti.dtype, device=DEV)
+    emap = torch.full((E,), -1, dtype=torch.int32, device=DEV)
+    emap[:8] = torch.arange(8, dtype=torch.int32, device=DEV)
+    part = fg.fused_experts_impl(x, w1[:8].contiguous(), w2[:8].contiguous(), tw, ti2, global_num_experts=E,
+                                 expert_map=emap)
+    assert torch.all(part[0] == 0)
+    xw = T.make_activations(M, H, DEV, seed=9)
+    tw1, ti1 = _route(M, E, 1, torch.bfloat16)
+    out = fg.fused_experts_impl(xw, w1, w2, tw1, ti1, apply_router_weight_on_input=True)
+    _assert_parity(out, O.fused_moe_half_oracle(xw, w1, w2, tw1, ti1, apply_router_weight_on_input=True))
+    assert fg.read_status() == 0
+
+
 # ---------------------------------------------------------------- API behaviour
 def _small_half(dtype=torch.bfloat16, M=16, E=8, H=256, I=512, k=2):
     x = T.make_activations(M, H, DEV, dtype=dtype)
