@@ -7,7 +7,7 @@ from __future__ import annotations
 
 import ctypes
 import os
-from ctypes import c_char_p, c_float, c_int, c_int64, c_void_p
+from ctypes import c_char_p, c_float, c_int, c_int64, c_uint64, c_void_p
 
 import torch
 
@@ -23,6 +23,8 @@ _DTYPE_CODE = {torch.float32: MOE_F32, torch.float16: MOE_F16, torch.bfloat16: M
 SYMBOLS = {
     "moe_abi_version": (c_int, []),
     "moe_last_error": (c_char_p, []),
+    "moe_set_wait_limit_ns": (c_uint64, [c_uint64]),
+    "moe_debug_wait_timeout": (c_int, [c_void_p, c_uint64, c_void_p, c_void_p]),
     "moe_grouped_topk": (c_int, [c_void_p, c_int, c_int64, c_int64, c_void_p, c_int, c_void_p, c_int64, c_int,
                                  c_int, c_int, c_int, c_int, c_float, c_int, c_void_p, c_void_p, c_void_p]),
     "moe_topk_route": (c_int, [c_void_p, c_int, c_void_p, c_void_p, c_int64, c_int, c_int, c_int, c_int, c_float,
@@ -58,7 +60,7 @@ _lib = None
 _status = {}
 # calls of entry points that enqueue a kernel (bench.py reports the count of its timed region)
 LAUNCHES = 0
-_NO_KERNEL = ("moe_abi_version", "moe_last_error", "moe_small_m_plan")
+_NO_KERNEL = ("moe_abi_version", "moe_last_error", "moe_small_m_plan", "moe_set_wait_limit_ns")
 
 
 class _Counted:

@@ -1,6 +1,6 @@
 // C ABI of the two expert grouped GEMMs: argument checks and the choice
 // between the tcgen05 kernel and the generic kernel.
-#include "moe_common.cuh"
+#include "tc_common.cuh"
 
 namespace moe {
 int simt_gemm(bool gemm1, int mode, int act_dtype, const void* a, const float* a_scales_t, const void* w,
@@ -80,4 +80,26 @@ extern "C" int moe_gemm2(int mode, int act_dtype, const void* act_sorted, const 
   return simt_gemm(false, mode, act_dtype, act_sorted, act_scales_t, w2, w2_scale, expert_ids, sorted_ids,
                    num_post_pad, route_weight, mul_weight, numel, rows_cap, 0, 1, block_m, E, I, H, y, nullptr, status,
                    (cudaStream_t)stream);
+}
+
+namespace moe {
+// One warp waits on a barrier nobody arrives at, with the given limit; the wait gives up, sets
+// MOE_ST_WAIT_TIMEOUT and the kernel returns.  Nothing faults and nothing waits without a bound.
+__global__ void wait_timeout_probe_kernel(int32_t* status, unsigned long long limit_ns, int32_t* gave_up) {
+  __shared__ uint64_t bar;
+  if (threadIdx.x == 0) {
+    tc::mbar_init(&bar, 1);
+    asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
+  }
+  __syncthreads();
+  const bool ok = tc::mbar_wait(&bar, 0, status, limit_ns);
+  if (threadIdx.x == 0 && gave_up != nullptr) *gave_up = ok ? 0 : 1;
+}
+}  // namespace moe
+
+extern "C" int moe_debug_wait_timeout(int32_t* status, unsigned long long limit_ns, int32_t* gave_up, void* stream) {
+  using namespace moe;
+  if (limit_ns == 0 || limit_ns > 100000000ull) return fail(MOE_E_BADARG, "debug_wait_timeout: limit must be 1 ns .. 100 ms");
+  wait_timeout_probe_kernel<<<1, 32, 0, (cudaStream_t)stream>>>(status, limit_ns, gave_up);
+  return check_launch("debug_wait_timeout");
 }

@@ -66,6 +66,7 @@ struct Params {
   int32_t* unit_cnt;          // [rows_cap / 8 * NT * 8 warps], zero before and after the launch
   int32_t* tok_cnt;           // [tokens * NT * 8 warps] (GEMM2), zero before and after the launch
   int32_t* status;
+  unsigned long long wait_ns;  // limit of every bounded barrier wait
   int64_t numel, rows_cap, tokens;
   int ids_int64, num_experts_global;
   int topk, mul_weight, E, K, Nout, rows_w, NT, S, chunks_total, cps;
@@ -195,7 +196,7 @@ small_gemm_kernel(const __grid_constant__ CUtensorMap map_w, const Params P) {
         const int wrow = e * P.rows_w;
         for (int c = c0; c < c1; ++c, ++it) {
           const int st = it % STAGES;
-          if (!mbar_wait(&aux->empty[st], ((it / STAGES) & 1) ^ 1, P.status)) { alive = false; break; }
+          if (!mbar_wait(&aux->empty[st], ((it / STAGES) & 1) ^ 1, P.status, P.wait_ns)) { alive = false; break; }
           mbar_expect_tx(&aux->full[st], STAGE_BYTES);
           uint8_t* dst = ring + (size_t)st * STAGE_BYTES;
           if constexpr (GEMM1) {
@@ -256,6 +257,7 @@ small_gemm_kernel(const __grid_constant__ CUtensorMap map_w, const Params P) {
         const int64_t p = (int64_t)b * ROWS + threadIdx.x;
         const int64_t sidv = p < P.rows_cap ? (int64_t)P.sorted_ids[p] : P.numel;
         aux->sid[threadIdx.x] = (sidv >= 0 && sidv < P.numel) ? (int32_t)sidv : -1;
+        if (sidv < 0 || sidv > P.numel) set_status(P.status, MOE_ST_BAD_ROW);  // the pad value is numel
       }
       bar_compute();
       if constexpr (FP8) {
@@ -353,7 +355,7 @@ small_gemm_kernel(const __grid_constant__ CUtensorMap map_w, const Params P) {
       const uint8_t* x_row = xs + g * F::XPITCH;
       for (int ci = 0; ci < nchunks; ++ci, ++it) {
         const int st = it % STAGES;
-        if (!mbar_wait(&aux->full[st], (it / STAGES) & 1, P.status)) { alive = false; break; }
+        if (!mbar_wait(&aux->full[st], (it / STAGES) & 1, P.status, P.wait_ns)) { alive = false; break; }
         const uint8_t* sa = ring + (size_t)st * STAGE_BYTES + rowA * 128;
         const uint8_t* sb = ring + (size_t)st * STAGE_BYTES + rowB * 128;
                 if constexpr (MODE == MOE_MODE_HALF) {
@@ -591,7 +593,7 @@ extern "C" int moe_small_m_gemm(int gemm1, int mode, int act_dtype, const void* 
   if (rc) return rc;
   P.a = a; P.w_scale = w_scale; P.expert_ids = expert_ids; P.sorted_ids = sorted_ids; P.num_post_pad = num_post_pad;
   P.expert_map = expert_map; P.route_weight = route_weight; P.topk_ids = topk_ids; P.out = out; P.final_out = final_out;
-  P.partial = partial; P.unit_cnt = unit_counters; P.tok_cnt = token_counters; P.status = status;
+  P.partial = partial; P.unit_cnt = unit_counters; P.tok_cnt = token_counters; P.status = status; P.wait_ns = wait_limit_ns();
   P.numel = num_tokens * topk; P.rows_cap = rows_cap; P.tokens = num_tokens; P.ids_int64 = ids_int64;
   P.num_experts_global = num_experts_global; P.topk = gemm1 ? topk : topk; P.mul_weight = mul_weight; P.E = E; P.K = K;
   P.Nout = Nout; P.rows_w = rows_w;

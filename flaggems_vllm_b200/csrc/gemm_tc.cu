@@ -109,6 +109,7 @@ struct Params {
   void* out;
   float* out_scales_t;      // [I/128, rows_cap]          (FP8 GEMM1)
   int32_t* status;
+  unsigned long long wait_ns;  // limit of every bounded barrier wait
   int64_t numel;
   int64_t rows_cap;
   int64_t a_scale_ld;       // tokens (GEMM1) or rows_cap (GEMM2)
@@ -270,7 +271,7 @@ tc_gemm_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant_
           const int s = it % STAGES;
           const uint32_t ph = (it / STAGES) & 1;
           MOE_TR(0, kb, 0);
-          if (!mbar_wait(&aux->empty[s], ph ^ 1, P.status)) { alive = false; break; }
+          if (!mbar_wait(&aux->empty[s], ph ^ 1, P.status, P.wait_ns)) { alive = false; break; }
           MOE_TR(0, kb, 1);
           if constexpr (GATHER) {
             mbar_expect_tx(&aux->full[s], B_LOCAL_BYTES);  // A rows arrive by cp.async (warps 2-3)
@@ -316,11 +317,11 @@ tc_gemm_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant_
             const uint64_t adesc = adesc0 + (uint64_t)(s * (uint32_t)(A_LOCAL_BYTES >> 4));
             const uint32_t d0 = tmem_base + a * BN;
             MOE_TR(1, kb, 0);
-            if (!mbar_wait(&aux->full[s], sph, P.status)) { alive = false; break; }
+            if (!mbar_wait(&aux->full[s], sph, P.status, P.wait_ns)) { alive = false; break; }
             MOE_TR(1, kb, 1);
             if constexpr (GATHER) asm volatile("fence.proxy.async.shared::cta;" ::: "memory");  // cp.async writes -> tensor core reads
             if (FP8 || kb == 0) {
-              if (!mbar_wait(&aux->tmem_empty[a], aph ^ 1, P.status)) { alive = false; break; }
+              if (!mbar_wait(&aux->tmem_empty[a], aph ^ 1, P.status, P.wait_ns)) { alive = false; break; }
             }
             MOE_TR(1, kb, 2);
             tc_fence_after();
@@ -359,12 +360,12 @@ tc_gemm_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant_
           const uint32_t a = RB == 2 ? 0u : (acc_it & 1);
           const uint32_t aph = RB == 2 ? (acc_it & 1) : ((acc_it >> 1) & 1);
           if (FP8 || kb == 0) {
-            if (!mbar_wait<PAIR>(&aux->tmem_empty[a], aph ^ 1, P.status)) { alive = false; break; }
+            if (!mbar_wait<PAIR>(&aux->tmem_empty[a], aph ^ 1, P.status, P.wait_ns)) { alive = false; break; }
             tc_fence_after();
           }
           const int s = it % STAGES;
-          if (!mbar_wait(&aux->full[s], (it / STAGES) & 1, P.status)) { alive = false; break; }
-          if (!mbar_wait<true>(&aux->peer_full[s], (it / STAGES) & 1, P.status)) { alive = false; break; }
+          if (!mbar_wait(&aux->full[s], (it / STAGES) & 1, P.status, P.wait_ns)) { alive = false; break; }
+          if (!mbar_wait<true>(&aux->peer_full[s], (it / STAGES) & 1, P.status, P.wait_ns)) { alive = false; break; }
           if constexpr (GATHER) asm volatile("fence.proxy.async.shared::cta;" ::: "memory");  // cp.async writes -> tensor core reads
           tc_fence_after();
           const uint64_t bdesc = make_smem_desc(smem_u32(sB + (size_t)s * B_LOCAL_BYTES));
@@ -396,7 +397,7 @@ tc_gemm_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant_
         if (e < 0 || e >= P.E) continue;
         for (int kb = 0; kb < KB; ++kb, ++it) {
           const int s = it % STAGES;
-          if (!mbar_wait(&aux->full[s], (it / STAGES) & 1, P.status)) { alive = false; break; }
+          if (!mbar_wait(&aux->full[s], (it / STAGES) & 1, P.status, P.wait_ns)) { alive = false; break; }
           asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
           mbar_arrive_remote(&aux->peer_full[s], 0);
         }
@@ -445,7 +446,7 @@ tc_gemm_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant_
         for (int kb = 0; kb < KB; ++kb, ++it) {
           const int s = it % STAGES;
           if (g == 0) MOE_TR(2, kb, 0);
-          if (!mbar_wait(&aux->empty[s], ((it / STAGES) & 1) ^ 1, P.status)) { alive = false; break; }
+          if (!mbar_wait(&aux->empty[s], ((it / STAGES) & 1) ^ 1, P.status, P.wait_ns)) { alive = false; break; }
           if (g == 0) MOE_TR(2, kb, 1);
           const uint32_t base = smem_u32(sA + (size_t)s * A_LOCAL_BYTES);
 #pragma unroll
@@ -484,7 +485,7 @@ tc_gemm_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant_
         const float* ws_src = P.w_scale + ((int64_t)e * sblk_per_e + wblk) * KB;
         for (int kb = 0; kb < KB; ++kb, ++it) {
           const int s = it % STAGES;
-          if (!mbar_wait(&aux->empty[s], ((it / STAGES) & 1) ^ 1, P.status)) { alive = false; break; }
+          if (!mbar_wait(&aux->empty[s], ((it / STAGES) & 1) ^ 1, P.status, P.wait_ns)) { alive = false; break; }
           const int slot = it % SCALE_SLOTS;
           cp_async16(smem_u32(&aux->sc_a[slot][4 * lane]), as_row + (int64_t)kb * P.a_scale_ld);
           if (lane < 2) cp_async4(smem_u32(&aux->sc_w[slot][lane]), ws_src + kb);
@@ -521,6 +522,7 @@ tc_gemm_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant_
       int64_t sid = P.numel;
       if (p < P.rows_cap) sid = (int64_t)P.sorted_ids[p];
       const bool row_ok = sid >= 0 && sid < P.numel;
+      if (sid < 0 || sid > P.numel) set_status(P.status, MOE_ST_BAD_ROW);  // the pad value is numel; anything else outside is corrupt
       float acc[128];
       float rw = 1.0f;  // route weight of this row, fetched early: the epilogue must not wait for it
       if constexpr (FP8) {
@@ -561,7 +563,7 @@ tc_gemm_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant_
         for (int kb = 0; kb < KB; ++kb) {
           const int slot = acc_it % SCALE_SLOTS;
           if (threadIdx.x == 128) MOE_TR(3, kb, 0);
-          if (!mbar_wait(&aux->tmem_full[acc_it & 1], (acc_it >> 1) & 1, P.status)) { alive = false; break; }
+          if (!mbar_wait(&aux->tmem_full[acc_it & 1], (acc_it >> 1) & 1, P.status, P.wait_ns)) { alive = false; break; }
           if (threadIdx.x == 128) MOE_TR(3, kb, 1);
           if (threadIdx.x == 128 && kb == 0) MOE_TRN(3, 61, 2);
           const float sa = aux->sc_a[slot][row];
@@ -577,7 +579,7 @@ tc_gemm_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant_
         const uint32_t aph = RB == 2 ? (acc_it & 1) : ((acc_it >> 1) & 1);
         if (P.mul_weight && row_ok) rw = P.route_weight[sid];
         if (sub == 0) {
-          if (!mbar_wait(&aux->tmem_full[a], aph, P.status)) { alive = false; break; }
+          if (!mbar_wait(&aux->tmem_full[a], aph, P.status, P.wait_ns)) { alive = false; break; }
           tc_fence_after();
         }
         const uint32_t t0 = t_lane + (RB == 2 ? (uint32_t)sub : a) * BN;
@@ -632,7 +634,7 @@ tc_gemm_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant_
           float* x = &aux->xch[tile_it & 1][0][0];
           x[h * BM + row] = amax;
           mbar_arrive(&aux->xch_bar);
-          if (!mbar_wait(&aux->xch_bar, tile_it & 1, P.status)) { alive = false; break; }
+          if (!mbar_wait(&aux->xch_bar, tile_it & 1, P.status, P.wait_ns)) { alive = false; break; }
           amax = fmaxf(amax, x[(1 - h) * BM + row]);
           const float s = fmaxf(amax, kQuantEps) * (1.0f / kFp8Max);
           const float inv_s = 1.0f / s;  // one reciprocal per row instead of 64 divisions
@@ -793,7 +795,7 @@ int tc_gemm(bool gemm1, int mode, int act_dtype, const void* a, const float* a_s
   P.a_rows = (const uint8_t*)a; P.a_scale_ld = (gemm1 && !sorted) ? a_tokens : rows_cap; P.topk = gemm1 ? topk : 1;
   P.a_scales_t = a_scales_t; P.w_scale = w_scale; P.expert_ids = expert_ids; P.sorted_ids = sorted_ids;
   P.num_post_pad = npp; P.route_weight = route_weight; P.out = out; P.out_scales_t = out_scales_t;
-  P.status = status; P.numel = numel; P.rows_cap = rows_cap; P.mul_weight = mul_weight; P.E = E; P.K = K;
+  P.status = status; P.wait_ns = wait_limit_ns(); P.numel = numel; P.rows_cap = rows_cap; P.mul_weight = mul_weight; P.E = E; P.K = K;
   P.Nout = Nout; P.rows_w = rows_w;
   P.n_tiles = gemm1 ? Nout / 128 : (Nout + BN - 1) / BN;
   P.wide_store = ((uintptr_t)out & 31) == 0;

@@ -76,6 +76,7 @@ struct Params {
   const float* route_weight;
   void* out;
   int32_t* status;
+  unsigned long long wait_ns;  // limit of every bounded barrier wait
   int64_t numel;
   int64_t rows_cap;
   int topk;
@@ -172,7 +173,7 @@ w8_gemm_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant_
         const int wrow0 = e * P.rows_w;
         for (int kb = 0; kb < KB; ++kb, ++it) {
           const int s = it % SR;
-          if (!mbar_wait(&aux->r_empty[s], ((it / SR) & 1) ^ 1, P.status)) { alive = false; break; }
+          if (!mbar_wait(&aux->r_empty[s], ((it / SR) & 1) ^ 1, P.status, P.wait_ns)) { alive = false; break; }
           mbar_expect_tx(&aux->r_full[s], RAW_BYTES);
 #pragma unroll
           for (int c = 0; c < RawBox<GEMM1>::COUNT; ++c)
@@ -189,12 +190,12 @@ w8_gemm_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant_
         MOE_TILE_COORDS(tile)
         if (e < 0 || e >= P.E) continue;
         const uint32_t a = acc_it & 1;
-        if (!mbar_wait(&aux->tmem_empty[a], ((acc_it >> 1) & 1) ^ 1, P.status)) { alive = false; break; }
+        if (!mbar_wait(&aux->tmem_empty[a], ((acc_it >> 1) & 1) ^ 1, P.status, P.wait_ns)) { alive = false; break; }
         tc_fence_after();
         for (int kb = 0; kb < KB; ++kb, ++it) {
           const int sa = it % SA, sb = it % SB;
-          if (!mbar_wait(&aux->a_full[sa], (it / SA) & 1, P.status)) { alive = false; break; }
-          if (!mbar_wait(&aux->b_full[sb], (it / SB) & 1, P.status)) { alive = false; break; }
+          if (!mbar_wait(&aux->a_full[sa], (it / SA) & 1, P.status, P.wait_ns)) { alive = false; break; }
+          if (!mbar_wait(&aux->b_full[sb], (it / SB) & 1, P.status, P.wait_ns)) { alive = false; break; }
           if constexpr (GEMM1) asm volatile("fence.proxy.async.shared::cta;" ::: "memory");  // cp.async writes -> tensor core reads
           tc_fence_after();
           const uint64_t adesc = make_smem_desc(smem_u32(sA + (size_t)sa * A_BYTES));
@@ -220,7 +221,7 @@ w8_gemm_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant_
         if (e < 0 || e >= P.E) continue;
         for (int kb = 0; kb < KB; ++kb, ++it) {
           const int s = it % SA;
-          if (!mbar_wait(&aux->a_empty[s], ((it / SA) & 1) ^ 1, P.status)) { alive = false; break; }
+          if (!mbar_wait(&aux->a_empty[s], ((it / SA) & 1) ^ 1, P.status, P.wait_ns)) { alive = false; break; }
           mbar_expect_tx(&aux->a_full[s], A_BYTES);
           tma_load_2d(&map_a, &aux->a_full[s], sA + (size_t)s * A_BYTES, kb * KBE, blk * BM);
         }
@@ -248,7 +249,7 @@ w8_gemm_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant_
         }
         for (int kb = 0; kb < KB; ++kb, ++it) {
           const int s = it % SA;
-          if (!mbar_wait(&aux->a_empty[s], ((it / SA) & 1) ^ 1, P.status)) { alive = false; break; }
+          if (!mbar_wait(&aux->a_empty[s], ((it / SA) & 1) ^ 1, P.status, P.wait_ns)) { alive = false; break; }
           const uint32_t base = smem_u32(sA + (size_t)s * A_BYTES);
 #pragma unroll
           for (int j = 0; j < 4; ++j) {
@@ -301,7 +302,7 @@ w8_gemm_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant_
       }
       if (!alive) continue;
       const uint32_t a = acc_it & 1;
-      if (!mbar_wait_idle(&aux->tmem_full[a], (acc_it >> 1) & 1, P.status)) { alive = false; continue; }
+      if (!mbar_wait_idle(&aux->tmem_full[a], (acc_it >> 1) & 1, P.status, P.wait_ns)) { alive = false; continue; }
       tc_fence_after();
 #pragma unroll 1
       for (int h = 0; h < 2; ++h) {
@@ -370,8 +371,8 @@ w8_gemm_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant_
       if (e < 0 || e >= P.E) continue;
       for (int kb = 0; kb < KB; ++kb, ++it) {
         const int sr = it % SR, sb = it % SB;
-        if (!mbar_wait(&aux->r_full[sr], (it / SR) & 1, P.status)) { alive = false; break; }
-        if (!mbar_wait(&aux->b_empty[sb], ((it / SB) & 1) ^ 1, P.status)) { alive = false; break; }
+        if (!mbar_wait(&aux->r_full[sr], (it / SR) & 1, P.status, P.wait_ns)) { alive = false; break; }
+        if (!mbar_wait(&aux->b_empty[sb], ((it / SB) & 1) ^ 1, P.status, P.wait_ns)) { alive = false; break; }
         const uint8_t* raw = sR + (size_t)sr * RAW_BYTES;
         uint8_t* dst = sB + (size_t)sb * B_BYTES;
         // 1024 chunks of 16 int8; chunk q = 16 K elements (q & 3) of weight row q >> 2.  A warp
@@ -474,7 +475,7 @@ int w8_gemm(bool gemm1, int act_dtype, const void* a, const void* w, const float
 
   Params P;
   P.a_rows = (const uint8_t*)a; P.w_scale = w_scale; P.expert_ids = expert_ids; P.sorted_ids = sorted_ids;
-  P.num_post_pad = npp; P.route_weight = route_weight; P.out = out; P.status = status; P.numel = numel;
+  P.num_post_pad = npp; P.route_weight = route_weight; P.out = out; P.status = status; P.wait_ns = wait_limit_ns(); P.numel = numel;
   P.rows_cap = rows_cap; P.topk = gemm1 ? topk : 1; P.mul_weight = mul_weight; P.E = E; P.K = K; P.Nout = Nout;
   P.rows_w = rows_w; P.n_tiles = gemm1 ? Nout / 128 : (Nout + BN - 1) / BN;
   P.wide_store = ((uintptr_t)out & 31) == 0;

@@ -16,6 +16,9 @@ namespace moe {
 int fail(int code, const char* fmt, ...);
 // Checks the launch error of the kernel just enqueued; returns 0 or the cudaError_t.
 int check_launch(const char* what);
+// Limit, in nanoseconds, of every bounded barrier wait of the kernels launched from now on
+// (moe_set_wait_limit_ns; 2 s unless changed).
+unsigned long long wait_limit_ns();
 
 template <typename T> struct ToF32;
 template <> struct ToF32<float> {

@@ -13,7 +13,7 @@
 namespace moe {
 namespace tc {
 
-constexpr unsigned long long WAIT_LIMIT_NS = 2000000000ull;  // 2 s
+constexpr unsigned long long WAIT_LIMIT_NS = 2000000000ull;  // 2 s: the default of moe_set_wait_limit_ns
 
 // ------------------------------------------------------------------ PTX wrappers
 __device__ __forceinline__ uint32_t smem_u32(const void* p) {
@@ -79,13 +79,14 @@ __device__ __forceinline__ unsigned long long now_ns() {
 // Bounded wait: false when the limit ran out (status word is set).
 // CLUSTER: the barrier is also arrived on by the partner CTA (acquire at cluster scope).
 template <bool CLUSTER = false>
-__device__ __forceinline__ bool mbar_wait(uint64_t* bar, uint32_t parity, int32_t* status) {
+__device__ __forceinline__ bool mbar_wait(uint64_t* bar, uint32_t parity, int32_t* status,
+                                          unsigned long long limit_ns = WAIT_LIMIT_NS) {
   auto probe = [&]() { return CLUSTER ? mbar_try_cluster(bar, parity) : mbar_try(bar, parity); };
   if (probe()) return true;
   const unsigned long long t0 = now_ns();
   uint32_t spins = 0;
   while (!probe()) {
-    if ((++spins & 0x3FF) == 0 && now_ns() - t0 > WAIT_LIMIT_NS) {
+    if ((++spins & 0x3FF) == 0 && now_ns() - t0 > limit_ns) {
       set_status(status, MOE_ST_WAIT_TIMEOUT);
       return false;
     }
@@ -95,13 +96,14 @@ __device__ __forceinline__ bool mbar_wait(uint64_t* bar, uint32_t parity, int32_
 // The same bounded wait for warps that expect to wait long (an epilogue warp waiting for a
 // whole K loop): they sleep between probes, so their polling does not take issue slots from
 // the warps that feed the tensor core.
-__device__ __forceinline__ bool mbar_wait_idle(uint64_t* bar, uint32_t parity, int32_t* status) {
+__device__ __forceinline__ bool mbar_wait_idle(uint64_t* bar, uint32_t parity, int32_t* status,
+                                               unsigned long long limit_ns = WAIT_LIMIT_NS) {
   if (mbar_try(bar, parity)) return true;
   const unsigned long long t0 = now_ns();
   uint32_t spins = 0;
   while (!mbar_try(bar, parity)) {
     __nanosleep(128);
-    if ((++spins & 0xFF) == 0 && now_ns() - t0 > WAIT_LIMIT_NS) {
+    if ((++spins & 0xFF) == 0 && now_ns() - t0 > limit_ns) {
       set_status(status, MOE_ST_WAIT_TIMEOUT);
       return false;
     }

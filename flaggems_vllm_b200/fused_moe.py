@@ -383,8 +383,9 @@ def run_chunk(x, w1, w2, topk_weights, topk_ids, out, *, mode, w1_scale, w2_scal
     records CUDA events there)."""
     if mark is None:
         mark = STAGE_HOOK or _no_mark
-    if use_tensor_cores is None and _use_small_path(mode, x.dtype, x.shape[1], w1.shape[1] // 2,
-                                                    x.shape[0] * topk_ids.shape[1], topk_ids.shape[1]):
+    # (half-precision weights with per-channel scales -- the widened int8 experiment -- stay on the tile kernels)
+    if use_tensor_cores is None and not (mode == _lib.MODE_HALF and w1_scale is not None) and _use_small_path(
+            mode, x.dtype, x.shape[1], w1.shape[1] // 2, x.shape[0] * topk_ids.shape[1], topk_ids.shape[1]):
         run_chunk_small(x, w1, w2, topk_weights, topk_ids, out, mode=mode, w1_scale=w1_scale, w2_scale=w2_scale,
                         global_num_experts=global_num_experts, expert_map=expert_map,
                         apply_router_weight_on_input=apply_router_weight_on_input, keep=keep, mark=mark)
@@ -514,6 +515,13 @@ def fused_experts_impl(
                   out_hidden_states[begin:end], mode=mode, w1_scale=s1, w2_scale=s2,
                   global_num_experts=global_num_experts, expert_map=expert_map,
                   apply_router_weight_on_input=apply_router_weight_on_input)
+    if os.environ.get("FLAGGEMS_B200_CHECK_STATUS", "0") == "1":
+        # debugging aid (one device synchronisation per call): a kernel that gave up on a wait or met
+        # corrupt routing data leaves the output undefined; say so instead of returning it
+        st = _lib.read_status(hidden_states.device)
+        if st != 0:
+            raise _lib.MoeKernelError(f"fused_experts_impl: kernel status word = {st} "
+                                      "(1 bad expert id, 2 wait timed out, 4 bad sorted row)")
     return out_hidden_states
 
 

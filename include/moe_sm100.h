@@ -52,6 +52,19 @@ int moe_abi_version(void);
 const char* moe_last_error(void);
 
 /*
+ * Failure handling hooks; neither has a counterpart in the reference (its Triton kernels have no
+ * waits of their own).
+ * moe_set_wait_limit_ns: limit of every bounded barrier wait of the kernels launched afterwards
+ *   (default 2 s; 0 only queries).  Returns the previous limit.  Host-side, process-wide.
+ * moe_debug_wait_timeout: launches one warp that waits, with the given limit (at most 100 ms),
+ *   on a barrier nobody arrives at.  The wait runs out, MOE_ST_WAIT_TIMEOUT is ORed into
+ *   `status`, `gave_up[0]` (optional) becomes 1 and the kernel returns: how the status path is
+ *   exercised without hanging or faulting a GPU.
+ */
+unsigned long long moe_set_wait_limit_ns(unsigned long long ns);
+int moe_debug_wait_timeout(int32_t* status, unsigned long long limit_ns, int32_t* gave_up, void* stream);
+
+/*
  * Group-limited top-k routing, one warp per token.
  * Stands in for grouped_topk (src/flaggems_vllm/ops/grouped_topk.py:1674-1976)
  * and its kernels (:333-794, :887-1081).  scores[M,E] with element strides

@@ -21,7 +21,7 @@ def test_library_builds_and_exports_every_declared_symbol():
     path = build.build()
     handle = ctypes.CDLL(path)
     header = open(os.path.join(ROOT, "include", "moe_sm100.h")).read()
-    declared = set(re.findall(r"^(?:int|const char\*)\s+(moe_[a-z0-9_]+)\s*\(", header, flags=re.M))
+    declared = set(re.findall(r"^(?:int|unsigned long long|const char\*)\s+(moe_[a-z0-9_]+)\s*\(", header, flags=re.M))
     assert declared, "no declarations found in the header"
     for name in declared:
         assert hasattr(handle, name), f"{name} declared in the header but not exported"
@@ -72,6 +72,27 @@ def test_signatures_match_reference():
     assert [n for n, _, _ in _sig(fg.supports_fp32_router_gemm)] == [
         "hidden_size", "num_experts", "input_dtype", "weight_dtype"]
     assert flaggems_vllm.router_gemm is fg.router_gemm
+
+
+_KIND = {inspect.Parameter.POSITIONAL_OR_KEYWORD: "positional", inspect.Parameter.POSITIONAL_ONLY: "positional",
+         inspect.Parameter.KEYWORD_ONLY: "keyword_only", inspect.Parameter.VAR_POSITIONAL: "var_positional",
+         inspect.Parameter.VAR_KEYWORD: "var_keyword"}
+
+
+def test_signatures_match_the_reference_source():
+    """Names, order, kinds and defaults of every public function of the path, against
+    tests/golden/signatures.json, which tests/golden/make_signatures.py reads from the
+    reference's source with ast."""
+    import json
+
+    with open(os.path.join(ROOT, "tests", "golden", "signatures.json")) as fh:
+        ref = json.load(fh)
+    assert len(ref) >= 14
+    for name, info in ref.items():
+        ours = [[n, _KIND[p.kind], None if p.default is inspect._empty else repr(p.default)]
+                for n, p in inspect.signature(getattr(fg, name)).parameters.items()]
+        assert ours == info["params"], f"{name} differs from {info['source']}"
+        assert getattr(flaggems_vllm, name) is getattr(fg, name)
 
 
 def test_grouped_topk_validation_errors():
