@@ -611,3 +611,82 @@ extern "C" int moe_small_m_gemm(int gemm1, int mode, int act_dtype, const void* 
 #undef MOE_SM_MODE
 #undef MOE_SM_LAUNCH
 }
+
+// ---------------------------------------------------------------------------------------------
+// GEMM 2 of the small-batch schedule for hosts that cannot allocate.
+//
+// A serving engine that has handed every free byte of device memory to its own pools at
+// start-up has nothing left for cudaMalloc to give, and cudaMalloc / cudaFree stall the whole
+// device while they run, which a decode loop cannot afford between two kernels.  Such a host can
+// call this entry point: it takes the same inputs and the same output as moe_small_m_gemm with
+// gemm1 = 0, and keeps everything else -- the route rows y, the split-K partial sums and the two
+// counter tables -- in the fixed array below, which lives in the library's device image.
+//
+//   * The array is kSmallStaticBytes (8 MiB) on every GPU that loads the library, from the load
+//     to process exit.  A call whose scratch does not fit is rejected with MOE_E_TOOBIG and the
+//     required size in the message; nothing is launched.
+//   * No cudaMalloc, cudaFree or other allocating call is made, here or in what it calls.
+//   * The first call on a device looks the array's device address up (cudaGetSymbolAddress, with
+//     that device current) and remembers it; make that first call outside any stream capture.
+//   * All calls on a device share the one array, and it keeps what the last call left.  The
+//     counter tables are cleared on `stream` at the start of every call; the rest is written
+//     before it is read.  Two calls whose kernels overlap on the GPU (different streams, no
+//     ordering between them) race on it: order them.
+static __device__ __align__(256) unsigned char g_small_static[8u << 20];
+static constexpr size_t kSmallStaticBytes = 8u << 20;
+static unsigned char* g_small_static_ptr[64] = {};  // device address per device ordinal, filled on first use
+
+static int small_static_base(unsigned char** base) {
+  using namespace moe;
+  int dev = -1;
+  cudaError_t ce = cudaGetDevice(&dev);
+  if (ce != cudaSuccess) return fail((int)ce, "small-batch GEMM2 (static scratch): cudaGetDevice: %s", cudaGetErrorString(ce));
+  if (dev < 0 || dev >= 64) return fail(MOE_E_BADARG, "small-batch GEMM2 (static scratch): device ordinal %d not supported", dev);
+  if (g_small_static_ptr[dev] == nullptr) {
+    // In host code `g_small_static` names a host-side shadow of the symbol, not device memory:
+    // the device address has to be asked for, once per device, with that device current.
+    unsigned char* p = nullptr;
+    ce = cudaGetSymbolAddress((void**)&p, g_small_static);
+    if (ce != cudaSuccess || p == nullptr)
+      return fail(ce != cudaSuccess ? (int)ce : MOE_E_DRIVER, "small-batch GEMM2 (static scratch): cudaGetSymbolAddress: %s",
+                  cudaGetErrorString(ce));
+    g_small_static_ptr[dev] = p;
+  }
+  *base = g_small_static_ptr[dev];
+  return 0;
+}
+
+extern "C" int moe_small_m_gemm2_static(int mode, int act_dtype, const void* act_sorted, int64_t num_tokens, int topk,
+                                        const void* w2, const float* w2_scale, const int32_t* expert_ids,
+                                        const int32_t* sorted_ids, const int32_t* num_post_pad,
+                                        const int32_t* expert_map, int num_experts_global, const float* route_weight,
+                                        int mul_weight, const void* topk_ids, int ids_int64, int64_t rows_cap, int E,
+                                        int K, int Nout, void* final_out, int k_slices, int32_t* status, void* stream) {
+  using namespace moe;
+  if (num_tokens < 0 || topk <= 0 || rows_cap < 0 || Nout <= 0) return fail(MOE_E_BADARG, "small-batch GEMM2 (static scratch): bad extent");
+  if (num_tokens == 0 || rows_cap == 0) return 0;
+  int64_t partial_floats = 0, unit_counters = 0, token_counters = 0;
+  int rc = moe_small_m_plan(0, mode, K, Nout, rows_cap, num_tokens, k_slices, &partial_floats, &unit_counters, &token_counters);
+  if (rc) return rc;
+  auto up256 = [](size_t v) { return (v + 255) & ~(size_t)255; };
+  const size_t counters_bytes = up256((size_t)(unit_counters + token_counters) * sizeof(int32_t));
+  const size_t y_bytes = up256((size_t)num_tokens * topk * Nout * 2);  // f16 / bf16 rows
+  const size_t partial_bytes = up256((size_t)partial_floats * sizeof(float));
+  const size_t need = counters_bytes + y_bytes + partial_bytes;
+  if (need > kSmallStaticBytes)
+    return fail(MOE_E_TOOBIG, "small-batch GEMM2 (static scratch): this call needs %zu bytes of scratch, the fixed array holds %zu",
+                need, kSmallStaticBytes);
+  unsigned char* base = nullptr;
+  rc = small_static_base(&base);
+  if (rc) return rc;
+  // the counter tables must start at zero whatever the previous call (or a failed one) left
+  cudaError_t ce = cudaMemsetAsync(base, 0, counters_bytes, (cudaStream_t)stream);
+  if (ce != cudaSuccess) return fail((int)ce, "small-batch GEMM2 (static scratch): clearing the counters: %s", cudaGetErrorString(ce));
+  int32_t* unit_cnt = reinterpret_cast<int32_t*>(base);
+  int32_t* tok_cnt = unit_cnt + unit_counters;
+  void* y = base + counters_bytes;
+  float* partial = partial_floats ? reinterpret_cast<float*>(base + counters_bytes + y_bytes) : nullptr;
+  return moe_small_m_gemm(0, mode, act_dtype, act_sorted, num_tokens, topk, w2, w2_scale, expert_ids, sorted_ids, num_post_pad,
+                          expert_map, num_experts_global, route_weight, mul_weight, topk_ids, ids_int64, rows_cap, E, K, Nout,
+                          y, final_out, k_slices, partial, unit_cnt, tok_cnt, status, stream);
+}

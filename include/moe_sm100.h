@@ -250,6 +250,28 @@ int moe_small_m_gemm(int gemm1, int mode, int act_dtype, const void* a, int64_t 
                      float* partial, int32_t* unit_counters, int32_t* token_counters, int32_t* status, void* stream);
 
 /*
+ * GEMM 2 of the small-batch schedule without any allocation by anyone: same inputs and output
+ * as moe_small_m_gemm(gemm1 = 0, ...), but the route rows y, the partial sums and both counter
+ * tables live in a fixed 8 MiB array inside the library's device image instead of in buffers
+ * the caller would have to allocate.  It is for hosts that cannot get device memory at call
+ * time: an engine whose pools already own all of it, or a decode loop that must not run
+ * cudaMalloc / cudaFree (both stall the device).  This entry point has no counterpart in the
+ * reference, which allocates its intermediates with torch on every call.
+ *   - A call that needs more scratch than the array holds returns MOE_E_TOOBIG (the message
+ *     gives both sizes) and launches nothing.
+ *   - The first call on a device resolves the array's device address; make it before any
+ *     stream capture.  Calls share the array: the counters are cleared on `stream` at the start
+ *     of each call, everything else is written before it is read, and calls whose kernels
+ *     overlap on the GPU race on it.
+ */
+int moe_small_m_gemm2_static(int mode, int act_dtype, const void* act_sorted, int64_t num_tokens, int topk,
+                             const void* w2, const float* w2_scale, const int32_t* expert_ids,
+                             const int32_t* sorted_ids, const int32_t* num_post_pad, const int32_t* expert_map,
+                             int num_experts_global, const float* route_weight, int mul_weight, const void* topk_ids,
+                             int ids_int64, int64_t rows_cap, int E, int K, int Nout, void* final_out, int k_slices,
+                             int32_t* status, void* stream);
+
+/*
  * out[m, :] = sum_j in[m, j, :] in fp32, fixed order j = 0..topk-1, stored in
  * the io dtype.  Stands in for moe_sum (src/flaggems_vllm/ops/moe_sum.py:250-310).
  * When topk_ids is given, slot j is skipped if its id is outside
