@@ -481,8 +481,12 @@ def main():
     ap.add_argument("--ref-budget-s", type=float, default=240.0, help="wall-clock budget of the CPU reference arm")
     ap.add_argument("--cpu-baseline-tokens", type=int, default=256)
     ap.add_argument("--no-cpu-baseline", action="store_true")
-    ap.add_argument("--ep-check-tokens", type=int, default=16,
-                    help="tokens per rank of the full-size expert-parallel step checked against the CPU oracle (0: skip)")
+    ap.add_argument("--ep-chunks", type=int, default=1,
+                    help="token chunks per expert-parallel step (each on its own stream and communicator)")
+    ap.add_argument("--ep-check-tokens", type=int, default=-1,
+                    help="tokens per rank of the full-size expert-parallel step checked against the CPU oracle "
+                         "(0: skip; default 16 at 2 GPUs, 8 at 4, 4 at 8: every rank runs the oracle on its share "
+                         "of the host cores, and each token brings about 8 experts to widen)")
     ap.add_argument("--router-bias-std", type=float, default=0.02,
                     help="spread of the synthetic score-correction bias; the scores are i.i.d., so a small "
                          "spread gives the balanced expert load a trained bias produces")
@@ -530,8 +534,10 @@ def main():
     if world > 1:
         dist.broadcast(bias, 0)
     flush = torch.empty(2 * L2_BYTES, dtype=torch.uint8, device=dev)
-    layer = ep.ExpertParallelMoE(w1, w2, s1, s2, E, dist.group.WORLD) if world > 1 else None
+    layer = ep.ExpertParallelMoE(w1, w2, s1, s2, E, dist.group.WORLD, chunks=args.ep_chunks) if world > 1 else None
     ep_parity = None
+    if args.ep_check_tokens < 0:
+        args.ep_check_tokens = max(4, 32 // max(world, 2))
     if world > 1 and args.ep_check_tokens > 0:
         ep_parity = ep_parity_check(dist, dev, rank, world, layer, x, logits, bias, c, args.ep_check_tokens)
     fp8_peak = measure_fp8_peak(dev) if world == 1 else None
@@ -681,7 +687,7 @@ def main():
         "steps": args.steps, "warmup": args.warmup, "ms_per_step": ms, "higher_is_better": True,
         "scaling": "weak", "vs_baseline": None, "dtype": "fp8_e4m3", "data": "synthetic",
         "config": {"workload": "deepseek_v3_fp8_block_moe_layer", "tokens_per_gpu": M, "global_tokens": total_tokens,
-                   **c, "experts_per_gpu": E_local, "router_bias_std": args.router_bias_std, "parallelism": f"ep{world}" if world > 1 else "single",
+                   **c, "experts_per_gpu": E_local, "router_bias_std": args.router_bias_std, "parallelism": f"ep{world}" if world > 1 else "single", "ep_chunks": args.ep_chunks if world > 1 else None,
                    "l2": "flushed between iterations (252 MB memset); weights 11.3 GB >> L2"},
         "tflops": flops / (ms * 1e-3) / 1e12,
         "e2e": {"value": total_tokens / (e2e_ms * 1e-3), "unit": "tokens/s", "ms_per_step": e2e_ms,

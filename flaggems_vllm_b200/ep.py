@@ -64,7 +64,7 @@ class ExpertParallelMoE:
     """Holds this rank's expert shard and runs the dispatch/compute/combine step."""
 
     def __init__(self, w1, w2, w1_scale, w2_scale, num_experts_global: int, group=None, *,
-                 mode: int = _lib.MODE_FP8_BLOCK, compute_fn=None, combine_fn=None):
+                 mode: int = _lib.MODE_FP8_BLOCK, compute_fn=None, combine_fn=None, chunks: int = 1):
         """``compute_fn(a_rows, a_scales_t, slot_weights, slot_ids, act_dtype) -> rows``
         and ``combine_fn(rows_back, out, index)`` replace the CUDA steps; the CPU
         (gloo) tests of the dispatch/combine plumbing inject them."""
@@ -80,6 +80,18 @@ class ExpertParallelMoE:
         self.last_counts = None
         self.compute_fn = compute_fn or self._compute_cuda
         self.combine_fn = combine_fn or self._combine_cuda
+        # Token chunks run as independent dispatch/compute/combine steps on their own streams and
+        # their own communicators, so one chunk's all-to-alls travel under the other chunk's GEMMs
+        # (collectives of one communicator run in issue order, which would chain the chunks).
+        self.chunks = max(1, int(chunks))
+        self._lanes = None
+
+    def _chunk_lanes(self, device):
+        if self._lanes is None:
+            ranks = dist.get_process_group_ranks(self.group)
+            self._lanes = [(torch.cuda.Stream(device=device), self.group if c == 0 else dist.new_group(ranks))
+                           for c in range(self.chunks)]
+        return self._lanes
 
     def _compute_cuda(self, a_rows, a_scales_t, slot_weights, slot_ids, act_dtype):
         y = route_pipeline(a_rows, a_scales_t, self.w1, self.w2, slot_weights, slot_ids, mode=self.mode,
@@ -94,16 +106,37 @@ class ExpertParallelMoE:
         # one slot per rank; ranks the token did not visit have index -1
         combine_routes(rows_back, out, None, 0, None, row_index=index)
 
-    def _a2a(self, out, inp, out_splits, in_splits):
+    def _a2a(self, out, inp, out_splits, in_splits, group=None):
         dist.all_to_all_single(out, inp, output_split_sizes=out_splits, input_split_sizes=in_splits,
-                               group=self.group)
+                               group=group if group is not None else self.group)
 
     def forward(self, x: torch.Tensor, topk_weights: torch.Tensor, topk_ids: torch.Tensor) -> torch.Tensor:
         if x.is_cuda and self.compute_fn == self._compute_cuda:
-            return self._forward_cuda(x, topk_weights, topk_ids)
+            if self.chunks > 1 and x.shape[0] >= 2 * self.chunks:
+                return self._forward_chunked(x, topk_weights, topk_ids)
+            return self._forward_cuda(x, topk_weights, topk_ids, self.group)
         return self._forward_torch(x, topk_weights, topk_ids)
 
-    def _forward_cuda(self, x, topk_weights, topk_ids):
+    def _forward_chunked(self, x, topk_weights, topk_ids):
+        """Every rank cuts its tokens into the same number of chunks; chunk c of all ranks forms one
+        dispatch/compute/combine step on lane c (stream + communicator).  Results land in one
+        output tensor; the caller's stream waits for every lane."""
+        M = x.shape[0]
+        main = torch.cuda.current_stream(x.device)
+        lanes = self._chunk_lanes(x.device)
+        out = torch.empty_like(x)
+        bounds = [M * c // self.chunks for c in range(self.chunks + 1)]
+        for c, (stream, group) in enumerate(lanes):
+            lo, hi = bounds[c], bounds[c + 1]
+            stream.wait_stream(main)
+            with torch.cuda.stream(stream):
+                part = self._forward_cuda(x[lo:hi], topk_weights[lo:hi], topk_ids[lo:hi], group, out=out[lo:hi])
+                part.record_stream(stream)
+        for stream, _ in lanes:
+            main.wait_stream(stream)
+        return out
+
+    def _forward_cuda(self, x, topk_weights, topk_ids, group=None, out=None):
         """The same step with the bookkeeping done by three kernels (plan, pack, unpack) instead
         of some thirty small tensor operations; one host read (the pair counts) remains."""
         M, H = x.shape
@@ -120,7 +153,8 @@ class ExpertParallelMoE:
         tok = torch.empty((max(M * R, 1),), dtype=torch.int32, device=dev)
         _lib.check(L.moe_ep_plan(ids.data_ptr(), M, k, self.E_local, R, index.data_ptr(), both[0].data_ptr(),
                                  tok.data_ptr(), st))
-        dist.all_to_all_single(both[1], both[0], group=self.group)
+        group = group if group is not None else self.group
+        dist.all_to_all_single(both[1], both[0], group=group)
         counts = both.tolist()  # the one host sync of the step
         send_splits, recv_splits = counts[0], counts[1]
         n_send, n_recv = sum(send_splits), sum(recv_splits)
@@ -140,9 +174,9 @@ class ExpertParallelMoE:
         side_recv = torch.empty((n_recv, g + 2 * k), dtype=torch.float32, device=dev)
         a_rows = torch.empty((n_recv, H), dtype=rows_dtype, device=dev)
         # the fp8 rows travel as bytes (NCCL has no e4m3 all-to-all on every version)
-        self._a2a(side_recv, side_send, recv_splits, send_splits)
+        self._a2a(side_recv, side_send, recv_splits, send_splits, group)
         self._a2a(a_rows.view(torch.uint8) if fp8 else a_rows, rows_send.view(torch.uint8) if fp8 else rows_send,
-                  recv_splits, send_splits)
+                  recv_splits, send_splits, group)
         a_scales_t = torch.empty((g, n_recv), dtype=torch.float32, device=dev) if fp8 else None
         slot_ids = torch.empty((n_recv, k), dtype=torch.int32, device=dev)
         slot_w = torch.empty((n_recv, k), dtype=torch.float32, device=dev)
@@ -153,8 +187,9 @@ class ExpertParallelMoE:
         else:
             rows = torch.empty((0, H), dtype=x.dtype, device=dev)
         rows_back = torch.empty((n_send, H), dtype=x.dtype, device=dev)
-        self._a2a(rows_back, rows, send_splits, recv_splits)
-        out = torch.empty_like(x)
+        self._a2a(rows_back, rows, send_splits, recv_splits, group)
+        if out is None:
+            out = torch.empty_like(x)
         self.combine_fn(rows_back, out, index)
         return out
 

@@ -48,6 +48,13 @@ def main():
                                          mode=_lib.MODE_HALF)
         out = layer.forward(x, tw, ti)
         torch.cuda.synchronize()
+        if M >= 8:
+            # the same step cut into two token chunks on two streams / communicators: identical rows
+            layer.chunks = 2
+            out2 = layer.forward(x, tw, ti)
+            torch.cuda.synchronize()
+            layer.chunks = 1
+            assert torch.equal(out2, out), "chunked expert-parallel step differs from the unchunked one"
         a, b = out.float(), full.float()
         rl2 = ((a - b).norm() / b.norm().clamp_min(1e-20)).item()
         st = fg.read_status(dev)
