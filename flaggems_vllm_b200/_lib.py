@@ -15,7 +15,8 @@ HERE = os.path.dirname(os.path.abspath(__file__))
 LIB_PATH = os.path.join(HERE, "libmoe_sm100.so")
 
 MOE_F32, MOE_F16, MOE_BF16, MOE_FP8E4M3, MOE_INT8 = 0, 1, 2, 3, 4
-MODE_HALF, MODE_FP8_BLOCK, MODE_W8A16 = 0, 1, 2
+MODE_HALF, MODE_FP8_BLOCK, MODE_W8A16, MODE_FP8_ROW, MODE_INT8_ROW = 0, 1, 2, 3, 4
+ACT_SILU, ACT_SWIGLUOAI = 0, 1
 ST_BAD_EXPERT_ID, ST_WAIT_TIMEOUT, ST_BAD_ROW = 1, 2, 4
 
 _DTYPE_CODE = {torch.float32: MOE_F32, torch.float16: MOE_F16, torch.bfloat16: MOE_BF16}
@@ -33,6 +34,8 @@ SYMBOLS = {
                                      c_int64, c_void_p, c_void_p, c_void_p]),
     "moe_per_token_group_quant_fp8": (c_int, [c_void_p, c_int, c_int64, c_int64, c_int, c_void_p, c_void_p,
                                               c_int, c_int64, c_void_p]),
+    "moe_per_token_group_quant_fp8_ex": (c_int, [c_void_p, c_int, c_int64, c_int64, c_int, c_float, c_int, c_void_p,
+                                                 c_void_p, c_int, c_int64, c_void_p]),
     "moe_widen_int8": (c_int, [c_void_p, c_void_p, c_int, c_int64, c_void_p]),
     "moe_ep_plan": (c_int, [c_void_p, c_int64, c_int, c_int, c_int, c_void_p, c_void_p, c_void_p, c_void_p]),
     "moe_ep_pack": (c_int, [c_void_p, c_int64, c_void_p, c_int, c_void_p, c_void_p, c_int, c_void_p, c_int64,
@@ -45,6 +48,11 @@ SYMBOLS = {
     "moe_gemm1": (c_int, [c_int, c_int, c_void_p, c_int, c_void_p, c_int64, c_int, c_void_p, c_void_p, c_void_p,
                           c_void_p, c_void_p, c_void_p, c_int, c_int64, c_int, c_int, c_int, c_int, c_void_p,
                           c_void_p, c_int, c_void_p, c_void_p]),
+    "moe_gemm1_ex": (c_int, [c_int, c_int, c_void_p, c_int, c_void_p, c_int64, c_int, c_void_p, c_void_p, c_void_p,
+                             c_void_p, c_void_p, c_void_p, c_int, c_int64, c_int, c_int, c_int, c_int, c_void_p,
+                             c_void_p, c_int, c_int, c_float, c_float, c_float, c_void_p, c_void_p]),
+    "moe_rowwise_quant": (c_int, [c_void_p, c_int, c_int64, c_int64, c_int, c_void_p, c_void_p, c_int64, c_void_p,
+                                  c_void_p, c_void_p]),
     "moe_gemm2": (c_int, [c_int, c_int, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p,
                           c_void_p, c_int, c_int64, c_int64, c_int, c_int, c_int, c_int, c_void_p, c_int,
                           c_void_p, c_void_p]),

@@ -6,7 +6,8 @@ namespace moe {
 int simt_gemm(bool gemm1, int mode, int act_dtype, const void* a, const float* a_scales_t, const void* w,
               const float* w_scale, const int32_t* expert_ids, const int32_t* sorted_ids, const int32_t* npp,
               const float* route_weight, int mul_weight, int64_t numel, int64_t rows_cap, int64_t a_tokens, int topk,
-              int block_m, int E, int K, int Nout, void* out, float* out_scales_t, int32_t* status, cudaStream_t st);
+              int block_m, int E, int K, int Nout, void* out, float* out_scales_t, int32_t* status, cudaStream_t st,
+              int act_kind = MOE_ACT_SILU, float alpha = 0.0f, float beta = 0.0f, float limit = 0.0f);
 int tc_gemm(bool gemm1, int mode, int act_dtype, const void* a, const float* a_scales_t, const void* w,
             const float* w_scale, const int32_t* expert_ids, const int32_t* sorted_ids, const int32_t* npp,
             const float* route_weight, int mul_weight, int64_t numel, int64_t rows_cap, int64_t a_tokens, int topk,
@@ -25,7 +26,8 @@ static int check_common(const char* who, int mode, const void* a, const float* a
     return fail(MOE_E_BADARG, "%s: bad extent", who);
   if (!a || !w || !expert_ids || !sorted_ids || !npp || !out) return fail(MOE_E_BADARG, "%s: null pointer", who);
   if (mul_weight && !route_weight) return fail(MOE_E_BADARG, "%s: route weights missing", who);
-  if (mode == MOE_MODE_FP8_BLOCK && (!a_scales || !w_scale)) return fail(MOE_E_BADARG, "%s: scales missing", who);
+  if ((mode == MOE_MODE_FP8_BLOCK || mode == MOE_MODE_FP8_ROW || mode == MOE_MODE_INT8_ROW) && (!a_scales || !w_scale))
+    return fail(MOE_E_BADARG, "%s: scales missing", who);
   if (mode == MOE_MODE_W8A16 && !w_scale) return fail(MOE_E_BADARG, "%s: weight scales missing", who);
   return 0;
 }
@@ -37,7 +39,21 @@ extern "C" int moe_gemm1(int mode, int act_dtype, const void* a, int a_sorted, c
                          const int32_t* sorted_ids, const int32_t* num_post_pad, const float* route_weight,
                          int mul_weight, int64_t rows_cap, int block_m, int E, int H, int I, void* out,
                          float* out_scales_t, int use_tensor_cores, int32_t* status, void* stream) {
+  return moe_gemm1_ex(mode, act_dtype, a, a_sorted, a_scales_t, num_tokens, topk, w1, w1_scale, expert_ids, sorted_ids,
+                      num_post_pad, route_weight, mul_weight, rows_cap, block_m, E, H, I, out, out_scales_t,
+                      use_tensor_cores, MOE_ACT_SILU, 0.0f, 0.0f, 0.0f, status, stream);
+}
+
+extern "C" int moe_gemm1_ex(int mode, int act_dtype, const void* a, int a_sorted, const float* a_scales_t,
+                            int64_t num_tokens, int topk, const void* w1, const float* w1_scale,
+                            const int32_t* expert_ids, const int32_t* sorted_ids, const int32_t* num_post_pad,
+                            const float* route_weight, int mul_weight, int64_t rows_cap, int block_m, int E, int H,
+                            int I, void* out, float* out_scales_t, int use_tensor_cores, int activation, float alpha,
+                            float beta, float limit, int32_t* status, void* stream) {
   using namespace moe;
+  if (activation != MOE_ACT_SILU && activation != MOE_ACT_SWIGLUOAI) return fail(MOE_E_BADARG, "gemm1: unknown activation %d", activation);
+  if (use_tensor_cores && (activation != MOE_ACT_SILU || mode == MOE_MODE_FP8_ROW || mode == MOE_MODE_INT8_ROW))
+    return fail(MOE_E_SHAPE, "gemm1: the row-scaled modes and activations other than SiLU are served by the generic kernel");
   if (num_tokens < 0 || topk <= 0) return fail(MOE_E_BADARG, "gemm1: bad token count or topk");
   const int64_t numel = num_tokens * topk;
   int rc = check_common("gemm1", mode, a, a_scales_t, w1, w1_scale, expert_ids, sorted_ids, num_post_pad,
@@ -57,7 +73,7 @@ extern "C" int moe_gemm1(int mode, int act_dtype, const void* a, int a_sorted, c
                    status, (cudaStream_t)stream, use_tensor_cores, a_sorted);
   return simt_gemm(true, mode, act_dtype, a, a_scales_t, w1, w1_scale, expert_ids, sorted_ids, num_post_pad,
                    route_weight, mul_weight, numel, rows_cap, num_tokens, topk, block_m, E, H, I, out, out_scales_t,
-                   status, (cudaStream_t)stream);
+                   status, (cudaStream_t)stream, activation, alpha, beta, limit);
 }
 
 extern "C" int moe_gemm2(int mode, int act_dtype, const void* act_sorted, const float* act_scales_t, const void* w2,
@@ -70,6 +86,8 @@ extern "C" int moe_gemm2(int mode, int act_dtype, const void* act_sorted, const 
                         route_weight, mul_weight, numel, rows_cap, block_m, E, H, I, y);
   if (rc) return rc;
   if (rows_cap == 0 || numel == 0) return 0;
+  if (use_tensor_cores && (mode == MOE_MODE_FP8_ROW || mode == MOE_MODE_INT8_ROW))
+    return fail(MOE_E_SHAPE, "gemm2: the row-scaled modes are served by the generic kernel");
   if (use_tensor_cores && mode == MOE_MODE_W8A16)
     return w8_gemm(false, act_dtype, act_sorted, w2, w2_scale, expert_ids, sorted_ids, num_post_pad, route_weight,
                    mul_weight, numel, rows_cap, 0, 1, block_m, E, I, H, y, status, (cudaStream_t)stream);

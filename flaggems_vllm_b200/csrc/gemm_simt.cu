@@ -18,14 +18,26 @@ template <int MODE, typename AT> struct Elem;  // element types of A and W per m
 template <typename AT> struct Elem<MOE_MODE_HALF, AT> { using A = AT; using W = AT; };
 template <typename AT> struct Elem<MOE_MODE_FP8_BLOCK, AT> { using A = uint8_t; using W = uint8_t; };
 template <typename AT> struct Elem<MOE_MODE_W8A16, AT> { using A = AT; using W = int8_t; };
+template <typename AT> struct Elem<MOE_MODE_FP8_ROW, AT> { using A = uint8_t; using W = uint8_t; };
+template <typename AT> struct Elem<MOE_MODE_INT8_ROW, AT> { using A = int8_t; using W = int8_t; };
+
+// gate/up -> activation value; `kind` is MOE_ACT_SILU or MOE_ACT_SWIGLUOAI
+// (src/flaggems_vllm/ops/fused_moe.py:733-773: clamps that let NaN through, sigmoid(alpha * gate))
+__device__ __forceinline__ float gated_activation(int kind, float g, float u, float alpha, float beta, float limit) {
+  if (kind == MOE_ACT_SILU) return silu_mul(g, u);
+  g = (g != g) ? g : fminf(g, limit);
+  u = (u != u) ? u : fminf(fmaxf(u, -limit), limit);
+  return g * (1.0f / (1.0f + expf(-alpha * g))) * (u + beta);
+}
 
 template <int MODE, typename T> __device__ __forceinline__ float load_a(const T* p) {
-  if constexpr (MODE == MOE_MODE_FP8_BLOCK) return fp8e4m3_to_f32(*p);
+  if constexpr (MODE == MOE_MODE_FP8_BLOCK || MODE == MOE_MODE_FP8_ROW) return fp8e4m3_to_f32(*p);
+  else if constexpr (MODE == MOE_MODE_INT8_ROW) return (float)(*p);
   else return ToF32<T>::get(*p);
 }
 template <int MODE, typename T> __device__ __forceinline__ float load_w(const T* p) {
-  if constexpr (MODE == MOE_MODE_FP8_BLOCK) return fp8e4m3_to_f32(*p);
-  else if constexpr (MODE == MOE_MODE_W8A16) return (float)(*p);
+  if constexpr (MODE == MOE_MODE_FP8_BLOCK || MODE == MOE_MODE_FP8_ROW) return fp8e4m3_to_f32(*p);
+  else if constexpr (MODE == MOE_MODE_W8A16 || MODE == MOE_MODE_INT8_ROW) return (float)(*p);
   else return ToF32<T>::get(*p);
 }
 
@@ -38,7 +50,8 @@ __global__ void __launch_bounds__(256) simt_gemm_kernel(
     const int32_t* __restrict__ expert_ids, const int32_t* __restrict__ sorted_ids,
     const int32_t* __restrict__ num_post_pad, const float* __restrict__ route_weight, int mul_weight,
     int64_t numel, int64_t rows_cap, int64_t a_tokens, int topk, int block_m, int E, int K, int Nout,
-    void* __restrict__ out, float* __restrict__ out_scales_t, int32_t* __restrict__ status) {
+    void* __restrict__ out, float* __restrict__ out_scales_t, int32_t* __restrict__ status, int act_kind,
+    float alpha, float beta, float limit) {
   using WT = typename Elem<MODE, AT>::W;
   using AE = typename Elem<MODE, AT>::A;
   __shared__ float As[TM][BK + 1];
@@ -122,7 +135,15 @@ __global__ void __launch_bounds__(256) simt_gemm_kernel(
   const bool row_ok = sid >= 0 && sid < numel;
   float rw = 1.0f;
   if (mul_weight && row_ok) rw = route_weight[sid];
-  if (MODE == MOE_MODE_W8A16 || (MODE == MOE_MODE_HALF && w_scale != nullptr)) {
+  constexpr bool ROW_SCALED = MODE == MOE_MODE_FP8_ROW || MODE == MOE_MODE_INT8_ROW;
+  if constexpr (ROW_SCALED) {
+    // one activation scale per row: of the token (GEMM1) or of the sorted intermediate row (GEMM2)
+    float as = 0.0f;
+    if (row_ok) as = GEMM1 ? a_scales_t[sid / topk] : a_scales_t[p];
+#pragma unroll
+    for (int i = 0; i < CPT; ++i) { accg[i] *= as; accu[i] *= as; }
+  }
+  if (ROW_SCALED || MODE == MOE_MODE_W8A16 || (MODE == MOE_MODE_HALF && w_scale != nullptr)) {
 #pragma unroll
     for (int i = 0; i < CPT; ++i) {
       const int n = n0 + tx + 16 * i;
@@ -139,7 +160,18 @@ __global__ void __launch_bounds__(256) simt_gemm_kernel(
     for (int i = 0; i < CPT; ++i) {
       // rounded to the activation dtype first: that is what the reference
       // stores and re-quantises (src/flaggems_vllm/ops/fused_moe.py:1969, 2658-2666)
-      v[i] = ToF32<AT>::get(from_f32<AT>(silu_mul(accg[i] * rw, accu[i] * rw)));
+      if constexpr (ROW_SCALED) {
+        // the reference rounds GEMM 1's output to the activation dtype before the activation kernel reads it
+        accg[i] = ToF32<AT>::get(from_f32<AT>(accg[i] * rw));
+        accu[i] = ToF32<AT>::get(from_f32<AT>(accu[i] * rw));
+        v[i] = ToF32<AT>::get(from_f32<AT>(gated_activation(act_kind, accg[i], accu[i], alpha, beta, limit)));
+      } else if (act_kind != MOE_ACT_SILU) {
+        // unfused activations read GEMM 1's output after it was stored in the activation dtype
+        const float gq = ToF32<AT>::get(from_f32<AT>(accg[i] * rw)), uq = ToF32<AT>::get(from_f32<AT>(accu[i] * rw));
+        v[i] = ToF32<AT>::get(from_f32<AT>(gated_activation(act_kind, gq, uq, alpha, beta, limit)));
+      } else {
+        v[i] = ToF32<AT>::get(from_f32<AT>(silu_mul(accg[i] * rw, accu[i] * rw)));
+      }
       amax = fmaxf(amax, fabsf(v[i]));
     }
     if constexpr (MODE == MOE_MODE_FP8_BLOCK) {
@@ -180,13 +212,14 @@ template <int MODE, typename AT, bool GEMM1>
 int launch(const void* a, const float* a_scales_t, const void* w, const float* w_scale,
            const int32_t* expert_ids, const int32_t* sorted_ids, const int32_t* npp,
            const float* route_weight, int mul_weight, int64_t numel, int64_t rows_cap, int64_t a_tokens, int topk, int block_m,
-           int E, int K, int Nout, void* out, float* out_scales_t, int32_t* status, cudaStream_t st) {
+           int E, int K, int Nout, void* out, float* out_scales_t, int32_t* status, cudaStream_t st, int act_kind,
+           float alpha, float beta, float limit) {
   dim3 grid((unsigned)((Nout + TN - 1) / TN), (unsigned)((rows_cap + TM - 1) / TM));
   if (grid.y > 65535) return fail(MOE_E_TOOBIG, "generic GEMM: more than 65535 row tiles");
   simt_gemm_kernel<MODE, AT, GEMM1><<<grid, 256, 0, st>>>(
       (const typename Elem<MODE, AT>::A*)a, a_scales_t, (const typename Elem<MODE, AT>::W*)w, w_scale,
       expert_ids, sorted_ids, npp, route_weight, mul_weight, numel, rows_cap, a_tokens, topk, block_m, E, K, Nout, out,
-      out_scales_t, status);
+      out_scales_t, status, act_kind, alpha, beta, limit);
   return check_launch(GEMM1 ? "gemm1 (generic)" : "gemm2 (generic)");
 }
 
@@ -195,14 +228,19 @@ int dispatch_mode(int mode, const void* a, const float* a_scales_t, const void* 
                   const float* w_scale, const int32_t* expert_ids, const int32_t* sorted_ids,
                   const int32_t* npp, const float* route_weight, int mul_weight, int64_t numel,
                   int64_t rows_cap, int64_t a_tokens, int topk, int block_m, int E, int K, int Nout, void* out,
-                  float* out_scales_t, int32_t* status, cudaStream_t st) {
+                  float* out_scales_t, int32_t* status, cudaStream_t st, int act_kind, float alpha, float beta,
+                  float limit) {
   switch (mode) {
     case MOE_MODE_HALF:
-      return launch<MOE_MODE_HALF, AT, GEMM1>(a, a_scales_t, w, w_scale, expert_ids, sorted_ids, npp, route_weight, mul_weight, numel, rows_cap, a_tokens, topk, block_m, E, K, Nout, out, out_scales_t, status, st);
+      return launch<MOE_MODE_HALF, AT, GEMM1>(a, a_scales_t, w, w_scale, expert_ids, sorted_ids, npp, route_weight, mul_weight, numel, rows_cap, a_tokens, topk, block_m, E, K, Nout, out, out_scales_t, status, st, act_kind, alpha, beta, limit);
     case MOE_MODE_FP8_BLOCK:
-      return launch<MOE_MODE_FP8_BLOCK, AT, GEMM1>(a, a_scales_t, w, w_scale, expert_ids, sorted_ids, npp, route_weight, mul_weight, numel, rows_cap, a_tokens, topk, block_m, E, K, Nout, out, out_scales_t, status, st);
+      return launch<MOE_MODE_FP8_BLOCK, AT, GEMM1>(a, a_scales_t, w, w_scale, expert_ids, sorted_ids, npp, route_weight, mul_weight, numel, rows_cap, a_tokens, topk, block_m, E, K, Nout, out, out_scales_t, status, st, act_kind, alpha, beta, limit);
     case MOE_MODE_W8A16:
-      return launch<MOE_MODE_W8A16, AT, GEMM1>(a, a_scales_t, w, w_scale, expert_ids, sorted_ids, npp, route_weight, mul_weight, numel, rows_cap, a_tokens, topk, block_m, E, K, Nout, out, out_scales_t, status, st);
+      return launch<MOE_MODE_W8A16, AT, GEMM1>(a, a_scales_t, w, w_scale, expert_ids, sorted_ids, npp, route_weight, mul_weight, numel, rows_cap, a_tokens, topk, block_m, E, K, Nout, out, out_scales_t, status, st, act_kind, alpha, beta, limit);
+    case MOE_MODE_FP8_ROW:
+      return launch<MOE_MODE_FP8_ROW, AT, GEMM1>(a, a_scales_t, w, w_scale, expert_ids, sorted_ids, npp, route_weight, mul_weight, numel, rows_cap, a_tokens, topk, block_m, E, K, Nout, out, out_scales_t, status, st, act_kind, alpha, beta, limit);
+    case MOE_MODE_INT8_ROW:
+      return launch<MOE_MODE_INT8_ROW, AT, GEMM1>(a, a_scales_t, w, w_scale, expert_ids, sorted_ids, npp, route_weight, mul_weight, numel, rows_cap, a_tokens, topk, block_m, E, K, Nout, out, out_scales_t, status, st, act_kind, alpha, beta, limit);
     default:
       return fail(MOE_E_BADARG, "unknown GEMM mode %d", mode);
   }
@@ -215,17 +253,19 @@ int simt_gemm(bool gemm1, int mode, int act_dtype, const void* a, const float* a
               const void* w, const float* w_scale, const int32_t* expert_ids,
               const int32_t* sorted_ids, const int32_t* npp, const float* route_weight,
               int mul_weight, int64_t numel, int64_t rows_cap, int64_t a_tokens, int topk, int block_m, int E, int K, int Nout,
-              void* out, float* out_scales_t, int32_t* status, cudaStream_t st) {
+              void* out, float* out_scales_t, int32_t* status, cudaStream_t st, int act_kind, float alpha, float beta,
+              float limit) {
   if (block_m % TM != 0) return fail(MOE_E_SHAPE, "generic GEMM: align block must be a multiple of 16");
   if (mode == MOE_MODE_FP8_BLOCK && (K % 128 != 0 || (gemm1 && Nout % 128 != 0)))
     return fail(MOE_E_SHAPE, "generic GEMM: FP8 block mode needs sizes that are multiples of 128");
 #define MOE_SIMT_DISPATCH(G1, T)                                                                    \
   dispatch_mode<G1, T>(mode, a, a_scales_t, w, w_scale, expert_ids, sorted_ids, npp, route_weight, \
-                       mul_weight, numel, rows_cap, a_tokens, topk, block_m, E, K, Nout, out, out_scales_t, status, st)
+                       mul_weight, numel, rows_cap, a_tokens, topk, block_m, E, K, Nout, out, out_scales_t, status, st, \
+                       act_kind, alpha, beta, limit)
   if (act_dtype == MOE_BF16) return gemm1 ? MOE_SIMT_DISPATCH(true, __nv_bfloat16) : MOE_SIMT_DISPATCH(false, __nv_bfloat16);
   if (act_dtype == MOE_F16) return gemm1 ? MOE_SIMT_DISPATCH(true, __half) : MOE_SIMT_DISPATCH(false, __half);
   if (act_dtype == MOE_F32) {
-    if (mode == MOE_MODE_FP8_BLOCK) return fail(MOE_E_DTYPE, "FP8 block mode needs f16/bf16 activations");
+    if (mode != MOE_MODE_HALF && mode != MOE_MODE_W8A16) return fail(MOE_E_DTYPE, "8-bit activation modes need f16/bf16 as the activation dtype");
     return gemm1 ? MOE_SIMT_DISPATCH(true, float) : MOE_SIMT_DISPATCH(false, float);
   }
 #undef MOE_SIMT_DISPATCH

@@ -89,6 +89,37 @@ __global__ void __launch_bounds__(kRowThreads) quant_rows_kernel(
   }
 }
 
+// Any group size, clamp value and 8-bit float format: one warp per group, lanes stride over the
+// group (the 128-wide e4m3 kernel above is the fast case of this one).
+template <typename T, bool UE8M0, bool E5M2>
+__global__ void __launch_bounds__(kRowThreads) quant_rows_generic_kernel(
+    const T* __restrict__ x, int64_t rows, int64_t cols, int group, float eps, uint8_t* __restrict__ q,
+    float* __restrict__ scales, int transposed, int64_t scale_ld) {
+  const int lane = threadIdx.x & 31;
+  const float fmax_q = E5M2 ? 57344.0f : kFp8Max;
+  const int64_t groups_per_row = cols / group;
+  const int64_t total = rows * groups_per_row;
+  const int64_t warp0 = (int64_t)blockIdx.x * (kRowThreads / 32) + (threadIdx.x >> 5);
+  const int64_t stride = (int64_t)gridDim.x * (kRowThreads / 32);
+  for (int64_t w = warp0; w < total; w += stride) {
+    const T* src = x + w * group;  // rows are contiguous: group w starts at w * group
+    float amax = 0.0f;
+    for (int i = lane; i < group; i += 32) amax = fmaxf(amax, fabsf(ToF32<T>::get(src[i])));
+#pragma unroll
+    for (int off = 16; off > 0; off >>= 1) amax = fmaxf(amax, __shfl_xor_sync(0xFFFFFFFFu, amax, off));
+    float s = fmaxf(amax, eps) * (1.0f / fmax_q);
+    if (UE8M0) s = exp2f(ceilf(log2f(fmaxf(fabsf(s), 1e-10f))));
+    for (int i = lane; i < group; i += 32) {
+      const float v = fminf(fmaxf(ToF32<T>::get(src[i]) / s, -fmax_q), fmax_q);
+      q[w * group + i] = E5M2 ? (uint8_t)__nv_cvt_float_to_fp8(v, __NV_SATFINITE, __NV_E5M2) : f32_to_fp8e4m3(v);
+    }
+    if (lane == 0) {
+      const int64_t r = w / groups_per_row, g = w % groups_per_row;
+      *(transposed ? scales + g * scale_ld + r : scales + r * groups_per_row + g) = s;
+    }
+  }
+}
+
 // out[m, h] = sum_j in[m, j, h]; 8 elements (16 B) of 2-byte types per thread.
 template <typename T, typename IdT>
 __global__ void __launch_bounds__(256) moe_sum_kernel(
@@ -206,6 +237,88 @@ __global__ void gather_rows_kernel(const uint4* __restrict__ x, const int32_t* _
   }
 }
 
+// Round-half-even of a value already clamped to [-128, 127]; NaN gives 0 (as the reference kernel,
+// src/flaggems_vllm/ops/fused_moe.py:973-990).
+__device__ __forceinline__ int8_t round_int8_even(float v) {
+  if (!(v == v)) v = 0.0f;
+  v = fminf(fmaxf(v, -128.0f), 127.0f);
+  return (int8_t)__float2int_rn(v);
+}
+
+// One warp per row.  KIND as in moe_rowwise_quant.
+template <typename T, int KIND>
+__global__ void __launch_bounds__(256) rowwise_quant_kernel(const T* __restrict__ x, int64_t rows, int64_t cols,
+                                                            const float* __restrict__ scale_in,
+                                                            const int32_t* __restrict__ row_ids, int64_t valid_below,
+                                                            uint8_t* __restrict__ q, float* __restrict__ scale_out) {
+  const int lane = threadIdx.x & 31;
+  const int64_t warp0 = ((int64_t)blockIdx.x * blockDim.x + threadIdx.x) >> 5;
+  const int64_t warps = ((int64_t)gridDim.x * blockDim.x) >> 5;
+  for (int64_t r = warp0; r < rows; r += warps) {
+    if (row_ids != nullptr) {
+      const int64_t id = row_ids[r];
+      if (id < 0 || id >= valid_below) continue;
+    }
+    const T* src = x + r * cols;
+    float scale;
+    if constexpr (KIND == 0 || KIND == 1) {
+      float amax = 0.0f, nan_term = 0.0f;
+      for (int64_t c = lane; c < cols; c += 32) {
+        const float v = ToF32<T>::get(src[c]);
+        amax = fmaxf(amax, fabsf(v));
+        if (!(v == v)) nan_term = v;
+      }
+#pragma unroll
+      for (int off = 16; off > 0; off >>= 1) {
+        amax = fmaxf(amax, __shfl_xor_sync(0xFFFFFFFFu, amax, off));
+        nan_term += __shfl_xor_sync(0xFFFFFFFFu, nan_term, off);
+      }
+      if constexpr (KIND == 0) {
+        // the clamp constant takes the rounding of the input dtype (1e-10 is zero in f16)
+        const float eps = ToF32<T>::get(from_f32<T>(1e-10f));
+        scale = (fmaxf(amax, eps) + nan_term) * (1.0f / 127.0f);
+      } else {
+        scale = fmaxf(fmaxf(amax, 1e-10f) / kFp8Max, 1.0f / (kFp8Max * 512.0f));
+      }
+      if (lane == 0) scale_out[r] = scale;
+    } else {
+      scale = scale_in[0];
+    }
+    for (int64_t c = lane; c < cols; c += 32) {
+      const float v = ToF32<T>::get(src[c]);
+      uint8_t o;
+      if constexpr (KIND == 0 || KIND == 4) o = (uint8_t)round_int8_even(__fdiv_rn(v, scale));
+      else if constexpr (KIND == 3) o = f32_to_fp8e4m3(fminf(fmaxf(v * (1.0f / scale), -kFp8Max), kFp8Max));
+      else o = f32_to_fp8e4m3(fminf(fmaxf(v / scale, -kFp8Max), kFp8Max));
+      q[r * cols + c] = o;
+    }
+  }
+}
+
+// amax of the rows that count, as the bits of a non-negative float (atomicMax on the bits orders them)
+template <typename T>
+__global__ void __launch_bounds__(256) tensor_amax_kernel(const T* __restrict__ x, int64_t rows, int64_t cols,
+                                                          const int32_t* __restrict__ row_ids, int64_t valid_below,
+                                                          unsigned int* __restrict__ amax_bits) {
+  const int lane = threadIdx.x & 31;
+  const int64_t warp0 = ((int64_t)blockIdx.x * blockDim.x + threadIdx.x) >> 5;
+  const int64_t warps = ((int64_t)gridDim.x * blockDim.x) >> 5;
+  float amax = 0.0f;
+  for (int64_t r = warp0; r < rows; r += warps) {
+    if (row_ids != nullptr) {
+      const int64_t id = row_ids[r];
+      if (id < 0 || id >= valid_below) continue;
+    }
+    for (int64_t c = lane; c < cols; c += 32) amax = fmaxf(amax, fabsf(ToF32<T>::get(x[r * cols + c])));
+  }
+#pragma unroll
+  for (int off = 16; off > 0; off >>= 1) amax = fmaxf(amax, __shfl_xor_sync(0xFFFFFFFFu, amax, off));
+  if (lane == 0 && amax > 0.0f) atomicMax(amax_bits, __float_as_uint(amax));
+}
+__global__ void amax_to_scale_kernel(float* scale) {  // in place: bits of amax -> max(amax, 1e-10) / 448
+  scale[0] = fmaxf(scale[0], 1e-10f) / kFp8Max;
+}
+
 // out_t[g][p] = scales_t[g][sorted_ids[p] / topk] for the occupied slots p < num_post_pad
 __global__ void gather_scales_kernel(const float* __restrict__ scales_t, int groups, int64_t tokens,
                                      const int32_t* __restrict__ sorted_ids, const int32_t* __restrict__ num_post_pad,
@@ -221,6 +334,52 @@ __global__ void gather_scales_kernel(const float* __restrict__ scales_t, int gro
 
 }  // namespace
 }  // namespace moe
+
+template <typename T>
+static int rowwise_quant_launch(const void* x, int64_t rows, int64_t cols, int kind, const float* scale_in,
+                                const int32_t* row_ids, int64_t valid_below, void* q, float* scale_out, cudaStream_t st) {
+  using namespace moe;
+  const int grid = grid_for((rows + 7) / 8, 8);
+#define MOE_RQ(K, SIN) rowwise_quant_kernel<T, K><<<grid, 256, 0, st>>>((const T*)x, rows, cols, SIN, row_ids, valid_below, (uint8_t*)q, scale_out)
+  switch (kind) {
+    case 0: MOE_RQ(0, nullptr); break;
+    case 1: MOE_RQ(1, nullptr); break;
+    case 2: MOE_RQ(2, scale_in); break;
+    case 4: MOE_RQ(4, scale_in); break;
+    case 3: {
+      cudaError_t ce = cudaMemsetAsync(scale_out, 0, sizeof(float), st);
+      if (ce != cudaSuccess) return fail((int)ce, "rowwise_quant: %s", cudaGetErrorString(ce));
+      tensor_amax_kernel<T><<<grid, 256, 0, st>>>((const T*)x, rows, cols, row_ids, valid_below, (unsigned int*)scale_out);
+      amax_to_scale_kernel<<<1, 1, 0, st>>>(scale_out);
+      MOE_RQ(3, scale_out);
+      break;
+    }
+    default: return fail(MOE_E_BADARG, "rowwise_quant: unknown kind %d", kind);
+  }
+#undef MOE_RQ
+  return check_launch("rowwise_quant");
+}
+
+extern "C" int moe_rowwise_quant(const void* x, int x_dtype, int64_t rows, int64_t cols, int kind, const float* scale_in,
+                                 const int32_t* row_ids, int64_t valid_below, void* q, float* scale_out, void* stream) {
+  using namespace moe;
+  if (rows < 0 || cols <= 0) return fail(MOE_E_BADARG, "rowwise_quant: bad extent");
+  if (rows == 0) return 0;
+  if (!x || !q) return fail(MOE_E_BADARG, "rowwise_quant: null pointer");
+  if ((kind == 2 || kind == 4) && !scale_in) return fail(MOE_E_BADARG, "rowwise_quant: static scale missing");
+  if ((kind == 0 || kind == 1 || kind == 3) && !scale_out) return fail(MOE_E_BADARG, "rowwise_quant: scale output missing");
+  cudaStream_t st = (cudaStream_t)stream;
+  if ((kind == 2 || kind == 4) && scale_out && scale_out != scale_in) {
+    cudaError_t ce = cudaMemcpyAsync(scale_out, scale_in, sizeof(float), cudaMemcpyDeviceToDevice, st);
+    if (ce != cudaSuccess) return fail((int)ce, "rowwise_quant: %s", cudaGetErrorString(ce));
+  }
+  switch (x_dtype) {
+    case MOE_F32: return rowwise_quant_launch<float>(x, rows, cols, kind, scale_in, row_ids, valid_below, q, scale_out, st);
+    case MOE_F16: return rowwise_quant_launch<__half>(x, rows, cols, kind, scale_in, row_ids, valid_below, q, scale_out, st);
+    case MOE_BF16: return rowwise_quant_launch<__nv_bfloat16>(x, rows, cols, kind, scale_in, row_ids, valid_below, q, scale_out, st);
+    default: return fail(MOE_E_DTYPE, "rowwise_quant: unsupported dtype %d", x_dtype);
+  }
+}
 
 extern "C" int moe_gather_scales_t(const float* scales_t, int groups, int64_t num_tokens, int topk,
                                    const int32_t* sorted_ids, const int32_t* num_post_pad, int64_t rows_cap,
@@ -251,12 +410,40 @@ extern "C" int moe_gather_rows(const void* x, int64_t num_tokens, int topk, int6
   return check_launch("gather_rows");
 }
 
+extern "C" int moe_per_token_group_quant_fp8_ex(const void* x, int x_dtype, int64_t rows, int64_t cols, int group,
+                                                float eps, int e5m2, void* q, float* scales, int scales_transposed,
+                                                int64_t scale_ld, void* stream) {
+  using namespace moe;
+  if (rows < 0 || cols <= 0 || group <= 0) return fail(MOE_E_BADARG, "quant_fp8: bad extent");
+  if (cols % group != 0) return fail(MOE_E_SHAPE, "quant_fp8: cols must be a multiple of the group size %d", group);
+  if (!(eps >= 0.0f)) return fail(MOE_E_BADARG, "quant_fp8: eps must be non-negative");
+  if (rows == 0) return 0;
+  if (!x || !q || !scales) return fail(MOE_E_BADARG, "quant_fp8: null pointer");
+  cudaStream_t st = (cudaStream_t)stream;
+  const int grid = grid_for((rows * (cols / group) + 7) / 8, 8);
+  const int transposed = scales_transposed & 1;
+  const bool ue8m0 = (scales_transposed & 2) != 0;
+#define MOE_QG(T, U, F) quant_rows_generic_kernel<T, U, F><<<grid, kRowThreads, 0, st>>>((const T*)x, rows, cols, group, eps, (uint8_t*)q, scales, transposed, scale_ld)
+#define MOE_QG_T(T) (ue8m0 ? (e5m2 ? MOE_QG(T, true, true) : MOE_QG(T, true, false)) : (e5m2 ? MOE_QG(T, false, true) : MOE_QG(T, false, false)))
+  switch (x_dtype) {
+    case MOE_F32: MOE_QG_T(float); break;
+    case MOE_F16: MOE_QG_T(__half); break;
+    case MOE_BF16: MOE_QG_T(__nv_bfloat16); break;
+    default: return fail(MOE_E_DTYPE, "quant_fp8: unsupported dtype %d", x_dtype);
+  }
+#undef MOE_QG_T
+#undef MOE_QG
+  return check_launch("per_token_group_quant_fp8");
+}
+
 extern "C" int moe_per_token_group_quant_fp8(const void* x, int x_dtype, int64_t rows, int64_t cols,
                                              int group, void* q, float* scales,
                                              int scales_transposed, int64_t scale_ld, void* stream) {
   using namespace moe;
   if (rows < 0 || cols <= 0) return fail(MOE_E_BADARG, "quant_fp8: bad extent");
-  if (group != 128) return fail(MOE_E_SHAPE, "quant_fp8: group size must be 128 (got %d)", group);
+  if (group != 128)  // other group sizes: the general kernel with the default clamp
+    return moe_per_token_group_quant_fp8_ex(x, x_dtype, rows, cols, group, kQuantEps, 0, q, scales, scales_transposed,
+                                            scale_ld, stream);
   if (cols % 128 != 0) return fail(MOE_E_SHAPE, "quant_fp8: cols must be a multiple of 128");
   if (rows == 0) return 0;
   if (!x || !q || !scales) return fail(MOE_E_BADARG, "quant_fp8: null pointer");

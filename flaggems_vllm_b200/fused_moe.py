@@ -119,11 +119,21 @@ def _check_activation(activation, gemm1_alpha, gemm1_beta, gemm1_clamp_limit):
     if activation not in _ALL_ACTIVATIONS:
         raise ValueError(f"Unknown MoE activation: {activation!r}. Valid activations: {list(_ALL_ACTIVATIONS)}")
     if activation == "swigluoai_uninterleave":
-        raise NotImplementedError("activation 'swigluoai_uninterleave' is not implemented by the B200 kernels")
+        # the reference's parameter checks (src/flaggems_vllm/ops/fused_moe.py:688-730): finite scalars, limit >= 0
+        vals = []
+        for name, value in (("gemm1_alpha", gemm1_alpha), ("gemm1_beta", gemm1_beta),
+                            ("gemm1_clamp_limit", gemm1_clamp_limit)):
+            if value is None or isinstance(value, bool) or not isinstance(value, (int, float)) \
+                    or value != value or value in (float("inf"), float("-inf")):
+                raise ValueError(f"swigluoai_uninterleave requires a finite scalar {name}, got {value!r}")
+            vals.append(float(value))
+        if vals[2] < 0:
+            raise ValueError("swigluoai_uninterleave requires gemm1_clamp_limit >= 0")
+        return (_lib.ACT_SWIGLUOAI, vals[0], vals[1], vals[2])
     if activation == "silu":
         if any(v is not None for v in (gemm1_alpha, gemm1_beta, gemm1_clamp_limit)):
             raise ValueError("gemm1_alpha/beta/clamp_limit require swigluoai_uninterleave")
-        return
+        return (_lib.ACT_SILU, 0.0, 0.0, 0.0)
     raise ValueError(
         f"Only 'silu' and 'swigluoai_uninterleave' activations are supported, got {activation!r}")
 
@@ -268,13 +278,15 @@ def quantize_rows(x, mark=None):
 
 def route_pipeline(a_rows, a_scales_t, w1, w2, route_weight, topk_ids, *, mode, act_dtype, w1_scale, w2_scale,
                    global_num_experts, expert_map, apply_router_weight_on_input, use_tensor_cores=None,
-                   keep=None, mark=None):
+                   keep=None, mark=None, act_fn=(0, 0.0, 0.0, 0.0), row_quant=None):
     """align -> GEMM1 -> GEMM2 for ``a_rows`` [tokens, H] (activation dtype, or
     e4m3 with ``a_scales_t`` [H/128, tokens] in FP8 mode) and ``topk_ids``
     [tokens, k].  Returns y [tokens * k, H] in ``act_dtype``: row = flat route
     index, already multiplied by the route weight (unless the weight was
     applied on the input).  Rows of routes whose expert is not local are left
-    unwritten."""
+    unwritten.  ``act_fn`` = (activation code, alpha, beta, limit).  Row-scaled W8A8 modes:
+    ``a_rows`` is e4m3 / int8 with ``a_scales_t`` [tokens]; ``row_quant`` = (kind, static scale or
+    None) says how the intermediate is quantised between the two GEMMs."""
     if mark is None:
         mark = STAGE_HOOK or _no_mark
     L = _lib.lib()
@@ -289,6 +301,9 @@ def route_pipeline(a_rows, a_scales_t, w1, w2, route_weight, topk_ids, *, mode, 
     act_code = _lib.dtype_code(act_dtype)
     if use_tensor_cores is None:
         kernel = _choose_kernel(mode, act_dtype, H, I, numel, global_num_experts)
+        if act_fn[0] != _lib.ACT_SILU or mode in (_lib.MODE_FP8_ROW, _lib.MODE_INT8_ROW):
+            # activations other than SiLU and the row-scaled W8A8 modes run on the generic kernel
+            kernel = KERNEL_GENERIC
     else:
         kernel = int(use_tensor_cores)
     block_m = {KERNEL_GENERIC: GENERIC_BLOCK_M, KERNEL_TC: TC_BLOCK_M, KERNEL_TC_PAIR: TC_PAIR_BLOCK_M,
@@ -310,6 +325,7 @@ def route_pipeline(a_rows, a_scales_t, w1, w2, route_weight, topk_ids, *, mode, 
         expert_ids = expert_map[expert_ids.long()].to(torch.int32)
 
     fp8 = mode == _lib.MODE_FP8_BLOCK
+    row_scaled = mode in (_lib.MODE_FP8_ROW, _lib.MODE_INT8_ROW)
     if fp8:
         act = torch.empty((rows_cap, I), dtype=torch.float8_e4m3fn, device=dev)
         act_scales = torch.empty((I // 128, rows_cap), dtype=torch.float32, device=dev)
@@ -333,13 +349,28 @@ def route_pipeline(a_rows, a_scales_t, w1, w2, route_weight, topk_ids, *, mode, 
             a_scales_in = sc_in
         a_sorted = 1
         mark("gather")
-    _lib.check(L.moe_gemm1(mode, act_code, a_in.data_ptr(), a_sorted, _lib.ptr(a_scales_in), M, k, w1.data_ptr(),
-                           _lib.ptr(w1_scale), expert_ids.data_ptr(), sorted_ids.data_ptr(), npp.data_ptr(),
-                           rw.data_ptr(), int(apply_router_weight_on_input), rows_cap, block_m, E_local, H, I,
-                           act.data_ptr(), _lib.ptr(act_scales), tc, status.data_ptr(), st))
+    _lib.check(L.moe_gemm1_ex(mode, act_code, a_in.data_ptr(), a_sorted, _lib.ptr(a_scales_in), M, k, w1.data_ptr(),
+                              _lib.ptr(w1_scale), expert_ids.data_ptr(), sorted_ids.data_ptr(), npp.data_ptr(),
+                              rw.data_ptr(), int(apply_router_weight_on_input), rows_cap, block_m, E_local, H, I,
+                              act.data_ptr(), _lib.ptr(act_scales), tc, act_fn[0], act_fn[1], act_fn[2], act_fn[3],
+                              status.data_ptr(), st))
     mark("gemm1")
+    act_in = act
+    if row_scaled:
+        # quantise the intermediate (sorted rows) the way the mode says: one scale per row, or one for
+        # the whole tensor (dynamic: over the occupied rows only; padding rows hold stale bytes)
+        kind, static = row_quant
+        act_in = torch.empty((rows_cap, I), dtype=torch.int8 if mode == _lib.MODE_INT8_ROW else torch.float8_e4m3fn,
+                             device=dev)
+        per_row = kind in (0, 1)
+        sc = torch.empty(rows_cap if per_row else 1, dtype=torch.float32, device=dev)
+        _lib.check(L.moe_rowwise_quant(act.data_ptr(), act_code, rows_cap, I, kind, _lib.ptr(static),
+                                       sorted_ids.data_ptr() if kind == 3 else None, numel, act_in.data_ptr(),
+                                       sc.data_ptr(), st))
+        act_scales = sc if per_row else sc.expand(rows_cap).contiguous()
+        mark("quant2")
     y = torch.empty((numel, H), dtype=act_dtype, device=dev)
-    _lib.check(L.moe_gemm2(mode, act_code, act.data_ptr(), _lib.ptr(act_scales), w2.data_ptr(), _lib.ptr(w2_scale),
+    _lib.check(L.moe_gemm2(mode, act_code, act_in.data_ptr(), _lib.ptr(act_scales), w2.data_ptr(), _lib.ptr(w2_scale),
                            expert_ids.data_ptr(), sorted_ids.data_ptr(), npp.data_ptr(), rw.data_ptr(),
                            int(not apply_router_weight_on_input), numel, rows_cap, block_m, E_local, H, I,
                            y.data_ptr(), tc, status.data_ptr(), st))
@@ -377,29 +408,44 @@ def combine_routes(y, out, topk_ids, global_num_experts, expert_map=None, row_in
 
 
 def run_chunk(x, w1, w2, topk_weights, topk_ids, out, *, mode, w1_scale, w2_scale, global_num_experts,
-              expert_map, apply_router_weight_on_input, use_tensor_cores=None, keep=None, mark=None):
+              expert_map, apply_router_weight_on_input, use_tensor_cores=None, keep=None, mark=None,
+              act_fn=(0, 0.0, 0.0, 0.0), row_quant=None):
     """One chunk of the layer.  ``keep`` (a dict) receives the intermediates for
     tests; ``mark(name)`` is called after each stage has been enqueued (bench.py
     records CUDA events there)."""
     if mark is None:
         mark = STAGE_HOOK or _no_mark
     # (half-precision weights with per-channel scales -- the widened int8 experiment -- stay on the tile kernels)
-    if use_tensor_cores is None and not (mode == _lib.MODE_HALF and w1_scale is not None) and _use_small_path(
+    if use_tensor_cores is None and act_fn[0] == _lib.ACT_SILU and not (
+            mode == _lib.MODE_HALF and w1_scale is not None) and _use_small_path(
             mode, x.dtype, x.shape[1], w1.shape[1] // 2, x.shape[0] * topk_ids.shape[1], topk_ids.shape[1]):
         run_chunk_small(x, w1, w2, topk_weights, topk_ids, out, mode=mode, w1_scale=w1_scale, w2_scale=w2_scale,
                         global_num_experts=global_num_experts, expert_map=expert_map,
                         apply_router_weight_on_input=apply_router_weight_on_input, keep=keep, mark=mark)
         return
+    row_quant2 = None
     if mode == _lib.MODE_FP8_BLOCK:
         # activations are quantised once per token; the GEMM gathers rows by token
         a_rows, a_scales = quantize_rows(x)
+    elif mode in (_lib.MODE_FP8_ROW, _lib.MODE_INT8_ROW):
+        # row_quant = ((kind, static scale) of the input, (kind, static scale) of the intermediate)
+        (kind, static), row_quant2 = row_quant
+        M = x.shape[0]
+        a_rows = torch.empty(x.shape, dtype=torch.int8 if mode == _lib.MODE_INT8_ROW else torch.float8_e4m3fn,
+                             device=x.device)
+        per_row = kind in (0, 1)
+        sc = torch.empty(M if per_row else 1, dtype=torch.float32, device=x.device)
+        _lib.check(_lib.lib().moe_rowwise_quant(x.data_ptr(), _lib.dtype_code(x.dtype), M, x.shape[1], kind,
+                                                _lib.ptr(static), None, 0, a_rows.data_ptr(), sc.data_ptr(),
+                                                _lib.stream_of(x)))
+        a_scales = sc if per_row else sc.expand(M).contiguous()
     else:
         a_rows, a_scales = x, None
     mark("quant")
     y = route_pipeline(a_rows, a_scales, w1, w2, topk_weights, topk_ids, mode=mode, act_dtype=x.dtype,
                        w1_scale=w1_scale, w2_scale=w2_scale, global_num_experts=global_num_experts,
                        expert_map=expert_map, apply_router_weight_on_input=apply_router_weight_on_input,
-                       use_tensor_cores=use_tensor_cores, keep=keep, mark=mark)
+                       use_tensor_cores=use_tensor_cores, keep=keep, mark=mark, act_fn=act_fn, row_quant=row_quant2)
     combine_routes(y, out, topk_ids, global_num_experts, expert_map)
     mark("sum")
 
@@ -436,7 +482,7 @@ def fused_experts_impl(
     gemm1_clamp_limit: float | None = None,
 ) -> torch.Tensor:
     logger.debug("GEMS FUSED MOE")
-    _check_activation(activation, gemm1_alpha, gemm1_beta, gemm1_clamp_limit)
+    act = _check_activation(activation, gemm1_alpha, gemm1_beta, gemm1_clamp_limit)
 
     if ocp_mx_scheme is not None:
         if not (ocp_mx_scheme.startswith("w_mxfp4") or ocp_mx_scheme.startswith("w_mxfp6")):
@@ -449,14 +495,10 @@ def fused_experts_impl(
     assert w2.stride(-1) == 1, "Stride of last dimension must be 1"
     assert hidden_states.dtype in [torch.float32, torch.float16, torch.bfloat16]
 
-    if use_int8_w8a8:
-        raise NotImplementedError("INT8 W8A8 is not implemented by the B200 kernels")
     if w1_zp is not None or w2_zp is not None:
         raise NotImplementedError("zero points are not implemented by the B200 kernels")
     if w1_bias is not None or w2_bias is not None:
         raise NotImplementedError("expert biases are not implemented by the B200 kernels")
-    if a1_scale is not None or a2_scale is not None:
-        raise NotImplementedError("static activation scales are not implemented by the B200 kernels")
 
     num_tokens = hidden_states.size(0)
     E, N, _ = w1.size()
@@ -466,11 +508,14 @@ def fused_experts_impl(
     if global_num_experts == -1:
         global_num_experts = E
 
-    if use_fp8_w8a8:
-        if block_shape is None or list(block_shape) != [128, 128]:
-            raise NotImplementedError("FP8 W8A8 is implemented for block_shape=[128, 128] only")
+    row_quant = None
+    if use_fp8_w8a8 and block_shape is not None:
+        if list(block_shape) != [128, 128]:
+            raise NotImplementedError("FP8 block quantisation is implemented for block_shape=[128, 128] only")
         if per_channel_quant:
-            raise NotImplementedError("per-token FP8 activation scales are not implemented")
+            raise NotImplementedError("per-token activation scales cannot be combined with block_shape")
+        if a1_scale is not None or a2_scale is not None:
+            raise NotImplementedError("static activation scales are not used with block_shape")
         assert w1.dtype == torch.float8_e4m3fn and w2.dtype == torch.float8_e4m3fn, "FP8 weights expected"
         assert w1_scale is not None and w2_scale is not None, "FP8 block scales expected"
         assert hidden_states.dtype != torch.float32, "FP8 path needs f16/bf16 activations"
@@ -478,6 +523,27 @@ def fused_experts_impl(
         assert tuple(w1_scale.shape) == (E, ceil_div(N, 128), K // 128), "w1_scale shape"
         assert tuple(w2_scale.shape) == (E, K // 128, (N // 2) // 128), "w2_scale shape"
         mode = _lib.MODE_FP8_BLOCK
+    elif use_fp8_w8a8 or use_int8_w8a8:
+        # per-tensor or per-token/per-channel W8A8 (src/flaggems_vllm/ops/fused_moe.py:853-1010): the scales
+        # multiply the finished dot products
+        if use_int8_w8a8 and block_shape is not None:
+            raise NotImplementedError("block-quantised INT8 W8A8 is not implemented")
+        wdt = torch.float8_e4m3fn if use_fp8_w8a8 else torch.int8
+        assert w1.dtype == wdt and w2.dtype == wdt, f"{wdt} weights expected"
+        assert w1_scale is not None and w2_scale is not None, "weight scales expected"
+        assert hidden_states.dtype != torch.float32, "W8A8 paths need f16/bf16 activations"
+        mode = _lib.MODE_FP8_ROW if use_fp8_w8a8 else _lib.MODE_INT8_ROW
+        if per_channel_quant:
+            kinds = (1, 1) if use_fp8_w8a8 else (0, 0)
+            statics = (None, None)
+        elif use_fp8_w8a8:
+            kinds = (2 if a1_scale is not None else 3, 2 if a2_scale is not None else 3)
+            statics = (a1_scale, a2_scale)
+        else:
+            assert a1_scale is not None and a2_scale is not None, "int8 per-tensor requires A_scale"
+            kinds, statics = (4, 4), (a1_scale, a2_scale)
+        statics = tuple(None if t is None else t.to(torch.float32).reshape(-1)[:1].contiguous() for t in statics)
+        row_quant = ((kinds[0], statics[0]), (kinds[1], statics[1]))
     elif use_int8_w8a16 or use_int4_w4a16:
         if block_shape is not None and len(block_shape) == 2 and block_shape[1] > 0:
             raise NotImplementedError("group-quantised weight-only formats are not implemented")
@@ -494,7 +560,15 @@ def fused_experts_impl(
     w1c = w1 if w1.is_contiguous() else w1.contiguous()
     w2c = w2 if w2.is_contiguous() else w2.contiguous()
     s1 = s2 = None
-    if mode != _lib.MODE_HALF:
+    if mode in (_lib.MODE_FP8_ROW, _lib.MODE_INT8_ROW):
+        # one scale per output channel; a per-tensor scale ([E], [E, 1] or [E, 1, 1]) is that vector filled
+        def per_channel(ws, rows):
+            ws = ws.to(torch.float32).reshape(E, -1)
+            assert ws.shape[1] in (1, rows), "weight scales must be per tensor or per output channel"
+            return ws.expand(E, rows).contiguous()
+
+        s1, s2 = per_channel(w1_scale, N), per_channel(w2_scale, K)
+    elif mode != _lib.MODE_HALF:
         s1 = w1_scale.to(torch.float32).contiguous()
         s2 = w2_scale.to(torch.float32).contiguous()
 
@@ -514,7 +588,7 @@ def fused_experts_impl(
         run_chunk(hidden_states[begin:end], w1c, w2c, topk_weights[begin:end], topk_ids[begin:end],
                   out_hidden_states[begin:end], mode=mode, w1_scale=s1, w2_scale=s2,
                   global_num_experts=global_num_experts, expert_map=expert_map,
-                  apply_router_weight_on_input=apply_router_weight_on_input)
+                  apply_router_weight_on_input=apply_router_weight_on_input, act_fn=act, row_quant=row_quant)
     if os.environ.get("FLAGGEMS_B200_CHECK_STATUS", "0") == "1":
         # debugging aid (one device synchronisation per call): a kernel that gave up on a wait or met
         # corrupt routing data leaves the output undefined; say so instead of returning it

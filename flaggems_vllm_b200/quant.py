@@ -36,26 +36,31 @@ def per_token_group_quant_fp8(
     )
     assert x.stride(-1) == 1, "`x` groups must be contiguous"
     _lib.require_cuda(x, "per_token_group_quant_fp8")
-    if fp8_dtype != torch.float8_e4m3fn:
-        raise NotImplementedError("only float8_e4m3fn output is implemented")
-    if group_size != 128:
-        raise NotImplementedError("only group_size=128 is implemented")
-    if abs(eps - 1e-10) > 1e-16:
-        raise NotImplementedError("only eps=1e-10 is implemented")
+    if fp8_dtype not in (torch.float8_e4m3fn, torch.float8_e5m2):
+        raise NotImplementedError(f"8-bit float format {fp8_dtype} is not implemented (e4m3fn and e5m2 are)")
     xc = x if x.is_contiguous() else x.contiguous()
     cols = xc.shape[-1]
     rows = xc.numel() // cols if cols else 0
     x_q = torch.empty(xc.shape, device=x.device, dtype=fp8_dtype)
     groups = cols // group_size
+    lead = rows
     if column_major_scales:
-        x_s = torch.empty((groups,) + tuple(xc.shape[:-1]), device=x.device, dtype=torch.float32)
         if xc.ndim != 2:
-            raise NotImplementedError("column-major scales need a 2-D input")
+            raise ValueError("column-major scales need a 2-D input (the reference's (-1, -2) permutation of a "
+                             "[groups, rows] buffer)")
+        # the reference lays the scales out as [groups, *leading dims] and returns the (-1, -2) permutation
+        x_s = torch.empty((groups,) + tuple(xc.shape[:-1]), device=x.device, dtype=torch.float32)
     else:
         x_s = torch.empty(tuple(xc.shape[:-1]) + (groups,), device=x.device, dtype=torch.float32)
-    rc = _lib.lib().moe_per_token_group_quant_fp8(
-        xc.data_ptr(), _lib.dtype_code(xc.dtype), rows, cols, group_size, x_q.data_ptr(), x_s.data_ptr(),
-        int(column_major_scales) | (2 if scale_ue8m0 else 0), rows, _lib.stream_of(x))
+    flags = int(column_major_scales) | (2 if scale_ue8m0 else 0)
+    if group_size == 128 and fp8_dtype == torch.float8_e4m3fn and abs(eps - 1e-10) <= 1e-16:
+        rc = _lib.lib().moe_per_token_group_quant_fp8(
+            xc.data_ptr(), _lib.dtype_code(xc.dtype), rows, cols, group_size, x_q.data_ptr(), x_s.data_ptr(), flags,
+            lead, _lib.stream_of(x))
+    else:
+        rc = _lib.lib().moe_per_token_group_quant_fp8_ex(
+            xc.data_ptr(), _lib.dtype_code(xc.dtype), rows, cols, group_size, float(eps),
+            int(fp8_dtype == torch.float8_e5m2), x_q.data_ptr(), x_s.data_ptr(), flags, lead, _lib.stream_of(x))
     _lib.check(rc)
     if column_major_scales:
         x_s = x_s.permute(-1, -2)

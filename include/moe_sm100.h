@@ -46,7 +46,16 @@ enum {
 };
 
 /* GEMM modes (moe_gemm*_ entry points) */
-enum { MOE_MODE_HALF = 0, MOE_MODE_FP8_BLOCK = 1, MOE_MODE_W8A16 = 2 };
+enum {
+  MOE_MODE_HALF = 0,
+  MOE_MODE_FP8_BLOCK = 1,
+  MOE_MODE_W8A16 = 2,
+  MOE_MODE_FP8_ROW = 3,  /* e4m3 activations with one fp32 scale per row, e4m3 weights with one per output channel */
+  MOE_MODE_INT8_ROW = 4  /* int8 activations with one fp32 scale per row, int8 weights with one per output channel */
+};
+
+/* GEMM 1 activations */
+enum { MOE_ACT_SILU = 0, MOE_ACT_SWIGLUOAI = 1 };
 
 int moe_abi_version(void);
 const char* moe_last_error(void);
@@ -120,6 +129,14 @@ int moe_align_block_size(const void* topk_ids, int ids_int64, int64_t numel, int
 int moe_per_token_group_quant_fp8(const void* x, int x_dtype, int64_t rows, int64_t cols, int group,
                                   void* q, float* scales, int scales_transposed, int64_t scale_ld,
                                   void* stream);
+/*
+ * The same quantiser with every option of the reference function: any group size that divides
+ * cols, the amax clamp `eps`, and e5m2 output (e5m2 = 1; clamp range +-57344) besides e4m3.
+ * moe_per_token_group_quant_fp8 is this call with eps = 1e-10 and e4m3.
+ */
+int moe_per_token_group_quant_fp8_ex(const void* x, int x_dtype, int64_t rows, int64_t cols, int group, float eps,
+                                     int e5m2, void* q, float* scales, int scales_transposed, int64_t scale_ld,
+                                     void* stream);
 
 /*
  * Exact widening of int8 weights to f16/bf16 (n elements, n % 16 == 0).  The
@@ -199,6 +216,39 @@ int moe_gemm1(int mode, int act_dtype, const void* a, int a_sorted, const float*
               const int32_t* sorted_ids, const int32_t* num_post_pad, const float* route_weight,
               int mul_weight, int64_t rows_cap, int block_m, int E, int H, int I, void* out,
               float* out_scales_t, int use_tensor_cores, int32_t* status, void* stream);
+
+/*
+ * moe_gemm1 with the activation spelled out: MOE_ACT_SILU, or MOE_ACT_SWIGLUOAI
+ * (min(gate, limit) * sigmoid(alpha * gate) * (clamp(up, -limit, limit) + beta) on the gate | up halves,
+ * src/flaggems_vllm/ops/fused_moe.py:733-773).  The row-scaled modes MOE_MODE_FP8_ROW / MOE_MODE_INT8_ROW
+ * (per-tensor and per-token W8A8, src/flaggems_vllm/ops/fused_moe.py:853-1010, scales applied to the
+ * finished dot product as in :1894-1925) and every activation other than SiLU are served by the
+ * generic kernel (use_tensor_cores = 0): a [num_tokens, H] in e4m3 / int8, a_scales_t [num_tokens]
+ * (one per row), w1_scale [E, 2I]; the intermediate is written in the activation dtype, unquantised.
+ * In moe_gemm2 the same modes take act_scales_t [rows_cap] and w2_scale [E, H].
+ */
+int moe_gemm1_ex(int mode, int act_dtype, const void* a, int a_sorted, const float* a_scales_t, int64_t num_tokens,
+                 int topk, const void* w1, const float* w1_scale, const int32_t* expert_ids,
+                 const int32_t* sorted_ids, const int32_t* num_post_pad, const float* route_weight,
+                 int mul_weight, int64_t rows_cap, int block_m, int E, int H, int I, void* out,
+                 float* out_scales_t, int use_tensor_cores, int activation, float alpha, float beta, float limit,
+                 int32_t* status, void* stream);
+
+/*
+ * Row-wise activation quantisers of the W8A8 modes (moe_kernel_quantize_input,
+ * src/flaggems_vllm/ops/fused_moe.py:1196-1220).  kind:
+ *   0  int8, one dynamic scale per row: amax clamped at 1e-10 in the input dtype, scale = amax * (1/127),
+ *      q = round-half-even(x / scale) in [-128, 127]            (:994-1010)
+ *   1  e4m3, one dynamic scale per row: max(amax, 1e-10) / 448, at least 1 / (448 * 512)   (:899-911)
+ *   2  e4m3, static per-tensor scale scale_in[0]: q = clamp(x / scale)                      (:913-917)
+ *   3  e4m3, dynamic per-tensor scale: amax of the whole tensor / 448, q = clamp(x * (1 / scale)); rows whose
+ *      row_ids entry is outside [0, valid_below) are skipped when row_ids is given            (:918-922)
+ *   4  int8, static per-tensor scale scale_in[0]: q = round-half-even(x / scale)             (:966-969)
+ * x [rows, cols] F32/F16/BF16 contiguous, q [rows, cols] bytes, scale_out [rows] (kinds 0, 1) or [1]
+ * (kind 3; kinds 2 and 4 copy scale_in[0] to scale_out[0] when scale_out is given).
+ */
+int moe_rowwise_quant(const void* x, int x_dtype, int64_t rows, int64_t cols, int kind, const float* scale_in,
+                      const int32_t* row_ids, int64_t valid_below, void* q, float* scale_out, void* stream);
 
 /*
  * Expert grouped GEMM 2: y[sorted_ids[p], :] = (act[p] W2[e]^T) * route_weight.

@@ -322,7 +322,7 @@ def _expert_rows(topk_ids: torch.Tensor, e: int):
 
 
 def fused_moe_half_oracle(hidden, w1, w2, topk_weights, topk_ids, *,
-                          faithful: bool = False, apply_router_weight_on_input: bool = False):
+                          faithful: bool = False, apply_router_weight_on_input: bool = False, act_fn=None):
     """bf16/fp16 layer with fp32 math (tests/test_fused_experts_impl.py:149-191):
     ``out[m] = sum_j w[m,j] * W2[e] (SiLU(G) * U)``, ``[G;U] = W1[e] x[m]``.
 
@@ -349,8 +349,9 @@ def fused_moe_half_oracle(hidden, w1, w2, topk_weights, topk_ids, *,
             z = (xin @ w1[e].cpu().float().t()) * wts[rows, None]
         else:
             z = xin @ w1[e].cpu().float().t()
-        s = _silu_mul(z)
-        if faithful:
+        # an unfused activation (``act_fn``) reads GEMM 1's output after it was stored in the activation dtype
+        s = _silu_mul(z) if act_fn is None else act_fn(z.to(dt))
+        if faithful or act_fn is not None:
             s = s.to(dt).float()
         r = s @ w2[e].cpu().float().t()
         if not apply_router_weight_on_input:
@@ -426,6 +427,99 @@ def fused_moe_w8a16_oracle(hidden, w1_i8, w2_i8, w1_s, w2_s, topk_weights, topk_
         w2d = w2_i8[e].cpu().float() * w2_s[e].cpu().float().unsqueeze(-1)
         s = _silu_mul(x[tok] @ w1d.t())
         per_route[rows] = (s @ w2d.t()) * wts[rows, None]
+    return per_route.view(M, k, H).sum(dim=1)
+
+
+def int8_per_token_quant_oracle(x: torch.Tensor):
+    """Per-row dynamic INT8 quantisation (tests/test_fused_moe.py:22-25, ``literal_quant``; kernel
+    src/flaggems_vllm/ops/fused_moe.py:994-1010): amax clamped at 1e-10 IN THE INPUT DTYPE, scale =
+    amax * fp32(1/127) as the kernel forms it (the literal divides by 127: the same value except
+    for one ulp on rare rows), q = round-half-even(x / scale) clamped to [-128, 127]."""
+    x = x.detach().cpu()
+    amax = x.abs().amax(-1, keepdim=True).clamp(min=1e-10).float()
+    scale = amax * torch.tensor(1.0 / 127.0, dtype=torch.float32)
+    q = (x.float() / scale).round().clamp(-128, 127)
+    q = torch.where(torch.isnan(q), torch.zeros_like(q), q).to(torch.int8)
+    return q, scale
+
+
+def fp8_per_token_quant_oracle(x: torch.Tensor):
+    """Per-row dynamic e4m3 quantisation (src/flaggems_vllm/ops/fused_moe.py:899-911)."""
+    x = x.detach().cpu()
+    amax = x.abs().amax(-1, keepdim=True).clamp(min=1e-10).float()
+    scale = (amax / FP8_MAX).clamp(min=1.0 / (FP8_MAX * 512.0))
+    q = (x.float() / scale).clamp(-FP8_MAX, FP8_MAX).to(FP8)
+    return q, scale
+
+
+def fp8_per_tensor_quant_oracle(x: torch.Tensor, scale: torch.Tensor | None = None):
+    """Per-tensor e4m3 quantisation, static (``scale`` given: x / scale) or dynamic (amax / 448,
+    multiplied by the reciprocal) -- src/flaggems_vllm/ops/fused_moe.py:913-922."""
+    x = x.detach().cpu()
+    if scale is not None:
+        sc = scale.detach().cpu().float().reshape(1, 1)
+        return (x.float() / sc).clamp(-FP8_MAX, FP8_MAX).to(FP8), sc.reshape(1)
+    amax = x.abs().amax().clamp(min=1e-10).float()
+    sc = amax / FP8_MAX
+    q = (x.float() * (1.0 / sc)).clamp(-FP8_MAX, FP8_MAX).to(FP8)
+    return q, sc.reshape(1)
+
+
+def swigluoai_oracle(z: torch.Tensor, alpha: float = 1.702, beta: float = 1.0, limit: float = 7.0) -> torch.Tensor:
+    """gate|up halves: min(gate, limit) * sigmoid(alpha * gate) * (clamp(up, -limit, limit) + beta), fp32
+    (tests/test_fused_moe.py:15-19 ``literal_oai``; kernel src/flaggems_vllm/ops/fused_moe.py:733-773)."""
+    gate, up = z.float().chunk(2, dim=-1)
+    gate = gate.clamp(max=limit)
+    up = up.clamp(-limit, limit)
+    return gate * torch.sigmoid(alpha * gate) * (up + beta)
+
+
+def fused_moe_row_scaled_oracle(hidden, w1_q, w2_q, w1_s, w2_s, topk_weights, topk_ids, *, fmt: str,
+                                per_token: bool = True, a1_scale=None, a2_scale=None, activation: str = "silu",
+                                alpha: float = 1.702, beta: float = 1.0, limit: float = 7.0):
+    """W8A8 layers whose scales multiply the finished dot product: INT8 (``fmt="int8"``) or e4m3
+    (``fmt="fp8"``) activations with one scale per row (``per_token``) or per tensor, weights with one
+    scale per output channel ``[E, N]`` (a per-tensor weight scale is that vector filled with one
+    value).  Restates the literal loop of tests/test_fused_moe.py:143-160 per expert:
+    ``up = (qx @ W1^T) * sx * s1`` rounded to the activation dtype, activation in fp32 rounded to the
+    activation dtype, re-quantised, ``down = (qa @ W2^T) * sa * s2``, times the route weight, rounded to
+    the activation dtype, summed over the routes in fp32."""
+    hidden = hidden.detach().cpu()
+    dt = hidden.dtype
+    M, H = hidden.shape
+    k = topk_ids.shape[1]
+    ids = topk_ids.cpu().long()
+    wts = topk_weights.cpu().float().reshape(-1)
+
+    def quant(t, static):
+        if fmt == "int8":
+            if per_token:
+                return int8_per_token_quant_oracle(t)
+            sc = static.detach().cpu().float().reshape(1, 1)
+            return (t.float() / sc).round().clamp(-128, 127).to(torch.int8), sc.expand(t.shape[0], 1)
+        if per_token:
+            return fp8_per_token_quant_oracle(t)
+        q, sc = fp8_per_tensor_quant_oracle(t, static)
+        return q, sc.reshape(1, 1).expand(t.shape[0], 1)
+
+    # both activations are evaluated in fp32 on the stored (activation-dtype) output of GEMM 1
+    act_fn = (lambda z: swigluoai_oracle(z, alpha, beta, limit)) if activation == "swigluoai_uninterleave" \
+        else (lambda z: _silu_mul(z.float()))
+    xq, xs = quant(hidden, a1_scale)
+    rows_all = [(_expert_rows(ids, e), e) for e in range(w1_q.shape[0])]
+    inter = torch.zeros(M * k, w1_q.shape[1] // 2, dtype=dt)
+    for rows, e in rows_all:
+        if rows.numel():
+            tok = rows // k
+            up = (xq[tok].float() @ w1_q[e].cpu().float().t()) * xs[tok] * w1_s[e].cpu().float().reshape(1, -1)
+            inter[rows] = act_fn(up.to(dt)).to(dt)
+    # the per-tensor dynamic scale of the intermediate is taken over all routes at once, as the reference does
+    aq, as_ = quant(inter, a2_scale)
+    per_route = torch.zeros(M * k, H, dtype=torch.float32)
+    for rows, e in rows_all:
+        if rows.numel():
+            down = (aq[rows].float() @ w2_q[e].cpu().float().t()) * as_[rows] * w2_s[e].cpu().float().reshape(1, -1)
+            per_route[rows] = (down * wts[rows, None]).to(dt).float()
     return per_route.view(M, k, H).sum(dim=1)
 
 

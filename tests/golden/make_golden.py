@@ -220,6 +220,53 @@ def main(ref_root: str):
     save("quant_fp8_0.npz", x=x, q=q, s=s)
     q, s = qt["native_per_token_group_quant_fp8"](x, 128, dtype=torch.float8_e4m3fn, scale_ue8m0=True)
     save("quant_fp8_ue8m0_0.npz", x=x, q=q, s=s)
+    # other group sizes and a larger clamp (a group of zeros then takes the clamp as its amax)
+    for i, (group, eps) in enumerate([(64, 1e-10), (256, 1e-10), (32, 1e-4), (384, 1e-2)]):
+        torch.manual_seed(70 + i)
+        xg = torch.randn(5, 768, dtype=torch.bfloat16) * 2.0
+        xg[1, :group] = 0
+        q, s = qt["native_per_token_group_quant_fp8"](xg, group, eps=eps, dtype=torch.float8_e4m3fn)
+        save(f"quant_fp8_group_{i}.npz", x=xg, q=q, s=s, params=np.array([group, eps]))
+
+    # ------------------------------------------------------------ INT8 W8A8 with the swigluoai activation
+    fm = lift(os.path.join(tests, "test_fused_moe.py"), ["literal_oai", "literal_quant"], base)
+    for i, (dt, shape) in enumerate([(torch.bfloat16, (7, 384)), (torch.float16, (32, 768)), (torch.bfloat16, (1, 127))]):
+        torch.manual_seed(43 + i)
+        x = torch.randn(shape, dtype=dt) * 8
+        if i == 0:  # the half-way and all-zero rows the reference tests spell out
+            x[0, :4] = torch.tensor([127.0, 0.5, 1.5, 2.5], dtype=dt)
+            x[0, 4:] = 0
+            x[1] = 0
+            x[2, :4] = torch.tensor([52.0, 26.0, 13.0, 0.0], dtype=dt)
+        q, sc = fm["literal_quant"](x)
+        packed = torch.randn((shape[0], 2 * shape[1]), dtype=dt) * 8
+        save(f"quant_int8_{i}.npz", dtype=str(dt), x=x, q=q, s=sc, packed=packed, oai=fm["literal_oai"](packed))
+    for i, (dt, m, inter) in enumerate([(torch.bfloat16, 7, 384), (torch.float16, 5, 256)]):
+        # the literal loop of tests/test_fused_moe.py:143-160, with that file's own quantiser and activation
+        torch.manual_seed(47 + i)
+        e, h, k = 4, 128, 2
+        x = torch.randn((m, h), dtype=dt)
+        w1 = torch.randint(-64, 64, (e, 2 * inter, h), dtype=torch.int8)
+        w2 = torch.randint(-64, 64, (e, h, inter), dtype=torch.int8)
+        s1 = torch.rand((e, 2 * inter)) * 0.001 + 0.001
+        s2 = torch.rand((e, h)) * 0.001 + 0.001
+        ids = (torch.arange(m * k).view(m, k) % e).int()
+        weights = torch.rand((m, k))
+        weights /= weights.sum(-1, keepdim=True)
+        qx, sx = fm["literal_quant"](x)
+        contributions = []
+        for t in range(m):
+            row = []
+            for rank in range(k):
+                ex = int(ids[t, rank])
+                up = (qx[t:t + 1].float() @ w1[ex].float().t()) * sx[t] * s1[ex]
+                activated = fm["literal_oai"](up.to(dt))
+                qa, sa = fm["literal_quant"](activated)
+                down = (qa.float() @ w2[ex].float().t()) * sa * s2[ex]
+                row.append((down * weights[t, rank]).to(dt))
+            contributions.append(torch.stack(row).float().sum(0).to(dt))
+        save(f"layer_w8a8_int8_{i}.npz", dtype=str(dt), x=x, w1=w1, w2=w2, w1_scale=s1, w2_scale=s2,
+             topk_weights=weights, topk_ids=ids, out=torch.cat(contributions).float())
 
 
 if __name__ == "__main__":

@@ -283,6 +283,143 @@ def test_config4_qwen3_shape(M):
     assert torch.equal(out, fg.fused_experts_impl(x, w1, w2, tw, ti, **kw))
 
 
+# ---------------------------------------------------------------- row-scaled W8A8 modes and swigluoai
+@pytest.mark.parametrize("name", golden_files("quant_int8_"))
+def test_rowwise_int8_quant_matches_oracle_and_reference_vectors(name):
+    g = load_golden(name)
+    dt = DT[g["dtype"]]
+    x = g["x"].to(dt).to(DEV)
+    L = _lib.lib()
+    q = torch.empty(x.shape, dtype=torch.int8, device=DEV)
+    sc = torch.empty(x.shape[0], dtype=torch.float32, device=DEV)
+    _lib.check(L.moe_rowwise_quant(x.data_ptr(), _lib.dtype_code(dt), x.shape[0], x.shape[1], 0, None, None, 0,
+                                   q.data_ptr(), sc.data_ptr(), _lib.stream_of(x)))
+    oq, os_ = O.int8_per_token_quant_oracle(g["x"].to(dt))
+    assert torch.equal(q.cpu(), oq) and torch.equal(sc.cpu().reshape(-1, 1), os_)
+    same = (os_ == g["s"]).expand_as(oq)  # rows where the kernel's amax * (1/127) equals the literal's amax / 127
+    assert torch.equal(q.cpu()[same], g["q"][same])
+
+
+def _rowwise(x, kind, static=None, row_ids=None, valid_below=0):
+    L = _lib.lib()
+    q = torch.empty(x.shape, dtype=torch.uint8, device=DEV)
+    sc = torch.empty(x.shape[0] if kind in (0, 1) else 1, dtype=torch.float32, device=DEV)
+    _lib.check(L.moe_rowwise_quant(x.data_ptr(), _lib.dtype_code(x.dtype), x.shape[0], x.shape[1], kind,
+                                   _lib.ptr(static), _lib.ptr(row_ids), valid_below, q.data_ptr(), sc.data_ptr(),
+                                   _lib.stream_of(x)))
+    return q.cpu(), sc.cpu()
+
+
+@pytest.mark.parametrize("dtype", [torch.bfloat16, torch.float16])
+def test_rowwise_fp8_quant_kinds(dtype):
+    x = (torch.randn(19, 320, device=DEV) * 4).to(dtype)
+    x[3] = 0
+    q, sc = _rowwise(x, 1)
+    oq, os_ = O.fp8_per_token_quant_oracle(x)
+    assert torch.equal(q, oq.view(torch.uint8)) and torch.equal(sc.reshape(-1, 1), os_)
+    static = torch.tensor([0.037], device=DEV)
+    q, sc = _rowwise(x, 2, static)
+    oq, _ = O.fp8_per_tensor_quant_oracle(x, static)
+    assert torch.equal(q, oq.view(torch.uint8)) and float(sc) == float(static)
+    q, sc = _rowwise(x, 3)
+    oq, os_ = O.fp8_per_tensor_quant_oracle(x)
+    assert torch.equal(sc, os_) and torch.equal(q, oq.view(torch.uint8))
+    # dynamic per-tensor scale over a subset of rows (padding rows of the sorted intermediate are skipped)
+    ids = torch.arange(19, dtype=torch.int32, device=DEV)
+    ids[5:] += 100
+    x2 = x.clone()
+    x2[10] = 1000.0  # a skipped row must not move the scale
+    q2, sc2 = _rowwise(x2, 3, None, ids, 50)
+    oq2, os2 = O.fp8_per_tensor_quant_oracle(x2[:5])
+    assert torch.equal(sc2, os2) and torch.equal(q2[:5], oq2.view(torch.uint8))
+
+
+@pytest.mark.parametrize("name", golden_files("layer_w8a8_int8_"))
+def test_golden_int8_w8a8_swigluoai(name):
+    g = load_golden(name)
+    dt = DT[g["dtype"]]
+    x, w1, w2 = g["x"].to(dt).to(DEV), g["w1"].to(DEV), g["w2"].to(DEV)
+    s1, s2 = g["w1_scale"].to(DEV), g["w2_scale"].to(DEV)
+    tw, ti = g["topk_weights"].to(DEV), g["topk_ids"].to(DEV)
+    kw = dict(activation="swigluoai_uninterleave", use_int8_w8a8=True, per_channel_quant=True, w1_scale=s1, w2_scale=s2,
+              gemm1_alpha=1.702, gemm1_beta=1.0, gemm1_clamp_limit=7.0)
+    out = fg.fused_experts_impl(x, w1, w2, tw, ti, **kw)
+    ref = O.fused_moe_row_scaled_oracle(x, w1, w2, s1, s2, tw, ti, fmt="int8", per_token=True,
+                                        activation="swigluoai_uninterleave")
+    _assert_parity(out, ref, name)
+    # the reference test's own tolerance against its literal loop (tests/test_fused_moe.py:161-166)
+    torch.testing.assert_close(out.float().cpu(), g["out"], atol=0.0005 if dt == torch.float16 else 0.004,
+                               rtol=0.003 if dt == torch.float16 else 0.016)
+    buf = x.clone()
+    assert fg.inplace_fused_experts(buf, w1, w2, tw, ti, **kw) is None and torch.equal(buf, out)
+
+
+@pytest.mark.parametrize("variant", ["tensor_dynamic", "tensor_static", "token_channel"])
+def test_fp8_per_tensor_and_per_token_layers(variant):
+    M, E, H, I, k = 33, 8, 256, 384, 2
+    x = T.make_activations(M, H, DEV)
+    w1f = torch.randn(E, 2 * I, H, device=DEV) * H**-0.5
+    w2f = torch.randn(E, H, I, device=DEV) * I**-0.5
+    tw, ti = _route(M, E, k, torch.bfloat16)
+    if variant == "token_channel":
+        s1 = w1f.abs().amax(-1) / 448.0
+        s2 = w2f.abs().amax(-1) / 448.0
+        w1, w2 = (w1f / s1[..., None]).to(torch.float8_e4m3fn), (w2f / s2[..., None]).to(torch.float8_e4m3fn)
+        out = fg.fused_experts_impl(x, w1, w2, tw, ti, use_fp8_w8a8=True, per_channel_quant=True, w1_scale=s1, w2_scale=s2)
+        ref = O.fused_moe_row_scaled_oracle(x, w1, w2, s1, s2, tw, ti, fmt="fp8", per_token=True)
+    else:
+        s1 = w1f.abs().amax(dim=(1, 2)) / 448.0
+        s2 = w2f.abs().amax(dim=(1, 2)) / 448.0
+        w1 = (w1f / s1[:, None, None]).to(torch.float8_e4m3fn)
+        w2 = (w2f / s2[:, None, None]).to(torch.float8_e4m3fn)
+        a1 = a2 = None
+        if variant == "tensor_static":
+            a1, a2 = torch.tensor([0.02], device=DEV), torch.tensor([0.004], device=DEV)
+        out = fg.fused_experts_impl(x, w1, w2, tw, ti, use_fp8_w8a8=True, w1_scale=s1, w2_scale=s2, a1_scale=a1,
+                                    a2_scale=a2)
+        ref = O.fused_moe_row_scaled_oracle(x, w1, w2, s1[:, None].expand(E, 2 * I), s2[:, None].expand(E, H), tw, ti,
+                                            fmt="fp8", per_token=False, a1_scale=a1, a2_scale=a2)
+    _assert_parity(out, ref, variant)
+
+
+@pytest.mark.parametrize("fmt", ["half", "w8a16", "fp8"])
+def test_swigluoai_activation_on_the_other_weight_formats(fmt):
+    M, E, H, I, k = 21, 8, 256, 256, 2
+    x = T.make_activations(M, H, DEV)
+    tw, ti = _route(M, E, k, torch.bfloat16)
+    act = lambda z: O.swigluoai_oracle(z, 1.5, 0.5, 3.0)
+    kw = dict(activation="swigluoai_uninterleave", gemm1_alpha=1.5, gemm1_beta=0.5, gemm1_clamp_limit=3.0)
+    if fmt == "half":
+        w1 = T.make_half_weights(E, 2 * I, H, DEV, seed=1, std=H**-0.5)
+        w2 = T.make_half_weights(E, H, I, DEV, seed=2, std=I**-0.5)
+        out = fg.fused_experts_impl(x, w1, w2, tw, ti, **kw)
+        ref = O.fused_moe_half_oracle(x, w1, w2, tw, ti, act_fn=act)
+    elif fmt == "w8a16":
+        w1, s1 = T.make_int8_channel_weights(E, 2 * I, H, DEV, seed=1, std=H**-0.5)
+        w2, s2 = T.make_int8_channel_weights(E, H, I, DEV, seed=2, std=I**-0.5)
+        out = fg.fused_experts_impl(x, w1, w2, tw, ti, use_int8_w8a16=True, per_channel_quant=True, w1_scale=s1,
+                                    w2_scale=s2, **kw)
+        wd1 = (w1.float() * s1[..., None]).to(torch.bfloat16)
+        wd2 = (w2.float() * s2[..., None]).to(torch.bfloat16)
+        ref = O.fused_moe_half_oracle(x, wd1.float(), wd2.float(), tw, ti, act_fn=act)
+    else:
+        w1, s1 = T.make_fp8_block_weights(E, 2 * I, H, DEV, seed=1, std=H**-0.5)
+        w2, s2 = T.make_fp8_block_weights(E, H, I, DEV, seed=2, std=I**-0.5)
+        out = fg.fused_experts_impl(x, w1, w2, tw, ti, use_fp8_w8a8=True, w1_scale=s1, w2_scale=s2,
+                                    block_shape=[128, 128], **kw)
+        # same layer with SiLU swapped for the other activation: compare with the half oracle on the dequantised
+        # weights and activations is too loose; check against the structure instead: the SiLU result must differ
+        silu = fg.fused_experts_impl(x, w1, w2, tw, ti, use_fp8_w8a8=True, w1_scale=s1, w2_scale=s2,
+                                     block_shape=[128, 128])
+        assert O.rel_l2(out.float(), silu.float()) > 1e-2
+        wd1 = (w1.float().view(E, 2 * I // 128, 128, H // 128, 128) * s1[:, :, None, :, None]).view(E, 2 * I, H)
+        wd2 = (w2.float().view(E, H // 128, 128, I // 128, 128) * s2[:, :, None, :, None]).view(E, H, I)
+        ref = O.fused_moe_half_oracle(x, wd1, wd2, tw, ti, act_fn=act)
+        assert O.rel_l2(out.float(), ref) < 6e-2 and O.cosine(out.float(), ref) > 0.998  # two e4m3 quantisations apart
+        return
+    _assert_parity(out, ref, fmt)
+
+
 # ---------------------------------------------------------------- small-batch schedule
 @pytest.mark.parametrize("M", [1, 2, 7, 16, 32, 64])
 @pytest.mark.parametrize("fmt", ["half", "fp8", "w8a16"])
@@ -486,6 +623,35 @@ def test_quant_and_sum_wrappers():
             fg.moe_sum(inp, o)
             torch.testing.assert_close(o.float().cpu(), O.moe_sum_oracle(inp).to(dt).float(),
                                        rtol=1.6e-2 if dt != torch.float32 else 1.3e-6, atol=1e-4 * k)
+
+
+@pytest.mark.parametrize("name", golden_files("quant_fp8_group_"))
+def test_quant_other_group_sizes_and_clamps(name):
+    """Any group size and eps, bit for bit against the oracle (which the reference-made vectors pin)."""
+    g = load_golden(name)
+    group, eps = int(g["params"][0]), float(g["params"][1])
+    x = g["x"].to(DEV)
+    q, s = fg.per_token_group_quant_fp8(x, group, eps=eps)
+    oq, os_ = O.per_token_group_quant_fp8_oracle(g["x"], group, eps=eps)
+    assert torch.equal(q.cpu().view(torch.uint8), oq.view(torch.uint8)) and torch.equal(s.cpu(), os_)
+    q2, s2 = fg.per_token_group_quant_fp8(x, group, eps=eps, column_major_scales=True)
+    assert s2.stride(0) == 1 and torch.equal(s2.contiguous(), s) and torch.equal(q2.view(torch.uint8), q.view(torch.uint8))
+    for dt in (torch.float32, torch.float16):
+        xx = (torch.randn(17, 4 * group, device=DEV) * 3).to(dt)
+        qq, ss = fg.per_token_group_quant_fp8(xx, group, eps=eps)
+        oq, os_ = O.per_token_group_quant_fp8_oracle(xx, group, eps=eps)
+        assert torch.equal(qq.cpu().view(torch.uint8), oq.view(torch.uint8)) and torch.equal(ss.cpu(), os_)
+
+
+def test_quant_e5m2_output():
+    x = torch.randn(9, 512, device=DEV, dtype=torch.bfloat16) * 4
+    q, s = fg.per_token_group_quant_fp8(x, 128, dtype=torch.float8_e5m2)
+    assert q.dtype == torch.float8_e5m2
+    xr = x.float().cpu().reshape(-1, 128)
+    sc = xr.abs().amax(dim=1, keepdim=True).clamp(min=1e-10) * torch.tensor(1.0 / 57344.0)
+    ref = (xr / sc).clamp(-57344.0, 57344.0).to(torch.float8_e5m2)
+    assert torch.equal(s.cpu().reshape(-1, 1), sc)
+    assert torch.equal(q.cpu().view(torch.uint8).reshape(-1, 128), ref.view(torch.uint8))
 
 
 def test_moe_sum_accepts_strided_tensors():

@@ -136,10 +136,17 @@ def test_fused_experts_validation_errors():
         fg.fused_experts_impl(x, w1, w2, torch.zeros(4, 3), ti)
     with pytest.raises(AssertionError, match="contiguous"):
         fg.fused_experts_impl(torch.zeros(64, 4, dtype=torch.bfloat16).t(), w1, w2, tw, ti)
-    with pytest.raises(NotImplementedError, match="W8A8"):
-        fg.fused_experts_impl(x, w1, w2, tw, ti, use_int8_w8a8=True)
+    with pytest.raises(AssertionError, match="weights expected"):
+        fg.fused_experts_impl(x, w1, w2, tw, ti, use_int8_w8a8=True)  # bf16 weights are not int8 weights
+    with pytest.raises(NotImplementedError, match="block-quantised INT8"):
+        fg.fused_experts_impl(x, w1.to(torch.int8), w2.to(torch.int8), tw, ti, use_int8_w8a8=True, block_shape=[128, 128])
     with pytest.raises(NotImplementedError, match="block_shape"):
-        fg.fused_experts_impl(x, w1, w2, tw, ti, use_fp8_w8a8=True)
+        fg.fused_experts_impl(x, w1, w2, tw, ti, use_fp8_w8a8=True, block_shape=[64, 64])
+    with pytest.raises(ValueError, match="finite scalar gemm1_alpha"):
+        fg.fused_experts_impl(x, w1, w2, tw, ti, activation="swigluoai_uninterleave")
+    with pytest.raises(ValueError, match="gemm1_clamp_limit >= 0"):
+        fg.fused_experts_impl(x, w1, w2, tw, ti, activation="swigluoai_uninterleave", gemm1_alpha=1.702,
+                              gemm1_beta=1.0, gemm1_clamp_limit=-1.0)
     with pytest.raises(RuntimeError, match="no CPU path"):
         fg.fused_experts_impl(x, w1, w2, tw, ti)
 

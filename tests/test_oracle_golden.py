@@ -129,6 +129,51 @@ def test_quant_fp8_matches_reference_golden():
     assert torch.equal(q.view(torch.uint8), g["q"].view(torch.uint8))
 
 
+@pytest.mark.parametrize("name", golden_files("quant_fp8_group_"))
+def test_quant_fp8_other_group_sizes_match_reference_golden(name):
+    g = load_golden(name)
+    group, eps = int(g["params"][0]), float(g["params"][1])
+    q, s = O.per_token_group_quant_fp8_oracle(g["x"], group, eps=eps, reciprocal=True)
+    # the golden clamps in bf16 (the input dtype), the kernel and the oracle in fp32: groups whose
+    # amax is below the clamp may differ in the last bits of the scale
+    big = g["x"].float().reshape(-1, group).abs().amax(dim=1).reshape(s.shape) > eps
+    assert torch.equal(s[big], g["s"][big])
+    torch.testing.assert_close(s[~big], g["s"][~big], rtol=1e-2, atol=0)
+    rows_big = big.repeat_interleave(group, dim=-1)
+    assert torch.equal(q.view(torch.uint8)[rows_big], g["q"].view(torch.uint8)[rows_big])
+
+
+@pytest.mark.parametrize("name", golden_files("quant_int8_"))
+def test_int8_per_token_quant_and_swigluoai_match_reference_literals(name):
+    g = load_golden(name)
+    dt = {"torch.bfloat16": torch.bfloat16, "torch.float16": torch.float16}[g["dtype"]]
+    x = g["x"].to(dt)
+    q, s = O.int8_per_token_quant_oracle(x)
+    # amax * fp32(1/127) (the kernel, which the oracle follows) against amax / 127 (the literal): the same
+    # fp32 value or its neighbour; where they differ, a quotient that sits on a half-way point (26 / (52/127)
+    # = 63.5) may round to either side
+    torch.testing.assert_close(s, g["s"], rtol=2e-7, atol=0)
+    same = (s == g["s"]).expand_as(q)
+    assert torch.equal(q[same], g["q"][same])
+    assert (q.int() - g["q"].int()).abs().max() <= 1 and same.float().mean() > 0.7
+    out = O.swigluoai_oracle(g["packed"].to(dt)).to(dt)
+    assert torch.equal(out.float(), g["oai"].to(dt).float())
+
+
+@pytest.mark.parametrize("name", golden_files("layer_w8a8_int8_"))
+def test_int8_w8a8_layer_oracle_matches_reference_literal_loop(name):
+    g = load_golden(name)
+    dt = {"torch.bfloat16": torch.bfloat16, "torch.float16": torch.float16}[g["dtype"]]
+    out = O.fused_moe_row_scaled_oracle(g["x"].to(dt), g["w1"], g["w2"], g["w1_scale"], g["w2_scale"],
+                                        g["topk_weights"], g["topk_ids"], fmt="int8", per_token=True,
+                                        activation="swigluoai_uninterleave")
+    ref = g["out"]
+    # the literal rounds the sum of the routes to the activation dtype; the oracle returns fp32
+    torch.testing.assert_close(out.to(dt).float(), ref, rtol=1.6e-2 if dt == torch.bfloat16 else 3e-3,
+                               atol=4e-3 if dt == torch.bfloat16 else 5e-4)
+    assert O.rel_l2(out, ref) < 4e-3
+
+
 def test_quant_fp8_power_of_two_scales_match_reference_golden():
     g = load_golden("quant_fp8_ue8m0_0.npz")
     q, s = O.per_token_group_quant_fp8_oracle(g["x"], 128, reciprocal=True, scale_ue8m0=True)
