@@ -43,6 +43,9 @@ SYMBOLS = {
     "moe_ep_unpack": (c_int, [c_void_p, c_int64, c_int, c_int, c_int, c_int, c_void_p, c_void_p, c_void_p,
                               c_void_p]),
     "moe_router_gemm": (c_int, [c_void_p, c_int, c_int64, c_void_p, c_int, c_int64, c_int, c_int, c_void_p, c_void_p]),
+    "moe_router_gemm_grouped_topk": (c_int, [c_void_p, c_int, c_int64, c_void_p, c_int, c_void_p, c_int64, c_int, c_int,
+                                             c_int, c_int, c_int, c_int, c_float, c_int, c_void_p, c_void_p, c_void_p,
+                                             c_void_p]),
     "moe_gather_rows": (c_int, [c_void_p, c_int64, c_int, c_int64, c_void_p, c_void_p, c_int64, c_void_p, c_void_p]),
     "moe_gather_scales_t": (c_int, [c_void_p, c_int, c_int64, c_int, c_void_p, c_void_p, c_int64, c_void_p, c_void_p]),
     "moe_gemm1": (c_int, [c_int, c_int, c_void_p, c_int, c_void_p, c_int64, c_int, c_void_p, c_void_p, c_void_p,

@@ -37,30 +37,17 @@ __device__ __forceinline__ uint64_t warp_max_u64(uint64_t k) {
   return k;
 }
 
+// The routing of one token by one warp: `row` holds the token's E scores (element stride
+// `stride1`; global or shared memory), the results go to w_row / id_row [topk].
 template <typename ST, typename BT, int VPT>
-__global__ void __launch_bounds__(128) grouped_topk_kernel(
-    const ST* __restrict__ scores, int64_t stride0, int64_t stride1, const BT* __restrict__ bias,
-    const uint8_t* __restrict__ is_padding, int64_t M, int E, int n_group, int topk_group, int topk,
-    int renormalize, float scaling, int scoring_func, float* __restrict__ out_w,
-    int32_t* __restrict__ out_ids) {
-  const int lane = threadIdx.x & 31;
-  const int64_t token = (int64_t)blockIdx.x * (blockDim.x >> 5) + (threadIdx.x >> 5);
-  if (token >= M) return;
-  float* w_row = out_w + token * topk;
-  int32_t* id_row = out_ids + token * topk;
-  if (is_padding != nullptr && is_padding[token]) {
-    if (lane < topk) {
-      w_row[lane] = 0.0f;
-      id_row[lane] = -1;
-    }
-    return;
-  }
+__device__ __forceinline__ void route_row(const ST* row, int64_t stride1, const BT* __restrict__ bias, int E,
+                                          int n_group, int topk_group, int topk, int renormalize, float scaling,
+                                          int scoring_func, float* w_row, int32_t* id_row, int lane) {
   const int per_group = E / n_group;
   const float NEG_INF = __int_as_float(0xff800000);
 
   float u[VPT];      // unbiased score
   uint64_t key[VPT]; // ranking key of u + bias (0 = absent / consumed)
-  const ST* row = scores + token * stride0;
 #pragma unroll
   for (int j = 0; j < VPT; ++j) {
     const int e = j * 32 + lane;
@@ -154,6 +141,76 @@ __global__ void __launch_bounds__(128) grouped_topk_kernel(
   }
 }
 
+template <typename ST, typename BT, int VPT>
+__global__ void __launch_bounds__(128) grouped_topk_kernel(
+    const ST* __restrict__ scores, int64_t stride0, int64_t stride1, const BT* __restrict__ bias,
+    const uint8_t* __restrict__ is_padding, int64_t M, int E, int n_group, int topk_group, int topk,
+    int renormalize, float scaling, int scoring_func, float* __restrict__ out_w,
+    int32_t* __restrict__ out_ids) {
+  const int lane = threadIdx.x & 31;
+  const int64_t token = (int64_t)blockIdx.x * (blockDim.x >> 5) + (threadIdx.x >> 5);
+  if (token >= M) return;
+  float* w_row = out_w + token * topk;
+  int32_t* id_row = out_ids + token * topk;
+  if (is_padding != nullptr && is_padding[token]) {
+    if (lane < topk) {
+      w_row[lane] = 0.0f;
+      id_row[lane] = -1;
+    }
+    return;
+  }
+  route_row<ST, BT, VPT>(scores + token * stride0, stride1, bias, E, n_group, topk_group, topk, renormalize, scaling,
+                         scoring_func, w_row, id_row, lane);
+}
+
+// Router GEMM and routing in one launch for decode batches: one CTA per token computes the
+// token's E logits (x[token] . w[e], fp32) into shared memory and its first warp routes them, so
+// the [M, E] logits never travel through global memory.  The dot products are formed exactly as
+// router_gemm_kernel forms them (128 threads per expert: 8-element chunks strided over the
+// threads, shuffle tree, four warp sums in warp order), so logits, ids and weights equal those of
+// the two separate launches bit for bit.  256 threads work on two experts at a time.
+template <typename XT, typename WT, typename BT, int VPT>
+__global__ void __launch_bounds__(256) router_topk_fused_kernel(
+    const XT* __restrict__ x, int64_t x_ld, const WT* __restrict__ w, const BT* __restrict__ bias, int64_t M, int E,
+    int K, int n_group, int topk_group, int topk, int renormalize, float scaling, int scoring_func,
+    float* __restrict__ out_w, int32_t* __restrict__ out_ids, float* __restrict__ logits_out) {
+  extern __shared__ float fused_smem[];
+  float* logits = fused_smem;             // [E]
+  float* part = fused_smem + E;           // [2][4]
+  const int64_t token = blockIdx.x;
+  const int half = threadIdx.x >> 7, t = threadIdx.x & 127, lane = threadIdx.x & 31, wq = (threadIdx.x >> 5) & 3;
+  const XT* xr = x + token * x_ld;
+  for (int e0 = 0; e0 < E; e0 += 2) {
+    const int e = e0 + half;
+    float acc = 0.0f;
+    if (e < E) {
+      const WT* wr = w + (int64_t)e * K;
+      for (int k = t * 8; k < K; k += 128 * 8) {
+        float wv[8], xv[8];
+        load8<WT>(wr + k, wv);
+        load8<XT>(xr + k, xv);
+#pragma unroll
+        for (int i = 0; i < 8; ++i) acc = fmaf(xv[i], wv[i], acc);
+      }
+    }
+#pragma unroll
+    for (int off = 16; off > 0; off >>= 1) acc += __shfl_xor_sync(0xFFFFFFFFu, acc, off);
+    if (lane == 0) part[half * 4 + wq] = acc;
+    __syncthreads();
+    if (t == 0 && e < E) {
+      float v = part[half * 4];
+#pragma unroll
+      for (int wi = 1; wi < 4; ++wi) v += part[half * 4 + wi];
+      logits[e] = v;
+      if (logits_out != nullptr) logits_out[token * E + e] = v;
+    }
+    __syncthreads();
+  }
+  if (threadIdx.x < 32)
+    route_row<float, BT, VPT>(logits, 1, bias, E, n_group, topk_group, topk, renormalize, scaling, scoring_func,
+                              out_w + token * topk, out_ids + token * topk, lane);
+}
+
 template <typename ST, typename BT>
 int launch_vpt(const ST* scores, int64_t s0, int64_t s1, const BT* bias, const uint8_t* pad,
                int64_t M, int E, int n_group, int topk_group, int topk, int renorm, float scaling,
@@ -230,4 +287,45 @@ extern "C" int moe_grouped_topk(const void* scores, int scores_dtype, int64_t st
     default:
       return fail(MOE_E_DTYPE, "grouped_topk: unsupported scores dtype %d", scores_dtype);
   }
+}
+
+extern "C" int moe_router_gemm_grouped_topk(const void* x, int x_dtype, int64_t x_ld, const void* w, int w_dtype,
+                                            const float* bias, int64_t M, int E, int K, int n_group, int topk_group,
+                                            int topk, int renormalize, float routed_scaling_factor, int scoring_func,
+                                            float* topk_weights, int32_t* topk_ids, float* logits_out, void* stream) {
+  using namespace moe;
+  if (M < 0 || E <= 0 || K <= 0 || n_group <= 0 || topk <= 0 || topk_group <= 0)
+    return fail(MOE_E_BADARG, "router_gemm_grouped_topk: non-positive extent");
+  if (E > 1024) return fail(MOE_E_TOOBIG, "router_gemm_grouped_topk: at most 1024 experts (got %d)", E);
+  if (n_group > 32 || topk > 32 || topk_group > n_group || E % n_group != 0 || topk > E)
+    return fail(MOE_E_SHAPE, "router_gemm_grouped_topk: bad group/top-k configuration");
+  if (scoring_func != 0 && scoring_func != 1) return fail(MOE_E_BADARG, "router_gemm_grouped_topk: scoring_func must be 0 or 1");
+  if (K % 8 != 0 || x_ld % 8 != 0 || x_ld < K) return fail(MOE_E_SHAPE, "router_gemm_grouped_topk: K and the row pitch must be multiples of 8");
+  if (M == 0) return 0;
+  if (!x || !w || !bias || !topk_weights || !topk_ids) return fail(MOE_E_BADARG, "router_gemm_grouped_topk: null pointer");
+  if (((uintptr_t)x & 15) || ((uintptr_t)w & 15)) return fail(MOE_E_BADARG, "router_gemm_grouped_topk: operands must be 16-byte aligned");
+  if (M > 65535 * 32) return fail(MOE_E_TOOBIG, "router_gemm_grouped_topk: too many rows");
+  cudaStream_t st = (cudaStream_t)stream;
+  const size_t smem = (size_t)(E + 8) * sizeof(float);
+#define MOE_RT_V(XT, WT, V)                                                                                         \
+  router_topk_fused_kernel<XT, WT, float, V><<<(unsigned)M, 256, smem, st>>>(                                        \
+      (const XT*)x, x_ld, (const WT*)w, bias, M, E, K, n_group, topk_group, topk, renormalize, routed_scaling_factor, \
+      scoring_func, topk_weights, topk_ids, logits_out)
+#define MOE_RT(XT, WT)                     \
+  do {                                     \
+    if (E <= 32) MOE_RT_V(XT, WT, 1);      \
+    else if (E <= 64) MOE_RT_V(XT, WT, 2); \
+    else if (E <= 128) MOE_RT_V(XT, WT, 4);\
+    else if (E <= 256) MOE_RT_V(XT, WT, 8);\
+    else if (E <= 512) MOE_RT_V(XT, WT, 16);\
+    else MOE_RT_V(XT, WT, 32);             \
+  } while (0)
+  if (x_dtype == MOE_BF16 && w_dtype == MOE_BF16) MOE_RT(__nv_bfloat16, __nv_bfloat16);
+  else if (x_dtype == MOE_F16 && w_dtype == MOE_F16) MOE_RT(__half, __half);
+  else if (x_dtype == MOE_BF16 && w_dtype == MOE_F32) MOE_RT(__nv_bfloat16, float);
+  else if (x_dtype == MOE_F32 && w_dtype == MOE_F32) MOE_RT(float, float);
+  else return fail(MOE_E_DTYPE, "router_gemm_grouped_topk: unsupported dtype pair (%d, %d)", x_dtype, w_dtype);
+#undef MOE_RT
+#undef MOE_RT_V
+  return check_launch("router_gemm_grouped_topk");
 }

@@ -3,9 +3,12 @@
 Mirrors ``router_gemm`` (src/flaggems_vllm/ops/router_gemm.py:207-237) and
 ``fp32_router_gemm`` / ``supports_fp32_router_gemm``
 (src/flaggems_vllm/ops/fp32_router_gemm.py:17-145): same names, argument meaning
-and error behaviour.  Decode-sized batches run the deterministic CUDA kernel of
-``csrc/router_gemm.cu``; a large prefill batch of ``router_gemm`` is a plain
-library GEMM (cuBLAS through ``torch.mm``) with fp32 output.
+and error behaviour.  Both kernels of ``csrc/router_gemm.cu`` are deterministic: a
+row-streaming fp32 kernel for decode-sized batches (and for every dtype pair), a
+tensor-core (warp MMA, fp32 accumulate) kernel for half-precision batches above 64 rows.
+No library GEMM is called.  ``router_gemm_grouped_topk`` fuses the GEMM with the
+group-limited routing for decode batches (no counterpart in the reference, which runs the
+two ops back to back).
 """
 
 from __future__ import annotations
@@ -18,8 +21,8 @@ from . import _lib
 
 logger = logging.getLogger(__name__)
 
-# above this many rows the plain [M, K] x [K, N] product is left to cuBLAS
-KERNEL_MAX_ROWS = 256
+# up to this many rows the fused GEMM + routing kernel (one CTA per token) beats two launches
+FUSED_MAX_ROWS = 64
 
 
 def _launch(x: torch.Tensor, weight: torch.Tensor) -> torch.Tensor:
@@ -45,14 +48,39 @@ def router_gemm(x: torch.Tensor, weight: torch.Tensor) -> torch.Tensor:
     if x.device != weight.device:
         raise ValueError("router_gemm expects x and weight to be on the same device")
     _lib.require_cuda(x, "router_gemm")
+    if x.shape[1] % 8 != 0:
+        raise ValueError("router_gemm: the hidden size must be a multiple of 8")
+    return _launch(x, weight)
+
+
+def router_gemm_grouped_topk(x: torch.Tensor, weight: torch.Tensor, n_group: int, topk_group: int, topk: int,
+                             renormalize: bool, routed_scaling_factor: float, bias: torch.Tensor,
+                             scoring_func: int = 0, return_logits: bool = False):
+    """``grouped_topk(router_gemm(x, weight), ...)`` in one launch: hidden states [M, K] and router
+    weight [E, K] in, (topk_weights fp32 [M, topk], topk_ids int32 [M, topk]) out; the logits stay on
+    chip (``return_logits=True`` also returns a copy).  Results equal the two separate calls bit for
+    bit.  Meant for decode batches (one CTA per token); any M is accepted."""
+    logger.debug("GEMS ROUTER GEMM + GROUPED TOPK")
+    if x.ndim != 2 or weight.ndim != 2 or x.shape[1] != weight.shape[1]:
+        raise ValueError("router_gemm_grouped_topk expects x [M, K] and weight [E, K]")
+    if scoring_func not in (0, 1):
+        raise ValueError(f"Unsupported scoring_func: {scoring_func}")
+    _lib.require_cuda(x, "router_gemm_grouped_topk")
     M, K = x.shape
-    if M <= KERNEL_MAX_ROWS and K % 8 == 0:
-        return _launch(x, weight)
-    # plain library GEMM with fp32 accumulation and output
-    try:
-        return torch.mm(x, weight.t(), out_dtype=torch.float32)
-    except TypeError:
-        return torch.mm(x.float(), weight.float().t())
+    E = weight.shape[0]
+    if bias.numel() != E:
+        raise ValueError(f"bias length {bias.numel()} does not match the expert count {E}")
+    xc = x if x.stride(1) == 1 and x.stride(0) % 8 == 0 and x.data_ptr() % 16 == 0 else x.contiguous()
+    wc = weight if weight.is_contiguous() else weight.contiguous()
+    b = bias.to(torch.float32).contiguous()
+    tw = torch.empty((M, topk), dtype=torch.float32, device=x.device)
+    ti = torch.empty((M, topk), dtype=torch.int32, device=x.device)
+    logits = torch.empty((M, E), dtype=torch.float32, device=x.device) if return_logits else None
+    _lib.check(_lib.lib().moe_router_gemm_grouped_topk(
+        xc.data_ptr(), _lib.dtype_code(xc.dtype), xc.stride(0), wc.data_ptr(), _lib.dtype_code(wc.dtype), b.data_ptr(),
+        M, E, K, n_group, topk_group, topk, int(bool(renormalize)), float(routed_scaling_factor), scoring_func,
+        tw.data_ptr(), ti.data_ptr(), _lib.ptr(logits), _lib.stream_of(x)))
+    return (tw, ti, logits) if return_logits else (tw, ti)
 
 
 def supports_fp32_router_gemm(hidden_size, num_experts, input_dtype, weight_dtype):

@@ -159,6 +159,19 @@ int moe_router_gemm(const void* x, int x_dtype, int64_t x_ld, const void* w, int
                     float* out, void* stream);
 
 /*
+ * Router GEMM fused with the group-limited routing, for decode batches: one launch takes the hidden
+ * states to (topk_weights, topk_ids); the [M, E] logits stay in shared memory (logits_out, optional,
+ * receives a copy for checks).  Logits, ids and weights equal those of moe_router_gemm followed by
+ * moe_grouped_topk bit for bit.  Removes the logits round trip in front of grouped_topk
+ * (src/flaggems_vllm/ops/router_gemm.py:207-237 + src/flaggems_vllm/ops/grouped_topk.py:1674-1976).
+ * x [M, K] (pitch x_ld), w [E, K]: bf16/bf16, f16/f16, bf16/f32 or f32/f32; bias [E] fp32.
+ */
+int moe_router_gemm_grouped_topk(const void* x, int x_dtype, int64_t x_ld, const void* w, int w_dtype,
+                                 const float* bias, int64_t M, int E, int K, int n_group, int topk_group, int topk,
+                                 int renormalize, float routed_scaling_factor, int scoring_func, float* topk_weights,
+                                 int32_t* topk_ids, float* logits_out, void* stream);
+
+/*
  * Copy of the token rows into sorted order: out[p] = x[sorted_ids[p] / topk] for
  * the occupied slots p < num_post_pad (padding slots and the tail are left
  * untouched).  Optional first step of GEMM 1 (a_sorted = 1): with many rows per

@@ -219,10 +219,10 @@ def test_topk_sigmoid_ties_nan_and_graph_replay():
 
 
 # ---------------------------------------------------------------- router GEMMs
-# shapes of the reference's tests/test_router_gemm.py:22-37 plus a prefill size served by cuBLAS
+# shapes of the reference's tests/test_router_gemm.py:22-37 plus prefill sizes served by the tensor-core kernel
 @pytest.mark.parametrize("shape", [(1, 256, 7168), (8, 256, 7168), (16, 256, 7168), (32, 256, 7168), (128, 256, 7168),
                                    (1, 64, 4096), (16, 128, 4096), (64, 384, 7168), (0, 256, 7168),
-                                   (1000, 256, 7168)])
+                                   (1000, 256, 7168), (8192, 256, 7168), (65, 200, 4096), (300, 8, 512)])
 def test_router_gemm_matches_oracle(shape):
     M, N, K = shape
     g = torch.Generator(device="cpu").manual_seed(M + N)
@@ -231,8 +231,39 @@ def test_router_gemm_matches_oracle(shape):
     out = fg.router_gemm(x, w)
     assert out.shape == (M, N) and out.dtype == torch.float32
     torch.testing.assert_close(out.cpu(), O.router_gemm_oracle(x, w), rtol=1e-4, atol=2e-3)
-    if 0 < M <= 256:  # the CUDA kernel reduces in a fixed order: bitwise repeatable
+    if M > 0:  # both kernels reduce in a fixed order: bitwise repeatable
         assert torch.equal(out, fg.router_gemm(x, w))
+    if M > 64:  # f16 takes the tensor-core kernel too; f32 operands the row-streaming kernel at any M
+        outh = fg.router_gemm(x.half(), w.half())
+        torch.testing.assert_close(outh.cpu(), O.router_gemm_oracle(x.half(), w.half()), rtol=1e-4, atol=2e-3)
+        if M <= 1000:
+            outf = fg.router_gemm(x.float(), w.float())
+            torch.testing.assert_close(outf.cpu(), O.router_gemm_oracle(x, w), rtol=1e-4, atol=2e-3)
+
+
+@pytest.mark.parametrize("M", [1, 7, 32, 64, 130])
+@pytest.mark.parametrize("cfg", [(256, 7168, 8, 4, 8, 1), (128, 2048, 1, 1, 8, 0), (64, 4096, 4, 2, 6, 1)])
+def test_router_gemm_fused_with_grouped_topk(M, cfg):
+    """One launch from hidden states to (weights, ids): bit for bit the two separate ops, and the ids are those
+    the oracle picks from the kernel's own logits."""
+    E, K, n_group, topk_group, k, scoring = cfg
+    g = torch.Generator(device="cpu").manual_seed(M + E)
+    x = (torch.randn((M, K), generator=g) * 0.5).to(torch.bfloat16).to(DEV)
+    w = (torch.randn((E, K), generator=g) * K**-0.5).to(torch.bfloat16).to(DEV)
+    bias = (torch.randn((E,), generator=g) * 0.1).to(DEV)
+    tw, ti, logits = fg.router_gemm_grouped_topk(x, w, n_group, topk_group, k, True, 2.5, bias, scoring,
+                                                 return_logits=True)
+    sep_logits = fg.router_gemm(x, w) if M <= 64 else None
+    if sep_logits is not None:
+        assert torch.equal(logits, sep_logits)
+    rw, ri = fg.grouped_topk(logits, n_group, topk_group, k, True, 2.5, bias, scoring)
+    assert torch.equal(ti, ri) and torch.equal(tw, rw)
+    ow, oi = O.grouped_topk_oracle(logits, n_group, topk_group, k, True, 2.5, bias, scoring)
+    assert torch.equal(ti.cpu(), oi)
+    torch.testing.assert_close(tw.cpu(), ow, atol=2e-6, rtol=2e-6)
+    torch.testing.assert_close(logits.cpu(), O.router_gemm_oracle(x, w), rtol=1e-4, atol=2e-3)
+    tw2, ti2 = fg.router_gemm_grouped_topk(x, w, n_group, topk_group, k, True, 2.5, bias, scoring)
+    assert torch.equal(ti2, ti) and torch.equal(tw2, tw)
 
 
 # tests/test_fp32_router_gemm.py:14-38 (same sizes, value scales, strides and tolerances)
