@@ -120,6 +120,7 @@ struct Params {
   int Nout;     // output columns (I for GEMM1, H for GEMM2)
   int rows_w;   // weight rows per expert (2I or H)
   int n_tiles;  // column tiles per align block
+  int group_m;  // align blocks per group of the tile order
   bool wide_store;  // the output is 32-byte aligned: rows are written with 32-byte stores
 #ifdef MOE_TC_TRACE
   long long* trace;  // [4 roles][64 K blocks][8 events] cycle stamps of CTA 0, third tile (experiment builds)
@@ -209,17 +210,43 @@ tc_gemm_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant_
   constexpr int CTAS = PAIR ? 2 : 1;
   const int cr = PAIR ? (int)cluster_ctarank() : 0;  // rank inside the pair; 0 leads
   const int tile0 = blockIdx.x / CTAS, tile_step = gridDim.x / CTAS;
-  const int total_tiles = ((npp + UNIT * BM - 1) / (UNIT * BM)) * P.n_tiles;
+  const int nblk = (npp + UNIT * BM - 1) / (UNIT * BM);
+  const int total_tiles = nblk * P.n_tiles;
+  // Tile order: groups of `group_m` consecutive align blocks; inside a group the block index runs
+  // fastest, then the column tile.  The CTAs that run at the same time then work on the blocks of
+  // one expert for the SAME few column tiles, so a weight tile is fetched from DRAM once and
+  // served to the other row blocks from L2.  (Column tile fastest sends every row block of an
+  // expert over the expert's whole weight matrix at a different time; a matrix larger than L2
+  // is then read once per row block.)
+  auto tile_blk_nt = [&](int tile, int& blk, int& nt) {
+    const int per_group = P.group_m * P.n_tiles;
+    const int grp = tile / per_group;
+    const int first = grp * P.group_m;
+    const int gsz = min(nblk - first, P.group_m);
+    const int within = tile - grp * per_group;
+    nt = within / gsz;
+    blk = first + within - nt * gsz;
+  };
   // tile -> expert_ids index (blk), this CTA's 128-row block (mb), column tile (nt).  The expert of
   // the NEXT tile is fetched while the current one is worked on: a tile starts without waiting
   // for a global load (every role walks the same tile list with its own copy of e_next).
-#define MOE_TILE_COORDS(tile)                      \
-  const int blk = (tile) / P.n_tiles;              \
-  [[maybe_unused]] const int nt = (tile) % P.n_tiles; \
-  [[maybe_unused]] const int mb = UNIT * blk + RB * cr; \
-  const int e = e_next;                            \
-  e_next = (tile) + tile_step < total_tiles ? P.expert_ids[((tile) + tile_step) / P.n_tiles] : -1;
-  int e_next = tile0 < total_tiles ? P.expert_ids[tile0 / P.n_tiles] : -1;
+#define MOE_TILE_COORDS(tile)                             \
+  int blk, nt;                                            \
+  tile_blk_nt((tile), blk, nt);                           \
+  [[maybe_unused]] const int mb = UNIT * blk + RB * cr;   \
+  const int e = e_next;                                   \
+  e_next = -1;                                            \
+  if ((tile) + tile_step < total_tiles) {                 \
+    int blk2, nt2;                                        \
+    tile_blk_nt((tile) + tile_step, blk2, nt2);           \
+    e_next = P.expert_ids[blk2];                          \
+  }
+  int e_next = -1;
+  if (tile0 < total_tiles) {
+    int blk0, nt0;
+    tile_blk_nt(tile0, blk0, nt0);
+    e_next = P.expert_ids[blk0];
+  }
 
 #ifdef MOE_TC_TRACE
   if (threadIdx.x == 0 && blockIdx.x == 0 && P.trace) { P.trace[2048] = clock64(); P.trace[2049] = (long long)now_ns(); P.trace[2052] = total_tiles; }
@@ -798,6 +825,12 @@ int tc_gemm(bool gemm1, int mode, int act_dtype, const void* a, const float* a_s
   P.status = status; P.wait_ns = wait_limit_ns(); P.numel = numel; P.rows_cap = rows_cap; P.mul_weight = mul_weight; P.E = E; P.K = K;
   P.Nout = Nout; P.rows_w = rows_w;
   P.n_tiles = gemm1 ? Nout / 128 : (Nout + BN - 1) / BN;
+  {
+    // about as many blocks per group as one expert owns (rows per expert / rows per block, one of them partial)
+    const int64_t per_expert = numel / (E > 0 ? E : 1);
+    int64_t gm = per_expert / unit_rows + 1;
+    P.group_m = (int)(gm < 1 ? 1 : (gm > 16 ? 16 : gm));
+  }
   P.wide_store = ((uintptr_t)out & 31) == 0;
 #ifdef MOE_TC_TRACE
   { const char* t = getenv(gemm1 ? "MOE_TRACE1" : "MOE_TRACE2"); P.trace = t ? (long long*)strtoull(t, nullptr, 0) : nullptr; }
