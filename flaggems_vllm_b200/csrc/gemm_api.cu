@@ -12,7 +12,7 @@ int tc_gemm(bool gemm1, int mode, int act_dtype, const void* a, const float* a_s
             const float* w_scale, const int32_t* expert_ids, const int32_t* sorted_ids, const int32_t* npp,
             const float* route_weight, int mul_weight, int64_t numel, int64_t rows_cap, int64_t a_tokens, int topk,
             int block_m, int E, int K, int Nout, void* out, float* out_scales_t, int32_t* status, cudaStream_t st,
-            int variant, int a_sorted);
+            int variant, int a_sorted, int32_t* inv = nullptr);
 int w8_gemm(bool gemm1, int act_dtype, const void* a, const void* w, const float* w_scale, const int32_t* expert_ids,
             const int32_t* sorted_ids, const int32_t* npp, const float* route_weight, int mul_weight, int64_t numel,
             int64_t rows_cap, int64_t a_tokens, int topk, int block_m, int E, int K, int Nout, void* out,
@@ -120,4 +120,22 @@ extern "C" int moe_debug_wait_timeout(int32_t* status, unsigned long long limit_
   if (limit_ns == 0 || limit_ns > 100000000ull) return fail(MOE_E_BADARG, "debug_wait_timeout: limit must be 1 ns .. 100 ms");
   wait_timeout_probe_kernel<<<1, 32, 0, (cudaStream_t)stream>>>(status, limit_ns, gave_up);
   return check_launch("debug_wait_timeout");
+}
+
+extern "C" int moe_gemm2_sorted(int mode, int act_dtype, const void* act_sorted, const float* act_scales_t, const void* w2,
+                                const float* w2_scale, const int32_t* expert_ids, const int32_t* sorted_ids,
+                                const int32_t* num_post_pad, const float* route_weight, int mul_weight, int64_t numel,
+                                int64_t rows_cap, int block_m, int E, int H, int I, void* y_sorted, int32_t* inv,
+                                int32_t* status, void* stream) {
+  using namespace moe;
+  int rc = check_common("gemm2 (sorted output)", mode, act_sorted, act_scales_t, w2, w2_scale, expert_ids, sorted_ids,
+                        num_post_pad, route_weight, mul_weight, numel, rows_cap, block_m, E, H, I, y_sorted);
+  if (rc) return rc;
+  if (!inv) return fail(MOE_E_BADARG, "gemm2 (sorted output): route index buffer missing");
+  if (mode != MOE_MODE_FP8_BLOCK && mode != MOE_MODE_HALF)
+    return fail(MOE_E_SHAPE, "gemm2 (sorted output): FP8 block-scale and half-precision modes only");
+  if (rows_cap == 0 || numel == 0) return 0;
+  return tc_gemm(false, mode, act_dtype, act_sorted, act_scales_t, w2, w2_scale, expert_ids, sorted_ids, num_post_pad,
+                 route_weight, mul_weight, numel, rows_cap, 0, 1, block_m, E, I, H, y_sorted, nullptr, status,
+                 (cudaStream_t)stream, 1, 0, inv);
 }

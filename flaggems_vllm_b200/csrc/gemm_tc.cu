@@ -96,7 +96,11 @@ struct SmemAux {
   float sc_a[SCALE_SLOTS][BM];  // activation scale of each tile row
   float sc_w[SCALE_SLOTS][4];   // weight scales of the two column halves
 };
-template <bool PAIR, int RB> constexpr size_t smem_bytes() { return (size_t)Cfg<PAIR, RB>::STAGES * Cfg<PAIR, RB>::STAGE_BYTES + sizeof(SmemAux) + 1024; }
+constexpr int OUT_STAGE_BYTES = BM * BN * 2;  // staged output tile of the TMAOUT variant
+template <bool PAIR, int RB, bool TMAOUT = false> constexpr size_t smem_bytes() {
+  return TMAOUT ? (size_t)3 * Cfg<PAIR, RB>::STAGE_BYTES + sizeof(SmemAux) + 1024 + OUT_STAGE_BYTES + 1024
+                : (size_t)Cfg<PAIR, RB>::STAGES * Cfg<PAIR, RB>::STAGE_BYTES + sizeof(SmemAux) + 1024;
+}
 
 struct Params {
   const uint8_t* a_rows;    // GEMM1: activations [tokens, K] in token order (gathered by cp.async)
@@ -108,6 +112,7 @@ struct Params {
   const float* route_weight;
   void* out;
   float* out_scales_t;      // [I/128, rows_cap]          (FP8 GEMM1)
+  int32_t* inv;             // TMAOUT: [numel] sorted row of every route
   int32_t* status;
   unsigned long long wait_ns;  // limit of every bounded barrier wait
   int64_t numel;
@@ -185,13 +190,23 @@ __device__ __forceinline__ int box_row(int nt, int c, int cr, int Nout) {
 // With many rows per expert the in-kernel cp.async gather is the limiter of GEMM1 (its
 // per-lane requests keep the load/store unit busier than the tensor core: 1.07 against
 // 1.37 PFLOP/s for the TMA-fed GEMM2 on the Mixtral shape), and the copy costs far less.
-template <bool FP8, typename AT, bool GEMM1, bool PAIR, int RB, bool SORTED = false>
+//
+// TMAOUT (GEMM2, single CTA): the output tile is staged in shared memory (bf16 / f16, the layout
+// a 128-byte-swizzled tensor map expects) and written by TMA bulk stores to y in SORTED row
+// order; the kernel also records where every route's row went (P.inv[route] = sorted row) for
+// the combine.  A thread owns one tile row, so direct stores hand the memory system 32
+// separate 32-byte sectors per warp instruction, and the consumers -- the same warps that fold
+// the next tile -- sat in those stores for ~5000 cycles per tile; staged, they are done after
+// sixteen conflict-free shared-memory stores.  Costs one pipeline stage of shared memory.
+template <bool FP8, typename AT, bool GEMM1, bool PAIR, int RB, bool SORTED = false, bool TMAOUT = false>
 __global__ void __launch_bounds__(THREADS, 1)
-tc_gemm_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant__ CUtensorMap map_b, const Params P) {
+tc_gemm_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant__ CUtensorMap map_b,
+               const __grid_constant__ CUtensorMap map_out, const Params P) {
+  static_assert(!TMAOUT || (!GEMM1 && !PAIR && RB == 1), "staged output: single-CTA GEMM2 only");
   static_assert(!SORTED || (GEMM1 && !PAIR), "pre-sorted A rows: single-CTA GEMM1 only");
   constexpr bool GATHER = GEMM1 && !SORTED;  // A rows gathered inside the kernel
   static_assert(RB == 1 || (RB == 2 && !FP8), "wide tiles: half precision only");
-  constexpr int STAGES = Cfg<PAIR, RB>::STAGES;
+  constexpr int STAGES = TMAOUT ? 3 : Cfg<PAIR, RB>::STAGES;
   constexpr int A_LOCAL_BYTES = Cfg<PAIR, RB>::A_LOCAL;
   constexpr int B_LOCAL_BYTES = PAIR ? B_HALF_BYTES : B_STAGE_BYTES;
   extern __shared__ uint8_t smem_raw[];
@@ -199,6 +214,8 @@ tc_gemm_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant_
   uint8_t* sA = smem;
   uint8_t* sB = smem + (size_t)STAGES * A_LOCAL_BYTES;
   SmemAux* aux = reinterpret_cast<SmemAux*>(smem + (size_t)STAGES * Cfg<PAIR, RB>::STAGE_BYTES);
+  // staged output tile: four sub-tiles of 128 rows x 64 columns (128 bytes per row), 1024-byte aligned
+  [[maybe_unused]] uint8_t* s_out = smem + (((size_t)STAGES * Cfg<PAIR, RB>::STAGE_BYTES + sizeof(SmemAux) + 1023) & ~(size_t)1023);
 
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
   constexpr int KBE = FP8 ? 128 : 64;  // elements of K per stage
@@ -693,6 +710,33 @@ tc_gemm_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant_
                                    pack2<AT>(acc[v * 8 + 4], acc[v * 8 + 5]), pack2<AT>(acc[v * 8 + 6], acc[v * 8 + 7]));
           store_row_pieces(reinterpret_cast<AT*>(P.out) + p * P.Nout + col0, pieces, P.wide_store);
         }
+      } else if constexpr (TMAOUT) {
+        // the previous tile's bulk stores have finished reading the staging buffer
+        if (threadIdx.x == 128) asm volatile("cp.async.bulk.wait_group.read 0;" ::: "memory");
+        asm volatile("bar.sync 2, %0;" ::"n"(EPI_THREADS) : "memory");
+#pragma unroll
+        for (int c = 0; c < 16; ++c) {  // 16-byte chunk c of this thread's 128 columns -> sub-tile 2h + c/8, chunk c%8
+          const uint4 piece = make_uint4(pack2<AT>(acc[c * 8 + 0] * rw, acc[c * 8 + 1] * rw),
+                                         pack2<AT>(acc[c * 8 + 2] * rw, acc[c * 8 + 3] * rw),
+                                         pack2<AT>(acc[c * 8 + 4] * rw, acc[c * 8 + 5] * rw),
+                                         pack2<AT>(acc[c * 8 + 6] * rw, acc[c * 8 + 7] * rw));
+          uint8_t* dst = s_out + (size_t)(2 * h + (c >> 3)) * (BM * 128) + row * 128 + (((c & 7) ^ (row & 7)) << 4);
+          *reinterpret_cast<uint4*>(dst) = piece;
+        }
+        if (row_ok && h == 0) P.inv[sid] = (int32_t)p;
+        asm volatile("fence.proxy.async.shared::cta;" ::: "memory");  // generic-proxy writes -> TMA reads
+        asm volatile("bar.sync 2, %0;" ::"n"(EPI_THREADS) : "memory");
+        if (threadIdx.x == 128) {
+#pragma unroll
+          for (int q4 = 0; q4 < 4; ++q4) {
+            const int c0 = nt * BN + q4 * 64;
+            if (c0 < P.Nout)
+              asm volatile("cp.async.bulk.tensor.2d.global.shared::cta.bulk_group [%0, {%1, %2}], [%3];"
+                           ::"l"(&map_out), "r"(c0), "r"((int)(mb * BM)), "r"(smem_u32(s_out + (size_t)q4 * (BM * 128)))
+                           : "memory");
+          }
+          asm volatile("cp.async.bulk.commit_group;" ::: "memory");
+        }
       } else if (row_ok) {
         const int col0 = nt * BN + 128 * h;
         AT* o = reinterpret_cast<AT*>(P.out) + sid * P.Nout + col0;
@@ -717,6 +761,9 @@ tc_gemm_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant_
   }
 
   // -------------------------------------------------------------------- teardown
+  if constexpr (TMAOUT) {
+    if (threadIdx.x == 128) asm volatile("cp.async.bulk.wait_group 0;" ::: "memory");  // the last tile's stores are complete
+  }
   tc_fence_before();
   if constexpr (PAIR) cluster_sync_all();  // no CTA leaves while its partner may still signal its barriers
   else __syncthreads();
@@ -734,10 +781,11 @@ tc_gemm_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant_
 }
 
 // ------------------------------------------------------------------ host side
-template <bool FP8, typename AT, bool GEMM1, bool PAIR, int RB, bool SORTED = false>
-static int launch(const CUtensorMap& ma, const CUtensorMap& mb, const Params& P, int grid, cudaStream_t st) {
-  auto kern = tc_gemm_kernel<FP8, AT, GEMM1, PAIR, RB, SORTED>;
-  constexpr size_t smem = smem_bytes<PAIR, RB>();
+template <bool FP8, typename AT, bool GEMM1, bool PAIR, int RB, bool SORTED = false, bool TMAOUT = false>
+static int launch(const CUtensorMap& ma, const CUtensorMap& mb, const Params& P, int grid, cudaStream_t st,
+                  const CUtensorMap* mo = nullptr) {
+  auto kern = tc_gemm_kernel<FP8, AT, GEMM1, PAIR, RB, SORTED, TMAOUT>;
+  constexpr size_t smem = smem_bytes<PAIR, RB, TMAOUT>();
   cudaFuncAttributes fa;
   cudaError_t ce = cudaFuncGetAttributes(&fa, kern);
   if (ce != cudaSuccess) return fail((int)ce, "tensor-core GEMM: cudaFuncGetAttributes: %s", cudaGetErrorString(ce));
@@ -759,7 +807,7 @@ static int launch(const CUtensorMap& ma, const CUtensorMap& mb, const Params& P,
   attr[0].val.clusterDim.z = 1;
   cfg.attrs = attr;
   cfg.numAttrs = 1;
-  ce = cudaLaunchKernelEx(&cfg, kern, ma, mb, P);
+  ce = cudaLaunchKernelEx(&cfg, kern, ma, mb, mo != nullptr ? *mo : ma, P);
   if (ce != cudaSuccess) return fail((int)ce, "tensor-core GEMM launch: %s", cudaGetErrorString(ce));
   return check_launch(GEMM1 ? "gemm1 (tcgen05)" : "gemm2 (tcgen05)");
 }
@@ -772,7 +820,9 @@ int tc_gemm(bool gemm1, int mode, int act_dtype, const void* a, const float* a_s
             const float* w_scale, const int32_t* expert_ids, const int32_t* sorted_ids, const int32_t* npp,
             const float* route_weight, int mul_weight, int64_t numel, int64_t rows_cap, int64_t a_tokens, int topk,
             int block_m, int E, int K, int Nout, void* out, float* out_scales_t, int32_t* status, cudaStream_t st,
-            int variant, int a_sorted) {
+            int variant, int a_sorted, int32_t* inv) {
+  // inv (gemm2, variant 1): `out` is y in SORTED row order [rows_cap, Nout], written by TMA from a staged
+  //   tile, and inv[route] receives the sorted row of every route
   // a_sorted (gemm1): `a` holds [rows_cap, K] rows already in sorted order (moe_gather_rows)
   // variant: 1 = one CTA per 128-row block, 2 = cta_group::2 CTA pair per 256-row block,
   //          3 = one CTA per 256-row block with a 256x256 tile (half precision only),
@@ -821,7 +871,7 @@ int tc_gemm(bool gemm1, int mode, int act_dtype, const void* a, const float* a_s
   if (sorted && (topk <= 0 || a_tokens * topk != numel)) return fail(MOE_E_BADARG, "tensor-core GEMM1: tokens * topk != numel");
   P.a_rows = (const uint8_t*)a; P.a_scale_ld = (gemm1 && !sorted) ? a_tokens : rows_cap; P.topk = gemm1 ? topk : 1;
   P.a_scales_t = a_scales_t; P.w_scale = w_scale; P.expert_ids = expert_ids; P.sorted_ids = sorted_ids;
-  P.num_post_pad = npp; P.route_weight = route_weight; P.out = out; P.out_scales_t = out_scales_t;
+  P.num_post_pad = npp; P.route_weight = route_weight; P.out = out; P.out_scales_t = out_scales_t; P.inv = nullptr;
   P.status = status; P.wait_ns = wait_limit_ns(); P.numel = numel; P.rows_cap = rows_cap; P.mul_weight = mul_weight; P.E = E; P.K = K;
   P.Nout = Nout; P.rows_w = rows_w;
   P.n_tiles = gemm1 ? Nout / 128 : (Nout + BN - 1) / BN;
@@ -846,6 +896,19 @@ int tc_gemm(bool gemm1, int mode, int act_dtype, const void* a, const float* a_s
 #define MOE_TC_LAUNCH2(F, T, G) \
   (pair ? launch<F, T, G, true, 1>(ma, mb, P, grid, st) : launch<F, T, G, false, 1>(ma, mb, P, grid, st))
 #define MOE_TC_LAUNCH(F, T) (gemm1 ? MOE_TC_LAUNCH2(F, T, true) : MOE_TC_LAUNCH2(F, T, false))
+  if (inv != nullptr) {
+    if (gemm1 || variant != 1) return fail(MOE_E_SHAPE, "tensor-core GEMM: sorted output is written by GEMM2 of kernel 1 only");
+    CUtensorMap mo;
+    rc = make_map(&mo, out, act_dtype == MOE_BF16 ? CU_TENSOR_MAP_DATA_TYPE_BFLOAT16 : CU_TENSOR_MAP_DATA_TYPE_FLOAT16, 2,
+                  (uint64_t)rows_cap, (uint64_t)Nout, BM, false);
+    if (rc) return rc;
+    P.inv = inv;
+    if (fp8)
+      return act_dtype == MOE_BF16 ? launch<true, __nv_bfloat16, false, false, 1, false, true>(ma, mb, P, grid, st, &mo)
+                                   : launch<true, __half, false, false, 1, false, true>(ma, mb, P, grid, st, &mo);
+    return act_dtype == MOE_BF16 ? launch<false, __nv_bfloat16, false, false, 1, false, true>(ma, mb, P, grid, st, &mo)
+                                 : launch<false, __half, false, false, 1, false, true>(ma, mb, P, grid, st, &mo);
+  }
   if (fp8 && sorted)
     return act_dtype == MOE_BF16 ? launch<true, __nv_bfloat16, true, false, 1, true>(ma, mb, P, grid, st)
                                  : launch<true, __half, true, false, 1, true>(ma, mb, P, grid, st);

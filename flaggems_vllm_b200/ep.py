@@ -94,12 +94,12 @@ class ExpertParallelMoE:
         return self._lanes
 
     def _compute_cuda(self, a_rows, a_scales_t, slot_weights, slot_ids, act_dtype):
-        y = route_pipeline(a_rows, a_scales_t, self.w1, self.w2, slot_weights, slot_ids, mode=self.mode,
-                           act_dtype=act_dtype, w1_scale=self.s1, w2_scale=self.s2,
-                           global_num_experts=self.E_local, expert_map=None,
-                           apply_router_weight_on_input=False)
+        y, row_index = route_pipeline(a_rows, a_scales_t, self.w1, self.w2, slot_weights, slot_ids, mode=self.mode,
+                                      act_dtype=act_dtype, w1_scale=self.s1, w2_scale=self.s2,
+                                      global_num_experts=self.E_local, expert_map=None,
+                                      apply_router_weight_on_input=False)
         rows = torch.empty((a_rows.shape[0], y.shape[1]), dtype=act_dtype, device=y.device)
-        combine_routes(y, rows, slot_ids, self.E_local)  # slots of other ranks (-1) are skipped
+        combine_routes(y, rows, slot_ids, self.E_local, row_index=row_index)  # slots of other ranks (-1) are skipped
         return rows
 
     def _combine_cuda(self, rows_back, out, index):

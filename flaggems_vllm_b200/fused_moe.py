@@ -105,6 +105,18 @@ def _presort_rows(mode, kernel, numel, num_experts) -> bool:
     return numel >= (128 if mode == _lib.MODE_FP8_BLOCK else 256) * num_experts
 
 
+def _sorted_output(mode, kernel, numel, num_experts) -> bool:
+    """GEMM2 of the 128-row tensor-core kernel writes its rows in sorted order through a staged tile and
+    TMA stores (FP8 block scales and half precision) when experts own enough rows for the epilogue to
+    matter: from 64 rows per expert on.  FLAGGEMS_B200_TMA_OUT = 0/1 forces it off/on."""
+    if kernel != KERNEL_TC or mode not in (_lib.MODE_FP8_BLOCK, _lib.MODE_HALF):
+        return False
+    force = _policy("FLAGGEMS_B200_TMA_OUT")
+    if force != "auto":
+        return force == "on"
+    return numel >= 64 * num_experts
+
+
 def _tc_eligible(mode: int, act_dtype: torch.dtype, H: int, I: int) -> bool:
     if act_dtype not in (torch.bfloat16, torch.float16):
         return False
@@ -281,10 +293,11 @@ def route_pipeline(a_rows, a_scales_t, w1, w2, route_weight, topk_ids, *, mode, 
                    keep=None, mark=None, act_fn=(0, 0.0, 0.0, 0.0), row_quant=None):
     """align -> GEMM1 -> GEMM2 for ``a_rows`` [tokens, H] (activation dtype, or
     e4m3 with ``a_scales_t`` [H/128, tokens] in FP8 mode) and ``topk_ids``
-    [tokens, k].  Returns y [tokens * k, H] in ``act_dtype``: row = flat route
-    index, already multiplied by the route weight (unless the weight was
-    applied on the input).  Rows of routes whose expert is not local are left
-    unwritten.  ``act_fn`` = (activation code, alpha, beta, limit).  Row-scaled W8A8 modes:
+    [tokens, k].  Returns ``(y, row_index)``: y holds one row per route in ``act_dtype``, already
+    multiplied by the route weight (unless the weight was applied on the input).  With
+    ``row_index`` None, y is [tokens * k, H] and row = flat route index; otherwise y is in
+    sorted order [rows_cap, H] and ``row_index`` [tokens, k] names the row of every route.  Rows
+    (and index entries) of routes whose expert is not local are left unwritten.  ``act_fn`` = (activation code, alpha, beta, limit).  Row-scaled W8A8 modes:
     ``a_rows`` is e4m3 / int8 with ``a_scales_t`` [tokens]; ``row_quant`` = (kind, static scale or
     None) says how the intermediate is quantised between the two GEMMs."""
     if mark is None:
@@ -369,17 +382,28 @@ def route_pipeline(a_rows, a_scales_t, w1, w2, route_weight, topk_ids, *, mode, 
                                        sc.data_ptr(), st))
         act_scales = sc if per_row else sc.expand(rows_cap).contiguous()
         mark("quant2")
-    y = torch.empty((numel, H), dtype=act_dtype, device=dev)
-    _lib.check(L.moe_gemm2(mode, act_code, act_in.data_ptr(), _lib.ptr(act_scales), w2.data_ptr(), _lib.ptr(w2_scale),
-                           expert_ids.data_ptr(), sorted_ids.data_ptr(), npp.data_ptr(), rw.data_ptr(),
-                           int(not apply_router_weight_on_input), numel, rows_cap, block_m, E_local, H, I,
-                           y.data_ptr(), tc, status.data_ptr(), st))
+    row_index = None
+    if _sorted_output(mode, kernel, numel, global_num_experts):
+        # the 128-row kernel stages its output tile and writes whole tiles (TMA) in sorted row order;
+        # the combine finds a route's row through `row_index`
+        y = torch.empty((rows_cap, H), dtype=act_dtype, device=dev)
+        row_index = torch.empty((M, k), dtype=torch.int32, device=dev)
+        _lib.check(L.moe_gemm2_sorted(mode, act_code, act_in.data_ptr(), _lib.ptr(act_scales), w2.data_ptr(),
+                                      _lib.ptr(w2_scale), expert_ids.data_ptr(), sorted_ids.data_ptr(), npp.data_ptr(),
+                                      rw.data_ptr(), int(not apply_router_weight_on_input), numel, rows_cap, block_m,
+                                      E_local, H, I, y.data_ptr(), row_index.data_ptr(), status.data_ptr(), st))
+    else:
+        y = torch.empty((numel, H), dtype=act_dtype, device=dev)
+        _lib.check(L.moe_gemm2(mode, act_code, act_in.data_ptr(), _lib.ptr(act_scales), w2.data_ptr(),
+                               _lib.ptr(w2_scale), expert_ids.data_ptr(), sorted_ids.data_ptr(), npp.data_ptr(),
+                               rw.data_ptr(), int(not apply_router_weight_on_input), numel, rows_cap, block_m, E_local,
+                               H, I, y.data_ptr(), tc, status.data_ptr(), st))
     mark("gemm2")
     if keep is not None:
         keep.update(sorted_ids=sorted_ids, expert_ids=expert_ids, num_post_pad=npp, a_rows=a_rows,
                     a_scales_t=a_scales_t, act=act, act_scales_t=act_scales, y=y, block_m=block_m,
-                    rows_cap=rows_cap, used_tensor_cores=kernel != KERNEL_GENERIC, kernel=kernel)
-    return y
+                    rows_cap=rows_cap, used_tensor_cores=kernel != KERNEL_GENERIC, kernel=kernel, row_index=row_index)
+    return y, row_index
 
 
 def combine_routes(y, out, topk_ids, global_num_experts, expert_map=None, row_index=None):
@@ -442,11 +466,11 @@ def run_chunk(x, w1, w2, topk_weights, topk_ids, out, *, mode, w1_scale, w2_scal
     else:
         a_rows, a_scales = x, None
     mark("quant")
-    y = route_pipeline(a_rows, a_scales, w1, w2, topk_weights, topk_ids, mode=mode, act_dtype=x.dtype,
+    y, row_index = route_pipeline(a_rows, a_scales, w1, w2, topk_weights, topk_ids, mode=mode, act_dtype=x.dtype,
                        w1_scale=w1_scale, w2_scale=w2_scale, global_num_experts=global_num_experts,
                        expert_map=expert_map, apply_router_weight_on_input=apply_router_weight_on_input,
                        use_tensor_cores=use_tensor_cores, keep=keep, mark=mark, act_fn=act_fn, row_quant=row_quant2)
-    combine_routes(y, out, topk_ids, global_num_experts, expert_map)
+    combine_routes(y, out, topk_ids, global_num_experts, expert_map, row_index=row_index)
     mark("sum")
 
 

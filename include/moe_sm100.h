@@ -279,6 +279,19 @@ int moe_gemm2(int mode, int act_dtype, const void* act_sorted, const float* act_
               void* y, int use_tensor_cores, int32_t* status, void* stream);
 
 /*
+ * moe_gemm2 on the 128-row tcgen05 kernel (use_tensor_cores = 1; FP8 block scales or half precision)
+ * with the route rows written in SORTED order: y_sorted [rows_cap, H] receives row p of the sorted
+ * intermediate at row p (whole tiles, staged in shared memory and written by TMA bulk stores), and
+ * inv[route] = p for every routed (token, slot).  moe_sum then reads the rows through
+ * row_index = inv.  Same arithmetic as moe_gemm2; only where the rows land differs.
+ */
+int moe_gemm2_sorted(int mode, int act_dtype, const void* act_sorted, const float* act_scales_t, const void* w2,
+                     const float* w2_scale, const int32_t* expert_ids, const int32_t* sorted_ids,
+                     const int32_t* num_post_pad, const float* route_weight, int mul_weight, int64_t numel,
+                     int64_t rows_cap, int block_m, int E, int H, int I, void* y_sorted, int32_t* inv,
+                     int32_t* status, void* stream);
+
+/*
  * Small-batch schedule of the two expert GEMMs (weight streaming, split-K): align blocks of
  * 8 routes, every routed expert's weights read once, K cut into slices whose fp32 partial
  * tiles are added in slice order by whichever CTA finishes a tile last (no floating-point
