@@ -62,7 +62,7 @@ extern "C" int moe_gemm1_ex(int mode, int act_dtype, const void* a, int a_sorted
   if (mode == MOE_MODE_FP8_BLOCK && !out_scales_t) return fail(MOE_E_BADARG, "gemm1: output scale buffer missing");
   if (rows_cap == 0 || numel == 0) return 0;
   if (a_sorted && !((mode == MOE_MODE_HALF && (use_tensor_cores == 1 || use_tensor_cores == 3)) ||
-                    (mode == MOE_MODE_FP8_BLOCK && use_tensor_cores == 1)))
+                    (mode == MOE_MODE_FP8_BLOCK && (use_tensor_cores == 1 || use_tensor_cores == 2))))
     return fail(MOE_E_SHAPE, "gemm1: pre-sorted rows are read by the tensor-core kernels 1 (half, fp8) and 3 (half) only");
   if (use_tensor_cores && mode == MOE_MODE_W8A16)  // int8 weights widened inside the kernel
     return w8_gemm(true, act_dtype, a, w1, w1_scale, expert_ids, sorted_ids, num_post_pad, route_weight, mul_weight,

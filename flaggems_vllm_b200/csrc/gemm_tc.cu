@@ -203,7 +203,7 @@ __global__ void __launch_bounds__(THREADS, 1)
 tc_gemm_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant__ CUtensorMap map_b,
                const __grid_constant__ CUtensorMap map_out, const Params P) {
   static_assert(!TMAOUT || (!GEMM1 && !PAIR && RB == 1), "staged output: single-CTA GEMM2 only");
-  static_assert(!SORTED || (GEMM1 && !PAIR), "pre-sorted A rows: single-CTA GEMM1 only");
+  static_assert(!SORTED || GEMM1, "pre-sorted A rows: GEMM1 only");
   constexpr bool GATHER = GEMM1 && !SORTED;  // A rows gathered inside the kernel
   static_assert(RB == 1 || (RB == 2 && !FP8), "wide tiles: half precision only");
   constexpr int STAGES = TMAOUT ? 3 : Cfg<PAIR, RB>::STAGES;
@@ -833,8 +833,8 @@ int tc_gemm(bool gemm1, int mode, int act_dtype, const void* a, const float* a_s
   if (wide && mode != MOE_MODE_HALF) return fail(MOE_E_SHAPE, "tensor-core GEMM: the 256-row-per-CTA tiles serve half precision only");
   const bool fp8 = mode == MOE_MODE_FP8_BLOCK;
   const bool sorted = gemm1 && a_sorted != 0;
-  if (sorted && (pair || (fp8 && wide)))
-    return fail(MOE_E_SHAPE, "tensor-core GEMM1: pre-sorted rows are served by the single-CTA kernels");
+  if (sorted && ((pair && !fp8) || (fp8 && wide)))
+    return fail(MOE_E_SHAPE, "tensor-core GEMM1: pre-sorted rows are served by the single-CTA kernels and the FP8 CTA pair");
   if (mode != MOE_MODE_FP8_BLOCK && mode != MOE_MODE_HALF)
     return fail(MOE_E_SHAPE, "tensor-core GEMM: mode %d is served by the generic kernel", mode);
   if (act_dtype != MOE_BF16 && act_dtype != MOE_F16)
@@ -909,6 +909,9 @@ int tc_gemm(bool gemm1, int mode, int act_dtype, const void* a, const float* a_s
     return act_dtype == MOE_BF16 ? launch<false, __nv_bfloat16, false, false, 1, false, true>(ma, mb, P, grid, st, &mo)
                                  : launch<false, __half, false, false, 1, false, true>(ma, mb, P, grid, st, &mo);
   }
+  if (fp8 && sorted && pair)
+    return act_dtype == MOE_BF16 ? launch<true, __nv_bfloat16, true, true, 1, true>(ma, mb, P, grid, st)
+                                 : launch<true, __half, true, true, 1, true>(ma, mb, P, grid, st);
   if (fp8 && sorted)
     return act_dtype == MOE_BF16 ? launch<true, __nv_bfloat16, true, false, 1, true>(ma, mb, P, grid, st)
                                  : launch<true, __half, true, false, 1, true>(ma, mb, P, grid, st);

@@ -95,7 +95,7 @@ def _presort_rows(mode, kernel, numel, num_experts) -> bool:
     (e4m3 rows and their transposed scales) on the 128-row kernel with >= 128 rows per expert.
     FLAGGEMS_B200_PRESORT = 0/1 forces it off/on."""
     if mode == _lib.MODE_FP8_BLOCK:
-        if kernel != KERNEL_TC:
+        if kernel not in (KERNEL_TC, KERNEL_TC_PAIR):
             return False
     elif mode != _lib.MODE_HALF or kernel not in (KERNEL_TC, KERNEL_TC_WIDE):
         return False
