@@ -601,6 +601,37 @@ def main():
             prev = ev
     status = fg.read_status(dev)
 
+    # ---- expert parallel: where the step's time goes and what the all-to-alls achieve.  A few extra
+    # steps with an event after every stage (outside the timed region above); bytes are the rows that
+    # leave this GPU, the time of a collective includes waiting for the slowest peer to reach it.
+    ep_stages = None
+    if world > 1 and args.ep_chunks == 1:
+        stage_events.clear()
+        timed(device_step, 5, record_stages=True)
+        per = {}
+        prev = None
+        for name, ev in stage_events:
+            if name != "begin" and prev is not None:
+                per.setdefault(name, []).append(prev.elapsed_time(ev))
+            prev = ev
+        med = {n: sorted(v)[len(v) // 2] for n, v in per.items()}
+        nb = layer.last_bytes
+        t = torch.tensor([med.get("ep_dispatch", 0.0), med.get("ep_combine", 0.0), float(nb["dispatch"]),
+                          float(nb["combine"])], dtype=torch.float64, device=dev)
+        tmax = t.clone()
+        dist.all_reduce(tmax, op=dist.ReduceOp.MAX)
+        dist.all_reduce(t, op=dist.ReduceOp.SUM)
+        mean = (t / world).tolist()
+        ep_stages = {
+            "stage_ms_rank0": med,
+            "a2a": {"dispatch_ms_max": float(tmax[0]), "combine_ms_max": float(tmax[1]),
+                    "dispatch_bytes_out_per_gpu": mean[2], "combine_bytes_out_per_gpu": mean[3],
+                    "dispatch_gbs_per_gpu": mean[2] / (float(tmax[0]) * 1e-3) / 1e9 if tmax[0] > 0 else None,
+                    "combine_gbs_per_gpu": mean[3] / (float(tmax[1]) * 1e-3) / 1e9 if tmax[1] > 0 else None,
+                    "nvlink_gbs_per_direction": {"nominal": 900.0, "measured_peer_copy": 770.0},
+                    "note": "bytes leaving one GPU / the slowest rank's time inside the collective (waiting for "
+                            "peers included), one direction"}}
+
     # ---- end to end with host buffers through the public API
     # Every step copies its activations and router logits from pinned host memory, runs the
     # public ops, and copies the layer output back to pinned host memory.  Two figures:
@@ -733,6 +764,8 @@ def main():
                              "peak_gbs": peaks["hbm_gbs"], "frac": B / (ms * 1e-3) / 1e9 / peaks["hbm_gbs"]}
     if ep_parity is not None:
         line["ep_parity"] = ep_parity
+    if ep_stages is not None:
+        line["ep_stages"] = ep_stages
     if rank == 0 and world == 1 and not args.no_cpu_baseline and E == DSV3["E"]:
         # same sample size as the reference arm; one sizing/warm-up pass, one timed pass
         Ms, step, threads, n_used, _ = fit_reference_tokens(args.cpu_baseline_tokens, 1, 1, 60.0)

@@ -30,6 +30,7 @@ SYMBOLS = {
                                  c_int, c_int, c_int, c_int, c_float, c_int, c_void_p, c_void_p, c_void_p]),
     "moe_topk_route": (c_int, [c_void_p, c_int, c_void_p, c_void_p, c_int64, c_int, c_int, c_int, c_int, c_float,
                                c_void_p, c_void_p, c_int, c_void_p, c_void_p]),
+    "moe_map_expert_ids": (c_int, [c_void_p, c_int64, c_void_p, c_int, c_void_p]),
     "moe_align_block_size": (c_int, [c_void_p, c_int, c_int64, c_int, c_int, c_void_p, c_int64, c_void_p,
                                      c_int64, c_void_p, c_void_p, c_void_p]),
     "moe_per_token_group_quant_fp8": (c_int, [c_void_p, c_int, c_int64, c_int64, c_int, c_void_p, c_void_p,

@@ -364,3 +364,27 @@ extern "C" int moe_align_block_size(const void* topk_ids, int ids_int64, int64_t
   }
   return check_launch("align");
 }
+
+
+namespace moe {
+// expert_ids[i] = expert_map[expert_ids[i]]; ids outside [0, num_experts) (the -1 of unused
+// blocks) become -1, which every GEMM kernel skips.
+__global__ void map_expert_ids_kernel(int32_t* expert_ids, int64_t n, const int32_t* __restrict__ expert_map,
+                                      int num_experts) {
+  const int64_t i = (int64_t)blockIdx.x * blockDim.x + threadIdx.x;
+  if (i >= n) return;
+  const int e = expert_ids[i];
+  expert_ids[i] = (e >= 0 && e < num_experts) ? expert_map[e] : -1;
+}
+}  // namespace moe
+
+extern "C" int moe_map_expert_ids(int32_t* expert_ids, int64_t n, const int32_t* expert_map, int num_experts,
+                                  void* stream) {
+  using namespace moe;
+  if (n < 0 || num_experts <= 0) return fail(MOE_E_BADARG, "map_expert_ids: negative or zero extent");
+  if (n == 0) return 0;
+  if (!expert_ids || !expert_map) return fail(MOE_E_BADARG, "map_expert_ids: null pointer");
+  map_expert_ids_kernel<<<(unsigned)((n + 255) / 256), 256, 0, (cudaStream_t)stream>>>(expert_ids, n, expert_map,
+                                                                                      num_experts);
+  return check_launch("map_expert_ids");
+}

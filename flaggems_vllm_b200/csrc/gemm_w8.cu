@@ -40,17 +40,23 @@ constexpr int A_BYTES = BM * 128;
 constexpr int B_BYTES = BN * 128;
 constexpr int RAW_BYTES = BN * KBE;
 constexpr int SA = 4, SB = 2, SR = 5;
-constexpr int THREADS = 640;
+#ifndef MOE_W8_CONV_WARPS
+#define MOE_W8_CONV_WARPS 12
+#define MOE_W8_LAUNCH_REGS 96
+#define MOE_W8_CONV_REGS 72
+#define MOE_W8_EPI_REGS 208
+#endif
 constexpr int EPI_WARPS = 4;
-constexpr int CONV_WARPS = 12;
+constexpr int CONV_WARPS = MOE_W8_CONV_WARPS;
+constexpr int THREADS = 256 + 32 * CONV_WARPS;
 constexpr int CONV_THREADS = CONV_WARPS * 32;
 constexpr int GATHER_THREADS = 64;
 // setmaxnreg moves registers inside the CTA's launch allocation (THREADS x LAUNCH_REGS);
 // the epilogue's increase must be covered by what the other warps give up.
-constexpr int LAUNCH_REGS = 96;
+constexpr int LAUNCH_REGS = MOE_W8_LAUNCH_REGS;
 constexpr int PRODUCER_REGS = 56;
-constexpr int CONV_REGS = 72;
-constexpr int EPI_REGS = 208;
+constexpr int CONV_REGS = MOE_W8_CONV_REGS;
+constexpr int EPI_REGS = MOE_W8_EPI_REGS;
 static_assert(128 * PRODUCER_REGS + CONV_THREADS * CONV_REGS + EPI_WARPS * 32 * EPI_REGS <= THREADS * LAUNCH_REGS,
               "register redistribution exceeds the CTA's allocation");
 static_assert(THREADS * LAUNCH_REGS <= 65536, "CTA does not fit the register file");

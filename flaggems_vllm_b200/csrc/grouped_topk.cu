@@ -28,13 +28,16 @@ __device__ __forceinline__ uint32_t ordered_bits(float v) {
 __device__ __forceinline__ uint64_t make_key(float v, uint32_t idx) {
   return ((uint64_t)ordered_bits(v) << 32) | (uint64_t)(0xFFFFFFFFu - idx);
 }
+// max of a 64-bit key over the warp with two 32-bit reductions (redux.sync): the largest high
+// word, then the largest low word among the lanes that hold it
 __device__ __forceinline__ uint64_t warp_max_u64(uint64_t k) {
-#pragma unroll
-  for (int off = 16; off > 0; off >>= 1) {
-    uint64_t o = __shfl_xor_sync(0xFFFFFFFFu, k, off);
-    k = o > k ? o : k;
-  }
-  return k;
+  const uint32_t hi = (uint32_t)(k >> 32), lo = (uint32_t)k;
+  const uint32_t mh = __reduce_max_sync(0xFFFFFFFFu, hi);
+  const uint32_t ml = __reduce_max_sync(0xFFFFFFFFu, hi == mh ? lo : 0u);
+  return ((uint64_t)mh << 32) | ml;
+}
+__device__ __forceinline__ float from_ordered_bits(uint32_t ob) {
+  return __uint_as_float((ob & 0x80000000u) ? (ob ^ 0x80000000u) : ~ob);
 }
 
 // The routing of one token by one warp: `row` holds the token's E scores (element stride
@@ -63,30 +66,30 @@ __device__ __forceinline__ void route_row(const ST* row, int64_t stride1, const 
   }
 
   if (n_group > 1) {
-    // group score -> lane g holds the score of group g
+    // group of every register of this lane, computed once (-1: no expert)
+    int grp[VPT];
+#pragma unroll
+    for (int j = 0; j < VPT; ++j) {
+      const int e = j * 32 + lane;
+      grp[j] = e < E ? e / per_group : -1;
+    }
+    // group score -> lane g holds the score of group g.  The two largest r of a group are found
+    // on the order-preserving integer image of r (the key's high word; 0 = none): the lane's own
+    // two, then the warp's largest, then the largest of what is left once its owner gave it up.
     float my_group_score = NEG_INF;
     for (int g = 0; g < n_group; ++g) {
-      float m1 = NEG_INF, m2 = NEG_INF;
+      uint32_t b1 = 0, b2 = 0;
 #pragma unroll
       for (int j = 0; j < VPT; ++j) {
-        const int e = j * 32 + lane;
-        if (e < E && e / per_group == g) {
-          // recover r from the key's high word
-          uint32_t ob = (uint32_t)(key[j] >> 32);
-          uint32_t b = (ob & 0x80000000u) ? (ob ^ 0x80000000u) : ~ob;
-          float r = __uint_as_float(b);
-          if (r > m1) { m2 = m1; m1 = r; } else if (r > m2) { m2 = r; }
+        if (grp[j] == g) {
+          const uint32_t ob = (uint32_t)(key[j] >> 32);
+          if (ob > b1) { b2 = b1; b1 = ob; } else if (ob > b2) { b2 = ob; }
         }
       }
-#pragma unroll
-      for (int off = 16; off > 0; off >>= 1) {
-        float o1 = __shfl_xor_sync(0xFFFFFFFFu, m1, off);
-        float o2 = __shfl_xor_sync(0xFFFFFFFFu, m2, off);
-        float hi = fmaxf(m1, o1), lo = fminf(m1, o1);
-        m2 = fmaxf(lo, fmaxf(m2, o2));
-        m1 = hi;
-      }
-      float gs = per_group >= 2 ? m1 + m2 : m1;
+      const uint32_t top1 = __reduce_max_sync(0xFFFFFFFFu, b1);
+      const int owner = __ffs(__ballot_sync(0xFFFFFFFFu, b1 == top1)) - 1;
+      const uint32_t top2 = __reduce_max_sync(0xFFFFFFFFu, lane == owner ? b2 : b1);
+      const float gs = per_group >= 2 ? from_ordered_bits(top1) + from_ordered_bits(top2) : from_ordered_bits(top1);
       if (lane == g) my_group_score = gs;
     }
     // choose topk_group groups
@@ -102,7 +105,7 @@ __device__ __forceinline__ void route_row(const ST* row, int64_t stride1, const 
 #pragma unroll
     for (int j = 0; j < VPT; ++j) {
       const int e = j * 32 + lane;
-      if (e < E && !((keep_mask >> (e / per_group)) & 1u)) key[j] = make_key(NEG_INF, (uint32_t)e);
+      if (grp[j] >= 0 && !((keep_mask >> grp[j]) & 1u)) key[j] = make_key(NEG_INF, (uint32_t)e);
     }
   }
 

@@ -199,8 +199,10 @@ extern "C" int moe_router_gemm(const void* x, int x_dtype, int64_t x_ld, const v
   if (((uintptr_t)x & 15) || ((uintptr_t)w & 15)) return fail(MOE_E_BADARG, "router_gemm: operands must be 16-byte aligned");
   if ((M + kRows - 1) / kRows > 65535) return fail(MOE_E_TOOBIG, "router_gemm: serves at most %d rows", 65535 * kRows);
   cudaStream_t st = (cudaStream_t)stream;
-  // prefill-sized half-precision products run on the tensor cores
-  if (M > 64 && x_dtype == w_dtype && (x_dtype == MOE_BF16 || x_dtype == MOE_F16) && K % PK == 0) {
+  // prefill-sized half-precision products run on the tensor cores.  Its grid is one CTA per
+  // 64 x 128 logits, a handful of CTAs for a few hundred rows (130-170 us at 128-256 rows of
+  // K = 7168), where the row-streaming kernel with one CTA per logit column still wins.
+  if (M > 320 && x_dtype == w_dtype && (x_dtype == MOE_BF16 || x_dtype == MOE_F16) && K % PK == 0) {
     const dim3 grid((unsigned)((N + PN - 1) / PN), (unsigned)((M + PM - 1) / PM));
     if (grid.y > 65535) return fail(MOE_E_TOOBIG, "router_gemm: serves at most %d rows", 65535 * PM);
     if (x_dtype == MOE_BF16)

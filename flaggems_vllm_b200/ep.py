@@ -34,6 +34,7 @@ import torch
 import torch.distributed as dist
 
 from . import _lib
+from . import fused_moe as _fm
 from .fused_moe import combine_routes, route_pipeline
 from .quant import per_token_group_quant_fp8
 
@@ -78,6 +79,7 @@ class ExpertParallelMoE:
         self.w1, self.w2, self.s1, self.s2 = w1, w2, w1_scale, w2_scale
         self.mode = mode
         self.last_counts = None
+        self.last_bytes = None
         self.compute_fn = compute_fn or self._compute_cuda
         self.combine_fn = combine_fn or self._combine_cuda
         # Token chunks run as independent dispatch/compute/combine steps on their own streams and
@@ -154,11 +156,14 @@ class ExpertParallelMoE:
         _lib.check(L.moe_ep_plan(ids.data_ptr(), M, k, self.E_local, R, index.data_ptr(), both[0].data_ptr(),
                                  tok.data_ptr(), st))
         group = group if group is not None else self.group
+        mark = _fm.STAGE_HOOK or _fm._no_mark  # the timing hook of the single-GPU pipeline also sees these stages
+        mark("ep_plan")
         dist.all_to_all_single(both[1], both[0], group=group)
         counts = both.tolist()  # the one host sync of the step
         send_splits, recv_splits = counts[0], counts[1]
         n_send, n_recv = sum(send_splits), sum(recv_splits)
         self.last_counts = (send_splits, recv_splits)
+        mark("ep_counts")
 
         g = H // 128 if fp8 else 0
         if fp8:
@@ -173,24 +178,35 @@ class ExpertParallelMoE:
                                  tok.data_ptr(), n_send, rows_send.data_ptr(), side_send.data_ptr(), st))
         side_recv = torch.empty((n_recv, g + 2 * k), dtype=torch.float32, device=dev)
         a_rows = torch.empty((n_recv, H), dtype=rows_dtype, device=dev)
+        # bytes that leave this GPU (pairs whose destination is another rank), per direction of the step
+        off_rank = n_send - send_splits[self.rank]
+        self.last_bytes = {"dispatch": off_rank * (row_bytes + (g + 2 * k) * 4),
+                           "combine_in": off_rank * H * x.element_size(),
+                           "combine": (n_recv - recv_splits[self.rank]) * H * x.element_size()}
+        mark("ep_pack")
         # the fp8 rows travel as bytes (NCCL has no e4m3 all-to-all on every version)
         self._a2a(side_recv, side_send, recv_splits, send_splits, group)
         self._a2a(a_rows.view(torch.uint8) if fp8 else a_rows, rows_send.view(torch.uint8) if fp8 else rows_send,
                   recv_splits, send_splits, group)
+        mark("ep_dispatch")
         a_scales_t = torch.empty((g, n_recv), dtype=torch.float32, device=dev) if fp8 else None
         slot_ids = torch.empty((n_recv, k), dtype=torch.int32, device=dev)
         slot_w = torch.empty((n_recv, k), dtype=torch.float32, device=dev)
         _lib.check(L.moe_ep_unpack(side_recv.data_ptr(), n_recv, g, k, self.rank, self.E_local, _lib.ptr(a_scales_t),
                                    slot_ids.data_ptr(), slot_w.data_ptr(), st))
+        mark("ep_unpack")
         if n_recv > 0:
             rows = self.compute_fn(a_rows, a_scales_t, slot_w, slot_ids, x.dtype)
         else:
             rows = torch.empty((0, H), dtype=x.dtype, device=dev)
         rows_back = torch.empty((n_send, H), dtype=x.dtype, device=dev)
+        mark("ep_local_sum")
         self._a2a(rows_back, rows, send_splits, recv_splits, group)
+        mark("ep_combine")
         if out is None:
             out = torch.empty_like(x)
         self.combine_fn(rows_back, out, index)
+        mark("ep_sum")
         return out
 
     def _forward_torch(self, x: torch.Tensor, topk_weights: torch.Tensor, topk_ids: torch.Tensor) -> torch.Tensor:

@@ -235,13 +235,25 @@ def run_chunk_small(x, w1, w2, topk_weights, topk_ids, out, *, mode, w1_scale, w
         emap = emap.contiguous()
     rw = topk_weights if topk_weights.dtype == torch.float32 else topk_weights.float()
     rw = rw if rw.is_contiguous() else rw.contiguous()
-    # enough units of work for every SM: ask for more K slices when few experts are routed to
+    # K slices per tile: every CTA takes a contiguous share of the (tile, slice) units, so the step
+    # lasts ceil(units / SMs) units of (chunks per slice + a fixed cost).  Pick the slice count
+    # that minimises that product; `blocks` is exact for one token and an upper bound otherwise.
     blocks = max(1, min(numel, global_num_experts))
-    want = 2 * _sm_count(dev)
+    sms = _sm_count(dev)
+    chunk_elems = 64 if mode == _lib.MODE_HALF else 128          # K elements in 128 bytes of weights
+    max_chunks = 16 if mode == _lib.MODE_W8A16 else 32           # what one unit holds of the activation rows
+    unit_overhead = 4                                            # staging + epilogue of a unit, in chunk times
 
     def plan(gemm1, K, N):
         nt = N // 64 if gemm1 else N // 128
-        hint = max(1, min(16, -(-want // (blocks * nt))))
+        chunks = max(1, K // chunk_elems)
+        best, hint = None, 1
+        for S in range(-(-chunks // max_chunks), min(16, chunks) + 1):
+            cps = -(-chunks // S)
+            units = blocks * nt * -(-chunks // cps)
+            cost = -(-units // sms) * (cps + unit_overhead)
+            if best is None or cost < best:
+                best, hint = cost, S
         sizes = (ctypes.c_int64 * 3)()
         _lib.check(L.moe_small_m_plan(int(gemm1), mode, K, N, rows_cap, M, hint, ctypes.addressof(sizes),
                                       ctypes.addressof(sizes) + 8, ctypes.addressof(sizes) + 16))
@@ -335,7 +347,9 @@ def route_pipeline(a_rows, a_scales_t, w1, w2, route_weight, topk_ids, *, mode, 
     if expert_map is not None:
         # same post-hoc lookup as the reference (moe_align_block_size.py:924-925);
         # unused blocks (-1) lie beyond num_tokens_post_padded and are never visited
-        expert_ids = expert_map[expert_ids.long()].to(torch.int32)
+        emap = expert_map if expert_map.dtype == torch.int32 else expert_map.to(torch.int32)
+        _lib.check(L.moe_map_expert_ids(expert_ids.data_ptr(), expert_ids.numel(), emap.data_ptr(),
+                                        emap.numel(), st))
 
     fp8 = mode == _lib.MODE_FP8_BLOCK
     row_scaled = mode in (_lib.MODE_FP8_ROW, _lib.MODE_INT8_ROW)

@@ -5,7 +5,7 @@ Mirrors ``router_gemm`` (src/flaggems_vllm/ops/router_gemm.py:207-237) and
 (src/flaggems_vllm/ops/fp32_router_gemm.py:17-145): same names, argument meaning
 and error behaviour.  Both kernels of ``csrc/router_gemm.cu`` are deterministic: a
 row-streaming fp32 kernel for decode-sized batches (and for every dtype pair), a
-tensor-core (warp MMA, fp32 accumulate) kernel for half-precision batches above 64 rows.
+tensor-core (warp MMA, fp32 accumulate) kernel for half-precision batches above 320 rows.
 No library GEMM is called.  ``router_gemm_grouped_topk`` fuses the GEMM with the
 group-limited routing for decode batches (no counterpart in the reference, which runs the
 two ops back to back).

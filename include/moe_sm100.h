@@ -118,6 +118,14 @@ int moe_align_block_size(const void* topk_ids, int ids_int64, int64_t numel, int
                          int32_t* status, void* stream);
 
 /*
+ * In place: expert_ids[i] = expert_map[expert_ids[i]] for n block ids (ids outside
+ * [0, num_experts), i.e. the -1 of unused blocks, become -1).  The lookup the reference does with
+ * tensor indexing after the sort (src/flaggems_vllm/ops/moe_align_block_size.py:924-925).
+ */
+int moe_map_expert_ids(int32_t* expert_ids, int64_t n, const int32_t* expert_map, int num_experts,
+                       void* stream);
+
+/*
  * 1 x group e4m3 quantisation of rows: scale = max(amax,1e-10) * (1/448),
  * q = clamp(x / scale).  Stands in for per_token_group_quant_fp8
  * (src/flaggems_vllm/ops/per_token_group_quant_fp8.py:226-335, kernel :115-162).
