@@ -618,19 +618,27 @@ def main():
         nb = layer.last_bytes
         t = torch.tensor([med.get("ep_dispatch", 0.0), med.get("ep_combine", 0.0), float(nb["dispatch"]),
                           float(nb["combine"])], dtype=torch.float64, device=dev)
-        tmax = t.clone()
+        tmax, tmin = t.clone(), t.clone()
         dist.all_reduce(tmax, op=dist.ReduceOp.MAX)
+        dist.all_reduce(tmin, op=dist.ReduceOp.MIN)
         dist.all_reduce(t, op=dist.ReduceOp.SUM)
         mean = (t / world).tolist()
+
+        def gbs(nbytes, ms_):
+            return nbytes / (ms_ * 1e-3) / 1e9 if ms_ > 0 else None
+
         ep_stages = {
             "stage_ms_rank0": med,
-            "a2a": {"dispatch_ms_max": float(tmax[0]), "combine_ms_max": float(tmax[1]),
+            "a2a": {"dispatch_ms_max": float(tmax[0]), "dispatch_ms_min": float(tmin[0]),
+                    "combine_ms_max": float(tmax[1]), "combine_ms_min": float(tmin[1]),
                     "dispatch_bytes_out_per_gpu": mean[2], "combine_bytes_out_per_gpu": mean[3],
-                    "dispatch_gbs_per_gpu": mean[2] / (float(tmax[0]) * 1e-3) / 1e9 if tmax[0] > 0 else None,
-                    "combine_gbs_per_gpu": mean[3] / (float(tmax[1]) * 1e-3) / 1e9 if tmax[1] > 0 else None,
+                    "dispatch_gbs_per_gpu": gbs(mean[2], float(tmax[0])), "combine_gbs_per_gpu": gbs(mean[3], float(tmax[1])),
+                    "dispatch_gbs_last_arriver": gbs(mean[2], float(tmin[0])),
+                    "combine_gbs_last_arriver": gbs(mean[3], float(tmin[1])),
                     "nvlink_gbs_per_direction": {"nominal": 900.0, "measured_peer_copy": 770.0},
-                    "note": "bytes leaving one GPU / the slowest rank's time inside the collective (waiting for "
-                            "peers included), one direction"}}
+                    "note": "bytes leaving one GPU, one direction, / time inside the collective: `max` is the rank "
+                            "that waited longest for its peers (load skew included), `min` the rank that arrived "
+                            "last and saw the transfer alone"}}
 
     # ---- end to end with host buffers through the public API
     # Every step copies its activations and router logits from pinned host memory, runs the
