@@ -556,15 +556,37 @@ tc_gemm_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant_
         else mbar_arrive(&aux->tmem_empty[a]);
       }
     };
+    // The consumers' own walk over the tile list.  Coordinates, expert and this thread's sorted id
+    // of the NEXT tile are fetched inside the K loop of the current one (FP8: while the warp would
+    // wait for the tensor core anyway), so a tile starts folding without integer divisions or a
+    // dependent global load in front of it.
+    int nx_blk = 0, nx_nt = 0, nx_e = -1;
+    int64_t nx_sid = P.numel;
+    auto prefetch_tile = [&](int t) {
+      nx_e = -1;
+      nx_sid = P.numel;
+      if (t < total_tiles) {
+        tile_blk_nt(t, nx_blk, nx_nt);
+        nx_e = P.expert_ids[nx_blk];
+        const int64_t pn = (int64_t)(UNIT * nx_blk + RB * cr) * BM + row;
+        if (pn < P.rows_cap) nx_sid = (int64_t)P.sorted_ids[pn];
+      }
+    };
+    prefetch_tile(tile0);
     for (int tile = tile0; tile < total_tiles && alive; tile += tile_step) {
       if (threadIdx.x == 128) MOE_TRN(3, 61, 0);
-      MOE_TILE_COORDS(tile)
+      const int blk = nx_blk, nt = nx_nt, e = nx_e;
+      const int64_t sid_first = nx_sid;
+      [[maybe_unused]] const int mb = UNIT * blk + RB * cr;
+      (void)blk;
+      if (!FP8 || e < 0 || e >= P.E) prefetch_tile(tile + tile_step);  // half precision has no K loop here
       if (e < 0 || e >= P.E) continue;
       if (threadIdx.x == 128) MOE_TRN(3, 61, 1);
       for (int sub = 0; sub < RB && alive; ++sub) {  // the 128-row blocks of this tile (two for wide tiles)
       const int64_t p = (int64_t)(mb + sub) * BM + row;
       int64_t sid = P.numel;
-      if (p < P.rows_cap) sid = (int64_t)P.sorted_ids[p];
+      if (sub == 0) sid = sid_first;
+      else if (p < P.rows_cap) sid = (int64_t)P.sorted_ids[p];
       const bool row_ok = sid >= 0 && sid < P.numel;
       if (sid < 0 || sid > P.numel) set_status(P.status, MOE_ST_BAD_ROW);  // the pad value is numel; anything else outside is corrupt
       float acc[128];
@@ -607,6 +629,7 @@ tc_gemm_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant_
         for (int kb = 0; kb < KB; ++kb) {
           const int slot = acc_it % SCALE_SLOTS;
           if (threadIdx.x == 128) MOE_TR(3, kb, 0);
+          if (kb == (KB > 1 ? 1 : 0)) prefetch_tile(tile + tile_step);
           if (!mbar_wait(&aux->tmem_full[acc_it & 1], (acc_it >> 1) & 1, P.status, P.wait_ns)) { alive = false; break; }
           if (threadIdx.x == 128) MOE_TR(3, kb, 1);
           if (threadIdx.x == 128 && kb == 0) MOE_TRN(3, 61, 2);
