@@ -61,3 +61,73 @@ def test_status_check_mode_raises(monkeypatch):
     with pytest.raises(fg.MoeKernelError, match="status word"):
         fg.fused_experts_impl(x, w1, w2, tw.to(torch.bfloat16), bad)
     assert fg.read_status() == 0
+
+
+class _GuardedAllocator:
+    """Stands in for torch.empty inside the layer: every workspace sits between two guard bands
+    filled with a byte pattern, so a kernel that writes outside its buffer is caught."""
+
+    GUARD = 4096  # bytes on either side (keeps the 16-byte / 1024-byte alignments the kernels ask for)
+    PATTERN = 0xA5
+
+    def __init__(self):
+        self.real_empty = torch.empty
+        self.blocks = []
+
+    def __call__(self, *size, dtype=None, device=None, **kw):
+        if len(size) == 1 and not isinstance(size[0], int):
+            size = tuple(size[0])
+        dtype = dtype or torch.get_default_dtype()
+        if device is None or torch.device(device).type != "cuda" or kw:
+            return self.real_empty(*size, dtype=dtype, device=device, **kw)
+        n = 1
+        for s in size:
+            n *= int(s)
+        nbytes = n * torch.empty((), dtype=dtype).element_size()
+        padded = (nbytes + 255) // 256 * 256
+        whole = torch.full((padded + 2 * self.GUARD,), self.PATTERN, dtype=torch.uint8, device=device)
+        self.blocks.append((whole, padded))
+        return whole[self.GUARD:self.GUARD + nbytes].view(dtype).view(size)
+
+    def check(self):
+        assert self.blocks, "no workspace was allocated through the guarded allocator"
+        for whole, padded in self.blocks:
+            lo, hi = whole[:self.GUARD], whole[self.GUARD + padded:]
+            assert bool((lo == self.PATTERN).all()) and bool((hi == self.PATTERN).all()), \
+                f"a kernel wrote outside a {padded}-byte workspace"
+        return len(self.blocks)
+
+
+@pytest.mark.parametrize("mode", ["bf16", "fp8", "w8a16"])
+@pytest.mark.parametrize("M", [1, 5, 200, 1500])
+def test_guard_bands_around_every_workspace_stay_intact(monkeypatch, mode, M):
+    """All internal buffers of the layer (sorted ids, expert ids, quantised rows and scales, the
+    sorted copies, the intermediate, y, the row index, split-K partial sums) are allocated with guard
+    bands on both sides; after the layer every band still holds its pattern.  The sizes cover the
+    small-batch schedule, the 128-row kernels with row stores and the staged TMA output."""
+    E, H, I, k = 8, 512, 512, 2
+    x = T.make_activations(M, H, DEV, seed=M)
+    logits, _ = T.make_router_inputs(M, E, DEV, seed=M + 1)
+    tw, ti = fg.grouped_topk(torch.softmax(logits, -1), 1, 1, k, True, 1.0, torch.zeros(E, device=DEV), 0)
+    kw = {}
+    if mode == "bf16":
+        w1 = T.make_half_weights(E, 2 * I, H, DEV, seed=1, std=H**-0.5)
+        w2 = T.make_half_weights(E, H, I, DEV, seed=2, std=I**-0.5)
+    elif mode == "fp8":
+        w1, s1 = T.make_fp8_block_weights(E, 2 * I, H, DEV, seed=1)
+        w2, s2 = T.make_fp8_block_weights(E, H, I, DEV, seed=2)
+        kw = dict(use_fp8_w8a8=True, w1_scale=s1, w2_scale=s2, block_shape=[128, 128])
+    else:
+        w1, s1 = T.make_int8_channel_weights(E, 2 * I, H, DEV, seed=1)
+        w2, s2 = T.make_int8_channel_weights(E, H, I, DEV, seed=2)
+        kw = dict(use_int8_w8a16=True, per_channel_quant=True, w1_scale=s1, w2_scale=s2)
+    ref = fg.fused_experts_impl(x, w1, w2, tw, ti, **kw)
+    guard = _GuardedAllocator()
+    monkeypatch.setattr(torch, "empty", guard)
+    try:
+        out = fg.fused_experts_impl(x, w1, w2, tw, ti, **kw)
+        torch.cuda.synchronize()
+    finally:
+        monkeypatch.undo()
+    assert guard.check() >= 4
+    assert torch.equal(out, ref) and fg.read_status(torch.device(DEV)) == 0
