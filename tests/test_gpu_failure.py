@@ -79,11 +79,11 @@ class _GuardedAllocator:
             size = tuple(size[0])
         dtype = dtype or torch.get_default_dtype()
         if device is None or torch.device(device).type != "cuda" or kw:
-            return self.real_empty(*size, dtype=dtype, device=device, **kw)
+            return self.real_empty(tuple(size), dtype=dtype, device=device, **kw)
         n = 1
         for s in size:
             n *= int(s)
-        nbytes = n * torch.empty((), dtype=dtype).element_size()
+        nbytes = n * self.real_empty((), dtype=dtype).element_size()
         padded = (nbytes + 255) // 256 * 256
         whole = torch.full((padded + 2 * self.GUARD,), self.PATTERN, dtype=torch.uint8, device=device)
         self.blocks.append((whole, padded))
