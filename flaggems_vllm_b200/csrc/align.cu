@@ -343,7 +343,11 @@ extern "C" int moe_align_block_size(const void* topk_ids, int ids_int64, int64_t
     }
     return check_launch("align (cluster)");
   }
+  // one slice (and one histogram) per 64 ids: a decode-sized call clears and scans one or two
+  // histograms instead of 32
   int n_warps = kAlignThreads / 32;
+  const int64_t slices = (numel + 63) / 64;
+  if (slices < n_warps) n_warps = slices < 1 ? 1 : (int)slices;
   const size_t budget = 200 * 1024;
   while (n_warps > 1 && ((size_t)n_warps * E + E + 1 + 33) * 4 > budget) n_warps >>= 1;
   const size_t smem = ((size_t)n_warps * E + E + 1 + 33) * 4;
