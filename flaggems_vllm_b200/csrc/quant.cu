@@ -332,82 +332,8 @@ __global__ void gather_scales_kernel(const float* __restrict__ scales_t, int gro
   }
 }
 
-// 1 x 128 e4m3 quantisation of the token rows straight into expert-sorted order:
-// q_sorted[p] = quant(x[sorted_ids[p] / topk]), scales_t[g][p] its group scales, for the occupied
-// slots p < num_post_pad (padding slots stay unwritten, as the GEMM never stores their rows).
-// The same arithmetic as quant_rows_kernel, so the bytes equal "quantise, then copy rows".
-// Work item = (group g, slot p) with p fastest: neighbouring warps write neighbouring scales.
-template <typename T>
-__global__ void __launch_bounds__(kRowThreads) quant_gather_kernel(
-    const T* __restrict__ x, int64_t cols, const int32_t* __restrict__ sorted_ids,
-    const int32_t* __restrict__ num_post_pad, int64_t numel, int topk, int64_t rows_cap, uint8_t* __restrict__ q,
-    float* __restrict__ scales_t) {
-  const int lane = threadIdx.x & 31;
-  const int64_t groups = cols / 128;
-  const int64_t npp = min((int64_t)num_post_pad[0], rows_cap);
-  const int64_t total = npp * groups;
-  const int64_t warp0 = (int64_t)blockIdx.x * (kRowThreads / 32) + (threadIdx.x >> 5);
-  const int64_t stride = (int64_t)gridDim.x * (kRowThreads / 32);
-  constexpr int U = 4;  // groups in flight per warp
-  for (int64_t w = warp0; w < total; w += U * stride) {
-    float v[U][4];
-    int64_t pu[U], gu[U];
-    bool live[U];
-#pragma unroll
-    for (int u = 0; u < U; ++u) {
-      const int64_t wu = w + u * stride;
-      live[u] = false;
-      if (wu < total) {
-        gu[u] = wu / npp;
-        pu[u] = wu - gu[u] * npp;
-        const int64_t sid = sorted_ids[pu[u]];
-        if (sid >= 0 && sid < numel) {
-          live[u] = true;
-          load_group_128<T>(x + (sid / topk) * cols + gu[u] * 128, lane, v[u]);
-        }
-      }
-    }
-#pragma unroll
-    for (int u = 0; u < U; ++u)
-      if (live[u])
-        quant_group_128<false>(v[u], q + pu[u] * cols + gu[u] * 128, scales_t + gu[u] * rows_cap + pu[u], lane);
-  }
-}
-
 }  // namespace
 }  // namespace moe
-
-extern "C" int moe_quant_gather_fp8(const void* x, int x_dtype, int64_t num_tokens, int topk, int64_t cols,
-                                    const int32_t* sorted_ids, const int32_t* num_post_pad, int64_t rows_cap,
-                                    void* q_sorted, float* scales_sorted_t, void* stream) {
-  using namespace moe;
-  if (num_tokens < 0 || topk <= 0 || cols <= 0 || rows_cap < 0) return fail(MOE_E_BADARG, "quant_gather_fp8: bad extent");
-  if (cols % 128 != 0) return fail(MOE_E_SHAPE, "quant_gather_fp8: cols must be a multiple of 128");
-  if (num_tokens == 0 || rows_cap == 0) return 0;
-  if (!x || !sorted_ids || !num_post_pad || !q_sorted || !scales_sorted_t)
-    return fail(MOE_E_BADARG, "quant_gather_fp8: null pointer");
-  if (((uintptr_t)x & 15) || ((uintptr_t)q_sorted & 3)) return fail(MOE_E_BADARG, "quant_gather_fp8: misaligned buffer");
-  cudaStream_t st = (cudaStream_t)stream;
-  const int grid = grid_for((rows_cap * (cols / 128) + 7) / 8, 8);
-  const int64_t numel = num_tokens * topk;
-  switch (x_dtype) {
-    case MOE_F32:
-      quant_gather_kernel<float><<<grid, kRowThreads, 0, st>>>((const float*)x, cols, sorted_ids, num_post_pad, numel, topk,
-                                                                rows_cap, (uint8_t*)q_sorted, scales_sorted_t);
-      break;
-    case MOE_F16:
-      quant_gather_kernel<__half><<<grid, kRowThreads, 0, st>>>((const __half*)x, cols, sorted_ids, num_post_pad, numel, topk,
-                                                                 rows_cap, (uint8_t*)q_sorted, scales_sorted_t);
-      break;
-    case MOE_BF16:
-      quant_gather_kernel<__nv_bfloat16><<<grid, kRowThreads, 0, st>>>((const __nv_bfloat16*)x, cols, sorted_ids,
-                                                                        num_post_pad, numel, topk, rows_cap,
-                                                                        (uint8_t*)q_sorted, scales_sorted_t);
-      break;
-    default: return fail(MOE_E_DTYPE, "quant_gather_fp8: unsupported dtype %d", x_dtype);
-  }
-  return check_launch("quant_gather_fp8");
-}
 
 template <typename T>
 static int rowwise_quant_launch(const void* x, int64_t rows, int64_t cols, int kind, const float* scale_in,

@@ -302,11 +302,10 @@ def quantize_rows(x, mark=None):
 
 def route_pipeline(a_rows, a_scales_t, w1, w2, route_weight, topk_ids, *, mode, act_dtype, w1_scale, w2_scale,
                    global_num_experts, expert_map, apply_router_weight_on_input, use_tensor_cores=None,
-                   keep=None, mark=None, act_fn=(0, 0.0, 0.0, 0.0), row_quant=None, x_raw=None):
+                   keep=None, mark=None, act_fn=(0, 0.0, 0.0, 0.0), row_quant=None):
     """align -> GEMM1 -> GEMM2 for ``a_rows`` [tokens, H] (activation dtype, or
     e4m3 with ``a_scales_t`` [H/128, tokens] in FP8 mode) and ``topk_ids``
-    [tokens, k].  FP8 mode also takes the unquantised rows as ``x_raw`` (with ``a_rows`` None):
-    they are quantised here, straight into sorted order when GEMM1 reads a sorted copy.  Returns ``(y, row_index)``: y holds one row per route in ``act_dtype``, already
+    [tokens, k].  Returns ``(y, row_index)``: y holds one row per route in ``act_dtype``, already
     multiplied by the route weight (unless the weight was applied on the input).  With
     ``row_index`` None, y is [tokens * k, H] and row = flat route index; otherwise y is in
     sorted order [rows_cap, H] and ``row_index`` [tokens, k] names the row of every route.  Rows
@@ -316,11 +315,10 @@ def route_pipeline(a_rows, a_scales_t, w1, w2, route_weight, topk_ids, *, mode, 
     if mark is None:
         mark = STAGE_HOOK or _no_mark
     L = _lib.lib()
-    src = a_rows if a_rows is not None else x_raw
-    dev = src.device
-    st = _lib.stream_of(src)
+    dev = a_rows.device
+    st = _lib.stream_of(a_rows)
     status = _lib.status_word(dev)
-    M, H = src.shape
+    M, H = a_rows.shape
     k = topk_ids.shape[1]
     E_local, N2, _ = w1.shape
     I = N2 // 2
@@ -364,20 +362,8 @@ def route_pipeline(a_rows, a_scales_t, w1, w2, route_weight, topk_ids, *, mode, 
     rw = route_weight if route_weight.dtype == torch.float32 else route_weight.float()
     rw = rw if rw.is_contiguous() else rw.contiguous()
     tc = kernel
-    presort = _presort_rows(mode, kernel, numel, global_num_experts)
-    if a_rows is None and not (fp8 and presort):
-        a_rows, a_scales_t = quantize_rows(x_raw)  # token order; GEMM1 gathers the rows itself
-        mark("quant_rows")
     a_in, a_sorted, a_scales_in = a_rows, 0, a_scales_t
-    if a_rows is None:
-        # FP8, many rows per expert: quantise every route's row straight into sorted order
-        a_in = torch.empty((rows_cap, H), dtype=torch.float8_e4m3fn, device=dev)
-        a_scales_in = torch.empty((H // 128, rows_cap), dtype=torch.float32, device=dev)
-        _lib.check(L.moe_quant_gather_fp8(x_raw.data_ptr(), _lib.dtype_code(x_raw.dtype), M, k, H, sorted_ids.data_ptr(),
-                                          npp.data_ptr(), rows_cap, a_in.data_ptr(), a_scales_in.data_ptr(), st))
-        a_sorted = 1
-        mark("gather")
-    elif presort:
+    if _presort_rows(mode, kernel, numel, global_num_experts):
         # many rows per expert: copy the token rows into sorted order once and let GEMM1 read
         # them with TMA boxes instead of gathering them inside the kernel
         a_in = torch.empty((rows_cap, H), dtype=a_rows.dtype, device=dev)
@@ -430,8 +416,7 @@ def route_pipeline(a_rows, a_scales_t, w1, w2, route_weight, topk_ids, *, mode, 
     if keep is not None:
         keep.update(sorted_ids=sorted_ids, expert_ids=expert_ids, num_post_pad=npp, a_rows=a_rows,
                     a_scales_t=a_scales_t, act=act, act_scales_t=act_scales, y=y, block_m=block_m,
-                    rows_cap=rows_cap, used_tensor_cores=kernel != KERNEL_GENERIC, kernel=kernel, row_index=row_index,
-                    a_sorted_rows=a_in if a_sorted else None, a_sorted_scales_t=a_scales_in if a_sorted else None)
+                    rows_cap=rows_cap, used_tensor_cores=kernel != KERNEL_GENERIC, kernel=kernel, row_index=row_index)
     return y, row_index
 
 
@@ -477,11 +462,9 @@ def run_chunk(x, w1, w2, topk_weights, topk_ids, out, *, mode, w1_scale, w2_scal
                         apply_router_weight_on_input=apply_router_weight_on_input, keep=keep, mark=mark)
         return
     row_quant2 = None
-    x_raw = None
     if mode == _lib.MODE_FP8_BLOCK:
-        # quantised inside route_pipeline: once per token when GEMM1 gathers the rows itself, once per
-        # route straight into sorted order when it reads a sorted copy
-        a_rows, a_scales, x_raw = None, None, (x if x.is_contiguous() else x.contiguous())
+        # activations are quantised once per token; the GEMM gathers rows by token
+        a_rows, a_scales = quantize_rows(x)
     elif mode in (_lib.MODE_FP8_ROW, _lib.MODE_INT8_ROW):
         # row_quant = ((kind, static scale) of the input, (kind, static scale) of the intermediate)
         (kind, static), row_quant2 = row_quant
@@ -500,8 +483,7 @@ def run_chunk(x, w1, w2, topk_weights, topk_ids, out, *, mode, w1_scale, w2_scal
     y, row_index = route_pipeline(a_rows, a_scales, w1, w2, topk_weights, topk_ids, mode=mode, act_dtype=x.dtype,
                        w1_scale=w1_scale, w2_scale=w2_scale, global_num_experts=global_num_experts,
                        expert_map=expert_map, apply_router_weight_on_input=apply_router_weight_on_input,
-                       use_tensor_cores=use_tensor_cores, keep=keep, mark=mark, act_fn=act_fn, row_quant=row_quant2,
-                       x_raw=x_raw)
+                       use_tensor_cores=use_tensor_cores, keep=keep, mark=mark, act_fn=act_fn, row_quant=row_quant2)
     combine_routes(y, out, topk_ids, global_num_experts, expert_map, row_index=row_index)
     mark("sum")
 

@@ -200,18 +200,6 @@ int moe_gather_scales_t(const float* scales_t, int groups, int64_t num_tokens, i
                         const int32_t* num_post_pad, int64_t rows_cap, float* out_t, void* stream);
 
 /*
- * Quantises token rows 1 x 128 to e4m3 (the arithmetic of moe_per_token_group_quant_fp8) straight
- * into expert-sorted order: q_sorted[rows_cap, cols] and scales_sorted_t[cols/128, rows_cap] get
- * the row and the scales of token sorted_ids[p] / topk at every occupied slot p < num_post_pad;
- * padding slots stay unwritten.  One pass instead of quantise + moe_gather_rows +
- * moe_gather_scales_t; the bytes are the same.  No counterpart in the reference, which gathers
- * rows inside its GEMM (src/flaggems_vllm/ops/fused_moe.py:1559).
- */
-int moe_quant_gather_fp8(const void* x, int x_dtype, int64_t num_tokens, int topk, int64_t cols,
-                         const int32_t* sorted_ids, const int32_t* num_post_pad, int64_t rows_cap,
-                         void* q_sorted, float* scales_sorted_t, void* stream);
-
-/*
  * Expert grouped GEMM 1: act[p] = SiLU(x_t Wg^T) * (x_t Wu^T) for every sorted
  * row p, where t = sorted_ids[p] / topk is the token of that route.  The kernel
  * gathers the token rows itself; no sorted copy of the activations is needed

@@ -596,32 +596,6 @@ def test_intermediates_follow_the_documented_layout():
     assert torch.isfinite(act[valid]).all()
 
 
-def test_fp8_rows_quantised_straight_into_sorted_order():
-    """Many rows per expert: GEMM1 reads a sorted copy of the quantised rows, made in one pass
-    from the unquantised tokens.  Every occupied slot holds exactly the bytes and scales the
-    stand-alone quantiser gives for its token."""
-    M, E, H, I, k = 1100, 8, 512, 256, 2
-    x = T.make_activations(M, H, DEV)
-    w1, s1 = T.make_fp8_block_weights(E, 2 * I, H, DEV, seed=1, std=H**-0.5)
-    w2, s2 = T.make_fp8_block_weights(E, H, I, DEV, seed=2, std=I**-0.5)
-    tw, ti = _route(M, E, k, torch.bfloat16)
-    keep = {}
-    out = torch.empty_like(x)
-    fused_moe.run_chunk(x, w1, w2, tw, ti, out, mode=_lib.MODE_FP8_BLOCK, w1_scale=s1, w2_scale=s2,
-                        global_num_experts=E, expert_map=None, apply_router_weight_on_input=False, keep=keep)
-    torch.cuda.synchronize()
-    assert keep["a_sorted_rows"] is not None and keep["a_rows"] is None, "the sorted-order quantiser was not used"
-    n = int(keep["num_post_pad"].item())
-    sid = keep["sorted_ids"][:n].cpu().long()
-    valid = sid < M * k
-    xq, xs = O.per_token_group_quant_fp8_oracle(x, 128)
-    tok = sid[valid] // k
-    got_q = keep["a_sorted_rows"][:n].cpu().view(torch.uint8)[valid]
-    got_s = keep["a_sorted_scales_t"][:, :n].cpu().t()[valid]
-    assert torch.equal(got_q, xq.view(torch.uint8)[tok]) and torch.equal(got_s, xs[tok])
-    _assert_parity(out, O.fused_moe_fp8_block_oracle(x, w1, w2, s1, s2, tw, ti))
-
-
 def test_quant_and_sum_wrappers():
     x = torch.randn(33, 512, device=DEV, dtype=torch.bfloat16) * 3
     x[0, :128] = 0
