@@ -307,7 +307,7 @@ def run_sweep(args):
             nbytes = e_act * (3 * H * I + (2 * I // 128) * (H // 128) * 4 + (H // 128) * (I // 128) * 4) \
                 + M * H * 2 * 2 + M * E * 4 + k * 8 * M
             extra = {"distinct_experts": e_act}
-            if M <= 128 and not args.no_graph:
+            if M <= 1024 and not args.no_graph:
                 extra["cuda_graph_replay_ms"] = graph_ms(step)
             report("dsv3_fp8", M, timeit(step, iters(10)), 6.0 * M * k * H * I, nbytes, 2 * peaks["bf16_tflops"], extra)
         del w1, w2, s1, s2
@@ -328,7 +328,7 @@ def run_sweep(args):
             e_act = int(torch.unique(ti).numel())
             nbytes = e_act * 3 * H * I * 2 + M * H * 2 * 2 + M * E * 4 + k * 8 * M
             extra = {"distinct_experts": e_act}
-            if M <= 128 and not args.no_graph:
+            if M <= 1024 and not args.no_graph:
                 extra["cuda_graph_replay_ms"] = graph_ms(step)
             report("mixtral_bf16", M, timeit(step, iters(6)), 6.0 * M * k * H * I, nbytes, peaks["bf16_tflops"], extra)
         del w1, w2
@@ -350,7 +350,7 @@ def run_sweep(args):
             e_act = int(torch.unique(ti).numel())
             nbytes = e_act * (3 * H * I + 3 * I * 4 + H * 4) + M * H * 2 * 2 + M * E * 4 + k * 8 * M
             extra = {"distinct_experts": e_act}
-            if M <= 128 and not args.no_graph:
+            if M <= 1024 and not args.no_graph:
                 extra["cuda_graph_replay_ms"] = graph_ms(step)
             report("qwen3_w8a16", M, timeit(step, iters(6)), 6.0 * M * k * H * I, nbytes, peaks["bf16_tflops"], extra)
     if "align" in which:
