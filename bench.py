@@ -718,6 +718,32 @@ def main():
     e2e_steps = max(4, args.steps)
     e2e_ms = e2e_pipelined(e2e_steps) / e2e_steps
 
+    # What the host link alone allows: the same H2D and D2H copies of one step, both directions at
+    # once, on every rank at the same time and with no kernels running (the ceiling of `e2e`).
+    def copies_only(reps=5):
+        barrier()
+        t0, t1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        t0.record(s_comp)
+        s_in.wait_event(t0)
+        s_out.wait_event(t0)
+        for _ in range(reps):
+            with torch.cuda.stream(s_in):
+                dx[0].copy_(hx, non_blocking=True)
+                dl[0].copy_(hl, non_blocking=True)
+            with torch.cuda.stream(s_out):
+                hout[0].copy_(dx[1], non_blocking=True)
+        s_comp.wait_stream(s_in)
+        s_comp.wait_stream(s_out)
+        t1.record(s_comp)
+        barrier()
+        tt = torch.tensor([t0.elapsed_time(t1) / reps], dtype=torch.float64, device=dev)
+        if dist is not None:
+            dist.all_reduce(tt, op=dist.ReduceOp.MAX)
+        return float(tt.item())
+
+    copies_only(2)
+    copy_ms = copies_only()
+
     total_tokens = M * world
     flops = 6.0 * total_tokens * k * H * I
     value = total_tokens / (ms * 1e-3)
@@ -733,6 +759,10 @@ def main():
                 "h2d_bytes_per_step": hx.numel() * 2 + hl.numel() * 4, "d2h_bytes_per_step": hout[0].numel() * 2,
                 "mode": "three streams, double-buffered: H2D / kernels / D2H of neighbouring steps overlap",
                 "serial_ms_per_step": e2e_serial_ms, "serial_value": total_tokens / (e2e_serial_ms * 1e-3),
+                "host_copies_only_ms_per_step": copy_ms,
+                "host_copies_only_gbs_per_rank": (hx.numel() * 2 + hl.numel() * 4 + hout[0].numel() * 2) / (copy_ms * 1e-3) / 1e9,
+                "host_copies_note": "one step's H2D and D2H copies alone, both directions at once on all ranks, no "
+                                    "kernels: the ceiling the host link puts on e2e",
                 "cpus_bound": numa},
         # kernel-launching calls into libmoe_sm100.so counted inside the timed region on this rank
         "gpu_launches": launches,
