@@ -80,6 +80,7 @@ class ExpertParallelMoE:
         self.mode = mode
         self.last_counts = None
         self.last_bytes = None
+        self._host_counts = {}  # (device, stream) -> (pinned [2, R] int32, event): the host's view of the pair counts
         self.compute_fn = compute_fn or self._compute_cuda
         self.combine_fn = combine_fn or self._combine_cuda
         # Token chunks run as independent dispatch/compute/combine steps on their own streams and
@@ -159,11 +160,19 @@ class ExpertParallelMoE:
         mark = _fm.STAGE_HOOK or _fm._no_mark  # the timing hook of the single-GPU pipeline also sees these stages
         mark("ep_plan")
         dist.all_to_all_single(both[1], both[0], group=group)
-        counts = both.tolist()  # the one host sync of the step
-        send_splits, recv_splits = counts[0], counts[1]
-        n_send, n_recv = sum(send_splits), sum(recv_splits)
-        self.last_counts = (send_splits, recv_splits)
-        mark("ep_counts")
+        # The one host read of the step (NCCL takes the split sizes from the host).  The counts are
+        # copied to pinned memory and the host waits for that copy only; the quantiser, which does
+        # not need them, is enqueued first, so the GPU has work while the host waits and then
+        # enqueues the rest of the step.
+        cur = torch.cuda.current_stream(dev)
+        key = (dev.index, cur.cuda_stream)
+        slot = self._host_counts.get(key)
+        if slot is None or slot[0].shape[1] != R:
+            slot = (torch.empty((2, R), dtype=torch.int32).pin_memory(), torch.cuda.Event())
+            self._host_counts[key] = slot
+        host_counts, copied = slot
+        host_counts.copy_(both, non_blocking=True)
+        copied.record(cur)
 
         g = H // 128 if fp8 else 0
         if fp8:
@@ -172,6 +181,12 @@ class ExpertParallelMoE:
         else:
             xs = None
             rows_src, row_bytes, rows_dtype = x if x.is_contiguous() else x.contiguous(), H * x.element_size(), x.dtype
+        copied.synchronize()
+        counts = host_counts.tolist()
+        send_splits, recv_splits = counts[0], counts[1]
+        n_send, n_recv = sum(send_splits), sum(recv_splits)
+        self.last_counts = (send_splits, recv_splits)
+        mark("ep_counts")
         rows_send = torch.empty((n_send, H), dtype=rows_dtype, device=dev)
         side_send = torch.empty((n_send, g + 2 * k), dtype=torch.float32, device=dev)
         _lib.check(L.moe_ep_pack(rows_src.data_ptr(), row_bytes, _lib.ptr(xs), g, ids.data_ptr(), tw.data_ptr(), k,
