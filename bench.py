@@ -483,6 +483,10 @@ def main():
     ap.add_argument("--no-cpu-baseline", action="store_true")
     ap.add_argument("--ep-chunks", type=int, default=1,
                     help="token chunks per expert-parallel step (each on its own stream and communicator)")
+    ap.add_argument("--ep-overlap", type=int, default=0,
+                    help="1: expert-parallel combine in two column halves, the first half's all-to-all beside the "
+                         "second half's GEMM 2")
+    ap.add_argument("--ep-free-sms", type=int, default=16, help="SMs the second GEMM 2 leaves to the all-to-all")
     ap.add_argument("--ep-check-tokens", type=int, default=-1,
                     help="tokens per rank of the full-size expert-parallel step checked against the CPU oracle "
                          "(0: skip; default 16 at 2 GPUs, 8 at 4, 4 at 8: every rank runs the oracle on its share "
@@ -534,7 +538,8 @@ def main():
     if world > 1:
         dist.broadcast(bias, 0)
     flush = torch.empty(2 * L2_BYTES, dtype=torch.uint8, device=dev)
-    layer = ep.ExpertParallelMoE(w1, w2, s1, s2, E, dist.group.WORLD, chunks=args.ep_chunks) if world > 1 else None
+    layer = ep.ExpertParallelMoE(w1, w2, s1, s2, E, dist.group.WORLD, chunks=args.ep_chunks,
+                                 overlap_combine=bool(args.ep_overlap), free_sms=args.ep_free_sms) if world > 1 else None
     ep_parity = None
     if args.ep_check_tokens < 0:
         args.ep_check_tokens = max(4, 32 // max(world, 2))
@@ -752,7 +757,7 @@ def main():
         "steps": args.steps, "warmup": args.warmup, "ms_per_step": ms, "higher_is_better": True,
         "scaling": "weak", "vs_baseline": None, "dtype": "fp8_e4m3", "data": "synthetic",
         "config": {"workload": "deepseek_v3_fp8_block_moe_layer", "tokens_per_gpu": M, "global_tokens": total_tokens,
-                   **c, "experts_per_gpu": E_local, "router_bias_std": args.router_bias_std, "parallelism": f"ep{world}" if world > 1 else "single", "ep_chunks": args.ep_chunks if world > 1 else None,
+                   **c, "experts_per_gpu": E_local, "router_bias_std": args.router_bias_std, "parallelism": f"ep{world}" if world > 1 else "single", "ep_chunks": args.ep_chunks if world > 1 else None, "ep_overlap_combine": bool(args.ep_overlap) if world > 1 else None,
                    "l2": "flushed between iterations (252 MB memset); weights 11.3 GB >> L2"},
         "tflops": flops / (ms * 1e-3) / 1e12,
         "e2e": {"value": total_tokens / (e2e_ms * 1e-3), "unit": "tokens/s", "ms_per_step": e2e_ms,

@@ -67,11 +67,16 @@ SYMBOLS = {
     "moe_small_m_gemm2_static": (c_int, [c_int, c_int, c_void_p, c_int64, c_int, c_void_p, c_void_p, c_void_p, c_void_p,
                                          c_void_p, c_void_p, c_int, c_void_p, c_int, c_void_p, c_int, c_int64, c_int,
                                          c_int, c_int, c_void_p, c_int, c_void_p, c_void_p]),
+    "moe_gemm2_sorted_cols": (c_int, [c_int, c_int, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p,
+                                      c_void_p, c_int, c_int64, c_int64, c_int, c_int, c_int, c_int, c_int, c_int,
+                                      c_void_p, c_void_p, c_int, c_void_p, c_void_p]),
     "moe_gemm2_sorted": (c_int, [c_int, c_int, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p,
                                  c_void_p, c_int, c_int64, c_int64, c_int, c_int, c_int, c_int, c_void_p, c_void_p,
                                  c_void_p, c_void_p]),
     "moe_sum": (c_int, [c_void_p, c_void_p, c_int, c_int64, c_int, c_int64, c_void_p, c_int, c_int, c_void_p,
                         c_void_p, c_void_p]),
+    "moe_sum_ld": (c_int, [c_void_p, c_void_p, c_int64, c_int, c_int64, c_int, c_int64, c_void_p, c_int, c_int, c_void_p,
+                           c_void_p, c_void_p]),
 }
 
 _lib = None

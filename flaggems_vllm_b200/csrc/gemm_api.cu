@@ -12,7 +12,7 @@ int tc_gemm(bool gemm1, int mode, int act_dtype, const void* a, const float* a_s
             const float* w_scale, const int32_t* expert_ids, const int32_t* sorted_ids, const int32_t* npp,
             const float* route_weight, int mul_weight, int64_t numel, int64_t rows_cap, int64_t a_tokens, int topk,
             int block_m, int E, int K, int Nout, void* out, float* out_scales_t, int32_t* status, cudaStream_t st,
-            int variant, int a_sorted, int32_t* inv = nullptr);
+            int variant, int a_sorted, int32_t* inv = nullptr, int w_row0 = 0, int w_rows = 0, int grid_limit = 0);
 int w8_gemm(bool gemm1, int act_dtype, const void* a, const void* w, const float* w_scale, const int32_t* expert_ids,
             const int32_t* sorted_ids, const int32_t* npp, const float* route_weight, int mul_weight, int64_t numel,
             int64_t rows_cap, int64_t a_tokens, int topk, int block_m, int E, int K, int Nout, void* out,
@@ -138,4 +138,28 @@ extern "C" int moe_gemm2_sorted(int mode, int act_dtype, const void* act_sorted,
   return tc_gemm(false, mode, act_dtype, act_sorted, act_scales_t, w2, w2_scale, expert_ids, sorted_ids, num_post_pad,
                  route_weight, mul_weight, numel, rows_cap, 0, 1, block_m, E, I, H, y_sorted, nullptr, status,
                  (cudaStream_t)stream, 1, 0, inv);
+}
+
+// moe_gemm2_sorted over a window of the output columns [col0, col0 + ncols) of H: y_window is
+// [rows_cap, ncols].  A caller that has other work for the first columns (an expert-parallel
+// combine that can start on them) runs the layer's GEMM 2 as two such calls; max_ctas > 0 leaves
+// the remaining SMs to that other work.
+extern "C" int moe_gemm2_sorted_cols(int mode, int act_dtype, const void* act_sorted, const float* act_scales_t,
+                                     const void* w2, const float* w2_scale, const int32_t* expert_ids,
+                                     const int32_t* sorted_ids, const int32_t* num_post_pad, const float* route_weight,
+                                     int mul_weight, int64_t numel, int64_t rows_cap, int block_m, int E, int H, int I,
+                                     int col0, int ncols, void* y_window, int32_t* inv, int max_ctas, int32_t* status,
+                                     void* stream) {
+  using namespace moe;
+  int rc = check_common("gemm2 (column window)", mode, act_sorted, act_scales_t, w2, w2_scale, expert_ids, sorted_ids,
+                        num_post_pad, route_weight, mul_weight, numel, rows_cap, block_m, E, H, I, y_window);
+  if (rc) return rc;
+  if (!inv) return fail(MOE_E_BADARG, "gemm2 (column window): route index buffer missing");
+  if (mode != MOE_MODE_FP8_BLOCK && mode != MOE_MODE_HALF)
+    return fail(MOE_E_SHAPE, "gemm2 (column window): FP8 block-scale and half-precision modes only");
+  if (col0 < 0 || ncols <= 0 || col0 + ncols > H) return fail(MOE_E_BADARG, "gemm2 (column window): window outside [0, H)");
+  if (rows_cap == 0 || numel == 0) return 0;
+  return tc_gemm(false, mode, act_dtype, act_sorted, act_scales_t, w2, w2_scale, expert_ids, sorted_ids, num_post_pad,
+                 route_weight, mul_weight, numel, rows_cap, 0, 1, block_m, E, I, ncols, y_window, nullptr, status,
+                 (cudaStream_t)stream, 1, 0, inv, col0, H, max_ctas);
 }

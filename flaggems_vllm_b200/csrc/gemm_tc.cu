@@ -126,6 +126,7 @@ struct Params {
   int rows_w;   // weight rows per expert (2I or H)
   int n_tiles;  // column tiles per align block
   int group_m;  // align blocks per group of the tile order
+  int w_row0;   // GEMM2 over a window of the output columns: first weight row (output column) of the window
   bool wide_store;  // the output is 32-byte aligned: rows are written with 32-byte stores
 #ifdef MOE_TC_TRACE
   long long* trace;  // [4 roles][64 K blocks][8 events] cycle stamps of CTA 0, third tile (experiment builds)
@@ -310,7 +311,7 @@ tc_gemm_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant_
         MOE_TILE_COORDS(tile)
         if (e < 0 || e >= P.E) continue;
         [[maybe_unused]] const int row0 = mb * BM;
-        const int wrow0 = e * P.rows_w;
+        const int wrow0 = e * P.rows_w + P.w_row0;
         for (int kb = 0; kb < KB; ++kb, ++it) {
           const int s = it % STAGES;
           const uint32_t ph = (it / STAGES) & 1;
@@ -525,7 +526,8 @@ tc_gemm_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant_
         if (e < 0 || e >= P.E) continue;
         const float* as_row = P.a_scales_t + (int64_t)mb * BM + 4 * lane;
         // GEMM2: the two 128-column weight blocks of the tile; GEMM1: the gate block and the up block
-        const int wblk = GEMM1 ? (lane == 1 ? (P.Nout >> 7) + nt : nt) : min(2 * nt + lane, sblk_per_e - 1);
+        const int wblk = GEMM1 ? (lane == 1 ? (P.Nout >> 7) + nt : nt)
+                               : min((P.w_row0 >> 7) + 2 * nt + lane, sblk_per_e - 1);
         const float* ws_src = P.w_scale + ((int64_t)e * sblk_per_e + wblk) * KB;
         for (int kb = 0; kb < KB; ++kb, ++it) {
           const int s = it % STAGES;
@@ -843,7 +845,10 @@ int tc_gemm(bool gemm1, int mode, int act_dtype, const void* a, const float* a_s
             const float* w_scale, const int32_t* expert_ids, const int32_t* sorted_ids, const int32_t* npp,
             const float* route_weight, int mul_weight, int64_t numel, int64_t rows_cap, int64_t a_tokens, int topk,
             int block_m, int E, int K, int Nout, void* out, float* out_scales_t, int32_t* status, cudaStream_t st,
-            int variant, int a_sorted, int32_t* inv) {
+            int variant, int a_sorted, int32_t* inv, int w_row0, int w_rows, int grid_limit) {
+  // w_row0, w_rows (gemm2 with inv only; 0, 0 = the whole matrix): the call produces the Nout output
+  //   columns that start at column w_row0 of a weight matrix with w_rows rows per expert, into an
+  //   `out` that is Nout wide; grid_limit > 0 caps the number of CTAs (SMs left to other work)
   // inv (gemm2, variant 1): `out` is y in SORTED row order [rows_cap, Nout], written by TMA from a staged
   //   tile, and inv[route] receives the sorted row of every route
   // a_sorted (gemm1): `a` holds [rows_cap, K] rows already in sorted order (moe_gather_rows)
@@ -871,7 +876,12 @@ int tc_gemm(bool gemm1, int mode, int act_dtype, const void* a, const float* a_s
   if (gemm1 && Nout % 128 != 0) return fail(MOE_E_SHAPE, "tensor-core GEMM1: intermediate size must be a multiple of 128");
   if (!gemm1 && Nout % 64 != 0) return fail(MOE_E_SHAPE, "tensor-core GEMM2: hidden size must be a multiple of 64");
   if (fp8 && !gemm1 && Nout % 128 != 0) return fail(MOE_E_SHAPE, "tensor-core GEMM2 (fp8): hidden size must be a multiple of 128");
-  const int rows_w = gemm1 ? 2 * Nout : Nout;
+  const bool window = w_rows > 0;
+  if (window && mode == MOE_MODE_HALF && w_scale != nullptr)
+    return fail(MOE_E_SHAPE, "tensor-core GEMM2: column windows do not serve per-channel scales");
+  if (window && (gemm1 || inv == nullptr || w_row0 < 0 || w_row0 % 256 != 0 || Nout % 256 != 0 || w_row0 + Nout > w_rows))
+    return fail(MOE_E_SHAPE, "tensor-core GEMM2: a column window starts and ends on multiples of 256 columns of the staged-output kernel");
+  const int rows_w = gemm1 ? 2 * Nout : (window ? w_rows : Nout);
   if ((int64_t)E * rows_w >= (1ll << 31) || rows_cap >= (1ll << 31)) return fail(MOE_E_TOOBIG, "tensor-core GEMM: extent exceeds int32 coordinates");
 
   const int eb = fp8 ? 1 : 2;
@@ -896,7 +906,7 @@ int tc_gemm(bool gemm1, int mode, int act_dtype, const void* a, const float* a_s
   P.a_scales_t = a_scales_t; P.w_scale = w_scale; P.expert_ids = expert_ids; P.sorted_ids = sorted_ids;
   P.num_post_pad = npp; P.route_weight = route_weight; P.out = out; P.out_scales_t = out_scales_t; P.inv = nullptr;
   P.status = status; P.wait_ns = wait_limit_ns(); P.numel = numel; P.rows_cap = rows_cap; P.mul_weight = mul_weight; P.E = E; P.K = K;
-  P.Nout = Nout; P.rows_w = rows_w;
+  P.Nout = Nout; P.rows_w = rows_w; P.w_row0 = window ? w_row0 : 0;
   P.n_tiles = gemm1 ? Nout / 128 : (Nout + BN - 1) / BN;
   {
     // about as many blocks per group as one expert owns (rows per expert / rows per block, one of them partial)
@@ -913,6 +923,7 @@ int tc_gemm(bool gemm1, int mode, int act_dtype, const void* a, const float* a_s
   cudaGetDevice(&dev);
   cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, dev);
   const int64_t cap_tiles = (rows_cap / unit_rows) * (int64_t)P.n_tiles;
+  if (grid_limit > 0 && grid_limit < sms) sms = grid_limit;
   const int units = pair ? sms / 2 : sms;  // work units resident at once: CTAs, or CTA pairs
   const int grid = (int)(cap_tiles < units ? cap_tiles : units) * (pair ? 2 : 1);
 

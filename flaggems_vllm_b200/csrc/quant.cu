@@ -125,7 +125,7 @@ template <typename T, typename IdT>
 __global__ void __launch_bounds__(256) moe_sum_kernel(
     const T* __restrict__ in, T* __restrict__ out, int64_t M, int topk, int64_t H,
     const IdT* __restrict__ ids, int num_experts, const int32_t* __restrict__ expert_map,
-    const int32_t* __restrict__ row_index, bool aligned) {
+    const int32_t* __restrict__ row_index, bool aligned, int64_t out_ld) {
   constexpr int V = 16 / sizeof(T);
   const int64_t vec_per_row = (H + V - 1) / V;
   const int64_t total = M * vec_per_row;
@@ -177,7 +177,7 @@ __global__ void __launch_bounds__(256) moe_sum_kernel(
         for (int i = 0; i < V && h0 + i < H; ++i) acc[i] += ToF32<T>::get(src[i]);
       }
     }
-    T* dst = out + m * H + h0;
+    T* dst = out + m * out_ld + h0;
     if (full) {
       uint4 raw;
       T* p = reinterpret_cast<T*>(&raw);
@@ -200,17 +200,17 @@ int grid_for(int64_t work_items, int per_sm) {
 
 template <typename T>
 int launch_sum(const void* in, void* out, int64_t M, int topk, int64_t H, const void* ids,
-               int ids_int64, int E, const int32_t* emap, const int32_t* row_index, cudaStream_t st) {
+               int ids_int64, int E, const int32_t* emap, const int32_t* row_index, cudaStream_t st, int64_t out_ld) {
   constexpr int V = 16 / sizeof(T);
   const int64_t total = M * ((H + V - 1) / V);
   const int grid = grid_for((total + 255) / 256, 8);
-  const bool aligned = (((uintptr_t)in | (uintptr_t)out) & 15) == 0;
+  const bool aligned = (((uintptr_t)in | (uintptr_t)out) & 15) == 0 && (out_ld * sizeof(T)) % 16 == 0;
   if (ids_int64)
     moe_sum_kernel<T, int64_t><<<grid, 256, 0, st>>>((const T*)in, (T*)out, M, topk, H,
-                                                     (const int64_t*)ids, E, emap, row_index, aligned);
+                                                     (const int64_t*)ids, E, emap, row_index, aligned, out_ld);
   else
     moe_sum_kernel<T, int32_t><<<grid, 256, 0, st>>>((const T*)in, (T*)out, M, topk, H,
-                                                     (const int32_t*)ids, E, emap, row_index, aligned);
+                                                     (const int32_t*)ids, E, emap, row_index, aligned, out_ld);
   return check_launch("moe_sum");
 }
 
@@ -485,18 +485,24 @@ extern "C" int moe_widen_int8(const void* src, void* dst, int dst_dtype, int64_t
   return check_launch("widen_int8");
 }
 
-extern "C" int moe_sum(const void* in, void* out, int dtype, int64_t M, int topk, int64_t H,
-                       const void* topk_ids, int ids_int64, int num_experts,
-                       const int32_t* expert_map, const int32_t* row_index, void* stream) {
+extern "C" int moe_sum_ld(const void* in, void* out, int64_t out_ld, int dtype, int64_t M, int topk, int64_t H,
+                          const void* topk_ids, int ids_int64, int num_experts, const int32_t* expert_map,
+                          const int32_t* row_index, void* stream) {
   using namespace moe;
-  if (M < 0 || topk <= 0 || H <= 0) return fail(MOE_E_BADARG, "moe_sum: bad extent");
+  if (M < 0 || topk <= 0 || H <= 0 || out_ld < H) return fail(MOE_E_BADARG, "moe_sum: bad extent");
   if (M == 0) return 0;
   if (!in || !out) return fail(MOE_E_BADARG, "moe_sum: null pointer");
   cudaStream_t st = (cudaStream_t)stream;
   switch (dtype) {
-    case MOE_F32: return launch_sum<float>(in, out, M, topk, H, topk_ids, ids_int64, num_experts, expert_map, row_index, st);
-    case MOE_F16: return launch_sum<__half>(in, out, M, topk, H, topk_ids, ids_int64, num_experts, expert_map, row_index, st);
-    case MOE_BF16: return launch_sum<__nv_bfloat16>(in, out, M, topk, H, topk_ids, ids_int64, num_experts, expert_map, row_index, st);
+    case MOE_F32: return launch_sum<float>(in, out, M, topk, H, topk_ids, ids_int64, num_experts, expert_map, row_index, st, out_ld);
+    case MOE_F16: return launch_sum<__half>(in, out, M, topk, H, topk_ids, ids_int64, num_experts, expert_map, row_index, st, out_ld);
+    case MOE_BF16: return launch_sum<__nv_bfloat16>(in, out, M, topk, H, topk_ids, ids_int64, num_experts, expert_map, row_index, st, out_ld);
     default: return fail(MOE_E_DTYPE, "moe_sum: unsupported dtype %d", dtype);
   }
+}
+
+extern "C" int moe_sum(const void* in, void* out, int dtype, int64_t M, int topk, int64_t H,
+                       const void* topk_ids, int ids_int64, int num_experts,
+                       const int32_t* expert_map, const int32_t* row_index, void* stream) {
+  return moe_sum_ld(in, out, H, dtype, M, topk, H, topk_ids, ids_int64, num_experts, expert_map, row_index, stream);
 }

@@ -65,7 +65,8 @@ class ExpertParallelMoE:
     """Holds this rank's expert shard and runs the dispatch/compute/combine step."""
 
     def __init__(self, w1, w2, w1_scale, w2_scale, num_experts_global: int, group=None, *,
-                 mode: int = _lib.MODE_FP8_BLOCK, compute_fn=None, combine_fn=None, chunks: int = 1):
+                 mode: int = _lib.MODE_FP8_BLOCK, compute_fn=None, combine_fn=None, chunks: int = 1,
+                 overlap_combine: bool = False, free_sms: int = 16):
         """``compute_fn(a_rows, a_scales_t, slot_weights, slot_ids, act_dtype) -> rows``
         and ``combine_fn(rows_back, out, index)`` replace the CUDA steps; the CPU
         (gloo) tests of the dispatch/combine plumbing inject them."""
@@ -88,6 +89,13 @@ class ExpertParallelMoE:
         # (collectives of one communicator run in issue order, which would chain the chunks).
         self.chunks = max(1, int(chunks))
         self._lanes = None
+        # The combine in two column halves: GEMM 2 runs once per half of the hidden columns, and the
+        # first half's local sum and all-to-all travel (on a side stream) while the second half's
+        # GEMM 2 runs on all but `free_sms` SMs.  Every rank takes the same decision (it depends on
+        # the layer only), so the ranks issue the same collectives; bitwise the same result.
+        self.overlap_combine = bool(overlap_combine)
+        self.free_sms = int(free_sms)
+        self._side = {}
 
     def _chunk_lanes(self, device):
         if self._lanes is None:
@@ -210,6 +218,12 @@ class ExpertParallelMoE:
         _lib.check(L.moe_ep_unpack(side_recv.data_ptr(), n_recv, g, k, self.rank, self.E_local, _lib.ptr(a_scales_t),
                                    slot_ids.data_ptr(), slot_w.data_ptr(), st))
         mark("ep_unpack")
+        if out is None:
+            out = torch.empty_like(x)
+        if self.overlap_combine and H % 512 == 0 and self.compute_fn == self._compute_cuda:
+            self._combine_in_halves(a_rows, a_scales_t, slot_w, slot_ids, x.dtype, send_splits, recv_splits, group,
+                                    out, index, mark)
+            return out
         if n_recv > 0:
             rows = self.compute_fn(a_rows, a_scales_t, slot_w, slot_ids, x.dtype)
         else:
@@ -218,11 +232,65 @@ class ExpertParallelMoE:
         mark("ep_local_sum")
         self._a2a(rows_back, rows, send_splits, recv_splits, group)
         mark("ep_combine")
-        if out is None:
-            out = torch.empty_like(x)
         self.combine_fn(rows_back, out, index)
         mark("ep_sum")
         return out
+
+    def _combine_in_halves(self, a_rows, a_scales_t, slot_w, slot_ids, act_dtype, send_splits, recv_splits, group,
+                           out, index, mark):
+        """Local experts, then the combine as two all-to-alls of half-width rows.  When GEMM 2 can
+        produce the column halves one after the other, the first half's all-to-all runs beside the
+        second half's GEMM 2; otherwise the finished rows are cut in two.  Either way every rank
+        issues the same two collectives."""
+        dev = out.device
+        M, H = out.shape
+        n_recv, n_send = a_rows.shape[0], sum(send_splits)
+        h0 = (H // 2) // 256 * 256
+        main = torch.cuda.current_stream(dev)
+        side = self._side.get(dev.index)
+        if side is None:
+            side = self._side[dev.index] = torch.cuda.Stream(device=dev)
+        sent = []  # (first column, returned rows, event after the all-to-all)
+
+        def send_half(c0, rows_h):
+            ready = torch.cuda.Event()
+            ready.record(main)
+            rows_back_h = torch.empty((n_send, rows_h.shape[1]), dtype=act_dtype, device=dev)
+            side.wait_event(ready)
+            with torch.cuda.stream(side):
+                self._a2a(rows_back_h, rows_h, send_splits, recv_splits, group)
+                done = torch.cuda.Event()
+                done.record(side)
+            rows_h.record_stream(side)
+            rows_back_h.record_stream(side)
+            sent.append((c0, rows_back_h, done))
+
+        def after_gemm2(half, c0, y_w, row_index):
+            rows_h = torch.empty((n_recv, y_w.shape[1]), dtype=act_dtype, device=dev)
+            combine_routes(y_w, rows_h, slot_ids, self.E_local, row_index=row_index)
+            mark("ep_local_sum")
+            send_half(c0, rows_h)
+
+        rows = None
+        if n_recv > 0:
+            y, row_index = route_pipeline(a_rows, a_scales_t, self.w1, self.w2, slot_w, slot_ids, mode=self.mode,
+                                          act_dtype=act_dtype, w1_scale=self.s1, w2_scale=self.s2,
+                                          global_num_experts=self.E_local, expert_map=None,
+                                          apply_router_weight_on_input=False,
+                                          column_halves=(after_gemm2, self.free_sms))
+            if y is not None:  # GEMM 2 wrote whole rows (few rows per expert): sum them, then cut
+                rows = torch.empty((n_recv, H), dtype=act_dtype, device=dev)
+                combine_routes(y, rows, slot_ids, self.E_local, row_index=row_index)
+        else:
+            rows = torch.empty((0, H), dtype=act_dtype, device=dev)
+        if rows is not None:
+            mark("ep_local_sum")
+            send_half(0, rows[:, :h0].contiguous())
+            send_half(h0, rows[:, h0:].contiguous())
+        for c0, rows_back_h, done in sent:
+            main.wait_event(done)
+            self.combine_fn(rows_back_h, out[:, c0:c0 + rows_back_h.shape[1]], index)  # into the column window
+        mark("ep_sum")
 
     def _forward_torch(self, x: torch.Tensor, topk_weights: torch.Tensor, topk_ids: torch.Tensor) -> torch.Tensor:
         M, H = x.shape

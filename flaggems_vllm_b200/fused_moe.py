@@ -302,7 +302,7 @@ def quantize_rows(x, mark=None):
 
 def route_pipeline(a_rows, a_scales_t, w1, w2, route_weight, topk_ids, *, mode, act_dtype, w1_scale, w2_scale,
                    global_num_experts, expert_map, apply_router_weight_on_input, use_tensor_cores=None,
-                   keep=None, mark=None, act_fn=(0, 0.0, 0.0, 0.0), row_quant=None):
+                   keep=None, mark=None, act_fn=(0, 0.0, 0.0, 0.0), row_quant=None, column_halves=None):
     """align -> GEMM1 -> GEMM2 for ``a_rows`` [tokens, H] (activation dtype, or
     e4m3 with ``a_scales_t`` [H/128, tokens] in FP8 mode) and ``topk_ids``
     [tokens, k].  Returns ``(y, row_index)``: y holds one row per route in ``act_dtype``, already
@@ -311,7 +311,11 @@ def route_pipeline(a_rows, a_scales_t, w1, w2, route_weight, topk_ids, *, mode, 
     sorted order [rows_cap, H] and ``row_index`` [tokens, k] names the row of every route.  Rows
     (and index entries) of routes whose expert is not local are left unwritten.  ``act_fn`` = (activation code, alpha, beta, limit).  Row-scaled W8A8 modes:
     ``a_rows`` is e4m3 / int8 with ``a_scales_t`` [tokens]; ``row_quant`` = (kind, static scale or
-    None) says how the intermediate is quantised between the two GEMMs."""
+    None) says how the intermediate is quantised between the two GEMMs.
+    ``column_halves`` = (callback, SMs to leave free): when GEMM2 writes sorted rows and H splits
+    into two windows of whole 256-column tiles, GEMM2 runs once per window and
+    ``callback(half, col0, y_window, row_index)`` is called after each launch (the second launch
+    keeps off the given number of SMs); the function then returns ``(None, row_index)``."""
     if mark is None:
         mark = STAGE_HOOK or _no_mark
     L = _lib.lib()
@@ -400,8 +404,22 @@ def route_pipeline(a_rows, a_scales_t, w1, w2, route_weight, topk_ids, *, mode, 
     if _sorted_output(mode, kernel, numel, global_num_experts):
         # the 128-row kernel stages its output tile and writes whole tiles (TMA) in sorted row order;
         # the combine finds a route's row through `row_index`
-        y = torch.empty((rows_cap, H), dtype=act_dtype, device=dev)
         row_index = torch.empty((M, k), dtype=torch.int32, device=dev)
+        if column_halves is not None and H % 512 == 0 and not (mode == _lib.MODE_HALF and w2_scale is not None):
+            callback, free_sms = column_halves
+            h0 = (H // 2) // 256 * 256
+            for half, (c0, nc) in enumerate(((0, h0), (h0, H - h0))):
+                y_w = torch.empty((rows_cap, nc), dtype=act_dtype, device=dev)
+                limit = max(1, _sm_count(dev) - free_sms) if half == 1 and free_sms > 0 else 0
+                _lib.check(L.moe_gemm2_sorted_cols(mode, act_code, act_in.data_ptr(), _lib.ptr(act_scales), w2.data_ptr(),
+                                                   _lib.ptr(w2_scale), expert_ids.data_ptr(), sorted_ids.data_ptr(),
+                                                   npp.data_ptr(), rw.data_ptr(), int(not apply_router_weight_on_input),
+                                                   numel, rows_cap, block_m, E_local, H, I, c0, nc, y_w.data_ptr(),
+                                                   row_index.data_ptr(), limit, status.data_ptr(), st))
+                mark("gemm2")
+                callback(half, c0, y_w, row_index)
+            return None, row_index
+        y = torch.empty((rows_cap, H), dtype=act_dtype, device=dev)
         _lib.check(L.moe_gemm2_sorted(mode, act_code, act_in.data_ptr(), _lib.ptr(act_scales), w2.data_ptr(),
                                       _lib.ptr(w2_scale), expert_ids.data_ptr(), sorted_ids.data_ptr(), npp.data_ptr(),
                                       rw.data_ptr(), int(not apply_router_weight_on_input), numel, rows_cap, block_m,
@@ -426,8 +444,10 @@ def combine_routes(y, out, topk_ids, global_num_experts, expert_map=None, row_in
     With ``topk_ids`` [M, k]: slot (m, j) is row m*k + j of ``y`` (or
     ``row_index[m, j]``), skipped when its expert id is negative, >= the expert
     count, or not local under ``expert_map``.  With ``topk_ids=None``:
-    ``row_index`` [M, S] alone names the rows; negative entries are skipped."""
+    ``row_index`` [M, S] alone names the rows; negative entries are skipped.  ``out`` may be a
+    column window of a wider tensor (rows ``out.stride(0)`` elements apart, columns contiguous)."""
     M, H = out.shape
+    assert out.stride(1) == 1 or H == 1, "the columns of the output must be contiguous"
     ids = None
     if topk_ids is not None:
         k = topk_ids.shape[1]
@@ -440,9 +460,10 @@ def combine_routes(y, out, topk_ids, global_num_experts, expert_map=None, row_in
         emap = emap.contiguous()
     if row_index is not None:
         row_index = row_index.contiguous()
-    _lib.check(_lib.lib().moe_sum(y.data_ptr(), out.data_ptr(), _lib.dtype_code(out.dtype), M, k, H, _lib.ptr(ids),
-                                  int(ids is not None and ids.dtype == torch.int64), global_num_experts,
-                                  _lib.ptr(emap), _lib.ptr(row_index), _lib.stream_of(out)))
+    _lib.check(_lib.lib().moe_sum_ld(y.data_ptr(), out.data_ptr(), out.stride(0) if M > 0 else H,
+                                     _lib.dtype_code(out.dtype), M, k, H, _lib.ptr(ids),
+                                     int(ids is not None and ids.dtype == torch.int64), global_num_experts,
+                                     _lib.ptr(emap), _lib.ptr(row_index), _lib.stream_of(out)))
 
 
 def run_chunk(x, w1, w2, topk_weights, topk_ids, out, *, mode, w1_scale, w2_scale, global_num_experts,

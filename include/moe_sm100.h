@@ -300,6 +300,19 @@ int moe_gemm2_sorted(int mode, int act_dtype, const void* act_sorted, const floa
                      int32_t* status, void* stream);
 
 /*
+ * moe_gemm2_sorted over a window of the output columns: y_window [rows_cap, ncols] receives columns
+ * [col0, col0 + ncols) of every row (col0 and ncols multiples of 256).  Two such calls make the
+ * whole y; a caller whose next step can start on the first columns (the expert-parallel combine)
+ * overlaps it with the second call, and max_ctas > 0 keeps that call off some SMs for it.  inv is
+ * written by every call (the same values).  No counterpart in the reference.
+ */
+int moe_gemm2_sorted_cols(int mode, int act_dtype, const void* act_sorted, const float* act_scales_t, const void* w2,
+                          const float* w2_scale, const int32_t* expert_ids, const int32_t* sorted_ids,
+                          const int32_t* num_post_pad, const float* route_weight, int mul_weight, int64_t numel,
+                          int64_t rows_cap, int block_m, int E, int H, int I, int col0, int ncols, void* y_window,
+                          int32_t* inv, int max_ctas, int32_t* status, void* stream);
+
+/*
  * Small-batch schedule of the two expert GEMMs (weight streaming, split-K): align blocks of
  * 8 routes, every routed expert's weights read once, K cut into slices whose fp32 partial
  * tiles are added in slice order by whichever CTA finishes a tile last (no floating-point
@@ -368,6 +381,12 @@ int moe_small_m_gemm2_static(int mode, int act_dtype, const void* act_sorted, in
 int moe_sum(const void* in, void* out, int dtype, int64_t M, int topk, int64_t H,
             const void* topk_ids, int ids_int64, int num_experts, const int32_t* expert_map,
             const int32_t* row_index, void* stream);
+
+/* moe_sum with the rows of `out` out_ld elements apart (out_ld >= H): the sum lands in a column
+ * window of a wider tensor. */
+int moe_sum_ld(const void* in, void* out, int64_t out_ld, int dtype, int64_t M, int topk, int64_t H,
+               const void* topk_ids, int ids_int64, int num_experts, const int32_t* expert_map,
+               const int32_t* row_index, void* stream);
 
 /*
  * Expert-parallel bookkeeping (experts partitioned over `world` ranks, rank r owning experts

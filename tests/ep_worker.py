@@ -25,7 +25,8 @@ def main():
     dist.init_process_group("nccl", device_id=dev)
     ok = True
     for mode, (M, E, H, I, k) in (("fp8", (96, 32, 512, 256, 8)), ("half", (64, 16, 256, 256, 4)),
-                                  ("fp8", (1, 32, 512, 256, 8))):
+                                  ("fp8", (1, 32, 512, 256, 8)), ("fp8", (2048, 32, 512, 256, 8)),
+                                  ("half", (1024, 16, 512, 256, 4))):
         x = T.make_activations(M, H, dev, seed=50 + rank)
         logits, bias = T.make_router_inputs(M, E, dev, seed=60 + rank)
         El = E // world
@@ -55,6 +56,13 @@ def main():
             torch.cuda.synchronize()
             layer.chunks = 1
             assert torch.equal(out2, out), "chunked expert-parallel step differs from the unchunked one"
+        # the combine in two column halves (the first half's all-to-all beside the second half's GEMM 2
+        # when there are enough rows per expert, otherwise the finished rows cut in two): identical rows
+        layer.overlap_combine = True
+        out3 = layer.forward(x, tw, ti)
+        torch.cuda.synchronize()
+        layer.overlap_combine = False
+        assert torch.equal(out3, out), "combine in column halves differs from the one-piece combine"
         a, b = out.float(), full.float()
         rl2 = ((a - b).norm() / b.norm().clamp_min(1e-20)).item()
         st = fg.read_status(dev)
