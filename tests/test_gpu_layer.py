@@ -596,6 +596,47 @@ def test_intermediates_follow_the_documented_layout():
     assert torch.isfinite(act[valid]).all()
 
 
+@pytest.mark.parametrize("mode", ["fp8", "bf16"])
+def test_gemm2_in_two_column_windows_equals_the_one_piece_gemm2(mode):
+    """GEMM 2 over the two halves of the hidden columns (the second on fewer SMs) writes exactly the
+    columns the one-piece GEMM 2 writes, and the sum into a column window of a wider tensor equals
+    the sum into a tensor of its own."""
+    M, E, H, I, k = 1500, 8, 1024, 256, 2
+    x = T.make_activations(M, H, DEV)
+    tw, ti = _route(M, E, k, torch.bfloat16)
+    if mode == "fp8":
+        w1, s1 = T.make_fp8_block_weights(E, 2 * I, H, DEV, seed=1, std=H**-0.5)
+        w2, s2 = T.make_fp8_block_weights(E, H, I, DEV, seed=2, std=I**-0.5)
+        a_rows, a_scales = fused_moe.quantize_rows(x)
+        m = _lib.MODE_FP8_BLOCK
+    else:
+        w1 = T.make_half_weights(E, 2 * I, H, DEV, seed=1, std=H**-0.5)
+        w2 = T.make_half_weights(E, H, I, DEV, seed=2, std=I**-0.5)
+        s1 = s2 = None
+        a_rows, a_scales = x, None
+        m = _lib.MODE_HALF
+    kw = dict(mode=m, act_dtype=x.dtype, w1_scale=s1, w2_scale=s2, global_num_experts=E, expert_map=None,
+              apply_router_weight_on_input=False, use_tensor_cores=fused_moe.KERNEL_TC)
+    y, row_index = fused_moe.route_pipeline(a_rows, a_scales, w1, w2, tw, ti, **kw)
+    assert row_index is not None, "this size is meant to take the sorted-output GEMM 2"
+    windows = []
+    y2, row_index2 = fused_moe.route_pipeline(a_rows, a_scales, w1, w2, tw, ti, **kw,
+                                              column_halves=(lambda h, c0, yw, ri: windows.append((c0, yw)), 24))
+    torch.cuda.synchronize()
+    assert y2 is None and len(windows) == 2 and torch.equal(row_index2, row_index)
+    n = int(row_index.max().item()) + 1
+    valid = torch.zeros(y.shape[0], dtype=torch.bool, device=DEV)
+    valid[row_index.flatten().long()] = True
+    for c0, yw in windows:
+        assert torch.equal(yw[valid], y[valid][:, c0:c0 + yw.shape[1]])
+    out = torch.empty((M, H), dtype=x.dtype, device=DEV)
+    fused_moe.combine_routes(y, out, ti, E, row_index=row_index)
+    out_w = torch.zeros((M, H), dtype=x.dtype, device=DEV)
+    for c0, yw in windows:
+        fused_moe.combine_routes(yw, out_w[:, c0:c0 + yw.shape[1]], ti, E, row_index=row_index)
+    assert torch.equal(out_w, out) and n <= y.shape[0] and fg.read_status(torch.device(DEV)) == 0
+
+
 def test_quant_and_sum_wrappers():
     x = torch.randn(33, 512, device=DEV, dtype=torch.bfloat16) * 3
     x[0, :128] = 0
