@@ -88,7 +88,7 @@ def test_caller_owned_buffers_and_determinism():
     ids = T.make_align_ids(8192, 8, 256, DEV, skewed=True, seed=11)
     cap = ids.numel() + 256 * 63
     first = None
-    for _ in range(20):
+    for _ in range(100):
         s = torch.full((cap,), -7, dtype=torch.int32, device=DEV)
         e = torch.full(((cap + 63) // 64,), -7, dtype=torch.int32, device=DEV)
         n = torch.full((1,), -7, dtype=torch.int32, device=DEV)
