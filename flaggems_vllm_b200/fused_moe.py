@@ -202,6 +202,26 @@ def _small_counters(dev, n):
     return buf
 
 
+def small_k_slices(mode, gemm1, K, N, blocks, sms) -> int:
+    """K slices per tile of the small-batch schedule.  Every CTA takes a contiguous share of the
+    (tile, slice) units, so a GEMM lasts ceil(units / SMs) units of (128-byte chunks per slice + a
+    fixed cost); the slice count that minimises that product is asked for.  ``blocks`` = align
+    blocks of 8 routes (one per routed expert for decode)."""
+    chunk_elems = 64 if mode == _lib.MODE_HALF else 128   # K elements in 128 bytes of weights
+    max_chunks = 16 if mode == _lib.MODE_W8A16 else 32    # what one unit holds of the activation rows
+    unit_overhead = 4                                     # staging + epilogue of a unit, in chunk times
+    nt = N // 64 if gemm1 else N // 128
+    chunks = max(1, K // chunk_elems)
+    best, hint = None, 1
+    for S in range(-(-chunks // max_chunks), min(16, chunks) + 1):
+        cps = -(-chunks // S)
+        units = blocks * nt * -(-chunks // cps)
+        cost = -(-units // sms) * (cps + unit_overhead)
+        if best is None or cost < best:
+            best, hint = cost, S
+    return hint
+
+
 def run_chunk_small(x, w1, w2, topk_weights, topk_ids, out, *, mode, w1_scale, w2_scale, global_num_experts,
                     expert_map, apply_router_weight_on_input, keep=None, mark=None):
     """One chunk on the small-batch schedule: align (blocks of 8 routes) -> GEMM1 -> GEMM2 with
@@ -235,25 +255,11 @@ def run_chunk_small(x, w1, w2, topk_weights, topk_ids, out, *, mode, w1_scale, w
         emap = emap.contiguous()
     rw = topk_weights if topk_weights.dtype == torch.float32 else topk_weights.float()
     rw = rw if rw.is_contiguous() else rw.contiguous()
-    # K slices per tile: every CTA takes a contiguous share of the (tile, slice) units, so the step
-    # lasts ceil(units / SMs) units of (chunks per slice + a fixed cost).  Pick the slice count
-    # that minimises that product; `blocks` is exact for one token and an upper bound otherwise.
-    blocks = max(1, min(numel, global_num_experts))
+    blocks = max(1, min(numel, global_num_experts))  # exact for one token, an upper bound otherwise
     sms = _sm_count(dev)
-    chunk_elems = 64 if mode == _lib.MODE_HALF else 128          # K elements in 128 bytes of weights
-    max_chunks = 16 if mode == _lib.MODE_W8A16 else 32           # what one unit holds of the activation rows
-    unit_overhead = 4                                            # staging + epilogue of a unit, in chunk times
 
     def plan(gemm1, K, N):
-        nt = N // 64 if gemm1 else N // 128
-        chunks = max(1, K // chunk_elems)
-        best, hint = None, 1
-        for S in range(-(-chunks // max_chunks), min(16, chunks) + 1):
-            cps = -(-chunks // S)
-            units = blocks * nt * -(-chunks // cps)
-            cost = -(-units // sms) * (cps + unit_overhead)
-            if best is None or cost < best:
-                best, hint = cost, S
+        hint = small_k_slices(mode, gemm1, K, N, blocks, sms)
         sizes = (ctypes.c_int64 * 3)()
         _lib.check(L.moe_small_m_plan(int(gemm1), mode, K, N, rows_cap, M, hint, ctypes.addressof(sizes),
                                       ctypes.addressof(sizes) + 8, ctypes.addressof(sizes) + 16))

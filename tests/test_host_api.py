@@ -182,3 +182,22 @@ def test_product_package_never_imports_the_oracle():
         if fn.endswith(".py"):
             src = open(os.path.join(pkg, fn)).read()
             assert "oracle" not in src, f"{fn} mentions the oracle"
+
+
+def test_small_batch_slice_count_model():
+    """The K-slice count asked of the small-batch GEMMs: never below what one unit can hold, never
+    above 16, and the choices the measurements were taken with."""
+    from flaggems_vllm_b200 import fused_moe
+
+    H, I = 4096, 14336  # one token of the Mixtral shape: two experts
+    assert fused_moe.small_k_slices(_lib.MODE_HALF, True, H, I, 2, 148) == 2      # 896 units, 7 per CTA at most
+    assert fused_moe.small_k_slices(_lib.MODE_HALF, False, I, H, 2, 148) == 9     # 576 units: four full waves
+    assert fused_moe.small_k_slices(_lib.MODE_W8A16, True, 2048, 768, 8, 148) == 1  # 96 units fit one wave
+    for mode in (_lib.MODE_HALF, _lib.MODE_FP8_BLOCK, _lib.MODE_W8A16):
+        for K in (128, 512, 2048, 7168, 14336):
+            for blocks in (1, 2, 8, 64):
+                for gemm1 in (True, False):
+                    S = fused_moe.small_k_slices(mode, gemm1, K, 1024, blocks, 148)
+                    chunks = K // (64 if mode == _lib.MODE_HALF else 128)
+                    need = -(-chunks // (16 if mode == _lib.MODE_W8A16 else 32))
+                    assert 1 <= S <= 16 and (S >= need or need > 16) and S <= max(chunks, 1)
