@@ -751,6 +751,43 @@ def test_layer_under_cuda_graph_replay_with_new_inputs():
         _assert_parity(out, O.fused_moe_fp8_block_oracle(x, w1, w2, s1, s2, ow, oi), f"replay {seed}")
 
 
+@pytest.mark.parametrize("case", ["bf16_small_batch", "w8a16_small_batch", "bf16_sorted_output"])
+def test_other_paths_under_cuda_graph_replay_with_new_inputs(case):
+    """The small-batch schedule (its counters clean themselves, its scratch is reused) and the
+    staged-output GEMM 2 replay correctly from a CUDA graph when the inputs change."""
+    E, H, I, k = 8, 512, 256, 2
+    M = {"bf16_small_batch": 2, "w8a16_small_batch": 1, "bf16_sorted_output": 700}[case]
+    if case == "w8a16_small_batch":
+        w1, s1 = T.make_int8_channel_weights(E, 2 * I, H, DEV, seed=1)
+        w2, s2 = T.make_int8_channel_weights(E, H, I, DEV, seed=2)
+        kw = dict(use_int8_w8a16=True, per_channel_quant=True, w1_scale=s1, w2_scale=s2)
+        oracle = lambda x, tw, ti: O.fused_moe_w8a16_oracle(x, w1, w2, s1, s2, tw, ti)
+    else:
+        w1 = T.make_half_weights(E, 2 * I, H, DEV, seed=1, std=H**-0.5)
+        w2 = T.make_half_weights(E, H, I, DEV, seed=2, std=I**-0.5)
+        kw = {}
+        oracle = lambda x, tw, ti: O.fused_moe_half_oracle(x, w1, w2, tw, ti)
+    x = T.make_activations(M, H, DEV, seed=3)
+    logits, _ = T.make_router_inputs(M, E, DEV, seed=4)
+    zero_bias = torch.zeros(E, device=DEV)
+
+    def step():
+        tw, ti = fg.grouped_topk(torch.softmax(logits, -1), 1, 1, k, True, 1.0, zero_bias, 0)
+        return tw, ti, fg.fused_experts_impl(x, w1, w2, tw, ti, **kw)
+
+    step()
+    torch.cuda.synchronize()
+    graph = torch.cuda.CUDAGraph()
+    with torch.cuda.graph(graph):
+        tw, ti, out = step()
+    for seed in (5, 6, 7):
+        x.copy_(T.make_activations(M, H, DEV, seed=seed))
+        logits.copy_(T.make_router_inputs(M, E, DEV, seed=seed)[0])
+        graph.replay()
+        torch.cuda.synchronize()
+        _assert_parity(out, oracle(x, tw, ti), f"{case} replay {seed}")
+
+
 def test_empty_batch_and_single_token():
     E, H, I, k = 8, 128, 256, 2
     w1 = T.make_half_weights(E, 2 * I, H, DEV, seed=1, std=H**-0.5)
