@@ -89,6 +89,57 @@ __global__ void __launch_bounds__(kRowThreads) quant_rows_kernel(
   }
 }
 
+// The same quantiser for 2-byte inputs with an even number of groups per row: a warp step covers
+// two neighbouring groups (8 elements = 16 bytes per lane, one half-warp per group), so a warp has
+// twice the bytes in flight per load instruction.  Bit for bit the arithmetic of quant_group_128.
+template <typename T>
+__global__ void __launch_bounds__(kRowThreads) quant_rows_pair_kernel(
+    const T* __restrict__ x, int64_t rows, int64_t cols, uint8_t* __restrict__ q, float* __restrict__ scales,
+    int transposed, int64_t scale_ld) {
+  static_assert(sizeof(T) == 2, "pairs of groups: 2-byte inputs");
+  const int lane = threadIdx.x & 31;
+  const int64_t groups_per_row = cols / 128;
+  const int64_t pairs = rows * (groups_per_row / 2);
+  const int64_t warp0 = (int64_t)blockIdx.x * (kRowThreads / 32) + (threadIdx.x >> 5);
+  const int64_t stride = (int64_t)gridDim.x * (kRowThreads / 32);
+  constexpr int U = 4;  // pairs in flight per warp
+  for (int64_t w = warp0; w < pairs; w += U * stride) {
+    uint4 raw[U];
+#pragma unroll
+    for (int u = 0; u < U; ++u) {
+      const int64_t wu = w + u * stride;
+      if (wu < pairs) raw[u] = *reinterpret_cast<const uint4*>(x + wu * 256 + lane * 8);  // rows are contiguous
+    }
+#pragma unroll
+    for (int u = 0; u < U; ++u) {
+      const int64_t wu = w + u * stride;
+      if (wu >= pairs) continue;
+      const T* pv = reinterpret_cast<const T*>(&raw[u]);
+      float v[8];
+#pragma unroll
+      for (int i = 0; i < 8; ++i) v[i] = ToF32<T>::get(pv[i]);
+      float amax = 0.0f;
+#pragma unroll
+      for (int i = 0; i < 8; ++i) amax = fmaxf(amax, fabsf(v[i]));
+#pragma unroll
+      for (int off = 8; off > 0; off >>= 1) amax = fmaxf(amax, __shfl_xor_sync(0xFFFFFFFFu, amax, off));  // 16 lanes = one group
+      const float s = fmaxf(amax, kQuantEps) * (1.0f / kFp8Max);
+      uint32_t lo = 0, hi = 0;
+#pragma unroll
+      for (int i = 0; i < 4; ++i) {
+        lo |= (uint32_t)f32_to_fp8e4m3(fminf(fmaxf(v[i] / s, -kFp8Max), kFp8Max)) << (8 * i);
+        hi |= (uint32_t)f32_to_fp8e4m3(fminf(fmaxf(v[4 + i] / s, -kFp8Max), kFp8Max)) << (8 * i);
+      }
+      *reinterpret_cast<uint2*>(q + wu * 256 + lane * 8) = make_uint2(lo, hi);
+      if ((lane & 15) == 0) {
+        const int64_t gflat = wu * 2 + (lane >> 4);
+        const int64_t r = gflat / groups_per_row, g = gflat % groups_per_row;
+        *(transposed ? scales + g * scale_ld + r : scales + r * groups_per_row + g) = s;
+      }
+    }
+  }
+}
+
 // Any group size, clamp value and 8-bit float format: one warp per group, lanes stride over the
 // group (the 128-wide e4m3 kernel above is the fast case of this one).
 template <typename T, bool UE8M0, bool E5M2>
@@ -456,6 +507,18 @@ extern "C" int moe_per_token_group_quant_fp8(const void* x, int x_dtype, int64_t
                                                                     transposed, scale_ld)                          \
          : quant_rows_kernel<T, false><<<grid, kRowThreads, 0, st>>>((const T*)x, rows, cols, (uint8_t*)q, scales, \
                                                                      transposed, scale_ld))
+  const bool pairs = !ue8m0 && (cols / 128) % 2 == 0 && (x_dtype == MOE_F16 || x_dtype == MOE_BF16) &&
+                     (((uintptr_t)x | (uintptr_t)q) & 15) == 0;
+  if (pairs) {
+    const int grid2 = grid_for((rows * (cols / 256) + 7) / 8, 8);
+    if (x_dtype == MOE_BF16)
+      quant_rows_pair_kernel<__nv_bfloat16><<<grid2, kRowThreads, 0, st>>>((const __nv_bfloat16*)x, rows, cols, (uint8_t*)q,
+                                                                           scales, transposed, scale_ld);
+    else
+      quant_rows_pair_kernel<__half><<<grid2, kRowThreads, 0, st>>>((const __half*)x, rows, cols, (uint8_t*)q, scales,
+                                                                    transposed, scale_ld);
+    return check_launch("per_token_group_quant_fp8");
+  }
   switch (x_dtype) {
     case MOE_F32: MOE_QUANT_LAUNCH(float); break;
     case MOE_F16: MOE_QUANT_LAUNCH(__half); break;
