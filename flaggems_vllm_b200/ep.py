@@ -243,7 +243,7 @@ class ExpertParallelMoE:
         second half's GEMM 2; otherwise the finished rows are cut in two.  Either way every rank
         issues the same two collectives."""
         dev = out.device
-        M, H = out.shape
+        H = out.shape[1]
         n_recv, n_send = a_rows.shape[0], sum(send_splits)
         h0 = (H // 2) // 256 * 256
         main = torch.cuda.current_stream(dev)
