@@ -7,8 +7,9 @@ the reference project's own tests use as goldens for the path
 
 It exists to check the CUDA kernels and to provide the timed CPU baseline.  It
 is never imported by the product package: only ``tests/``, the smoke check of
-``__graft_entry__`` and the ``cpu_baseline`` / ``--impl reference`` legs of
-``bench.py`` may use it.
+``__graft_entry__`` and, in ``bench.py``, the ``cpu_baseline`` / ``--impl reference`` legs and
+the expert-parallel parity check (as the checker of sampled tokens, outside every timed region)
+may use it.
 
 Parity is PINNED: ``tests/golden/`` holds vectors produced by executing the
 reference's own golden functions (extracted from its test files by
