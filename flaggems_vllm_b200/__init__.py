@@ -4,6 +4,7 @@ operator names: ``grouped_topk``, ``moe_align_block_size`` and
 CUDA kernels reached through the C ABI of ``libmoe_sm100.so``."""
 
 from ._lib import MoeKernelError, read_status  # noqa: F401
+from .activation import silu_and_mul, silu_and_mul_out  # noqa: F401
 from .align import (  # noqa: F401
     moe_align_block_size,
     moe_align_block_size_no_tle,
@@ -35,4 +36,5 @@ __all__ = [
     "fused_experts_impl", "inplace_fused_experts", "outplace_fused_experts", "ops_experts_impl", "moe_sum",
     "per_token_group_quant_fp8", "SUPPORTED_FP8_DTYPE", "read_status", "MoeKernelError", "topk_softmax",
     "topk_sigmoid", "router_gemm", "fp32_router_gemm", "supports_fp32_router_gemm", "router_gemm_grouped_topk",
+    "silu_and_mul", "silu_and_mul_out",
 ]

@@ -75,6 +75,8 @@ SYMBOLS = {
                                  c_void_p, c_void_p]),
     "moe_sum": (c_int, [c_void_p, c_void_p, c_int, c_int64, c_int, c_int64, c_void_p, c_int, c_int, c_void_p,
                         c_void_p, c_void_p]),
+    "moe_silu_and_mul": (c_int, [c_void_p, c_void_p, c_void_p, c_int, c_int64, c_void_p]),
+    "moe_silu_and_mul_grad": (c_int, [c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_int, c_int64, c_void_p]),
     "moe_sum_ld": (c_int, [c_void_p, c_void_p, c_int64, c_int, c_int64, c_int, c_int64, c_void_p, c_int, c_int, c_void_p,
                            c_void_p, c_void_p]),
 }

@@ -569,3 +569,79 @@ extern "C" int moe_sum(const void* in, void* out, int dtype, int64_t M, int topk
                        const int32_t* expert_map, const int32_t* row_index, void* stream) {
   return moe_sum_ld(in, out, H, dtype, M, topk, H, topk_ids, ids_int64, num_experts, expert_map, row_index, stream);
 }
+
+
+// ---------------------------------------------------------------------------------------------
+// Stand-alone SiLU(a) * b and its gradients: the reference's silu_and_mul / silu_and_mul_out
+// (src/flaggems_vllm/ops/silu_and_mul.py:26-70), which its fused_experts_impl uses on the
+// un-fused GEMM1 path.  fp32 arithmetic as there: a / (1 + exp(-a)) * b, one rounding to the
+// output dtype.  The layer of this library never calls it (the activation is fused into GEMM1).
+namespace moe {
+namespace {
+template <typename T>
+__global__ void __launch_bounds__(256) silu_and_mul_kernel(const T* __restrict__ a, const T* __restrict__ b,
+                                                           T* __restrict__ out, int64_t n) {
+  for (int64_t i = (int64_t)blockIdx.x * blockDim.x + threadIdx.x; i < n; i += (int64_t)gridDim.x * blockDim.x) {
+    const float x = ToF32<T>::get(a[i]), y = ToF32<T>::get(b[i]);
+    out[i] = from_f32<T>((x / (1.0f + expf(-x))) * y);
+  }
+}
+template <typename T>
+__global__ void __launch_bounds__(256) silu_and_mul_grad_kernel(const T* __restrict__ a, const T* __restrict__ b,
+                                                                const T* __restrict__ dgrad, T* __restrict__ da,
+                                                                T* __restrict__ db, int64_t n) {
+  for (int64_t i = (int64_t)blockIdx.x * blockDim.x + threadIdx.x; i < n; i += (int64_t)gridDim.x * blockDim.x) {
+    const float x = ToF32<T>::get(a[i]), y = ToF32<T>::get(b[i]), g = ToF32<T>::get(dgrad[i]);
+    const float sig = 1.0f / (1.0f + expf(-x));
+    da[i] = from_f32<T>(sig * (1.0f + x * (1.0f - sig)) * g * y);
+    db[i] = from_f32<T>(g * (x * sig));
+  }
+}
+}  // namespace
+}  // namespace moe
+
+extern "C" int moe_silu_and_mul(const void* a, const void* b, void* out, int dtype, int64_t n, void* stream) {
+  using namespace moe;
+  if (n < 0) return fail(MOE_E_BADARG, "silu_and_mul: negative size");
+  if (n == 0) return 0;
+  if (!a || !b || !out) return fail(MOE_E_BADARG, "silu_and_mul: null pointer");
+  const int grid = grid_for((n + 255) / 256, 16);
+  cudaStream_t st = (cudaStream_t)stream;
+  switch (dtype) {
+    case MOE_F32: silu_and_mul_kernel<float><<<grid, 256, 0, st>>>((const float*)a, (const float*)b, (float*)out, n); break;
+    case MOE_F16: silu_and_mul_kernel<__half><<<grid, 256, 0, st>>>((const __half*)a, (const __half*)b, (__half*)out, n); break;
+    case MOE_BF16:
+      silu_and_mul_kernel<__nv_bfloat16><<<grid, 256, 0, st>>>((const __nv_bfloat16*)a, (const __nv_bfloat16*)b,
+                                                               (__nv_bfloat16*)out, n);
+      break;
+    default: return fail(MOE_E_DTYPE, "silu_and_mul: unsupported dtype %d", dtype);
+  }
+  return check_launch("silu_and_mul");
+}
+
+extern "C" int moe_silu_and_mul_grad(const void* a, const void* b, const void* dgrad, void* da, void* db, int dtype,
+                                     int64_t n, void* stream) {
+  using namespace moe;
+  if (n < 0) return fail(MOE_E_BADARG, "silu_and_mul_grad: negative size");
+  if (n == 0) return 0;
+  if (!a || !b || !dgrad || !da || !db) return fail(MOE_E_BADARG, "silu_and_mul_grad: null pointer");
+  const int grid = grid_for((n + 255) / 256, 16);
+  cudaStream_t st = (cudaStream_t)stream;
+  switch (dtype) {
+    case MOE_F32:
+      silu_and_mul_grad_kernel<float><<<grid, 256, 0, st>>>((const float*)a, (const float*)b, (const float*)dgrad, (float*)da,
+                                                            (float*)db, n);
+      break;
+    case MOE_F16:
+      silu_and_mul_grad_kernel<__half><<<grid, 256, 0, st>>>((const __half*)a, (const __half*)b, (const __half*)dgrad,
+                                                             (__half*)da, (__half*)db, n);
+      break;
+    case MOE_BF16:
+      silu_and_mul_grad_kernel<__nv_bfloat16><<<grid, 256, 0, st>>>((const __nv_bfloat16*)a, (const __nv_bfloat16*)b,
+                                                                    (const __nv_bfloat16*)dgrad, (__nv_bfloat16*)da,
+                                                                    (__nv_bfloat16*)db, n);
+      break;
+    default: return fail(MOE_E_DTYPE, "silu_and_mul_grad: unsupported dtype %d", dtype);
+  }
+  return check_launch("silu_and_mul_grad");
+}

@@ -389,6 +389,15 @@ int moe_sum_ld(const void* in, void* out, int64_t out_ld, int dtype, int64_t M, 
                const int32_t* row_index, void* stream);
 
 /*
+ * out[i] = SiLU(a[i]) * b[i] in fp32, rounded once to the tensors' dtype (F32/F16/BF16), n
+ * contiguous elements; and its gradients da = dSiLU(a) * dgrad * b, db = dgrad * SiLU(a).
+ * Stand in for silu_and_mul / silu_and_mul_out (src/flaggems_vllm/ops/silu_and_mul.py:26-70).
+ */
+int moe_silu_and_mul(const void* a, const void* b, void* out, int dtype, int64_t n, void* stream);
+int moe_silu_and_mul_grad(const void* a, const void* b, const void* dgrad, void* da, void* db, int dtype, int64_t n,
+                          void* stream);
+
+/*
  * Expert-parallel bookkeeping (experts partitioned over `world` ranks, rank r owning experts
  * [r * experts_per_rank, (r + 1) * experts_per_rank); tokens data-parallel).  The reference
  * has no all-to-all path (its hook is expert_map with replicated tokens,

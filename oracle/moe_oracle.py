@@ -602,3 +602,9 @@ def make_align_ids(M, topk=8, E=256, skewed=False, seed=0):
 
 def expected_distinct_experts(M, topk, E):
     return E * (1.0 - math.pow(1.0 - 1.0 / E, M * topk))
+
+
+def silu_and_mul_oracle(a: torch.Tensor, b: torch.Tensor) -> torch.Tensor:
+    """SiLU(a) * b as the reference's test states it (tests/test_silu_and_mul.py:35,63:
+    ``torch.mul(torch.nn.functional.silu(a), b)`` on upcast operands), in float64."""
+    return torch.mul(torch.nn.functional.silu(a.double().cpu()), b.double().cpu())

@@ -25,6 +25,7 @@ WANTED = {
     "topk_sigmoid.py": ["topk_sigmoid"],
     "router_gemm.py": ["router_gemm"],
     "fp32_router_gemm.py": ["fp32_router_gemm", "supports_fp32_router_gemm"],
+    "silu_and_mul.py": ["silu_and_mul", "silu_and_mul_out"],
 }
 
 

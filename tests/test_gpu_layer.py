@@ -637,6 +637,38 @@ def test_gemm2_in_two_column_windows_equals_the_one_piece_gemm2(mode):
     assert torch.equal(out_w, out) and n <= y.shape[0] and fg.read_status(torch.device(DEV)) == 0
 
 
+# shapes and dtypes of the reference's tests/test_silu_and_mul.py (accuracy_utils.POINTWISE_SHAPES, FLOAT_DTYPES)
+@pytest.mark.parametrize("shape", [(), (1,), (1024, 1024), (20, 320, 15), (16, 128, 64, 60), (16, 7, 57, 32, 29)])
+@pytest.mark.parametrize("dtype", [torch.float16, torch.float32, torch.bfloat16])
+def test_silu_and_mul_and_its_gradients(shape, dtype):
+    g = torch.Generator(device="cpu").manual_seed(len(shape) + 7)
+    a = torch.randn(shape, generator=g).to(dtype).to(DEV).requires_grad_(True)
+    b = torch.randn(shape, generator=g).to(dtype).to(DEV).requires_grad_(True)
+    # one rounding to the dtype: within half an ulp of the float64 value (plus fp32 evaluation error)
+    tol = {torch.float32: dict(rtol=2e-6, atol=1e-6), torch.float16: dict(rtol=1e-3, atol=1e-4),
+           torch.bfloat16: dict(rtol=8e-3, atol=1e-4)}[dtype]
+    out = fg.silu_and_mul(a, b)
+    assert out.shape == tuple(shape) and out.dtype == dtype
+    ref = O.silu_and_mul_oracle(a.detach(), b.detach())
+    torch.testing.assert_close(out.detach().double().cpu(), ref, **tol)
+    buf = torch.empty_like(a.detach())
+    assert fg.silu_and_mul_out(a.detach(), b.detach(), buf) is buf and torch.equal(buf, out.detach())
+    grad = torch.randn(shape, generator=g).to(dtype).to(DEV)
+    da, db = torch.autograd.grad(out, (a, b), grad)
+    ad, bd = a.detach().double().cpu().requires_grad_(True), b.detach().double().cpu().requires_grad_(True)
+    rda, rdb = torch.autograd.grad(torch.mul(torch.nn.functional.silu(ad), bd), (ad, bd), grad.double().cpu())
+    torch.testing.assert_close(da.double().cpu(), rda, **tol)
+    torch.testing.assert_close(db.double().cpu(), rdb, **tol)
+
+
+def test_silu_and_mul_broadcasts_and_promotes():
+    a = torch.randn(4, 1, 8, device=DEV, dtype=torch.bfloat16)
+    b = torch.randn(5, 8, device=DEV, dtype=torch.float32)
+    out = fg.silu_and_mul(a, b)
+    assert out.shape == (4, 5, 8) and out.dtype == torch.float32
+    torch.testing.assert_close(out.double().cpu(), O.silu_and_mul_oracle(a, b).expand(4, 5, 8), rtol=2e-6, atol=1e-6)
+
+
 def test_quant_and_sum_wrappers():
     x = torch.randn(33, 512, device=DEV, dtype=torch.bfloat16) * 3
     x[0, :128] = 0

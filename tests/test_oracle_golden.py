@@ -260,3 +260,15 @@ def test_topk_softmax_known_answer_bias_padding_nonfinite():
         assert torch.equal(ids, exp_ids.masked_fill(padding[:, None], -1))
         torch.testing.assert_close(w, exp_w.masked_fill(padding[:, None], 0))
         assert torch.equal(src, (torch.arange(3)[None, :] * 6 + torch.arange(6)[:, None]).int())
+
+
+def test_silu_and_mul_oracle_known_answers():
+    """tests/test_silu_and_mul.py of the reference states the golden as torch.mul(silu(a), b)."""
+    import math
+
+    a = torch.tensor([0.0, 1.0, -1.0, 20.0, -20.0], dtype=torch.float32)
+    b = torch.tensor([3.0, 2.0, 2.0, 0.5, 1.0], dtype=torch.float32)
+    out = O.silu_and_mul_oracle(a, b)
+    sig = lambda v: 1.0 / (1.0 + math.exp(-v))
+    want = torch.tensor([0.0, 2.0 * sig(1.0), -2.0 * sig(-1.0), 10.0 * sig(20.0), -20.0 * sig(-20.0)], dtype=torch.float64)
+    torch.testing.assert_close(out, want, rtol=1e-12, atol=1e-15)
