@@ -77,9 +77,12 @@ def moe_sum(input: torch.Tensor, output: torch.Tensor):
         raise ValueError("moe_sum: output must be [M, H] with the dtype and device of input")
     _lib.require_cuda(input, "moe_sum")
     src = input if input.is_contiguous() else input.contiguous()
-    dst = output if output.is_contiguous() else torch.empty_like(output, memory_format=torch.contiguous_format)
-    rc = _lib.lib().moe_sum(src.data_ptr(), dst.data_ptr(), _lib.dtype_code(src.dtype), M, topk, H, None, 0, 0,
-                            None, None, _lib.stream_of(input))
+    # rows of the output may be any number of elements apart (a window of a wider tensor); only
+    # non-contiguous columns go through a temporary
+    direct = M == 0 or H == 1 or output.stride(1) == 1
+    dst = output if direct else torch.empty_like(output, memory_format=torch.contiguous_format)
+    rc = _lib.lib().moe_sum_ld(src.data_ptr(), dst.data_ptr(), dst.stride(0) if M > 0 and dst.stride(0) >= H else H,
+                               _lib.dtype_code(src.dtype), M, topk, H, None, 0, 0, None, None, _lib.stream_of(input))
     _lib.check(rc)
     if dst is not output:
         output.copy_(dst)

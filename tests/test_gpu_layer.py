@@ -737,6 +737,12 @@ def test_moe_sum_accepts_strided_tensors():
     torch.testing.assert_close(out.float().cpu(), O.moe_sum_oracle(inp.contiguous()).to(torch.bfloat16).float(),
                                rtol=1.6e-2, atol=1e-3)
     assert torch.all(out_big[:, 1::2] == 0)       # the gaps of the strided output stay untouched
+    # rows apart, columns contiguous: written in place (a column window of a wider tensor)
+    wide = torch.full((20, 1024), -3.0, device=DEV, dtype=torch.bfloat16)
+    cont = torch.randn(20, 4, 256, device=DEV, dtype=torch.bfloat16)
+    fg.moe_sum(cont, wide[:, 512:768])
+    assert torch.equal(wide[:, 512:768].float().cpu(), O.moe_sum_oracle(cont).to(torch.bfloat16).float())
+    assert torch.all(wide[:, :512] == -3.0) and torch.all(wide[:, 768:] == -3.0)
 
 
 def test_gather_rows_matches_index_select():
