@@ -166,6 +166,101 @@ __global__ void __launch_bounds__(128) grouped_topk_kernel(
                          scoring_func, w_row, id_row, lane);
 }
 
+// The same routing for more experts than a warp's registers hold (1024 < E <= 4096): one CTA of
+// 256 threads per token, the unbiased scores and the ranking keys in shared memory.  The same
+// ordering rules and the same arithmetic as route_row, so the ids agree with it wherever both
+// apply.  A correctness path for unusually wide routers, not a tuned one.
+template <typename ST, typename BT>
+__global__ void __launch_bounds__(256) grouped_topk_big_kernel(
+    const ST* __restrict__ scores, int64_t stride0, int64_t stride1, const BT* __restrict__ bias,
+    const uint8_t* __restrict__ is_padding, int64_t M, int E, int n_group, int topk_group, int topk,
+    int renormalize, float scaling, int scoring_func, float* __restrict__ out_w, int32_t* __restrict__ out_ids) {
+  extern __shared__ unsigned long long big_smem[];
+  uint64_t* key = reinterpret_cast<uint64_t*>(big_smem);                 // [E]
+  float* u = reinterpret_cast<float*>(key + E);                          // [E]
+  __shared__ uint64_t warp_best[8];
+  __shared__ uint64_t best_bc;
+  __shared__ float group_score[32];
+  __shared__ uint32_t keep_mask_s;
+  const int64_t token = blockIdx.x;
+  const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
+  float* w_row = out_w + token * topk;
+  int32_t* id_row = out_ids + token * topk;
+  if (is_padding != nullptr && is_padding[token]) {
+    if (tid < topk) { w_row[tid] = 0.0f; id_row[tid] = -1; }
+    return;
+  }
+  const float NEG_INF = __int_as_float(0xff800000);
+  const int per_group = E / n_group;
+  const ST* row = scores + token * stride0;
+  for (int e = tid; e < E; e += 256) {
+    float s = ToF32<ST>::get(row[(int64_t)e * stride1]);
+    if (scoring_func == 1) s = (float)(1.0 / (1.0 + exp(-(double)s)));
+    u[e] = s;
+    key[e] = make_key(s + ToF32<BT>::get(bias[e]), (uint32_t)e);
+  }
+  __syncthreads();
+  if (n_group > 1) {
+    for (int g = warp; g < n_group; g += 8) {  // a warp finds the two largest r of its groups
+      uint32_t b1 = 0, b2 = 0;
+      for (int e = g * per_group + lane; e < (g + 1) * per_group; e += 32) {
+        const uint32_t ob = (uint32_t)(key[e] >> 32);
+        if (ob > b1) { b2 = b1; b1 = ob; } else if (ob > b2) { b2 = ob; }
+      }
+      const uint32_t top1 = __reduce_max_sync(0xFFFFFFFFu, b1);
+      const int owner = __ffs(__ballot_sync(0xFFFFFFFFu, b1 == top1)) - 1;
+      const uint32_t top2 = __reduce_max_sync(0xFFFFFFFFu, lane == owner ? b2 : b1);
+      if (lane == 0)
+        group_score[g] = per_group >= 2 ? from_ordered_bits(top1) + from_ordered_bits(top2) : from_ordered_bits(top1);
+    }
+    __syncthreads();
+    if (warp == 0) {
+      uint32_t keep_mask = 0;
+      uint64_t gkey = lane < n_group ? make_key(group_score[lane], (uint32_t)lane) : 0;
+      for (int t = 0; t < topk_group; ++t) {
+        const uint64_t best = warp_max_u64(gkey);
+        keep_mask |= 1u << ((0xFFFFFFFFu - (uint32_t)(best & 0xFFFFFFFFu)) & 31);
+        if (gkey == best) gkey = 0;
+      }
+      if (lane == 0) keep_mask_s = keep_mask;
+    }
+    __syncthreads();
+    const uint32_t keep_mask = keep_mask_s;
+    for (int e = tid; e < E; e += 256)
+      if (!((keep_mask >> (e / per_group)) & 1u)) key[e] = make_key(NEG_INF, (uint32_t)e);
+    __syncthreads();
+  }
+  float my_w = 0.0f;  // thread t < topk keeps result t
+  int32_t my_id = 0;
+  for (int t = 0; t < topk; ++t) {
+    uint64_t local = 0;
+    for (int e = tid; e < E; e += 256) local = key[e] > local ? key[e] : local;
+    const uint64_t wb = warp_max_u64(local);
+    if (lane == 0) warp_best[warp] = wb;
+    __syncthreads();
+    if (warp == 0) {
+      const uint64_t b = warp_max_u64(lane < 8 ? warp_best[lane] : 0);
+      if (lane == 0) best_bc = b;
+    }
+    __syncthreads();
+    const uint64_t best = best_bc;
+    const uint32_t id = 0xFFFFFFFFu - (uint32_t)(best & 0xFFFFFFFFu);
+    if (tid == t) { my_id = (int32_t)id; my_w = best != 0 ? u[id] : 0.0f; }
+    if (best != 0 && (int)(id & 255u) == tid) key[id] = 0;  // the thread that scans this expert consumes it
+    __syncthreads();
+  }
+  if (warp == 0) {  // topk <= 32
+    float sum = lane < topk ? my_w : 0.0f;
+#pragma unroll
+    for (int off = 16; off > 0; off >>= 1) sum += __shfl_xor_sync(0xFFFFFFFFu, sum, off);
+    if (lane < topk) {
+      const float w = renormalize ? my_w / (sum + 1e-20f) : my_w;
+      w_row[lane] = w * scaling;
+      id_row[lane] = my_id;
+    }
+  }
+}
+
 // Router GEMM and routing in one launch for decode batches: one CTA per token computes the
 // token's E logits (x[token] . w[e], fp32) into shared memory and its first warp routes them, so
 // the [M, E] logits never travel through global memory.  The dot products are formed exactly as
@@ -218,6 +313,15 @@ template <typename ST, typename BT>
 int launch_vpt(const ST* scores, int64_t s0, int64_t s1, const BT* bias, const uint8_t* pad,
                int64_t M, int E, int n_group, int topk_group, int topk, int renorm, float scaling,
                int scoring, float* w, int32_t* ids, cudaStream_t st) {
+  if (E > 1024) {
+    auto kern = grouped_topk_big_kernel<ST, BT>;
+    const size_t smem = (size_t)E * (sizeof(uint64_t) + sizeof(float));
+    cudaError_t ce = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
+    if (ce != cudaSuccess) return fail((int)ce, "grouped_topk: shared memory attribute: %s", cudaGetErrorString(ce));
+    kern<<<(unsigned)M, 256, smem, st>>>(scores, s0, s1, bias, pad, M, E, n_group, topk_group, topk, renorm, scaling,
+                                        scoring, w, ids);
+    return check_launch("grouped_topk (wide router)");
+  }
   const int warps = 4;
   dim3 grid((unsigned)((M + warps - 1) / warps)), block(warps * 32);
 #define MOE_TOPK_LAUNCH(V)                                                                     \
@@ -265,7 +369,8 @@ extern "C" int moe_grouped_topk(const void* scores, int scores_dtype, int64_t st
   using namespace moe;
   if (M < 0 || E <= 0 || n_group <= 0 || topk <= 0 || topk_group <= 0)
     return fail(MOE_E_BADARG, "grouped_topk: non-positive extent");
-  if (E > 1024) return fail(MOE_E_TOOBIG, "grouped_topk: at most 1024 experts (got %d)", E);
+  if (E > 4096) return fail(MOE_E_TOOBIG, "grouped_topk: at most 4096 experts (got %d)", E);
+  if (E > 1024 && M > 2147483647ll) return fail(MOE_E_TOOBIG, "grouped_topk: too many rows");
   if (n_group > 32 || topk > 32 || topk_group > n_group || E % n_group != 0 || topk > E)
     return fail(MOE_E_SHAPE, "grouped_topk: bad group/top-k configuration");
   if (scoring_func != 0 && scoring_func != 1)

@@ -79,7 +79,8 @@ int moe_debug_wait_timeout(int32_t* status, unsigned long long limit_ns, int32_t
  * and its kernels (:333-794, :887-1081).  scores[M,E] with element strides
  * (stride0, stride1); bias[E] contiguous; is_padding[M] bytes or NULL.
  * Outputs topk_weights[M,topk] fp32 and topk_ids[M,topk] int32, row-major.
- * Limits: E <= 1024, n_group <= 32, topk <= 32.
+ * Limits: E <= 4096 (one warp per token up to 1024 experts, one CTA per token beyond), n_group <= 32,
+ * topk <= 32.
  */
 int moe_grouped_topk(const void* scores, int scores_dtype, int64_t stride0, int64_t stride1,
                      const void* bias, int bias_dtype, const uint8_t* is_padding,

@@ -60,6 +60,25 @@ def test_other_shapes(E, G, keep, k, sf):
         _check(logits.half(), G, keep, k, ren, 1.5, bias.half(), sf)
 
 
+@pytest.mark.parametrize("E,G,keep,k", [(2048, 8, 4, 8), (4096, 1, 1, 32), (1536, 16, 3, 6), (1280, 32, 32, 1),
+                                        (4096, 32, 2, 32)])
+@pytest.mark.parametrize("sf", [0, 1])
+def test_wide_routers_beyond_one_warp_of_registers(E, G, keep, k, sf):
+    """More than 1024 experts: the one-CTA-per-token kernel, same ordering rules (the reference
+    serves such widths through its generic path)."""
+    logits, bias = T.make_router_inputs(19, E, DEV, seed=E + G)
+    pad = torch.zeros(19, dtype=torch.bool, device=DEV)
+    pad[3] = True
+    for ren in (True, False):
+        _check(logits, G, keep, k, ren, 1.5, bias, sf)
+        _check(logits.to(torch.bfloat16), G, keep, k, ren, 1.5, bias, sf)
+    w, ids = fg.grouped_topk(logits, G, keep, k, True, 1.0, bias, sf, pad)
+    assert torch.all(ids[3] == -1) and torch.all(w[3] == 0)
+    # ties: equal scores are ranked by the lower expert id
+    w, ids = fg.grouped_topk(torch.ones((2, E), device=DEV), 1, 1, k, True, 1.0, torch.zeros(E, device=DEV), 0)
+    assert torch.equal(ids.cpu(), torch.arange(k, dtype=torch.int32).expand(2, k))
+
+
 @pytest.mark.parametrize("groups,keep", [(1, 1), (8, 4)])
 @pytest.mark.parametrize("dtype", [torch.float32, torch.float16, torch.bfloat16])
 @pytest.mark.parametrize("separate", [False, True])
