@@ -201,3 +201,37 @@ def test_small_batch_slice_count_model():
                     chunks = K // (64 if mode == _lib.MODE_HALF else 128)
                     need = -(-chunks // (16 if mode == _lib.MODE_W8A16 else 32))
                     assert 1 <= S <= 16 and (S >= need or need > 16) and S <= max(chunks, 1)
+
+
+def test_kernel_choice_at_the_benchmark_configurations(monkeypatch):
+    """Host policy (no device work): which schedule serves the configurations of the benchmark plan."""
+    from flaggems_vllm_b200 import fused_moe as fm
+
+    for var in ("FLAGGEMS_B200_GENERIC_GEMM", "FLAGGEMS_B200_TC_WIDE", "FLAGGEMS_B200_TC_PAIR", "FLAGGEMS_B200_TC_PAIR_WIDE",
+                "FLAGGEMS_B200_PRESORT", "FLAGGEMS_B200_TMA_OUT", "FLAGGEMS_B200_SMALL_M"):
+        monkeypatch.delenv(var, raising=False)
+    bf16 = torch.bfloat16
+    # DeepSeek-V3 shape, FP8 block scales: always the 128-row tcgen05 kernel, never the small-batch schedule
+    for M in (1, 32, 128, 1024, 8192):
+        numel = M * 8
+        assert fm._choose_kernel(_lib.MODE_FP8_BLOCK, bf16, 7168, 2048, numel, 256) == fm.KERNEL_TC
+        assert not fm._use_small_path(_lib.MODE_FP8_BLOCK, bf16, 7168, 2048, numel, 8)
+        assert fm._presort_rows(_lib.MODE_FP8_BLOCK, fm.KERNEL_TC, numel, 256) == (M >= 4096)
+        assert fm._sorted_output(_lib.MODE_FP8_BLOCK, fm.KERNEL_TC, numel, 256) == (M >= 2048)
+    # Mixtral shape, bf16: small-batch schedule up to 8 routes, the 256x256 tile from 256 rows per expert on
+    assert fm._use_small_path(_lib.MODE_HALF, bf16, 4096, 14336, 2, 2)
+    assert not fm._use_small_path(_lib.MODE_HALF, bf16, 4096, 14336, 32, 2)
+    assert fm._choose_kernel(_lib.MODE_HALF, bf16, 4096, 14336, 512, 8) == fm.KERNEL_TC
+    assert fm._choose_kernel(_lib.MODE_HALF, bf16, 4096, 14336, 2048, 8) == fm.KERNEL_TC_WIDE
+    assert not fm._sorted_output(_lib.MODE_HALF, fm.KERNEL_TC_WIDE, 8192, 8)
+    # Qwen3 shape, weight-only int8: small-batch schedule up to 16 routes, the converter kernel beyond
+    assert fm._use_small_path(_lib.MODE_W8A16, bf16, 2048, 768, 8, 8)
+    assert not fm._use_small_path(_lib.MODE_W8A16, bf16, 2048, 768, 512, 8)
+    assert fm._choose_kernel(_lib.MODE_W8A16, bf16, 2048, 768, 32768, 128) == fm.KERNEL_TC
+    # shapes the tensor-core kernels do not serve fall to the generic kernel; the switches override
+    assert fm._choose_kernel(_lib.MODE_HALF, torch.float32, 4096, 14336, 2048, 8) == fm.KERNEL_GENERIC
+    assert fm._choose_kernel(_lib.MODE_FP8_BLOCK, bf16, 7168 + 64, 2048, 64, 256) == fm.KERNEL_GENERIC
+    monkeypatch.setenv("FLAGGEMS_B200_TC_PAIR", "1")
+    assert fm._choose_kernel(_lib.MODE_FP8_BLOCK, bf16, 7168, 2048, 65536, 256) == fm.KERNEL_TC_PAIR
+    monkeypatch.setenv("FLAGGEMS_B200_GENERIC_GEMM", "1")
+    assert fm._choose_kernel(_lib.MODE_FP8_BLOCK, bf16, 7168, 2048, 65536, 256) == fm.KERNEL_GENERIC
